@@ -1,0 +1,173 @@
+// Attention over the paged cache on the CUDA cores, for any mix of prompt portions and single
+// decoded tokens: one warp per (token, query head), optional split of the key range over
+// blockIdx.z with a merge kernel.  Everything but the stored q/k/v is float32: scores, running
+// maximum, sum, accumulator, merge.  It is the float32 path's attention and the reference
+// against which faster kernels are checked.
+//
+// Token t (request r = tok_req[t], position p = positions[t]) sees keys lo..p of its request,
+// lo = max(0, p - window + 1) when window > 0, else 0.  Key n lives in page
+// block_table[r][n / page_size] at offset n % page_size of the layer's cache
+// [pages][2 (k,v)][nkv][page_size][d].  Query head h reads kv head h / (nq / nkv).
+#include "common.cuh"
+
+namespace ptl {
+
+constexpr int kMaxDimPerLane = 8;   // head sizes up to 256
+constexpr int kWarpsPerBlock = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+paged_attention_simt_kernel(T* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                            const T* __restrict__ q, const T* __restrict__ cache,
+                            const int* __restrict__ block_table, const int* __restrict__ tok_req,
+                            const int* __restrict__ positions, int q_stride, int out_stride,
+                            int bt_stride, int nq, int nkv, int d, int page_size, float scale,
+                            int window, int splits) {
+  extern __shared__ float qs_all[];  // [warps][d] scaled query
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int h = blockIdx.y * kWarpsPerBlock + warp;
+  if (h >= nq) return;
+  const int split = blockIdx.z;
+  float* qs = qs_all + warp * d;
+  const T* qrow = q + (size_t)t * q_stride + (size_t)h * d;
+  for (int i = lane; i < d; i += 32) qs[i] = to_f32(qrow[i]) * scale;
+  __syncwarp();
+
+  const int r = tok_req[t];
+  const int p = positions[t];
+  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  const int nkeys = p - lo + 1;
+  int chunk = (nkeys + splits - 1) / splits;
+  chunk = (chunk + 31) & ~31;
+  const int k_begin = lo + split * chunk;
+  const int k_end = min(lo + (split + 1) * chunk, p + 1);
+  const int kvh = h / (nq / nkv);
+  const size_t plane = (size_t)nkv * page_size * d;
+  const int* bt = block_table + (size_t)r * bt_stride;
+  constexpr int VN = Vec16<T>::N;
+
+  float m = -INFINITY, l = 0.f;
+  float acc[kMaxDimPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxDimPerLane; ++i) acc[i] = 0.f;
+
+  for (int k0 = k_begin; k0 < k_end; k0 += 32) {
+    const int key = k0 + lane;
+    const bool valid = key < k_end;
+    size_t base = 0;  // element offset of this lane's key row (k plane)
+    float s = -INFINITY;
+    if (valid) {
+      const int page = bt[key / page_size];
+      base = ((size_t)page * 2) * plane + ((size_t)kvh * page_size + key % page_size) * d;
+      const T* kp = cache + base;
+      float dot = 0.f;
+      for (int i = 0; i < d; i += VN) {
+        Vec16<T> kv = load16(kp + i);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) dot = fmaf(qs[i + e], kv.get(e), dot);
+      }
+      s = dot;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float pr = valid ? expf(s - m_new) : 0.f;
+    const float alpha = expf(m - m_new);  // m = -inf on the first block gives 0
+    l = l * alpha + warp_sum(pr);
+#pragma unroll
+    for (int i = 0; i < kMaxDimPerLane; ++i) acc[i] *= alpha;
+    m = m_new;
+    const int nvalid = min(32, k_end - k0);
+    for (int j = 0; j < nvalid; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, pr, j);
+      const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)base, j);
+      const T* vp = cache + (size_t)bj + plane;
+#pragma unroll
+      for (int i = 0; i < kMaxDimPerLane; ++i) {
+        const int dd = lane + 32 * i;
+        if (dd < d) acc[i] = fmaf(pj, to_f32(vp[dd]), acc[i]);
+      }
+    }
+  }
+
+  if (splits == 1) {
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    T* o = out + (size_t)t * out_stride + (size_t)h * d;
+#pragma unroll
+    for (int i = 0; i < kMaxDimPerLane; ++i) {
+      const int dd = lane + 32 * i;
+      if (dd < d) o[dd] = from_f32<T>(acc[i] * inv);
+    }
+  } else {
+    const size_t idx = ((size_t)t * nq + h) * splits + split;
+    float* pa = part_acc + idx * d;
+#pragma unroll
+    for (int i = 0; i < kMaxDimPerLane; ++i) {
+      const int dd = lane + 32 * i;
+      if (dd < d) pa[dd] = acc[i];
+    }
+    if (lane == 0) { part_ml[idx * 2] = m; part_ml[idx * 2 + 1] = l; }
+  }
+}
+
+// Merge of the per-split partial results: out = sum_z e^{m_z - M} acc_z / sum_z e^{m_z - M} l_z.
+template <typename T>
+__global__ void attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
+                                       const float* __restrict__ part_ml, int out_stride, int nq, int d,
+                                       int splits) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  const size_t idx0 = ((size_t)t * nq + h) * splits;
+  float M = -INFINITY;
+  for (int z = 0; z < splits; ++z) M = fmaxf(M, part_ml[(idx0 + z) * 2]);
+  float L = 0.f;
+  for (int z = 0; z < splits; ++z) {
+    const float mz = part_ml[(idx0 + z) * 2];
+    if (mz > -INFINITY) L += expf(mz - M) * part_ml[(idx0 + z) * 2 + 1];
+  }
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  for (int dd = threadIdx.x; dd < d; dd += blockDim.x) {
+    float a = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float mz = part_ml[(idx0 + z) * 2];
+      if (mz > -INFINITY) a = fmaf(expf(mz - M), part_acc[(idx0 + z) * d + dd], a);
+    }
+    out[(size_t)t * out_stride + (size_t)h * d + dd] = from_f32<T>(a * inv);
+  }
+}
+
+template <typename T>
+int paged_attention_simt(void* out, const void* q, const void* cache, const int* block_table,
+                         const int* tok_req, const int* positions, float* part_acc, float* part_ml,
+                         int tokens, int q_stride, int out_stride, int bt_stride, int nq, int nkv, int d,
+                         int page_size, float scale, int window, int splits, void* stream) {
+  PTL_REQUIRE(tokens >= 0 && nq > 0 && nkv > 0 && page_size > 0, "paged_attention: bad sizes");
+  PTL_REQUIRE(nq % nkv == 0, "paged_attention: %d query heads are no multiple of %d kv heads", nq, nkv);
+  PTL_REQUIRE(d % 16 == 0 && d >= 16 && d <= 32 * kMaxDimPerLane, "paged_attention: head size %d must be a multiple of 16 in [16, %d]", d, 32 * kMaxDimPerLane);
+  PTL_REQUIRE(splits >= 1 && splits <= 65535, "paged_attention: splits=%d", splits);
+  PTL_REQUIRE(splits == 1 || (part_acc && part_ml), "paged_attention: splits > 1 need scratch buffers");
+  PTL_REQUIRE(window >= 0, "paged_attention: window must be >= 0");
+  PTL_REQUIRE(aligned16(q) && aligned16(cache) && (q_stride * sizeof(T)) % 16 == 0, "paged_attention: q and cache must be 16-byte aligned");
+  if (tokens == 0) return 0;
+  dim3 grid(tokens, (nq + kWarpsPerBlock - 1) / kWarpsPerBlock, splits);
+  const size_t smem = (size_t)kWarpsPerBlock * d * sizeof(float);
+  paged_attention_simt_kernel<T><<<grid, kWarpsPerBlock * 32, smem, as_stream(stream)>>>(
+      (T*)out, part_acc, part_ml, (const T*)q, (const T*)cache, block_table, tok_req, positions,
+      q_stride, out_stride, bt_stride, nq, nkv, d, page_size, scale, window, splits);
+  int rc = check_launch("paged_attention");
+  if (rc) return rc;
+  if (splits > 1) {
+    dim3 g2(tokens, nq);
+    attention_merge_kernel<T><<<g2, d >= 128 ? 128 : (d >= 64 ? 64 : 32), 0, as_stream(stream)>>>(
+        (T*)out, part_acc, part_ml, out_stride, nq, d, splits);
+    rc = check_launch("attention_merge");
+  }
+  return rc;
+}
+
+}  // namespace ptl
+
+PTL_EXPORT int ptl_paged_attention_simt_f32(void* out, const void* q, const void* cache, const int* block_table, const int* tok_req, const int* positions, float* part_acc, float* part_ml, int tokens, int q_stride, int out_stride, int bt_stride, int nq, int nkv, int d, int page_size, float scale, int window, int splits, void* stream) {
+  return ptl::paged_attention_simt<float>(out, q, cache, block_table, tok_req, positions, part_acc, part_ml, tokens, q_stride, out_stride, bt_stride, nq, nkv, d, page_size, scale, window, splits, stream);
+}
+PTL_EXPORT int ptl_paged_attention_simt_bf16(void* out, const void* q, const void* cache, const int* block_table, const int* tok_req, const int* positions, float* part_acc, float* part_ml, int tokens, int q_stride, int out_stride, int bt_stride, int nq, int nkv, int d, int page_size, float scale, int window, int splits, void* stream) {
+  return ptl::paged_attention_simt<__nv_bfloat16>(out, q, cache, block_table, tok_req, positions, part_acc, part_ml, tokens, q_stride, out_stride, bt_stride, nq, nkv, d, page_size, scale, window, splits, stream);
+}

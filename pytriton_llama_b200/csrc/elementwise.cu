@@ -1,0 +1,167 @@
+// Row-wise kernels: embedding gather, residual add fused with RMSNorm, SiLU(gate)*up.
+// Each takes any width (no power of two needed); 16-byte packets are used when the row pitch
+// allows it, scalars otherwise.
+#include "common.cuh"
+
+namespace ptl {
+
+// ------------------------------------------------------------------ embedding
+// out[t, :] = table[ids[t], :].  An id outside [0, vocab) writes zeros and raises *status.
+template <typename T>
+__global__ void embed_gather_kernel(T* __restrict__ out, const T* __restrict__ table,
+                                    const int* __restrict__ ids, int hidden, int vocab,
+                                    int vec_ok, int* __restrict__ status) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool bad = id < 0 || id >= vocab;
+  if (bad && threadIdx.x == 0 && status) atomicExch(status, 1);
+  T* dst = out + (size_t)t * hidden;
+  const T* src = table + (size_t)(bad ? 0 : id) * hidden;
+  constexpr int VN = Vec16<T>::N;
+  if (vec_ok) {
+    for (int i = threadIdx.x * VN; i < hidden; i += blockDim.x * VN) {
+      Vec16<T> v = load16(src + i);
+      if (bad) {
+#pragma unroll
+        for (int k = 0; k < VN; ++k) v.set(k, 0.f);
+      }
+      store16(dst + i, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = bad ? from_f32<T>(0.f) : src[i];
+  }
+}
+
+// ------------------------------------------------------------------ add + RMSNorm
+// For output row m (input row r = rows ? rows[m] : m):
+//   s = (residual_in ? residual_in[r] : 0) + (x ? x[r] : 0)          in float32
+//   residual_out[m] = s                                              (if residual_out)
+//   y[m] = s * rsqrt(mean(s^2) + eps) * w                            rounded once to T
+// The row is kept in shared memory between the two passes.
+template <typename T>
+__global__ void add_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ residual_out,
+                                   const float* __restrict__ residual_in, const T* __restrict__ x,
+                                   const float* __restrict__ w, const int* __restrict__ rows,
+                                   int hidden, float eps) {
+  extern __shared__ float row[];
+  __shared__ float red[33];
+  const int m = blockIdx.x;
+  const int r = rows ? rows[m] : m;
+  const float* rin = residual_in ? residual_in + (size_t)r * hidden : nullptr;
+  const T* xin = x ? x + (size_t)r * hidden : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float s = rin ? rin[i] : 0.f;
+    if (xin) s += to_f32(xin[i]);
+    row[i] = s;
+    ss += s * s;
+  }
+  ss = block_sum(ss, red);
+  const float rrms = 1.0f / sqrtf(ss / (float)hidden + eps);
+  float* rout = residual_out ? residual_out + (size_t)m * hidden : nullptr;
+  T* yo = y + (size_t)m * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float s = row[i];
+    if (rout) rout[i] = s;
+    yo[i] = from_f32<T>(s * rrms * w[i]);
+  }
+}
+
+// ------------------------------------------------------------------ SiLU(gate) * up
+// gu is [T, 2*inter] (gate columns first); out[t, i] = g * sigmoid(g) * u in float32.
+template <typename T>
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, int vec_ok) {
+  const int t = blockIdx.y;
+  const T* g = gu + (size_t)t * 2 * inter;
+  const T* u = g + inter;
+  T* o = out + (size_t)t * inter;
+  constexpr int VN = Vec16<T>::N;
+  if (vec_ok) {
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * VN;
+    if (i < inter) {
+      Vec16<T> a = load16(g + i), b = load16(u + i), c;
+#pragma unroll
+      for (int k = 0; k < VN; ++k) {
+        const float gv = a.get(k);
+        c.set(k, gv / (1.0f + expf(-gv)) * b.get(k));
+      }
+      store16(o + i, c);
+    }
+  } else {
+    for (int k = 0; k < VN; ++k) {
+      const int i = (blockIdx.x * blockDim.x + threadIdx.x) * VN + k;
+      if (i < inter) {
+        const float gv = to_f32(g[i]);
+        o[i] = from_f32<T>(gv / (1.0f + expf(-gv)) * to_f32(u[i]));
+      }
+    }
+  }
+}
+
+template <typename T>
+int embed_gather(void* out, const void* table, const int* ids, int tokens, int hidden, int vocab,
+                 int* status, void* stream) {
+  PTL_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "embed_gather: bad sizes tokens=%d hidden=%d vocab=%d", tokens, hidden, vocab);
+  if (tokens == 0) return 0;
+  const int vec_ok = (hidden % Vec16<T>::N == 0) && aligned16(out) && aligned16(table);
+  int threads = 128;
+  embed_gather_kernel<T><<<tokens, threads, 0, as_stream(stream)>>>(
+      (T*)out, (const T*)table, ids, hidden, vocab, vec_ok, status);
+  return check_launch("embed_gather");
+}
+
+template <typename T>
+int add_rmsnorm(void* y, float* residual_out, const float* residual_in, const void* x, const float* w,
+                const int* rows, int out_rows, int hidden, float eps, void* stream) {
+  PTL_REQUIRE(out_rows >= 0 && hidden > 0, "add_rmsnorm: bad sizes rows=%d hidden=%d", out_rows, hidden);
+  PTL_REQUIRE(residual_in || x, "add_rmsnorm: needs a residual or an input");
+  PTL_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
+  if (out_rows == 0) return 0;
+  const size_t smem = (size_t)hidden * sizeof(float);
+  PTL_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: hidden=%d does not fit the row buffer (max %d)", hidden, 200 * 1024 / 4);
+  static bool raised[2] = {false, false};
+  constexpr int slot = sizeof(T) == 4 ? 0 : 1;
+  if (smem > 48 * 1024 && !raised[slot]) {
+    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    PTL_REQUIRE(e == cudaSuccess, "add_rmsnorm: cannot raise shared memory: %s", cudaGetErrorString(e));
+    raised[slot] = true;
+  }
+  int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
+  add_rmsnorm_kernel<T><<<out_rows, threads, smem, as_stream(stream)>>>(
+      (T*)y, residual_out, residual_in, (const T*)x, w, rows, hidden, eps);
+  return check_launch("add_rmsnorm");
+}
+
+template <typename T>
+int silu_mul(void* out, const void* gu, int tokens, int inter, void* stream) {
+  PTL_REQUIRE(tokens >= 0 && inter > 0, "silu_mul: bad sizes tokens=%d inter=%d", tokens, inter);
+  PTL_REQUIRE(tokens <= 65535, "silu_mul: at most 65535 rows per call, got %d", tokens);
+  if (tokens == 0) return 0;
+  constexpr int VN = Vec16<T>::N;
+  const int vec_ok = (inter % VN == 0) && aligned16(out) && aligned16(gu);
+  const int threads = 256;
+  dim3 grid((inter + threads * VN - 1) / (threads * VN), tokens);
+  silu_mul_kernel<T><<<grid, threads, 0, as_stream(stream)>>>((T*)out, (const T*)gu, inter, vec_ok);
+  return check_launch("silu_mul");
+}
+
+}  // namespace ptl
+
+PTL_EXPORT int ptl_embed_gather_f32(void* out, const void* table, const int* ids, int tokens, int hidden, int vocab, int* status, void* stream) {
+  return ptl::embed_gather<float>(out, table, ids, tokens, hidden, vocab, status, stream);
+}
+PTL_EXPORT int ptl_embed_gather_bf16(void* out, const void* table, const int* ids, int tokens, int hidden, int vocab, int* status, void* stream) {
+  return ptl::embed_gather<__nv_bfloat16>(out, table, ids, tokens, hidden, vocab, status, stream);
+}
+PTL_EXPORT int ptl_add_rmsnorm_f32(void* y, float* residual_out, const float* residual_in, const void* x, const float* w, const int* rows, int out_rows, int hidden, float eps, void* stream) {
+  return ptl::add_rmsnorm<float>(y, residual_out, residual_in, x, w, rows, out_rows, hidden, eps, stream);
+}
+PTL_EXPORT int ptl_add_rmsnorm_bf16(void* y, float* residual_out, const float* residual_in, const void* x, const float* w, const int* rows, int out_rows, int hidden, float eps, void* stream) {
+  return ptl::add_rmsnorm<__nv_bfloat16>(y, residual_out, residual_in, x, w, rows, out_rows, hidden, eps, stream);
+}
+PTL_EXPORT int ptl_silu_mul_f32(void* out, const void* gu, int tokens, int inter, void* stream) {
+  return ptl::silu_mul<float>(out, gu, tokens, inter, stream);
+}
+PTL_EXPORT int ptl_silu_mul_bf16(void* out, const void* gu, int tokens, int inter, void* stream) {
+  return ptl::silu_mul<__nv_bfloat16>(out, gu, tokens, inter, stream);
+}

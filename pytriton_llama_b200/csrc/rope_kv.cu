@@ -1,0 +1,85 @@
+// Rotary position encoding of q and k, fused with the write of k and v into the paged cache.
+//
+// qkv is the projection output of one step, [tokens, (nq + 2*nkv) * d]: q heads, then k heads,
+// then v heads, head-major with d contiguous.  For token t at position p and frequency index j
+// the angle is float(p) * inv_freq[j] in float32; the pair (x[j], x[j + rot/2]) of a head turns
+// into (x1*cos - x2*sin, x2*cos + x1*sin).  q is rewritten in place; rotated k and plain v go to
+// cache slot `slots[t]` (page = slot / page_size, offset = slot % page_size; a negative slot
+// skips the write).  Cache layout of one layer: [pages][2 (k,v)][nkv][page_size][d].
+// inv_freq == nullptr leaves q and k unrotated (a mixer with another position encoding).
+#include "common.cuh"
+
+namespace ptl {
+
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                     const float* __restrict__ inv_freq, const int* __restrict__ slots,
+                                     T* __restrict__ cache, int nq, int nkv, int d, int rot,
+                                     int page_size, int write_cache) {
+  const int t = blockIdx.x;
+  const int row_len = (nq + 2 * nkv) * d;
+  T* row = qkv + (size_t)t * row_len;
+  const float pos = (float)positions[t];
+  const int slot = write_cache ? slots[t] : -1;
+  const int page = slot >= 0 ? slot / page_size : 0;
+  const int off = slot >= 0 ? slot % page_size : 0;
+  const size_t plane = (size_t)nkv * page_size * d;         // one of k / v inside a page
+  T* kdst = cache ? cache + ((size_t)page * 2) * plane + (size_t)off * d : nullptr;
+  T* vdst = cache ? kdst + plane : nullptr;
+  const int half = rot / 2;
+  const int pairs_per_head = d - half;  // `half` rotated pairs, then d - rot pass-through elements
+  // q and k heads
+  for (int e = threadIdx.x; e < (nq + nkv) * pairs_per_head; e += blockDim.x) {
+    const int h = e / pairs_per_head;
+    const int j = e % pairs_per_head;
+    T* head = row + (size_t)h * d;
+    const bool is_k = h >= nq;
+    T* kd = (is_k && slot >= 0) ? kdst + (size_t)(h - nq) * page_size * d : nullptr;
+    if (j < half) {
+      float x1 = to_f32(head[j]), x2 = to_f32(head[j + half]);
+      float o1 = x1, o2 = x2;
+      if (inv_freq) {
+        float s, c;
+        sincosf(pos * inv_freq[j], &s, &c);
+        o1 = x1 * c - x2 * s;
+        o2 = x2 * c + x1 * s;
+      }
+      const T r1 = from_f32<T>(o1), r2 = from_f32<T>(o2);
+      if (!is_k) { head[j] = r1; head[j + half] = r2; }
+      else { head[j] = r1; head[j + half] = r2; if (kd) { kd[j] = r1; kd[j + half] = r2; } }
+    } else {
+      const int i = rot + (j - half);  // untouched tail when rot < d
+      if (kd) kd[i] = head[i];
+    }
+  }
+  // v heads
+  if (slot >= 0 && vdst) {
+    const T* vsrc = row + (size_t)(nq + nkv) * d;
+    for (int e = threadIdx.x; e < nkv * d; e += blockDim.x) {
+      const int h = e / d, i = e % d;
+      vdst[(size_t)h * page_size * d + i] = vsrc[e];
+    }
+  }
+}
+
+template <typename T>
+int rope_kv_write(void* qkv, const int* positions, const float* inv_freq, const int* slots, void* cache,
+                  int tokens, int nq, int nkv, int d, int rot, int page_size, long long num_slots,
+                  void* stream) {
+  PTL_REQUIRE(tokens >= 0 && nq > 0 && nkv > 0 && d > 0, "rope_kv_write: bad sizes");
+  PTL_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "rope_kv_write: rotary width %d must be even and <= head size %d", rot, d);
+  PTL_REQUIRE(cache == nullptr || (page_size > 0 && slots != nullptr && num_slots > 0), "rope_kv_write: a cache needs slots and a page size");
+  if (tokens == 0) return 0;
+  rope_kv_write_kernel<T><<<tokens, 128, 0, as_stream(stream)>>>(
+      (T*)qkv, positions, inv_freq, slots, (T*)cache, nq, nkv, d, rot, page_size, cache != nullptr);
+  return check_launch("rope_kv_write");
+}
+
+}  // namespace ptl
+
+PTL_EXPORT int ptl_rope_kv_write_f32(void* qkv, const int* positions, const float* inv_freq, const int* slots, void* cache, int tokens, int nq, int nkv, int d, int rot, int page_size, long long num_slots, void* stream) {
+  return ptl::rope_kv_write<float>(qkv, positions, inv_freq, slots, cache, tokens, nq, nkv, d, rot, page_size, num_slots, stream);
+}
+PTL_EXPORT int ptl_rope_kv_write_bf16(void* qkv, const int* positions, const float* inv_freq, const int* slots, void* cache, int tokens, int nq, int nkv, int d, int rot, int page_size, long long num_slots, void* stream) {
+  return ptl::rope_kv_write<__nv_bfloat16>(qkv, positions, inv_freq, slots, cache, tokens, nq, nkv, d, rot, page_size, num_slots, stream);
+}

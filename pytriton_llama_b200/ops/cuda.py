@@ -1,0 +1,260 @@
+"""Tensor-level wrappers of the hand-written sm_100a kernels.
+
+``CudaOps`` is the only implementation of the operator set that the engine's parts call.  It
+loads the library built from ``csrc/`` through ctypes and launches on torch's current CUDA stream;
+torch itself is used for allocation and, in bfloat16, for the plain library matrix products
+(cuBLAS) where lite_llama uses nn.Linear / F.linear too (lite_llama/models/llama.py:22-24,37-40).
+There is no CPU path: a tensor that is not on a CUDA device, or a library that cannot be built
+or loaded, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import build
+
+_c_int = ctypes.c_int
+_c_ll = ctypes.c_longlong
+_c_f = ctypes.c_float
+_ptr = ctypes.c_void_p
+
+_SIGNATURES = {
+    "ptl_embed_gather": [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr],
+    "ptl_add_rmsnorm": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_f, _ptr],
+    "ptl_silu_mul": [_ptr, _ptr, _c_int, _c_int, _ptr],
+    "ptl_rope_kv_write": [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _ptr],
+    "ptl_paged_attention_simt": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int,
+                                 _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _ptr],
+}
+_GEMM_SIG = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr]
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments or CUDA reported an error."""
+
+
+_LIB = None
+
+
+def load_library() -> ctypes.CDLL:
+    """The kernel library, built on first use.  Raises if it cannot be built or loaded."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = build.library_path()
+    lib = ctypes.CDLL(str(path))
+    for base, sig in _SIGNATURES.items():
+        for suffix in ("_f32", "_bf16"):
+            fn = getattr(lib, base + suffix)
+            fn.argtypes = sig
+            fn.restype = _c_int
+    for name in ("ptl_gemm_simt_f32", "ptl_gemm_simt_bf16", "ptl_gemm_simt_bf16_f32out"):
+        fn = getattr(lib, name)
+        fn.argtypes = _GEMM_SIG
+        fn.restype = _c_int
+    lib.ptl_sample.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
+    lib.ptl_sample.restype = _c_int
+    lib.ptl_last_error.restype = ctypes.c_char_p
+    _LIB = lib
+    return lib
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _suffix(dtype: torch.dtype) -> str:
+    if dtype == torch.float32:
+        return "_f32"
+    if dtype == torch.bfloat16:
+        return "_bf16"
+    raise KernelError(f"unsupported element type {dtype}")
+
+
+class CudaOps:
+    """The operator set of the engine on one CUDA device."""
+
+    name = "cuda"
+
+    def __init__(self, device: torch.device):
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise KernelError(f"the kernels run on CUDA devices only, got {device}")
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device is available; this engine has no CPU path")
+        self.device = device
+        self.lib = load_library()
+        major, minor = torch.cuda.get_device_capability(device)
+        if major != 10:
+            raise KernelError(f"the kernels are compiled for sm_100a only; device reports sm_{major}{minor}")
+        self._status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    # ------------------------------------------------------------------ helpers
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise KernelError(self.lib.ptl_last_error().decode())
+
+    def _want(self, t: torch.Tensor, name: str, dtype=None) -> None:
+        if t.device != self.device:
+            raise KernelError(f"{name} lives on {t.device}, expected {self.device}")
+        if not t.is_contiguous():
+            raise KernelError(f"{name} must be contiguous")
+        if dtype is not None and t.dtype != dtype:
+            raise KernelError(f"{name} has element type {t.dtype}, expected {dtype}")
+
+    def empty(self, shape, dtype) -> torch.Tensor:
+        return torch.empty(shape, dtype=dtype, device=self.device)
+
+    # ------------------------------------------------------------------ operators
+    def embed(self, ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+        self._want(ids, "ids", torch.int32)
+        self._want(table, "table")
+        out = self.empty((ids.shape[0], table.shape[1]), table.dtype)
+        fn = getattr(self.lib, "ptl_embed_gather" + _suffix(table.dtype))
+        self._check(fn(_p(out), _p(table), _p(ids), ids.shape[0], table.shape[1], table.shape[0],
+                       _p(self._status), self._stream()))
+        return out
+
+    def bad_token_seen(self) -> bool:
+        """True if an embedding lookup met an id outside the vocabulary since the last call (syncs)."""
+        bad = bool(self._status.item())
+        if bad:
+            self._status.zero_()
+        return bad
+
+    def add_rmsnorm(self, x: Optional[torch.Tensor], residual: Optional[torch.Tensor], weight: torch.Tensor,
+                    eps: float, rows: Optional[torch.Tensor] = None,
+                    dtype: Optional[torch.dtype] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        """y = rmsnorm(residual + x) * weight, the sum kept as the new float32 residual.
+
+        Without ``rows`` the residual tensor is updated in place (created from ``x`` when None).
+        With ``rows`` (int32 indices) only those rows are normed and no residual is written."""
+        src = x if x is not None else residual
+        hidden = src.shape[-1]
+        dtype = dtype or (x.dtype if x is not None else None)
+        if dtype is None:
+            raise KernelError("add_rmsnorm: give dtype when there is no x")
+        self._want(weight, "norm weight", torch.float32)
+        if x is not None:
+            self._want(x, "x", dtype)
+        if residual is not None:
+            self._want(residual, "residual", torch.float32)
+        if rows is not None:
+            self._want(rows, "rows", torch.int32)
+            n_out = rows.shape[0]
+            res_out = None
+        else:
+            n_out = src.shape[0]
+            res_out = residual if residual is not None else self.empty((n_out, hidden), torch.float32)
+        y = self.empty((n_out, hidden), dtype)
+        fn = getattr(self.lib, "ptl_add_rmsnorm" + _suffix(dtype))
+        self._check(fn(_p(y), _p(res_out), _p(residual), _p(x), _p(weight), _p(rows), n_out, hidden,
+                       float(eps), self._stream()))
+        return y, res_out
+
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """x[T, K] @ w[N, K]^T.  float32: the library's own FFMA kernel (true 32-bit);
+        bfloat16: a cuBLAS product with float32 accumulation."""
+        self._want(x, "x")
+        self._want(w, "w", x.dtype)
+        out_dtype = out_dtype or x.dtype
+        M, K = x.shape
+        N = w.shape[0]
+        if w.shape[1] != K:
+            raise KernelError(f"linear: x is [{M},{K}] but w is {list(w.shape)}")
+        if x.dtype == torch.float32:
+            out = self.empty((M, N), torch.float32)
+            self._check(self.lib.ptl_gemm_simt_f32(_p(out), _p(x), _p(w), M, N, K, K, K, N, 0, self._stream()))
+            return out
+        if out_dtype == torch.float32:
+            return torch.mm(x, w.t(), out_dtype=torch.float32)
+        return torch.mm(x, w.t())
+
+    def linear_simt(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """The CUDA-core product for any element type (checks of the tensor-core kernels)."""
+        self._want(x, "x")
+        self._want(w, "w", x.dtype)
+        out_dtype = out_dtype or x.dtype
+        M, K = x.shape
+        N = w.shape[0]
+        out = self.empty((M, N), out_dtype)
+        if x.dtype == torch.float32:
+            fn = self.lib.ptl_gemm_simt_f32
+        elif out_dtype == torch.float32:
+            fn = self.lib.ptl_gemm_simt_bf16_f32out
+        else:
+            fn = self.lib.ptl_gemm_simt_bf16
+        self._check(fn(_p(out), _p(x), _p(w), M, N, K, K, K, N, 0, self._stream()))
+        return out
+
+    def silu_mul(self, gu: torch.Tensor) -> torch.Tensor:
+        self._want(gu, "gate_up")
+        tokens, two_i = gu.shape
+        out = self.empty((tokens, two_i // 2), gu.dtype)
+        fn = getattr(self.lib, "ptl_silu_mul" + _suffix(gu.dtype))
+        self._check(fn(_p(out), _p(gu), tokens, two_i // 2, self._stream()))
+        return out
+
+    def rope_kv_write(self, qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                      rot: int, slots: Optional[torch.Tensor], cache: Optional[torch.Tensor],
+                      nq: int, nkv: int, d: int, page_size: int) -> None:
+        self._want(qkv, "qkv")
+        self._want(positions, "positions", torch.int32)
+        if inv_freq is not None:
+            self._want(inv_freq, "inv_freq", torch.float32)
+            if inv_freq.numel() < rot // 2:
+                raise KernelError("inv_freq shorter than half the rotary width")
+        if cache is not None:
+            self._want(cache, "cache", qkv.dtype)
+            self._want(slots, "slots", torch.int32)
+            num_slots = cache.shape[0] * page_size
+        else:
+            num_slots = 0
+        if qkv.shape[1] != (nq + 2 * nkv) * d:
+            raise KernelError(f"qkv rows have {qkv.shape[1]} elements, expected {(nq + 2 * nkv) * d}")
+        fn = getattr(self.lib, "ptl_rope_kv_write" + _suffix(qkv.dtype))
+        self._check(fn(_p(qkv), _p(positions), _p(inv_freq), _p(slots), _p(cache), qkv.shape[0], nq, nkv, d,
+                       rot, page_size, num_slots, self._stream()))
+
+    def paged_attention(self, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                        tok_req: torch.Tensor, positions: torch.Tensor, nq: int, nkv: int, d: int,
+                        page_size: int, scale: float, window: int = 0, splits: int = 1,
+                        hints=None) -> torch.Tensor:
+        """q is [T, >= nq*d] (the q part of a qkv buffer is fine); returns [T, nq*d]."""
+        self._want(q, "q")
+        self._want(cache, "cache", q.dtype)
+        self._want(block_table, "block_table", torch.int32)
+        self._want(tok_req, "tok_req", torch.int32)
+        self._want(positions, "positions", torch.int32)
+        tokens = q.shape[0]
+        out = self.empty((tokens, nq * d), q.dtype)
+        part_acc = part_ml = None
+        if splits > 1:
+            part_acc = self.empty((tokens, nq, splits, d), torch.float32)
+            part_ml = self.empty((tokens, nq, splits, 2), torch.float32)
+        fn = getattr(self.lib, "ptl_paged_attention_simt" + _suffix(q.dtype))
+        self._check(fn(_p(out), _p(q), _p(cache), _p(block_table), _p(tok_req), _p(positions), _p(part_acc),
+                       _p(part_ml), tokens, q.shape[1], nq * d, block_table.shape[1], nq, nkv, d, page_size,
+                       float(scale), int(window), int(splits), self._stream()))
+        return out
+
+    def sample(self, logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Optional[torch.Tensor],
+               u: Optional[torch.Tensor]) -> torch.Tensor:
+        """int32 token per row; rows with temperature <= 0 (or temperature None) take the argmax."""
+        self._want(logits, "logits", torch.float32)
+        rows, vocab = logits.shape
+        out = self.empty((rows,), torch.int32)
+        probs = None
+        if temperature is not None:
+            for name, t in (("temperature", temperature), ("top_p", top_p), ("u", u)):
+                self._want(t, name, torch.float32)
+            probs = self.empty((rows, vocab), torch.float32)
+        self._check(self.lib.ptl_sample(_p(out), _p(logits), _p(probs), _p(temperature), _p(top_p), _p(u), rows,
+                                        vocab, vocab, self._stream()))
+        return out

@@ -1,0 +1,68 @@
+"""Rotary position encoding with optional llama3 frequency scaling.
+
+lite_llama/models/RotaryEmbedding.py:51 gives inv_freq_j = theta^(-2j/d); :80-98 rescale it for
+rope_type "llama3" (wavelengths above original/low_freq_factor divided by ``factor``, a smooth
+blend down to original/high_freq_factor).  The angle of position p is float32(p) * inv_freq_j
+(:200-217) and the pairs (x_j, x_{j+d/2}) are turned (lite_llama/kernels/rope_emb.py:94-103).
+The table of frequencies is built once on the host in float32; the rotation itself happens in
+the fused cache-write kernel.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from .base import Part, PartSpec, Runtime, register_part
+
+
+def rope_inverse_frequencies(head_dim: int, theta: float, scaling: Optional[dict], rotary_dim: Optional[int] = None) -> torch.Tensor:
+    rot = head_dim if rotary_dim is None else rotary_dim
+    exponents = torch.arange(0, rot, 2, dtype=torch.int64).to(torch.float32) / rot
+    inv_freq = 1.0 / (theta ** exponents)
+    if scaling is None or scaling.get("rope_type", "default") == "default":
+        return inv_freq
+    if scaling["rope_type"] != "llama3":
+        raise ValueError(f"unknown rope scaling {scaling['rope_type']!r}")
+    factor = scaling["factor"]
+    low = scaling["low_freq_factor"]
+    high = scaling["high_freq_factor"]
+    original = scaling["original_max_position_embeddings"]
+    wavelen = 2 * math.pi / inv_freq
+    divided = torch.where(wavelen > original / low, inv_freq / factor, inv_freq)
+    blend = (original / wavelen - low) / (high - low)
+    blended = (1 - blend) * divided / factor + blend * divided
+    in_band = ~(wavelen < original / high) & ~(wavelen > original / low)
+    return torch.where(in_band, blended, divided)
+
+
+@register_part("position", "rope")
+class RotaryPosition(Part):
+    """params: ``head_dim``, ``theta``, ``scaling`` (None or the llama3 block), optional ``rotary_dim``."""
+
+    def __init__(self, spec: PartSpec, runtime: Runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.head_dim = int(p["head_dim"])
+        self.rot = int(p.get("rotary_dim") or self.head_dim)
+        if self.rot % 2 or self.rot > self.head_dim:
+            raise ValueError(f"rotary width {self.rot} must be even and at most the head size {self.head_dim}")
+        self.inv_freq = rope_inverse_frequencies(self.head_dim, float(p["theta"]), p.get("scaling"), self.rot).to(runtime.device)
+
+    def rotary_table(self) -> Optional[Tuple[torch.Tensor, int]]:
+        return self.inv_freq, self.rot
+
+    def apply(self, qk: torch.Tensor, positions: torch.Tensor, heads: int, head_dim: int) -> None:
+        raise NotImplementedError("rotation is applied by the fused cache-write kernel")
+
+
+@register_part("position", "none")
+class NoPosition(Part):
+    """No position encoding: q and k go to the cache as projected."""
+
+    def rotary_table(self):
+        return None, 0
+
+    def apply(self, qk, positions, heads, head_dim) -> None:
+        pass
