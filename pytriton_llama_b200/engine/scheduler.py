@@ -1,0 +1,200 @@
+"""Continuous batching above the step function.
+
+lite_llama has no scheduler: a list of prompts is one static batch, padded to the longest
+prompt, with the cache for its whole life reserved up front and every request stepping until
+the last one ends (lite_llama/generate.py:108-149).  Here requests wait in a queue, are admitted
+while slots and pages last, have their prompts cut into portions under a token budget, decode one
+token per step beside other requests' portions, and free their pages the moment they finish.
+
+When pages run out for a request that is already running, the request admitted last is
+pre-empted: its pages are given back, it returns to the front of the queue and later recomputes
+its prompt together with the tokens it had generated.  A request that could not fit even into an
+empty cache is finished with reason "cache_too_small" instead of waiting for ever.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, Hashable, List, Optional
+
+from ..sampling.params import SamplingParams
+
+WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+
+
+@dataclass
+class Request:
+    id: Hashable
+    prompt: List[int]
+    params: SamplingParams
+    number: int = 0                    # arrival number; also feeds the sampling counters
+    output: List[int] = field(default_factory=list)
+    computed: int = 0                  # tokens of prompt + output that are in the cache
+    status: str = WAITING
+    finish_reason: Optional[str] = None
+    preemptions: int = 0
+
+    @property
+    def all_tokens(self) -> List[int]:
+        return self.prompt + self.output
+
+    @property
+    def pending(self) -> int:
+        return len(self.prompt) + len(self.output) - self.computed
+
+
+@dataclass
+class Portion:
+    request: Request
+    start: int            # index into all_tokens
+    length: int
+    sample: bool          # True when the portion ends at the request's last token
+
+
+@dataclass
+class StepPlan:
+    portions: List[Portion] = field(default_factory=list)
+    preempted: List[Request] = field(default_factory=list)
+    finished: List[Request] = field(default_factory=list)   # ended by the scheduler itself (could never fit)
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(p.length for p in self.portions)
+
+
+class Scheduler:
+    """Decides what each step runs.  ``cache`` is the engine's CacheManager (only its host-side
+    bookkeeping is used); pages are actually taken when the engine runs the plan."""
+
+    def __init__(self, cache, max_num_seqs: int, max_batched_tokens: int, max_seq_len: int,
+                 eos_token_ids=(), max_portion: Optional[int] = None):
+        self.cache = cache
+        self.max_num_seqs = max_num_seqs
+        self.max_batched_tokens = max_batched_tokens
+        self.max_seq_len = max_seq_len
+        self.max_portion = max_portion or max_batched_tokens
+        self.eos_token_ids = set(eos_token_ids)
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []      # in admission order
+        self._counter = 0
+
+    # ------------------------------------------------------------------ intake
+    def add(self, request_id: Hashable, prompt: List[int], params: Optional[SamplingParams] = None) -> Request:
+        params = params or SamplingParams()
+        req = Request(request_id, list(prompt), params, number=self._counter)
+        self._counter += 1
+        if not req.prompt:
+            req.status, req.finish_reason = FINISHED, "empty_prompt"
+        elif len(req.prompt) >= self.max_seq_len:
+            req.status, req.finish_reason = FINISHED, "prompt_too_long"
+        else:
+            self.waiting.append(req)
+        return req
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------ planning
+    def _pages_short(self, asks) -> bool:
+        return not self.cache.can_append(asks)
+
+    def _fits_empty_cache(self, req: Request, n_tokens: int) -> bool:
+        blocks = -(-n_tokens // self.cache.page_size)
+        for grp in self.cache.groups:
+            if grp.paged and grp.need.kind == "full" and blocks > grp.pool.num_pages:
+                return False
+        return True
+
+    def _preempt(self, req: Request, plan: StepPlan) -> None:
+        self.running.remove(req)
+        if self.cache.has(req.id):
+            self.cache.release(req.id)
+        req.computed = 0
+        req.status = WAITING
+        req.preemptions += 1
+        self.waiting.appendleft(req)
+        plan.preempted.append(req)
+
+    def schedule(self) -> StepPlan:
+        plan = StepPlan()
+        budget = self.max_batched_tokens
+        asks = []          # (request id, tokens) accepted so far, for the joint page check
+        # 1. running requests, oldest first: one token when decoding, else the next prompt portion
+        for req in list(self.running):
+            if req not in self.running:
+                continue   # pre-empted while serving an older request
+            if budget <= 0:
+                break
+            n = min(req.pending, budget, self.max_portion)
+            while self._pages_short(asks + [(req.id, n)]):
+                victim = self.running[-1]
+                if victim is req:
+                    # nothing younger to evict: shrink the portion, else give up this request
+                    if n > 1:
+                        n = max(1, n // 2)
+                        continue
+                    if len(self.running) == 1 and not asks:
+                        self.running.remove(req)
+                        self.cache.release(req.id)
+                        req.status, req.finish_reason = FINISHED, "cache_too_small"
+                        plan.finished.append(req)
+                    else:
+                        self._preempt(req, plan)
+                    n = 0
+                    break
+                # a younger request gives way; drop anything already planned for it
+                plan.portions = [p for p in plan.portions if p.request is not victim]
+                asks = [(r, k) for r, k in asks if r != victim.id]
+                self._preempt(victim, plan)
+            if n <= 0:
+                continue
+            plan.portions.append(Portion(req, req.computed, n, sample=(n == req.pending)))
+            asks.append((req.id, n))
+            budget -= n
+        # 2. admissions, first come first served, not in a step that had to pre-empt
+        while self.waiting and not plan.preempted and budget > 0 and len(self.running) < self.max_num_seqs:
+            req = self.waiting[0]
+            total = len(req.prompt) + len(req.output)
+            if not self._fits_empty_cache(req, total + 1):
+                self.waiting.popleft()
+                req.status, req.finish_reason = FINISHED, "cache_too_small"
+                plan.finished.append(req)
+                continue
+            n = min(req.pending, budget, self.max_portion)
+            if self._pages_short(asks + [(req.id, n)]):
+                break
+            self.waiting.popleft()
+            req.status = RUNNING
+            self.running.append(req)
+            plan.portions.append(Portion(req, req.computed, n, sample=(n == req.pending)))
+            asks.append((req.id, n))
+            budget -= n
+        return plan
+
+    # ------------------------------------------------------------------ after the step
+    def update(self, plan: StepPlan, sampled: Dict[Hashable, int]) -> List[Request]:
+        """Records the step's progress; ``sampled`` has the new token of every portion with
+        ``sample`` set.  Returns the requests that finished (their pages are given back here)."""
+        done: List[Request] = []
+        for p in plan.portions:
+            req = p.request
+            req.computed += p.length
+            if not p.sample:
+                continue
+            tok = int(sampled[req.id])
+            req.output.append(tok)
+            stop = self.eos_token_ids | set(req.params.stop_token_ids)
+            limit = req.params.max_gen_len
+            if tok in stop:
+                req.finish_reason = "stop"
+            elif limit is not None and len(req.output) >= limit:
+                req.finish_reason = "length"
+            elif len(req.prompt) + len(req.output) >= self.max_seq_len:
+                req.finish_reason = "max_seq_len"
+            if req.finish_reason:
+                req.status = FINISHED
+                self.running.remove(req)
+                if self.cache.has(req.id):
+                    self.cache.release(req.id)
+                done.append(req)
+        return done

@@ -1,0 +1,3 @@
+from .params import SamplingParams  # noqa: F401
+from .rng import uniform  # noqa: F401
+from .sampler import Sampler  # noqa: F401

@@ -1,0 +1,40 @@
+"""Picks next tokens from a step's logits on the device.
+
+lite_llama/generate.py:135-137: logits / temperature -> softmax -> ``sample_top_p`` (:30-43: sort,
+cumulative sum, drop tokens whose preceding mass exceeds p, renormalise, draw); argmax when
+temperature is 0 (lite_llama/generate_stream.py:143-150).  The kernel applies the same rule
+without a sort and draws with a uniform number supplied per row.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import torch
+
+from .params import SamplingParams
+from .rng import uniform
+
+
+class Sampler:
+    def __init__(self, ops, device, seed: int = 0):
+        self.ops = ops
+        self.device = torch.device(device)
+        self.seed = seed
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], request_numbers: Sequence[int],
+               token_indices: Sequence[int]) -> List[int]:
+        """One token per logits row.  ``request_numbers`` and ``token_indices`` feed the counter-based
+        uniform numbers (the index is the count of tokens the request has generated so far)."""
+        rows = logits.shape[0]
+        if rows == 0:
+            return []
+        if all(p.temperature <= 0 for p in params):
+            return self.ops.sample(logits, None, None, None).tolist()
+        host = torch.empty((3, rows), dtype=torch.float32, pin_memory=self.device.type == "cuda")
+        for i, p in enumerate(params):
+            host[0, i] = p.temperature
+            host[1, i] = p.top_p
+            seed = self.seed if p.seed is None else p.seed
+            host[2, i] = uniform(seed, request_numbers[i], token_indices[i])
+        dev = host.to(self.device, non_blocking=True)
+        return self.ops.sample(logits, dev[0], dev[1], dev[2]).tolist()

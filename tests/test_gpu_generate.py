@@ -1,0 +1,151 @@
+"""Generation through the Python entry points and the command line: greedy tokens against the
+plain implementation, seeded sampling, and scheduling under page pressure (GPU)."""
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_llama
+from conftest import PAGE_SIZE, ROOT, TINY, random_tokens
+from gpu_common import stored_dtype
+
+pytestmark = pytest.mark.gpu
+
+
+def _llm(folder, name, dtype, pages, **extra):
+    from pytriton_llama_b200.config import EngineConfig
+    from pytriton_llama_b200.engine.llm import LLM
+    cfg = EngineConfig(dtype=dtype, page_size=PAGE_SIZE[name], max_gpu_num_blocks=pages, max_seq_len=extra.pop("max_seq_len", 128),
+                       max_num_seqs=extra.pop("max_num_seqs", 4), max_batched_tokens=extra.pop("max_batched_tokens", 16), **extra)
+    return LLM(folder, cfg)
+
+
+def _plain_greedy(folder, prompts, n, stop=()):
+    cfg, w = plain_llama.load_model_folder(folder, dtype=torch.float64)
+    return [plain_llama.greedy_generate(cfg, w, p, n, stop_ids=stop) for p in prompts]
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_float32_equals_plain(model_folders, name):
+    """BASELINE workload of the tiny models: prompts 5/11/17 (A) and 1/9/33/70 (B), 8 new tokens."""
+    from pytriton_llama_b200.sampling import SamplingParams
+    folder = model_folders(name)
+    vocab = TINY[name]["vocab_size"]
+    lens = {"A": [5, 11, 17], "B": [1, 9, 33, 70]}[name]
+    prompts = [random_tokens(n, vocab, 300 + n) for n in lens]
+    eos = TINY[name]["eos_token_id"]
+    stop = [eos] if isinstance(eos, int) else list(eos)
+    want = _plain_greedy(folder, prompts, 8, stop)
+    llm = _llm(folder, name, "float32", pages=60)
+    got = llm.generate(prompts, SamplingParams(temperature=0.0, max_gen_len=8))
+    assert got == want
+    assert llm.engine.cache.free_pages() == 60
+    # the same through lite_llama's class names
+    from pytriton_llama_b200 import GenerateStreamText, GenerateText
+    gen = GenerateText(str(folder), None, max_seq_len=128, max_gpu_num_blocks=60, dtype="float32", page_size=PAGE_SIZE[name])
+    out = gen.generate(prompts, max_gen_len=8, temperature=0.0)
+    trimmed = [w[: next((i for i, t in enumerate(w) if t in stop), len(w))] for w in want]
+    assert out == trimmed
+    assert gen.generate(prompts[:1], max_gen_len=8, temperature=0.0, echo=True) == [prompts[0] + trimmed[0]]
+    stream = GenerateStreamText(str(folder), None, max_gpu_num_blocks=60, max_seq_len=128, dtype="float32", page_size=PAGE_SIZE[name])
+    pieces = [[] for _ in prompts]
+    for batch in stream.generate_stream(prompts, max_gen_len=8, temperature=0.0):
+        for i, new in enumerate(batch):
+            pieces[i] += new
+    assert pieces == trimmed
+
+
+def test_greedy_generation_bfloat16(model_folders):
+    """bfloat16 may pick another token where two logits nearly tie; every picked token must be
+    within rounding of the best logit of the plain model fed with the same history."""
+    from pytriton_llama_b200.sampling import SamplingParams
+    name = "B"
+    folder = model_folders(name, torch.bfloat16)
+    cfg, w = plain_llama.load_model_folder(folder, dtype=torch.float64)
+    prompts = [random_tokens(n, 384, 400 + n) for n in (9, 33, 70)]
+    llm = _llm(folder, name, "bfloat16", pages=60)
+    got = llm.generate(prompts, SamplingParams(temperature=0.0, max_gen_len=8, stop_token_ids=[]))
+    agree = 0
+    for p, out in zip(prompts, got):
+        assert 1 <= len(out) <= 8
+        logits = plain_llama.forward(cfg, w, p + out)
+        for i, tok in enumerate(out):
+            row = logits[len(p) + i - 1]
+            assert row[tok] >= row.max() - 0.04 * float(logits.abs().max()), (i, tok)
+            agree += int(tok == int(row.argmax()))
+    assert agree >= 0.8 * sum(len(o) for o in got)
+
+
+def test_sampling_is_seeded_and_independent_of_batching(model_folders):
+    """Temperature 0.8 from a fixed seed (BASELINE config B): the float32 engine draws exactly the
+    tokens the plain implementation draws from the same uniform numbers, whether the requests run
+    together in portions of 16 or one at a time."""
+    from pytriton_llama_b200.sampling import SamplingParams, uniform
+    name = "B"
+    folder = model_folders(name)
+    cfg, w = plain_llama.load_model_folder(folder, dtype=torch.float64)
+    prompts = [random_tokens(n, 384, 500 + n) for n in (1, 9, 33, 70)]
+    params = SamplingParams(temperature=0.8, top_p=0.9, max_gen_len=6, stop_token_ids=[])
+    llm = _llm(folder, name, "float32", pages=60, seed=1234)
+    got = llm.generate(prompts, params)
+    for number, (p, out) in enumerate(zip(prompts, got)):
+        seq = list(p)
+        for i, tok in enumerate(out):
+            row = plain_llama.forward(cfg, w, seq)[-1]
+            want = plain_llama.sample_token(row, 0.8, 0.9, uniform(1234, number, i))
+            if tok != want:   # only a draw within rounding of a boundary of the distribution may differ
+                pr = torch.softmax(row / 0.8, -1)
+                keep = plain_llama.top_p_keep_mask(pr, 0.9)
+                assert keep[tok]
+                kept = torch.where(keep, pr, torch.zeros_like(pr))
+                cdf = torch.cumsum(kept, 0) / kept.sum()
+                u = uniform(1234, number, i)
+                assert float(cdf[tok] - kept[tok] / kept.sum()) - 1e-5 <= u <= float(cdf[tok]) + 1e-5
+            if tok in (382, 383):
+                break
+            seq.append(tok)
+    llm2 = _llm(folder, name, "float32", pages=60, seed=1234, max_num_seqs=1)
+    assert llm2.generate(prompts, params) == got
+    llm3 = _llm(folder, name, "float32", pages=60, seed=99)
+    assert llm3.generate(prompts, params) != got
+
+
+def test_generation_under_page_pressure_preempts_and_still_matches(model_folders):
+    """So few pages that running requests must give way and recompute: the tokens do not change."""
+    from pytriton_llama_b200.sampling import SamplingParams
+    name = "A"
+    folder = model_folders(name)
+    prompts = [random_tokens(n, 256, 600 + n) for n in (17, 11, 5, 14, 9)]
+    want = _plain_greedy(folder, prompts, 12, [255])
+    llm = _llm(folder, name, "float32", pages=14, max_batched_tokens=8)   # 56 tokens of cache for 5 requests of up to 29
+    reqs = [llm.add_request(p, SamplingParams(temperature=0.0, max_gen_len=12)) for p in prompts]
+    steps = 0
+    while llm.has_work():
+        llm.step()
+        llm.engine.cache.check_invariants()
+        steps += 1
+        assert steps < 400
+    assert [r.output for r in reqs] == want
+    assert sum(r.preemptions for r in reqs) > 0
+    assert llm.engine.cache.free_pages() == 14
+    too_big = llm.add_request(random_tokens(60, 256, 1), SamplingParams(temperature=0.0, max_gen_len=4))
+    while llm.has_work():
+        llm.step()
+    assert too_big.finish_reason == "cache_too_small"
+
+
+def test_command_line(model_folders, tmp_path):
+    folder = model_folders("A")
+    prompt = random_tokens(7, 256, 700)
+    want = _plain_greedy(folder, [prompt], 5, [255])[0]
+    want = want[: next((i for i, t in enumerate(want) if t == 255), len(want))]
+    base = [sys.executable, str(ROOT / "cli.py"), "--checkpoints_dir", str(folder), "--dtype", "float32", "--temperature", "0",
+            "--max_gen_len", "5", "--max_seq_len", "64", "--max_gpu_num_blocks", "16", "--page_size", "4"]
+    out = subprocess.run(base + ["--prompt_ids"] + [str(t) for t in prompt], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert [int(t) for t in out.stdout.split()] == want
+    # the prompt loop: token ids on standard input, 'exit' ends it
+    loop = subprocess.run(base, input=" ".join(str(t) for t in prompt) + "\nexit\n", capture_output=True, text=True, timeout=600)
+    assert loop.returncode == 0, loop.stderr[-2000:]
+    assert " ".join(str(t) for t in want) in loop.stdout

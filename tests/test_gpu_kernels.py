@@ -1,0 +1,272 @@
+"""Each CUDA kernel alone against its plain PyTorch statement (tests/torch_ops.py), at sizes other
+than the engine's tests use: widths that are no power of two, rows that are not 16-byte
+multiples, head sizes from 16 to 256, odd head counts and groups (GPU)."""
+import math
+
+import pytest
+import torch
+
+import plain_llama
+from torch_ops import TorchOps
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from pytriton_llama_b200.ops.cuda import CudaOps
+    return CudaOps(torch.device("cuda:0"))
+
+
+REF = TorchOps("cpu")
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (scale * torch.randn(shape, generator=g)).to(dtype)
+
+
+def close(got, ref, dtype, what="", scale=None):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    assert got.shape == ref.shape, (what, got.shape, ref.shape)
+    s = scale if scale is not None else max(1.0, float(ref.abs().max()))
+    tol = 2e-5 * s if dtype == "float32" else 2 ** -7 * s      # bfloat16: one rounding of the result, twice over
+    d = (got - ref).abs().max()
+    assert d <= tol, f"{what}: max |diff| {d:.3e} > {tol:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("vocab, hidden", [(1000, 200), (257, 100), (50, 2048), (33, 7)])
+def test_embed(ops, dtype, vocab, hidden):
+    table = rnd((vocab, hidden), DT[dtype], 1)
+    ids = torch.tensor([0, vocab - 1, 5, 5, vocab // 2], dtype=torch.int32)
+    out = ops.embed(ids.cuda(), table.cuda())
+    assert torch.equal(out.cpu(), table[ids.long()])
+    assert not ops.bad_token_seen()
+    ops.embed(torch.tensor([vocab], dtype=torch.int32).cuda(), table.cuda())
+    assert ops.bad_token_seen() and not ops.bad_token_seen()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows, hidden, eps", [(5, 200, 1e-5), (3, 2048, 1e-6), (2, 5000, 3e-4), (4, 100, 1e-2), (1, 30000, 1e-5)])
+def test_add_rmsnorm(ops, dtype, rows, hidden, eps):
+    x = rnd((rows, hidden), DT[dtype], 2, 3.0)
+    res = rnd((rows, hidden), torch.float32, 3, 5.0)
+    w = 1 + rnd((hidden,), torch.float32, 4, 0.1)
+    y_ref, r_ref = REF.add_rmsnorm(x.clone(), res.clone(), w, eps, dtype=DT[dtype])
+    rc = res.clone().cuda()
+    y, r = ops.add_rmsnorm(x.cuda(), rc, w.cuda(), eps)
+    assert r.data_ptr() == rc.data_ptr()                      # the residual is updated in place
+    close(r, r_ref, "float32", "residual")
+    close(y, y_ref, dtype, "normed")
+    # first layer: no residual yet, the input becomes it
+    y0_ref, r0_ref = REF.add_rmsnorm(x.clone(), None, w, eps, dtype=DT[dtype])
+    y0, r0 = ops.add_rmsnorm(x.cuda(), None, w.cuda(), eps)
+    assert torch.equal(r0.cpu(), x.float())
+    close(y0, y0_ref, dtype, "first layer")
+    # wanted rows only (the final norm): gathers, writes no residual
+    idx = torch.tensor([rows - 1, 0], dtype=torch.int32)
+    yg_ref, _ = REF.add_rmsnorm(x.clone(), res.clone(), w, eps, rows=idx, dtype=DT[dtype])
+    rc2 = res.clone().cuda()
+    yg, none = ops.add_rmsnorm(x.cuda(), rc2, w.cuda(), eps, rows=idx.cuda())
+    assert none is None and torch.equal(rc2.cpu(), res)
+    close(yg, yg_ref, dtype, "gathered rows")
+
+
+@pytest.mark.parametrize("M, N, K", [(1, 300, 77), (7, 64, 200), (130, 257, 96), (33, 1000, 513), (300, 48, 2048)])
+def test_linear_float32_is_true_32_bit(ops, M, N, K):
+    x, w = rnd((M, K), torch.float32, 5), rnd((N, K), torch.float32, 6)
+    ref = x.double() @ w.double().T
+    out = ops.linear(x.cuda(), w.cuda())
+    # a product of K terms in float32: error ~ sqrt(K) * 2^-24 * |x||w|; a 10-bit-mantissa tensor-core mode would be 1e-3
+    assert (out.double().cpu() - ref).abs().max() < 3e-6 * math.sqrt(K) * 4
+
+
+@pytest.mark.parametrize("M, N, K", [(1, 304, 80), (7, 64, 200), (130, 264, 96), (64, 1000, 512)])
+def test_linear_bfloat16(ops, M, N, K):
+    x, w = rnd((M, K), torch.bfloat16, 5), rnd((N, K), torch.bfloat16, 6)
+    ref = x.double() @ w.double().T
+    close(ops.linear(x.cuda(), w.cuda()), ref, "bfloat16", "bf16 out")
+    out32 = ops.linear(x.cuda(), w.cuda(), out_dtype=torch.float32)
+    assert out32.dtype == torch.float32
+    assert (out32.double().cpu() - ref).abs().max() < 1e-4 * math.sqrt(K)
+    close(ops.linear_simt(x.cuda(), w.cuda()), ref, "bfloat16", "CUDA-core product")
+    assert (ops.linear_simt(x.cuda(), w.cuda(), out_dtype=torch.float32).double().cpu() - ref).abs().max() < 1e-4 * math.sqrt(K)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows, inter", [(3, 264), (2, 8192), (5, 101), (1, 24)])
+def test_silu_mul(ops, dtype, rows, inter):
+    gu = rnd((rows, 2 * inter), DT[dtype], 7, 3.0)
+    close(ops.silu_mul(gu.cuda()), REF.silu_mul(gu), dtype)
+
+
+def _random_paging(num_reqs, lens, page_size, num_pages, seed):
+    """Block tables that scatter each request over random pages of the pool."""
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    width = max(-(-n // page_size) for n in lens)
+    bt = torch.full((num_reqs, width), -1, dtype=torch.int32)
+    for r, n in enumerate(lens):
+        for b in range(-(-n // page_size)):
+            bt[r, b] = perm.pop()
+    return bt
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq, nkv, d, rot, page", [(5, 5, 48, 48, 16), (6, 2, 32, 32, 8), (4, 1, 16, 16, 4), (3, 1, 64, 32, 16),
+                                                   (8, 2, 128, 128, 32), (2, 2, 256, 256, 16)])
+def test_rope_kv_write(ops, dtype, nq, nkv, d, rot, page):
+    T, pages = 9, 12
+    qkv = rnd((T, (nq + 2 * nkv) * d), DT[dtype], 8)
+    positions = torch.tensor([0, 1, 2, 63, 64, 65, 1000, 4095, 70000], dtype=torch.int32)
+    inv_freq = plain_llama.rope_inv_freq({"head_dim": rot, "hidden_size": 1, "num_attention_heads": 1, "rope_theta": 500000.0,
+                                          "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                                           "high_freq_factor": 4.0, "original_max_position_embeddings": 64}})
+    slots = torch.tensor([5, 0, page * 3 + 1, -1, page * pages - 1, 17, 18, page * 2, 7], dtype=torch.int32)
+    cache_ref = torch.zeros((pages, 2, nkv, page, d), dtype=DT[dtype])
+    q_ref = qkv.clone()
+    REF.rope_kv_write(q_ref, positions, inv_freq, rot, slots, cache_ref, nq, nkv, d, page)
+    cache = torch.zeros_like(cache_ref).cuda()
+    q = qkv.clone().cuda()
+    ops.rope_kv_write(q, positions.cuda(), inv_freq.cuda(), rot, slots.cuda(), cache, nq, nkv, d, page)
+    close(q[:, : nq * d], q_ref[:, : nq * d], dtype, "rotated q", scale=4.0)
+    close(cache, cache_ref, dtype, "cache", scale=4.0)
+    assert torch.equal(cache.cpu()[:, 1], cache_ref[:, 1])                 # values are copied, not rotated
+    # the rotation angle is float32(position) * inv_freq: exact against a float64 sin/cos of that product
+    if dtype == "float32":
+        t = 7   # position 4095
+        ang = (torch.tensor(4095.0) * inv_freq).double()
+        x = qkv[t, :d].double()
+        want = x[: rot // 2] * ang.cos() - x[rot // 2: rot] * ang.sin()
+        assert (q[t, : rot // 2].double().cpu() - want).abs().max() < 2e-6
+    # without a table nothing is rotated, everything is stored
+    cache2 = torch.zeros_like(cache)
+    q2 = qkv.clone().cuda()
+    ops.rope_kv_write(q2, positions.cuda(), None, 0, slots.cuda(), cache2, nq, nkv, d, page)
+    assert torch.equal(q2.cpu(), qkv)
+    page0, off0 = divmod(5, page)
+    assert torch.equal(cache2[page0, 0, :, off0].cpu().reshape(-1), qkv[0, nq * d:(nq + nkv) * d])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq, nkv, d, page, window, splits", [
+    (5, 5, 48, 16, 0, 1), (6, 2, 32, 8, 0, 3), (4, 1, 16, 4, 0, 1), (8, 2, 128, 32, 0, 4), (2, 1, 256, 16, 0, 1),
+    (6, 3, 64, 16, 37, 1), (3, 1, 80, 8, 9, 2), (32, 8, 64, 16, 0, 8)])
+def test_paged_attention_mixed_batch(ops, dtype, nq, nkv, d, page, window, splits):
+    """Three requests in one call: a 70-token prompt portion after 50 cached tokens, a single decoded
+    token after 333, and a whole 19-token prompt; pages scattered at random."""
+    q_lens, ctx = [70, 1, 19], [120, 334, 19]
+    pages = sum(-(-c // page) for c in ctx) + 3
+    bt = _random_paging(3, ctx, page, pages, seed=d + nq)
+    cache = rnd((pages, 2, nkv, page, d), DT[dtype], 9)
+    T = sum(q_lens)
+    q = rnd((T, (nq + 2 * nkv) * d), DT[dtype], 10, 2.0)      # a qkv buffer: only its q part is read
+    tok_req = torch.repeat_interleave(torch.arange(3), torch.tensor(q_lens)).int()
+    positions = torch.cat([torch.arange(c - n, c) for n, c in zip(q_lens, ctx)]).int()
+    scale = 1 / math.sqrt(d)
+    ref = REF.paged_attention(q, cache, bt, tok_req, positions, nq, nkv, d, page, scale, window=window)
+    out = ops.paged_attention(q.cuda(), cache.cuda(), bt.cuda(), tok_req.cuda(), positions.cuda(), nq, nkv, d, page,
+                              scale, window=window, splits=splits)
+    close(out, ref, dtype, "attention", scale=1.0 if dtype == "float32" else 4.0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [0, 100])
+def test_attention_finds_one_far_key(ops, dtype, window):
+    """Random scores would hide a key that is skipped or read from the wrong slot.  Here every query
+    has ONE key whose score stands out (the key equals the query direction, scaled up), at places
+    where paging can go wrong: the first and last slot of a page, key 0, the query's own position,
+    the far edge of the window.  The output must be that key's value."""
+    nq, nkv, d, page = 4, 2, 64, 16
+    ctx = 700
+    pages = -(-ctx // page) + 2
+    bt = _random_paging(1, [ctx], page, pages, seed=3)
+    g = torch.Generator().manual_seed(4)
+    k = 0.05 * torch.randn(ctx, nkv, d, generator=g)
+    v = torch.randn(ctx, nkv, d, generator=g)
+    positions = torch.tensor([ctx - 1, ctx - 2, 640, 639, 512, 300], dtype=torch.int32)
+    lo = [(int(p) - window + 1 if window else 0) for p in positions]
+    targets = [lo[0], int(positions[1]), 639 if window else 15, 624 if window else 16, lo[4] + 1, lo[5]]
+    T = len(targets)
+    q = torch.zeros(T, nq, d)
+    for t, key in enumerate(targets):
+        for h in range(nq):
+            direction = torch.randn(d, generator=g)
+            direction /= direction.norm()
+            q[t, h] = direction * 40.0
+            k[key, h // 2] = k[key, h // 2] + direction * 8.0
+    cache = torch.zeros(pages, 2, nkv, page, d)
+    for n in range(ctx):
+        p, o = int(bt[0, n // page]), n % page
+        cache[p, 0, :, o] = k[n]
+        cache[p, 1, :, o] = v[n]
+    cache = cache.to(DT[dtype])
+    out = ops.paged_attention(q.reshape(T, nq * d).to(DT[dtype]).cuda(), cache.cuda(), bt.cuda(),
+                              torch.zeros(T, dtype=torch.int32).cuda(), positions.cuda(), nq, nkv, d, page,
+                              1 / math.sqrt(d), window=window, splits=1 if window else 4).float().cpu().view(T, nq, d)
+    for t, key in enumerate(targets):
+        for h in range(nq):
+            want = cache[int(bt[0, key // page]), 1, h // 2, key % page].float()
+            assert (out[t, h] - want).abs().max() < 0.05, (t, h, key)
+
+
+@pytest.mark.parametrize("vocab", [1000, 128256, 37])
+def test_sampling(ops, vocab):
+    g = torch.Generator().manual_seed(vocab)
+    rows = 12
+    logits = 3.0 * torch.randn(rows, vocab, generator=g)
+    logits[0, vocab - 1] = logits[0, 5] = logits[0].max() + 1            # equal maxima: the lowest index wins
+    temperature = torch.tensor([0.0, 0.0, 0.8, 0.8, 0.8, 1.5, 0.3, 1.0, 1.0, 0.6, 0.6, 2.0])
+    top_p = torch.tensor([0.9, 0.9, 0.9, 0.5, 1.0, 0.95, 0.9, 0.01, 0.7, 0.9, 0.9, 0.999])
+    u = torch.tensor([0.5, 0.5, 0.0, 0.999999, 0.37, 0.81, 0.5, 0.9, 0.123, 0.25, 0.75, 0.6])
+    out = ops.sample(logits.cuda(), temperature.cuda(), top_p.cuda(), u.cuda()).cpu()
+    assert out[0] == 5 and out[1] == int(torch.argmax(logits[1]))
+    assert out[7] == int(torch.argmax(logits[7]))                        # a tiny top_p keeps the most likely token only
+    for i in range(2, rows):
+        want = plain_llama.sample_token(logits[i], float(temperature[i]), float(top_p[i]), float(u[i]))
+        if out[i] != want:
+            # float32 sums may tip a token that sits within rounding of a boundary; anything else is a fault
+            p = torch.softmax(logits[i].double() / float(temperature[i]), -1)
+            keep = plain_llama.top_p_keep_mask(p, float(top_p[i]))
+            assert keep[out[i]], f"row {i}: token {int(out[i])} is outside the nucleus"
+            kept = torch.where(keep, p, torch.zeros_like(p))
+            cdf = torch.cumsum(kept, 0) / kept.sum()
+            lo = float(cdf[out[i]] - kept[out[i]] / kept.sum())
+            assert lo - 1e-5 <= float(u[i]) <= float(cdf[out[i]]) + 1e-5, f"row {i}: token {int(out[i])} vs {want}"
+    greedy = ops.sample(logits.cuda(), None, None, None).cpu()
+    assert torch.equal(greedy[1:].long(), torch.argmax(logits[1:], -1))
+
+
+def test_sampling_follows_the_distribution(ops):
+    """Many draws with different uniform numbers reproduce the filtered probabilities."""
+    vocab, n = 50, 4000
+    g = torch.Generator().manual_seed(0)
+    row = 2.0 * torch.randn(vocab, generator=g)
+    logits = row.repeat(n, 1)
+    u = (torch.arange(n) + 0.5) / n
+    out = ops.sample(logits.cuda(), torch.full((n,), 0.9).cuda(), torch.full((n,), 0.8).cuda(), u.cuda()).cpu().long()
+    p = torch.softmax(row.double() / 0.9, -1)
+    keep = plain_llama.top_p_keep_mask(p, 0.8)
+    want = torch.where(keep, p, torch.zeros_like(p))
+    want /= want.sum()
+    freq = torch.bincount(out, minlength=vocab).double() / n
+    assert (freq[~keep] == 0).all()
+    assert (freq - want).abs().max() < 2.0 / n + 1e-9
+
+
+def test_kernels_refuse_sizes_they_cannot_take(ops):
+    from pytriton_llama_b200.ops.cuda import KernelError
+    q = torch.zeros(1, 3 * 24, device="cuda")
+    cache = torch.zeros(2, 2, 1, 16, 24, device="cuda")
+    z = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(KernelError, match="multiple of 16"):
+        ops.paged_attention(q, cache, z.view(1, 1), z, z, 1, 1, 24, 16, 1.0)
+    with pytest.raises(KernelError, match="no multiple"):
+        ops.paged_attention(torch.zeros(1, 5 * 32, device="cuda"), torch.zeros(2, 2, 2, 16, 32, device="cuda"), z.view(1, 1), z, z, 3, 2, 32, 16, 1.0)
+    with pytest.raises(KernelError):
+        ops.embed(torch.zeros(2, dtype=torch.int32), torch.zeros(4, 4))       # CPU tensors: there is no CPU path
+    with pytest.raises(KernelError, match="row buffer"):
+        ops.add_rmsnorm(torch.zeros(1, 60000, device="cuda"), None, torch.ones(60000, device="cuda"), 1e-5)

@@ -1,0 +1,277 @@
+"""Each part of a layer alone against the plain implementation's function for it, the block that
+arranges them, run orders that name a layer twice or share a cache entry, and a toy mixer with
+state of its own that is registered here, built and stepped without touching the package (GPU)."""
+import math
+
+import pytest
+import torch
+
+import plain_llama
+from conftest import TINY, TINY_B, random_tokens
+from gpu_common import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def rt():
+    from pytriton_llama_b200.ops.cuda import CudaOps
+    from pytriton_llama_b200.parts import Runtime
+    dev = torch.device("cuda:0")
+    return {d: Runtime(dev, d, CudaOps(dev)) for d in (torch.float32, torch.bfloat16)}
+
+
+def _ctx(q_lens, starts, page_size, tables, slots, window=0):
+    from pytriton_llama_b200.engine.context import GroupStepView, StepContext
+    R = len(q_lens)
+    dev = "cuda:0"
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    width = max(len(t) for t in tables)
+    bt = torch.full((R, width), -1, dtype=torch.int32)
+    for r, t in enumerate(tables):
+        bt[r, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    group = GroupStepView(page_size, bt.to(dev), i32(slots), window)
+    pos = [p for s, n in zip(starts, q_lens) for p in range(s, s + n)]
+    tok_req = [r for r, n in enumerate(q_lens) for _ in range(n)]
+    return StepContext(num_tokens=sum(q_lens), num_requests=R, positions=i32(pos), tok_req=i32(tok_req),
+                       q_start=i32([0] + list(torch.tensor(q_lens).cumsum(0))), ctx_len=i32([s + n for s, n in zip(starts, q_lens)]),
+                       state_slot=i32(list(range(R))), fresh=i32([int(s == 0) for s in starts]), groups={0: group},
+                       q_lens=q_lens, ctx_lens=[s + n for s, n in zip(starts, q_lens)], max_q_len=max(q_lens),
+                       max_ctx_len=max(s + n for s, n in zip(starts, q_lens))), group
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(rt, dtype):
+    from pytriton_llama_b200.parts import PartSpec, build_part
+    part = build_part("norm", PartSpec("rmsnorm", {"width": 200, "eps": 3e-4}, {"weight": "w"}), rt[dtype])
+    assert part.tensor_specs()["weight"].shape == (200,)
+    w = 1 + 0.1 * torch.randn(200)
+    part.load({"weight": w.to(torch.bfloat16)})            # stored in 16 bits: read exactly, kept as float32
+    assert part.weight.dtype == torch.float32
+    x = torch.randn(6, 200).to(dtype)
+    res = torch.randn(6, 200)
+    y, r = part.forward(x.cuda(), res.clone().cuda())
+    s = res.double() + x.double()
+    want = plain_llama.rms_norm(s, w.to(torch.bfloat16).double(), 3e-4)
+    assert (r.double().cpu() - s).abs().max() < 1e-6
+    assert (y.double().cpu() - want).abs().max() < (1e-5 if dtype == torch.float32 else 0.03)
+
+
+def test_rope_part_builds_the_reference_frequencies(rt):
+    from pytriton_llama_b200.parts import PartSpec, build_part
+    for cfg in TINY.values():
+        hd = cfg["head_dim"]
+        part = build_part("position", PartSpec("rope", {"head_dim": hd, "theta": cfg["rope_theta"], "scaling": cfg["rope_scaling"]}),
+                          rt[torch.float32])
+        inv, rot = part.rotary_table()
+        assert rot == hd and inv.dtype == torch.float32
+        assert torch.equal(inv.cpu(), plain_llama.rope_inv_freq(cfg))      # bit for bit, llama3 scaling included
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 13])
+def test_attention_part_over_two_steps(rt, dtype, window):
+    """The mixer alone with a cache of its own: a 29-token portion, then 11 more tokens, equals the
+    plain attention block over all 40 (projections, rotation, cache write, attention, output)."""
+    from pytriton_llama_b200.engine.context import LayerCacheView
+    from pytriton_llama_b200.parts import PartSpec, build_part
+    cfg = dict(TINY_B)
+    H, nq, nkv, d = 192, 6, 2, 32
+    spec = PartSpec("gqa_attention", {"hidden": H, "heads": nq, "kv_heads": nkv, "head_dim": d, "window": window},
+                    {"q": "q", "k": "k", "v": "v", "o": "o"},
+                    {"position": PartSpec("rope", {"head_dim": d, "theta": cfg["rope_theta"], "scaling": cfg["rope_scaling"]})})
+    part = build_part("mixer", spec, rt[dtype])
+    need = part.cache_need()
+    assert (need.kind, need.kv_heads, need.head_dim, need.window) == ("window" if window else "full", nkv, d, window)
+    g = torch.Generator().manual_seed(1)
+    w = {n: (0.12 * torch.randn(s.shape, generator=g)).to(dtype) for n, s in part.tensor_specs().items()}
+    part.load(w)
+    x = torch.randn(40, H, generator=g).to(dtype)
+    names = {"q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight", "v": "self_attn.v_proj.weight", "o": "self_attn.o_proj.weight"}
+    want = plain_llama.attention_block(x.double(), torch.arange(40), cfg, {names[n]: t.double() for n, t in w.items()}, "",
+                                       window=window or None)
+    page, pages = 8, 7
+    table = [5, 2, 6, 0, 3]
+    kv = torch.zeros(pages, 2, nkv, page, d, dtype=dtype, device="cuda")
+    slot = lambda p: table[p // page] * page + p % page
+    ctx, group = _ctx([29], [0], page, [table[:4]], [slot(p) for p in range(29)], window)
+    out1 = part.forward(x[:29].cuda(), ctx, LayerCacheView(group, kv, None, True))
+    ctx, group = _ctx([11], [29], page, [table], [slot(p) for p in range(29, 40)], window)
+    out2 = part.forward(x[29:].cuda(), ctx, LayerCacheView(group, kv, None, True))
+    got = torch.cat([out1, out2]).double().cpu()
+    tol = 2e-5 if dtype == torch.float32 else 0.03 * float(want.abs().max())
+    assert (got - want).abs().max() < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_part(rt, dtype):
+    from pytriton_llama_b200.parts import PartSpec, build_part
+    part = build_part("ffn", PartSpec("swiglu", {"hidden": 200, "inter": 264}, {"gate": "g", "up": "u", "down": "d"}), rt[dtype])
+    g = torch.Generator().manual_seed(2)
+    w = {n: (0.1 * torch.randn(s.shape, generator=g)).to(dtype) for n, s in part.tensor_specs().items()}
+    part.load(w)
+    x = torch.randn(9, 200, generator=g).to(dtype)
+    want = plain_llama.swiglu_ffn(x.double(), w["gate"].double(), w["up"].double(), w["down"].double())
+    got = part.forward(x.cuda()).double().cpu()
+    assert (got - want).abs().max() < (2e-5 if dtype == torch.float32 else 0.03 * float(want.abs().max()))
+
+
+# ---------------------------------------------------------------------------------------------
+# A toy mixer with state of its own, defined here: y_t = x_t * gain + decay * s_{t-1},  s_t = y_t,
+# one state vector per request that survives between steps.  It uses no attention cache at all.
+
+def _register_toy():
+    from pytriton_llama_b200.parts import CacheNeed, Part, TensorSpec, register_part
+
+    @register_part("mixer", "toy_running_state")
+    class ToyRunningState(Part):
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            self.hidden = spec.params["hidden"]
+            self.decay = spec.params["decay"]
+
+        def tensor_specs(self):
+            return {"gain": TensorSpec((self.hidden,), init="ones_jitter")}
+
+        def load(self, tensors):
+            self.gain = self._to_f32(tensors["gain"])
+
+        def cache_need(self):
+            return CacheNeed(kind="none", state_shape=(self.hidden,), state_dtype=torch.float32)
+
+        def forward(self, x, ctx, cache):
+            out = torch.empty_like(x)
+            starts = [0]
+            for n in ctx.q_lens:
+                starts.append(starts[-1] + n)
+            slots = ctx.state_slot.tolist()
+            fresh = ctx.fresh.tolist()
+            for r, n in enumerate(ctx.q_lens):
+                s = cache.state[slots[r]]
+                if fresh[r]:
+                    s.zero_()
+                for t in range(starts[r], starts[r] + n):
+                    y = x[t].float() * self.gain + self.decay * s
+                    s.copy_(y)
+                    out[t] = y.to(x.dtype)
+            return out
+    return ToyRunningState
+
+
+def _toy_spec(cfg, toy_layers, run_order=None):
+    from pytriton_llama_b200.config import LlamaConfig
+    from pytriton_llama_b200.models.llama import llama_spec
+    from pytriton_llama_b200.parts import PartSpec
+    spec = llama_spec(LlamaConfig.from_dict(cfg), norm_init="ones_jitter")
+    for i in toy_layers:
+        spec.layers[i].parts["mixer"] = PartSpec("toy_running_state", {"hidden": cfg["hidden_size"], "decay": 0.5},
+                                                 {"gain": f"model.layers.{i}.toy.gain"})
+    if run_order is not None:
+        spec.run_order = run_order
+    return spec
+
+
+def _plain_toy_forward(cfg, w, tokens, toy_layers, run_order):
+    """The plain implementation's pieces with the toy mixer in some layers (float64, whole sequence)."""
+    tokens = torch.as_tensor(tokens)
+    pos = torch.arange(len(tokens))
+    h = w["model.embed_tokens.weight"][tokens]
+    eps = cfg["rms_norm_eps"]
+    for layer in run_order:
+        p = f"model.layers.{layer}."
+        x = plain_llama.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+        if layer in toy_layers:
+            s = torch.zeros_like(x[0])
+            rows = []
+            for t in range(len(tokens)):
+                s = x[t] * w[p + "toy.gain"] + 0.5 * s
+                rows.append(s)
+            a = torch.stack(rows)
+        else:
+            a = plain_llama.attention_block(x, pos, cfg, w, p)
+        h = h + a
+        h = h + plain_llama.swiglu_ffn(plain_llama.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps),
+                                       w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    h = plain_llama.rms_norm(h, w["model.norm.weight"], eps)
+    return h @ w["model.embed_tokens.weight"].T
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    """One layer keeps attention, one gets the toy mixer: different mixers in different layers of
+    one model, fixed-size state in the manager's slots, no change to the package's files."""
+    import traces
+    from pytriton_llama_b200.config import EngineConfig, register_architecture, LlamaConfig
+    from pytriton_llama_b200.engine.engine import Engine
+    from pytriton_llama_b200.weights import read_folder, write_random_model
+    _register_toy()
+    cfg = dict(TINY["A"], architectures=["ToyStateForCausalLM"])
+    register_architecture("ToyStateForCausalLM", LlamaConfig.from_dict,
+                          lambda c, norm_init="ones": _toy_spec(cfg, toy_layers=[1]))
+    folder = write_random_model(tmp_path / "toy", cfg, seed=4, dtype=torch.float32, std=0.08)
+    tensors = read_folder(folder)
+    assert "model.layers.1.toy.gain" in tensors and "model.layers.1.self_attn.q_proj.weight" not in tensors
+    eng = Engine(folder, EngineConfig(dtype="float32", page_size=4, max_gpu_num_blocks=40, max_seq_len=128, max_num_seqs=3))
+    assert len(eng.cache.groups) == 2 and eng.cache.groups[1].state[1].shape == (3, 64)
+    seqs = {f"t{i}": random_tokens(n, 256, 50 + i) for i, n in enumerate([21, 9, 33, 14])}
+    w = {k: v.double() for k, v in tensors.items()}
+    ref = {r: _plain_toy_forward(cfg, w, s, [1], [0, 1]) for r, s in seqs.items()}
+    got = traces.replay(eng, traces.mixed(seqs, live=3))       # slots are reused: the state must restart at zero
+    for r in seqs:
+        assert_close(got[r], ref[r], "float32", r)
+
+
+def test_run_order_may_repeat_a_layer_and_share_a_cache_entry(tmp_path):
+    """Run order [0, 1, 0']: layer 0 runs twice; its second run has a cache entry of its own.  And
+    [0, 1(reads entry 0)]: layer 1 stores nothing and attends over the keys and values layer 0 wrote."""
+    import traces
+    from pytriton_llama_b200.config import EngineConfig, LlamaConfig, register_architecture
+    from pytriton_llama_b200.engine.engine import Engine
+    from pytriton_llama_b200.models.spec import RunEntry
+    from pytriton_llama_b200.weights import read_folder, write_random_model
+    base = dict(TINY["A"])
+    # (a) a layer twice
+    cfg = dict(base, architectures=["TwiceForCausalLM"])
+    register_architecture("TwiceForCausalLM", LlamaConfig.from_dict,
+                          lambda c, norm_init="ones": _toy_spec(cfg, [], [RunEntry(0, 0), RunEntry(1, 1), RunEntry(0, 2)]))
+    folder = write_random_model(tmp_path / "twice", cfg, seed=5, dtype=torch.float32, std=0.08)
+    w = {k: v.double() for k, v in read_folder(folder).items()}
+    seqs = {f"s{i}": random_tokens(n, 256, 70 + i) for i, n in enumerate([19, 30, 8])}
+    eng = Engine(folder, EngineConfig(dtype="float32", page_size=4, max_gpu_num_blocks=30, max_seq_len=64, max_num_seqs=3))
+    assert sorted(eng.cache.groups[0].entries) == [0, 1, 2]
+    got = traces.replay(eng, traces.mixed(seqs, live=3))
+    for r, s in seqs.items():
+        assert_close(got[r], _plain_toy_forward(cfg, w, s, [], [0, 1, 0]), "float32", r)
+    # (b) a layer that reads another layer's cache entry
+    cfg2 = dict(base, architectures=["SharedForCausalLM"])
+    register_architecture("SharedForCausalLM", LlamaConfig.from_dict,
+                          lambda c, norm_init="ones": _toy_spec(cfg2, [], [RunEntry(0, 0), RunEntry(1, 0, write=False)]))
+    folder2 = write_random_model(tmp_path / "shared", cfg2, seed=6, dtype=torch.float32, std=0.08)
+    w2 = {k: v.double() for k, v in read_folder(folder2).items()}
+    eng2 = Engine(folder2, EngineConfig(dtype="float32", page_size=4, max_gpu_num_blocks=30, max_seq_len=64, max_num_seqs=3))
+    assert eng2.cache.groups[0].entries == [0]                       # one entry: a third of the cache memory
+    got2 = traces.replay(eng2, traces.portions(seqs))
+
+    def shared_forward(tokens):
+        tokens = torch.as_tensor(tokens)
+        pos = torch.arange(len(tokens))
+        S = len(tokens)
+        h = w2["model.embed_tokens.weight"][tokens]
+        eps = base["rms_norm_eps"]
+        nq, nkv, d = 4, 1, 16
+        cos, sin = plain_llama.rope_cos_sin(plain_llama.rope_inv_freq(base), pos, torch.float64)
+        kv0 = None
+        for layer in (0, 1):
+            p = f"model.layers.{layer}."
+            x = plain_llama.rms_norm(h, w2[p + "input_layernorm.weight"], eps)
+            q = plain_llama.apply_rope((x @ w2[p + "self_attn.q_proj.weight"].T).view(S, nq, d), cos, sin)
+            if layer == 0:
+                k = plain_llama.apply_rope((x @ w2[p + "self_attn.k_proj.weight"].T).view(S, nkv, d), cos, sin)
+                v = (x @ w2[p + "self_attn.v_proj.weight"].T).view(S, nkv, d)
+                kv0 = (k, v)
+            a = plain_llama.causal_gqa_attention(q, *kv0).reshape(S, nq * d) @ w2[p + "self_attn.o_proj.weight"].T
+            h = h + a
+            h = h + plain_llama.swiglu_ffn(plain_llama.rms_norm(h, w2[p + "post_attention_layernorm.weight"], eps),
+                                           w2[p + "mlp.gate_proj.weight"], w2[p + "mlp.up_proj.weight"], w2[p + "mlp.down_proj.weight"])
+        return plain_llama.rms_norm(h, w2["model.norm.weight"], eps) @ w2["model.embed_tokens.weight"].T
+    for r, s in seqs.items():
+        assert_close(got2[r], shared_forward(s), "float32", r)
