@@ -22,7 +22,7 @@ paged_attention_simt_kernel(T* __restrict__ out, float* __restrict__ part_acc, f
                             const int* __restrict__ block_table, const int* __restrict__ tok_req,
                             const int* __restrict__ positions, int q_stride, int out_stride,
                             int bt_stride, int nq, int nkv, int d, int page_size, float scale,
-                            int window, int splits) {
+                            int window, int splits, int num_pages) {
   extern __shared__ float qs_all[];  // [warps][d] scaled query
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -34,17 +34,17 @@ paged_attention_simt_kernel(T* __restrict__ out, float* __restrict__ part_acc, f
   for (int i = lane; i < d; i += 32) qs[i] = to_f32(qrow[i]) * scale;
   __syncwarp();
 
-  const int r = tok_req[t];
+  const int r = tok_req[t];        // r < 0: a padding row of a fixed-size batch; it sees no key and yields zeros
   const int p = positions[t];
   const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-  const int nkeys = p - lo + 1;
+  const int nkeys = r < 0 ? 0 : p - lo + 1;
   int chunk = (nkeys + splits - 1) / splits;
   chunk = (chunk + 31) & ~31;
   const int k_begin = lo + split * chunk;
-  const int k_end = min(lo + (split + 1) * chunk, p + 1);
+  const int k_end = r < 0 ? k_begin : min(lo + (split + 1) * chunk, p + 1);
   const int kvh = h / (nq / nkv);
   const size_t plane = (size_t)nkv * page_size * d;
-  const int* bt = block_table + (size_t)r * bt_stride;
+  const int* bt = block_table + (size_t)(r < 0 ? 0 : r) * bt_stride;
   constexpr int VN = Vec16<T>::N;
 
   float m = -INFINITY, l = 0.f;
@@ -54,11 +54,12 @@ paged_attention_simt_kernel(T* __restrict__ out, float* __restrict__ part_acc, f
 
   for (int k0 = k_begin; k0 < k_end; k0 += 32) {
     const int key = k0 + lane;
-    const bool valid = key < k_end;
+    bool valid = key < k_end;
     size_t base = 0;  // element offset of this lane's key row (k plane)
     float s = -INFINITY;
+    const int page = valid ? bt[key / page_size] : 0;
+    if (page < 0 || page >= num_pages) valid = false;  // never follow a table entry outside the pool
     if (valid) {
-      const int page = bt[key / page_size];
       base = ((size_t)page * 2) * plane + ((size_t)kvh * page_size + key % page_size) * d;
       const T* kp = cache + base;
       float dot = 0.f;
@@ -80,6 +81,7 @@ paged_attention_simt_kernel(T* __restrict__ out, float* __restrict__ part_acc, f
     for (int j = 0; j < nvalid; ++j) {
       const float pj = __shfl_sync(0xffffffffu, pr, j);
       const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)base, j);
+      if (pj == 0.f) continue;   // uniform over the warp: a skipped key has no valid address
       const T* vp = cache + (size_t)bj + plane;
 #pragma unroll
       for (int i = 0; i < kMaxDimPerLane; ++i) {
@@ -138,20 +140,20 @@ template <typename T>
 int paged_attention_simt(void* out, const void* q, const void* cache, const int* block_table,
                          const int* tok_req, const int* positions, float* part_acc, float* part_ml,
                          int tokens, int q_stride, int out_stride, int bt_stride, int nq, int nkv, int d,
-                         int page_size, float scale, int window, int splits, void* stream) {
+                         int page_size, float scale, int window, int splits, int num_pages, void* stream) {
   PTL_REQUIRE(tokens >= 0 && nq > 0 && nkv > 0 && page_size > 0, "paged_attention: bad sizes");
   PTL_REQUIRE(nq % nkv == 0, "paged_attention: %d query heads are no multiple of %d kv heads", nq, nkv);
   PTL_REQUIRE(d % 16 == 0 && d >= 16 && d <= 32 * kMaxDimPerLane, "paged_attention: head size %d must be a multiple of 16 in [16, %d]", d, 32 * kMaxDimPerLane);
   PTL_REQUIRE(splits >= 1 && splits <= 65535, "paged_attention: splits=%d", splits);
   PTL_REQUIRE(splits == 1 || (part_acc && part_ml), "paged_attention: splits > 1 need scratch buffers");
-  PTL_REQUIRE(window >= 0, "paged_attention: window must be >= 0");
+  PTL_REQUIRE(window >= 0 && num_pages > 0, "paged_attention: window must be >= 0 and the pool non-empty");
   PTL_REQUIRE(aligned16(q) && aligned16(cache) && (q_stride * sizeof(T)) % 16 == 0, "paged_attention: q and cache must be 16-byte aligned");
   if (tokens == 0) return 0;
   dim3 grid(tokens, (nq + kWarpsPerBlock - 1) / kWarpsPerBlock, splits);
   const size_t smem = (size_t)kWarpsPerBlock * d * sizeof(float);
   paged_attention_simt_kernel<T><<<grid, kWarpsPerBlock * 32, smem, as_stream(stream)>>>(
       (T*)out, part_acc, part_ml, (const T*)q, (const T*)cache, block_table, tok_req, positions,
-      q_stride, out_stride, bt_stride, nq, nkv, d, page_size, scale, window, splits);
+      q_stride, out_stride, bt_stride, nq, nkv, d, page_size, scale, window, splits, num_pages);
   int rc = check_launch("paged_attention");
   if (rc) return rc;
   if (splits > 1) {
@@ -165,9 +167,9 @@ int paged_attention_simt(void* out, const void* q, const void* cache, const int*
 
 }  // namespace ptl
 
-PTL_EXPORT int ptl_paged_attention_simt_f32(void* out, const void* q, const void* cache, const int* block_table, const int* tok_req, const int* positions, float* part_acc, float* part_ml, int tokens, int q_stride, int out_stride, int bt_stride, int nq, int nkv, int d, int page_size, float scale, int window, int splits, void* stream) {
-  return ptl::paged_attention_simt<float>(out, q, cache, block_table, tok_req, positions, part_acc, part_ml, tokens, q_stride, out_stride, bt_stride, nq, nkv, d, page_size, scale, window, splits, stream);
+PTL_EXPORT int ptl_paged_attention_simt_f32(void* out, const void* q, const void* cache, const int* block_table, const int* tok_req, const int* positions, float* part_acc, float* part_ml, int tokens, int q_stride, int out_stride, int bt_stride, int nq, int nkv, int d, int page_size, float scale, int window, int splits, int num_pages, void* stream) {
+  return ptl::paged_attention_simt<float>(out, q, cache, block_table, tok_req, positions, part_acc, part_ml, tokens, q_stride, out_stride, bt_stride, nq, nkv, d, page_size, scale, window, splits, num_pages, stream);
 }
-PTL_EXPORT int ptl_paged_attention_simt_bf16(void* out, const void* q, const void* cache, const int* block_table, const int* tok_req, const int* positions, float* part_acc, float* part_ml, int tokens, int q_stride, int out_stride, int bt_stride, int nq, int nkv, int d, int page_size, float scale, int window, int splits, void* stream) {
-  return ptl::paged_attention_simt<__nv_bfloat16>(out, q, cache, block_table, tok_req, positions, part_acc, part_ml, tokens, q_stride, out_stride, bt_stride, nq, nkv, d, page_size, scale, window, splits, stream);
+PTL_EXPORT int ptl_paged_attention_simt_bf16(void* out, const void* q, const void* cache, const int* block_table, const int* tok_req, const int* positions, float* part_acc, float* part_ml, int tokens, int q_stride, int out_stride, int bt_stride, int nq, int nkv, int d, int page_size, float scale, int window, int splits, int num_pages, void* stream) {
+  return ptl::paged_attention_simt<__nv_bfloat16>(out, q, cache, block_table, tok_req, positions, part_acc, part_ml, tokens, q_stride, out_stride, bt_stride, nq, nkv, d, page_size, scale, window, splits, num_pages, stream);
 }

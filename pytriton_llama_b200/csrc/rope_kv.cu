@@ -15,12 +15,13 @@ template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                                      const float* __restrict__ inv_freq, const int* __restrict__ slots,
                                      T* __restrict__ cache, int nq, int nkv, int d, int rot,
-                                     int page_size, int write_cache) {
+                                     int page_size, int write_cache, long long num_slots) {
   const int t = blockIdx.x;
   const int row_len = (nq + 2 * nkv) * d;
   T* row = qkv + (size_t)t * row_len;
   const float pos = (float)positions[t];
-  const int slot = write_cache ? slots[t] : -1;
+  int slot = write_cache ? slots[t] : -1;
+  if (slot >= num_slots) slot = -1;  // never write outside the pool
   const int page = slot >= 0 ? slot / page_size : 0;
   const int off = slot >= 0 ? slot % page_size : 0;
   const size_t plane = (size_t)nkv * page_size * d;         // one of k / v inside a page
@@ -71,7 +72,7 @@ int rope_kv_write(void* qkv, const int* positions, const float* inv_freq, const 
   PTL_REQUIRE(cache == nullptr || (page_size > 0 && slots != nullptr && num_slots > 0), "rope_kv_write: a cache needs slots and a page size");
   if (tokens == 0) return 0;
   rope_kv_write_kernel<T><<<tokens, 128, 0, as_stream(stream)>>>(
-      (T*)qkv, positions, inv_freq, slots, (T*)cache, nq, nkv, d, rot, page_size, cache != nullptr);
+      (T*)qkv, positions, inv_freq, slots, (T*)cache, nq, nkv, d, rot, page_size, cache != nullptr, num_slots);
   return check_launch("rope_kv_write");
 }
 

@@ -45,12 +45,59 @@ def _pad4(n: int) -> int:
     return (n + 3) & ~3
 
 
+class _HostBatch:
+    """A step's requests as host lists, before they are packed for the device."""
+
+    def __init__(self, entries, q_lens, starts, fresh, state_slots, slots_by_group, logit_rows):
+        self.entries, self.q_lens, self.starts, self.fresh = entries, q_lens, starts, fresh
+        self.state_slots, self.slots_by_group, self.logit_rows = state_slots, slots_by_group, logit_rows
+        self.R = len(entries)
+        self.T = sum(q_lens)
+        self.max_q_len = max(q_lens)
+
+
+class _Layout:
+    """Where each integer array of a step lies inside one packed int32 buffer (one copy per step)."""
+
+    def __init__(self, T: int, R: int, M: int, bt_width: int, groups: List[int], static_rows: bool = False):
+        self.T, self.R, self.M, self.bt_width, self.groups, self.static_rows = T, R, M, bt_width, groups, static_rows
+        self.seg: Dict[str, tuple] = {}
+        cursor = 0
+        names = [("tokens", T), ("positions", T), ("tok_req", T), ("q_start", R + 1), ("ctx_len", R),
+                 ("state_slot", R), ("fresh", R), ("logit_rows", M)]
+        for g in groups:
+            names += [(f"slots{g}", T), (f"bt{g}", R * bt_width)]
+        for name, n in names:
+            self.seg[name] = (cursor, n)
+            cursor += _pad4(max(n, 1))
+        self.size = cursor
+
+    def view(self, dev: torch.Tensor, name: str) -> torch.Tensor:
+        lo, n = self.seg[name]
+        return dev[lo:lo + n]
+
+
+@dataclass
+class _DecodeGraph:
+    graph: object
+    layout: _Layout
+    staging: list          # ring of (pinned host buffer, event recorded after its last copy)
+    dev: torch.Tensor
+    logits: torch.Tensor
+    launches: int
+    turn: int = 0
+
+
 class Engine:
-    def __init__(self, model_dir: Union[str, Path], config: Optional[EngineConfig] = None,
-                 device: Union[str, torch.device] = "cuda:0", ops=None):
+    def __init__(self, model_dir: Union[str, Path, None], config: Optional[EngineConfig] = None,
+                 device: Union[str, torch.device] = "cuda:0", ops=None, model_config: Optional[dict] = None,
+                 random_seed: Optional[int] = None):
+        """Loads the model of ``model_dir`` (config.json + safetensors).  With ``model_dir`` None,
+        ``model_config`` (the content of a config.json) and ``random_seed`` build the same model
+        with random weights drawn on the device, without writing a folder."""
         self.config = config or EngineConfig()
         self.device = torch.device(device)
-        raw = read_config_json(model_dir)
+        raw = read_config_json(model_dir) if model_dir is not None else dict(model_config)
         arch = resolve_architecture(raw)
         self.model_config = arch.config_from_dict(raw)
         spec = arch.spec_from_config(self.model_config)
@@ -60,9 +107,14 @@ class Engine:
         self.ops = ops
         self.runtime = Runtime(self.device, self.config.dtype, ops)
         self.model = DecoderModel(spec, self.runtime)
-        tensors = read_folder(model_dir)
-        ignorable = ["lm_head.weight"] if spec.lm_head is None else []
-        check_tensors(self.model.expected_tensors(), tensors, ignorable=ignorable)
+        if model_dir is not None:
+            tensors = read_folder(model_dir)
+            ignorable = ["lm_head.weight"] if spec.lm_head is None else []
+            check_tensors(self.model.expected_tensors(), tensors, ignorable=ignorable)
+        else:
+            from ..weights.random_init import random_tensors_on_device
+            tensors = random_tensors_on_device(self.model.expected_tensors(), int(random_seed or 0),
+                                               spec.initializer_range, self.config.dtype, self.device)
         self.model.load(tensors)
         del tensors
         self.vocab_size = spec.vocab_size
@@ -73,6 +125,7 @@ class Engine:
                                   self.config.max_seq_len, self.device, self.config.dtype)
         self._pinned = self.device.type == "cuda"
         self.steps_run = 0
+        self._graphs = {}
 
     # ------------------------------------------------------------------ sizing
     def _pages_from_free_memory(self, entries) -> int:
@@ -121,9 +174,7 @@ class Engine:
         if not cache.can_append([(e.request, len(e.tokens)) for e in entries]):
             raise OutOfPages("the cache cannot hold this step's tokens")
 
-        R = len(entries)
         q_lens = [len(e.tokens) for e in entries]
-        T = sum(q_lens)
         fresh, starts, slots_by_group, state_slots = [], [], {}, []
         for e in entries:
             if not cache.has(e.request):
@@ -135,10 +186,6 @@ class Engine:
             for g, sl in cache.append(e.request, len(e.tokens)).items():
                 slots_by_group.setdefault(g, []).extend(sl)
             state_slots.append(cache.slot_of(e.request))
-        ctx_lens = [s + n for s, n in zip(starts, q_lens)]
-        paged_groups = [g for g, grp in enumerate(cache.groups) if grp.paged]
-        tables = {g: [cache.block_table(e.request, g) for e in entries] for g in paged_groups}
-        bt_width = _pad4(max([1] + [len(t) for g in paged_groups for t in tables[g]]))
         rows, logit_rows = [], []
         base = 0
         for e, n in zip(entries, q_lens):
@@ -146,72 +193,151 @@ class Engine:
                 rows.append((e.request, int(w)))
                 logit_rows.append(base + int(w))
             base += n
-        M = len(logit_rows)
-
-        # one packed int32 buffer, one copy to the device
-        seg = {}
-        cursor = 0
-
-        def reserve(name, n):
-            nonlocal cursor
-            seg[name] = (cursor, n)
-            cursor += _pad4(max(n, 1))
-
-        reserve("tokens", T); reserve("positions", T); reserve("tok_req", T)
-        reserve("q_start", R + 1); reserve("ctx_len", R); reserve("state_slot", R); reserve("fresh", R)
-        reserve("logit_rows", M)
-        for g in paged_groups:
-            reserve(f"slots{g}", T); reserve(f"bt{g}", R * bt_width)
-        host = torch.empty(cursor, dtype=torch.int32, pin_memory=self._pinned)
-        h = host.numpy()
-
-        def put(name, values):
-            lo, n = seg[name]
-            h[lo:lo + n] = values
-
-        put("tokens", np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries]))
-        put("positions", np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(starts, q_lens)]))
-        put("tok_req", np.repeat(np.arange(R, dtype=np.int32), q_lens))
-        put("q_start", np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32))
-        put("ctx_len", ctx_lens); put("state_slot", state_slots); put("fresh", fresh)
-        if M:
-            put("logit_rows", logit_rows)
-        for g in paged_groups:
-            put(f"slots{g}", slots_by_group[g])
-            bt = np.full((R, bt_width), -1, dtype=np.int32)
-            for i, t in enumerate(tables[g]):
-                bt[i, :len(t)] = t
-            put(f"bt{g}", bt.reshape(-1))
+        batch = _HostBatch(entries, q_lens, starts, fresh, state_slots, slots_by_group, logit_rows)
+        self.steps_run += 1
+        bucket = self._graph_bucket(batch)
+        if bucket:
+            logits = self._run_graph(bucket, batch)
+            if logit_rows != list(range(len(entries))):
+                idx = torch.tensor(logit_rows, dtype=torch.long, device=self.device)
+                logits = logits.index_select(0, idx) if logit_rows else None
+            return StepOutput(logits, rows, batch.T)
+        layout = _Layout(batch.T, batch.R, len(logit_rows), self._table_width(batch), self._paged_groups())
+        host = torch.empty(layout.size, dtype=torch.int32, pin_memory=self._pinned)
+        self._fill(host.numpy(), layout, batch)
         dev = host.to(self.device, non_blocking=True)
+        ctx, cache_view = self._context(dev, layout, batch.q_lens, [s + n for s, n in zip(starts, q_lens)],
+                                        self._choose_splits(batch.T, max(s + n for s, n in zip(starts, q_lens))))
+        logits = self.model.forward(layout.view(dev, "tokens"), ctx, cache_view,
+                                    layout.view(dev, "logit_rows") if logit_rows else None)
+        return StepOutput(logits, rows, batch.T)
 
-        def view(name):
-            lo, n = seg[name]
-            return dev[lo:lo + n]
+    # ------------------------------------------------------------------ batch assembly
+    def _paged_groups(self) -> List[int]:
+        return [g for g, grp in enumerate(self.cache.groups) if grp.paged]
 
+    def _table_width(self, batch: "_HostBatch") -> int:
+        widths = [len(self.cache.block_table(e.request, g)) for g in self._paged_groups() for e in batch.entries]
+        return _pad4(max([1] + widths))
+
+    def _fill(self, h: np.ndarray, layout: "_Layout", b: "_HostBatch") -> None:
+        """Writes the step's integers into the packed host buffer; rows beyond the batch (a padded
+        graph bucket) get request -1 and slot -1, which every kernel skips."""
+        T, R = b.T, b.R
+
+        def put(name, values, fill=0):
+            lo, n = layout.seg[name]
+            h[lo:lo + len(values)] = values
+            h[lo + len(values):lo + n] = fill
+
+        put("tokens", np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in b.entries]))
+        put("positions", np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(b.starts, b.q_lens)]))
+        put("tok_req", np.repeat(np.arange(R, dtype=np.int32), b.q_lens), fill=-1)
+        put("q_start", np.concatenate([[0], np.cumsum(b.q_lens)]).astype(np.int32), fill=T)
+        put("ctx_len", [s + n for s, n in zip(b.starts, b.q_lens)])
+        put("state_slot", b.state_slots)
+        put("fresh", b.fresh)
+        lo, n = layout.seg["logit_rows"]
+        if layout.static_rows:
+            h[lo:lo + n] = np.arange(n, dtype=np.int32)
+        elif n:
+            h[lo:lo + n] = b.logit_rows
+        for g in layout.groups:
+            put(f"slots{g}", b.slots_by_group[g], fill=-1)
+            lo, n = layout.seg[f"bt{g}"]
+            bt = h[lo:lo + n].reshape(layout.R, layout.bt_width)
+            bt.fill(-1)
+            for i, e in enumerate(b.entries):
+                t = self.cache.block_table(e.request, g)
+                bt[i, :len(t)] = t
+
+    def _context(self, dev: torch.Tensor, layout: "_Layout", q_lens, ctx_lens, splits: int):
+        cache = self.cache
         groups = {g: GroupStepView(page_size=cache.page_size,
-                                   block_table=view(f"bt{g}").view(R, bt_width), slots=view(f"slots{g}"),
-                                   window=cache.groups[g].need.window) for g in paged_groups}
-        max_ctx = max(ctx_lens)
-        ctx = StepContext(num_tokens=T, num_requests=R, positions=view("positions"), tok_req=view("tok_req"),
-                          q_start=view("q_start"), ctx_len=view("ctx_len"), state_slot=view("state_slot"),
-                          fresh=view("fresh"), groups=groups, q_lens=q_lens, ctx_lens=ctx_lens,
-                          max_q_len=max(q_lens), max_ctx_len=max_ctx,
-                          attn_splits=self._choose_splits(T, max_ctx))
+                                   block_table=layout.view(dev, f"bt{g}").view(layout.R, layout.bt_width),
+                                   slots=layout.view(dev, f"slots{g}"), window=cache.groups[g].need.window)
+                  for g in layout.groups}
+        ctx = StepContext(num_tokens=layout.T, num_requests=layout.R, positions=layout.view(dev, "positions"),
+                          tok_req=layout.view(dev, "tok_req"), q_start=layout.view(dev, "q_start"),
+                          ctx_len=layout.view(dev, "ctx_len"), state_slot=layout.view(dev, "state_slot"),
+                          fresh=layout.view(dev, "fresh"), groups=groups, q_lens=list(q_lens),
+                          ctx_lens=list(ctx_lens), max_q_len=max(q_lens), max_ctx_len=max(ctx_lens),
+                          attn_splits=splits)
 
         def cache_view(entry: int, write: bool) -> LayerCacheView:
             g = cache.entry_group[entry]
             grp = cache.groups[g]
             return LayerCacheView(group=groups.get(g), kv=grp.kv.get(entry), state=grp.state.get(entry), write=write)
-
-        logits = self.model.forward(view("tokens"), ctx, cache_view, view("logit_rows") if M else None)
-        self.steps_run += 1
-        return StepOutput(logits, rows, T)
+        return ctx, cache_view
 
     def _choose_splits(self, tokens: int, max_ctx: int) -> int:
         """Key-range splits for steps with few tokens and long contexts (more parallel work)."""
         if tokens > 64 or max_ctx < 512:
             return 1
         return int(min(32, max(1, max_ctx // 256)))
+
+    # ------------------------------------------------------------------ decode steps from CUDA graphs
+    def _graph_bucket(self, batch: "_HostBatch") -> int:
+        """The padded batch size whose captured graph can run this step, or 0.  Only steps of
+        single tokens qualify, and only models whose mixers keep nothing but paged keys and values
+        (lite_llama captures its decode step for batch sizes 1, 2, 4, 8, 16, ...:
+        lite_llama/executor/cuda_graph.py:6-7,113-132)."""
+        if not self.config.compiled_model or self.device.type != "cuda" or batch.max_q_len != 1:
+            return 0
+        if any(not grp.paged or grp.state for grp in self.cache.groups):
+            return 0
+        b = 1
+        while b < batch.R:
+            b *= 2
+        return b if b <= max(64, self.config.max_num_seqs) else 0
+
+    def _run_graph(self, bucket: int, batch: "_HostBatch") -> torch.Tensor:
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = self._graphs[bucket] = self._capture(bucket)
+        # The copy below is asynchronous: a staging buffer may be rewritten only after the copy that
+        # last read it has finished, so each buffer of the ring carries an event.
+        host, event = g.staging[g.turn % len(g.staging)]
+        g.turn += 1
+        event.synchronize()
+        self._fill(host.numpy(), g.layout, batch)
+        g.dev.copy_(host, non_blocking=True)
+        event.record(torch.cuda.current_stream(self.device))
+        g.graph.replay()
+        if hasattr(self.ops, "launches"):
+            self.ops.launches += g.launches
+        return g.logits[:batch.R]
+
+    def _capture(self, bucket: int) -> "_DecodeGraph":
+        layout = _Layout(bucket, bucket, bucket, _pad4(self.cache.max_blocks), self._paged_groups(), static_rows=True)
+        host = torch.empty(layout.size, dtype=torch.int32, pin_memory=True)
+        h = host.numpy()
+        h.fill(0)
+        for name, fill in [("tok_req", -1)] + [(f"slots{g}", -1) for g in layout.groups] + [(f"bt{g}", -1) for g in layout.groups]:
+            lo, n = layout.seg[name]
+            h[lo:lo + n] = fill
+        lo, n = layout.seg["logit_rows"]
+        h[lo:lo + n] = np.arange(n, dtype=np.int32)
+        dev = host.to(self.device)
+        splits = self._choose_splits(bucket, self.config.max_seq_len)
+        ctx, cache_view = self._context(dev, layout, [1] * bucket, [self.config.max_seq_len] * bucket, splits)
+
+        def run():
+            return self.model.forward(layout.view(dev, "tokens"), ctx, cache_view, layout.view(dev, "logit_rows"))
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):      # libraries set themselves up outside the capture
+                run()
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        before = getattr(self.ops, "launches", 0)
+        with torch.cuda.graph(graph):
+            logits = run()
+        launches = getattr(self.ops, "launches", 0) - before
+        staging = [(torch.empty(layout.size, dtype=torch.int32, pin_memory=True), torch.cuda.Event()) for _ in range(4)]
+        return _DecodeGraph(graph, layout, staging, dev, logits, launches)
 
     # ------------------------------------------------------------------ requests
     def finish(self, request: Hashable) -> None:

@@ -22,8 +22,9 @@ from .scheduler import Request, Scheduler
 
 
 class LLM:
-    def __init__(self, model_dir, config: Optional[EngineConfig] = None, device="cuda:0", ops=None):
-        self.engine = Engine(model_dir, config, device=device, ops=ops)
+    def __init__(self, model_dir, config: Optional[EngineConfig] = None, device="cuda:0", ops=None, **engine_options):
+        """``engine_options`` go to ``Engine`` (``model_config`` and ``random_seed`` for random weights)."""
+        self.engine = Engine(model_dir, config, device=device, ops=ops, **engine_options)
         cfg = self.engine.config
         self.scheduler = Scheduler(self.engine.cache, cfg.max_num_seqs, cfg.max_batched_tokens,
                                    cfg.max_seq_len, eos_token_ids=self.engine.eos_token_ids)

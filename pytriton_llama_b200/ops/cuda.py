@@ -27,7 +27,7 @@ _SIGNATURES = {
     "ptl_silu_mul": [_ptr, _ptr, _c_int, _c_int, _ptr],
     "ptl_rope_kv_write": [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _ptr],
     "ptl_paged_attention_simt": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int,
-                                 _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _ptr],
+                                 _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _ptr],
 }
 _GEMM_SIG = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr]
 
@@ -91,14 +91,16 @@ class CudaOps:
         if major != 10:
             raise KernelError(f"the kernels are compiled for sm_100a only; device reports sm_{major}{minor}")
         self._status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.launches = 0      # kernels of this library launched so far (library matrix products not counted)
 
     # ------------------------------------------------------------------ helpers
     def _stream(self) -> int:
         return torch.cuda.current_stream(self.device).cuda_stream
 
-    def _check(self, rc: int) -> None:
+    def _check(self, rc: int, kernels: int = 1) -> None:
         if rc != 0:
             raise KernelError(self.lib.ptl_last_error().decode())
+        self.launches += kernels
 
     def _want(self, t: torch.Tensor, name: str, dtype=None) -> None:
         if t.device != self.device:
@@ -241,7 +243,8 @@ class CudaOps:
         fn = getattr(self.lib, "ptl_paged_attention_simt" + _suffix(q.dtype))
         self._check(fn(_p(out), _p(q), _p(cache), _p(block_table), _p(tok_req), _p(positions), _p(part_acc),
                        _p(part_ml), tokens, q.shape[1], nq * d, block_table.shape[1], nq, nkv, d, page_size,
-                       float(scale), int(window), int(splits), self._stream()))
+                       float(scale), int(window), int(splits), cache.shape[0], self._stream()),
+                    kernels=2 if splits > 1 else 1)
         return out
 
     def sample(self, logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Optional[torch.Tensor],

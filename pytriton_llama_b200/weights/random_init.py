@@ -36,6 +36,28 @@ def random_tensors(expected: Dict[str, TensorSpec], seed: int, std: float, dtype
     return out
 
 
+def random_tensors_on_device(expected: Dict[str, TensorSpec], seed: int, std: float, dtype: torch.dtype,
+                             device) -> Dict[str, torch.Tensor]:
+    """The same distributions drawn with the device's generator (other numbers than the CPU draws):
+    for models too large to be worth a round trip through a file, as in benchmarks."""
+    device = torch.device(device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(int(seed))
+    out = {}
+    for name in sorted(expected):
+        spec = expected[name]
+        if spec.init == "ones":
+            t = torch.ones(spec.shape, dtype=torch.float32, device=device)
+        elif spec.init == "ones_jitter":
+            t = 1.0 + 0.01 * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
+        elif spec.init == "normal":
+            t = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device).mul_(std)
+        else:
+            raise ValueError(f"tensor {name}: unknown init {spec.init!r}")
+        out[name] = t.to(dtype)
+    return out
+
+
 def write_random_model(folder: Union[str, Path], config: Dict, seed: int = 0,
                        dtype: torch.dtype = torch.bfloat16, norm_init: str = "ones",
                        std: Optional[float] = None) -> Path:

@@ -60,6 +60,24 @@ def test_logits_do_not_depend_on_the_cut(model_folders, references, name, dtype,
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_decode_steps_from_cuda_graphs(model_folders, references, name, dtype):
+    """With ``compiled_model`` single-token steps replay captured graphs of padded batch sizes
+    (1, 2, 4): the logits are those of the plain implementation all the same, also when the batch
+    shrinks and grows and a prompt portion interrupts the decoding."""
+    seqs = _seqs(name)
+    ref = references(name, dtype)
+    steps = traces.mixed(seqs, live=3, sizes=(40, 23, 64), decode_tail=30)
+    ps = PAGE_SIZE[name]
+    pages = -(-traces.max_live_tokens(steps, ps) // ps)
+    eng = make_engine(model_folders(name, stored_dtype(dtype)), name, dtype, pages, compiled_model=True)
+    got = traces.replay(eng, steps)
+    assert set(eng._graphs) >= {1, 2, 4}
+    for r in seqs:
+        assert_close(got[r], ref[r], dtype, f"graph {r}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_first_tokens_of_a_sequence(model_folders, references, dtype):
     """Positions 0, 1, 2 each as a step of their own, and a request that is one token long."""
     name = "B"
