@@ -1,0 +1,261 @@
+// Decode attention over the paged cache in bfloat16: one block per (single-token request, kv
+// head, split of the key range).  All query heads of the group ride in the 16 rows of one
+// m16n8k16 tile, so each key and value is fetched from HBM once for the whole group; the kernel
+// is a streaming read of the cache.  Four warps share 64-key tiles brought in by a ring of
+// cp.async stages (16 keys per warp and tile), keep their own running max / sum / accumulator in
+// float32 and are merged through shared memory at the end.  With splits > 1 the block writes an
+// unnormalised partial result that `attention_merge` (attention_simt.cu) combines.
+//
+// The token list `items` names the tokens of the step that take this path (nullptr: tokens
+// 0..n-1).  Token t of request r = tok_req[t] at position p sees keys max(0, p-window+1)..p;
+// r < 0 marks a padding row, which yields zeros.
+#include "mma_utils.cuh"
+
+namespace ptl {
+
+constexpr int kDecKeys = 64;      // keys per tile
+constexpr int kDecWarps = 4;
+
+template <int D> struct DecodeCfg {
+  static constexpr int kStages = D <= 64 ? 4 : 3;
+  static constexpr int kChunks = D / 8;                       // 16-byte chunks per row
+  static constexpr int kTileBytes = kDecKeys * D * 2;          // one of K / V
+  static constexpr int kSmem = kStages * 2 * kTileBytes;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kDecWarps * 32)
+decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                        const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
+                        const int* __restrict__ block_table, const int* __restrict__ items,
+                        const int* __restrict__ tok_req, const int* __restrict__ positions, int q_stride,
+                        int out_stride, int bt_stride, int nq, int nkv, int page_size, float scale_log2,
+                        int window, int splits, int num_pages) {
+  using Cfg = DecodeCfg<D>;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int split = blockIdx.x % splits;
+  const int kvh = (blockIdx.x / splits) % nkv;
+  const int ti = blockIdx.x / (splits * nkv);
+  const int t = items ? items[ti] : ti;
+  const int G = nq / nkv;
+  const int r = tok_req[t];
+  const int p = positions[t];
+  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  const int nkeys = r < 0 ? 0 : p - lo + 1;
+  int chunk_keys = (nkeys + splits - 1) / splits;
+  chunk_keys = (chunk_keys + kDecKeys - 1) / kDecKeys * kDecKeys;
+  const int k_begin = lo + split * chunk_keys;
+  const int k_end = r < 0 ? k_begin : min(k_begin + chunk_keys, p + 1);
+  const int ntiles = k_end > k_begin ? (k_end - k_begin + kDecKeys - 1) / kDecKeys : 0;
+  const int* bt = block_table + (size_t)(r < 0 ? 0 : r) * bt_stride;
+  const size_t plane = (size_t)nkv * page_size * D;
+  const uint32_t smem_base = smem_u32(smem);
+
+  // ---- query fragments: row g (and g+8) of the tile is query head kvh*G + g (zero beyond the group)
+  uint32_t qa[D / 16][4];
+  {
+    const __nv_bfloat16* qrow = q + (size_t)t * q_stride + (size_t)kvh * G * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int col = ks * 16 + 2 * c;
+      qa[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col) : 0u;
+      qa[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col) : 0u;
+      qa[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col + 8) : 0u;
+      qa[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col + 8) : 0u;
+    }
+  }
+
+  // ---- loader: 64 keys x D of K and of V per tile, 16 bytes per cp.async, zero fill past the range
+  auto load_tile = [&](int tile, int stage) {
+    const uint32_t kbase = smem_base + stage * 2 * Cfg::kTileBytes;
+    const uint32_t vbase = kbase + Cfg::kTileBytes;
+#pragma unroll
+    for (int i = 0; i < kDecKeys * Cfg::kChunks / (kDecWarps * 32); ++i) {
+      const int idx = tid + i * kDecWarps * 32;
+      const int row = idx / Cfg::kChunks, ch = idx % Cfg::kChunks;
+      const int key = k_begin + tile * kDecKeys + row;
+      bool valid = key < k_end;
+      int page = valid ? bt[key / page_size] : 0;
+      if (page < 0 || page >= num_pages) { valid = false; page = 0; }
+      const __nv_bfloat16* src = cache + ((size_t)page * 2) * plane + ((size_t)kvh * page_size + key % page_size) * D + ch * 8;
+      const uint32_t off = tile_offset<D>(row, ch);
+      cp_async_16(kbase + off, src, valid);
+      cp_async_16(vbase + off, src + plane, valid);
+    }
+  };
+
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+
+#pragma unroll
+  for (int s = 0; s < Cfg::kStages - 1; ++s) {
+    if (s < ntiles) load_tile(s, s);
+    cp_async_commit();
+  }
+  for (int tile = 0; tile < ntiles; ++tile) {
+    cp_async_wait<Cfg::kStages - 2>();
+    __syncthreads();
+    {
+      const int nxt = tile + Cfg::kStages - 1;
+      if (nxt < ntiles) load_tile(nxt, nxt % Cfg::kStages);
+      cp_async_commit();
+    }
+    const int stage = tile % Cfg::kStages;
+    const uint32_t kbase = smem_base + stage * 2 * Cfg::kTileBytes;
+    const uint32_t vbase = kbase + Cfg::kTileBytes;
+    const int row0 = warp * 16;                               // this warp's 16 keys of the tile
+    // S = Q K^T for 16 keys: two n-tiles of 8
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t kb[4];
+      const int id = lane >> 3;
+      const int krow = row0 + (id >> 1) * 8 + (lane & 7);
+      ldmatrix_x4(kb, kbase + tile_offset<D>(krow, 2 * ks + (id & 1)));
+      mma_bf16_16816(s0, qa[ks], kb[0], kb[1]);
+      mma_bf16_16816(s1, qa[ks], kb[2], kb[3]);
+    }
+    // mask keys past the range, scale into log2 units
+    const int key0 = k_begin + tile * kDecKeys + row0 + 2 * c;
+    float sv[2][4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int kk0 = key0 + (e & 1), kk1 = key0 + 8 + (e & 1);
+      sv[0][e] = kk0 < k_end ? s0[e] * scale_log2 : -INFINITY;
+      sv[1][e] = kk1 < k_end ? s1[e] * scale_log2 : -INFINITY;
+    }
+    // online softmax for rows g (e = 0,1) and g+8 (e = 2,3)
+    uint32_t pa[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float mx = fmaxf(fmaxf(sv[0][2 * h], sv[0][2 * h + 1]), fmaxf(sv[1][2 * h], sv[1][2 * h + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[h], mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = exp2f(m_run[h] - m_use);
+      const float p00 = exp2f(sv[0][2 * h] - m_use), p01 = exp2f(sv[0][2 * h + 1] - m_use);
+      const float p10 = exp2f(sv[1][2 * h] - m_use), p11 = exp2f(sv[1][2 * h + 1] - m_use);
+      float sum = p00 + p01 + p10 + p11;
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      l_run[h] = l_run[h] * alpha + sum;
+      m_run[h] = m_new;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) { o[i][2 * h] *= alpha; o[i][2 * h + 1] *= alpha; }
+      pa[h] = pack_bf16(p00, p01);          // a0 / a1: keys 2c..2c+1
+      pa[2 + h] = pack_bf16(p10, p11);      // a2 / a3: keys 8+2c..
+    }
+    // O += P V over this warp's 16 keys
+#pragma unroll
+    for (int nt = 0; nt < D / 8; nt += 2) {
+      uint32_t vb[4];
+      const int id = lane >> 3;
+      const int vrow = row0 + (id & 1) * 8 + (lane & 7);
+      ldmatrix_x4_trans(vb, vbase + tile_offset<D>(vrow, nt + (id >> 1)));
+      mma_bf16_16816(o[nt], pa, vb[0], vb[1]);
+      mma_bf16_16816(o[nt + 1], pa, vb[2], vb[3]);
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- merge the four warps through shared memory
+  float* mo = reinterpret_cast<float*>(smem);                  // [warps][16][D]
+  float* mml = mo + kDecWarps * 16 * D;                        // [warps][16][2]
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) {
+    const int col = i * 8 + 2 * c;
+    mo[(warp * 16 + g) * D + col] = o[i][0];
+    mo[(warp * 16 + g) * D + col + 1] = o[i][1];
+    mo[(warp * 16 + g + 8) * D + col] = o[i][2];
+    mo[(warp * 16 + g + 8) * D + col + 1] = o[i][3];
+  }
+  if (c == 0) {
+    mml[(warp * 16 + g) * 2] = m_run[0];
+    mml[(warp * 16 + g) * 2 + 1] = l_run[0];
+    mml[(warp * 16 + g + 8) * 2] = m_run[1];
+    mml[(warp * 16 + g + 8) * 2 + 1] = l_run[1];
+  }
+  __syncthreads();
+  for (int e = tid; e < G * D; e += kDecWarps * 32) {
+    const int row = e / D, col = e % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) M = fmaxf(M, mml[(w * 16 + row) * 2]);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) {
+      const float mw = mml[(w * 16 + row) * 2];
+      const float wgt = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      L += wgt * mml[(w * 16 + row) * 2 + 1];
+      acc += wgt * mo[(w * 16 + row) * D + col];
+    }
+    const int h = kvh * G + row;
+    if (splits == 1) {
+      out[(size_t)t * out_stride + (size_t)h * D + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    } else {
+      const size_t idx = ((size_t)t * nq + h) * splits + split;
+      part_acc[idx * D + col] = acc;
+      if (col == 0) {
+        part_ml[idx * 2] = M == -INFINITY ? -INFINITY : M * 0.6931471805599453f;   // natural-log units for the merge
+        part_ml[idx * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+// defined in attention_simt.cu
+int attention_merge_bf16(void* out, const float* part_acc, const float* part_ml, int tokens, int out_stride,
+                         int nq, int d, int splits, const int* items, void* stream);
+
+template <int D>
+int launch_decode(void* out, float* part_acc, float* part_ml, const void* q, const void* cache,
+                  const int* block_table, const int* items, const int* tok_req, const int* positions, int n_items,
+                  int q_stride, int out_stride, int bt_stride, int nq, int nkv, int page_size, float scale,
+                  int window, int splits, int num_pages, void* stream) {
+  using Cfg = DecodeCfg<D>;
+  static bool raised = false;
+  if (!raised) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
+    PTL_REQUIRE(e == cudaSuccess, "decode_attention: cannot raise shared memory: %s", cudaGetErrorString(e));
+    raised = true;
+  }
+  const long long blocks = (long long)n_items * nkv * splits;
+  PTL_REQUIRE(blocks <= 0x7fffffffLL, "decode_attention: too many blocks");
+  decode_attention_kernel<D><<<(unsigned)blocks, kDecWarps * 32, Cfg::kSmem, as_stream(stream)>>>(
+      (__nv_bfloat16*)out, part_acc, part_ml, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_table, items,
+      tok_req, positions, q_stride, out_stride, bt_stride, nq, nkv, page_size, scale * 1.4426950408889634f, window,
+      splits, num_pages);
+  int rc = check_launch("decode_attention");
+  if (rc) return rc;
+  if (splits > 1) rc = attention_merge_bf16(out, part_acc, part_ml, n_items, out_stride, nq, D, splits, items, stream);
+  return rc;
+}
+
+}  // namespace ptl
+
+// Returns 0 on success; -2 if this kernel does not take the sizes (the caller then uses the
+// CUDA-core kernel); -1 on an error.
+PTL_EXPORT int ptl_decode_attention_bf16(void* out, float* part_acc, float* part_ml, const void* q, const void* cache,
+                                         const int* block_table, const int* items, const int* tok_req,
+                                         const int* positions, int n_items, int q_stride, int out_stride,
+                                         int bt_stride, int nq, int nkv, int d, int page_size, float scale, int window,
+                                         int splits, int num_pages, void* stream) {
+  using namespace ptl;
+  PTL_REQUIRE(n_items >= 0 && nq > 0 && nkv > 0 && page_size > 0 && num_pages > 0, "decode_attention: bad sizes");
+  PTL_REQUIRE(nq % nkv == 0, "decode_attention: %d query heads are no multiple of %d kv heads", nq, nkv);
+  if ((d != 64 && d != 128) || nq / nkv > 16) return -2;
+  PTL_REQUIRE(splits >= 1 && (splits == 1 || (part_acc && part_ml)), "decode_attention: splits > 1 need scratch buffers");
+  PTL_REQUIRE(aligned16(q) && aligned16(cache) && q_stride % 8 == 0, "decode_attention: q and cache must be 16-byte aligned");
+  if (n_items == 0) return 0;
+  if (d == 64)
+    return launch_decode<64>(out, part_acc, part_ml, q, cache, block_table, items, tok_req, positions, n_items, q_stride,
+                             out_stride, bt_stride, nq, nkv, page_size, scale, window, splits, num_pages, stream);
+  return launch_decode<128>(out, part_acc, part_ml, q, cache, block_table, items, tok_req, positions, n_items, q_stride,
+                            out_stride, bt_stride, nq, nkv, page_size, scale, window, splits, num_pages, stream);
+}

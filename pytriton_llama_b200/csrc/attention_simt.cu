@@ -115,8 +115,8 @@ paged_attention_simt_kernel(T* __restrict__ out, float* __restrict__ part_acc, f
 template <typename T>
 __global__ void attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
                                        const float* __restrict__ part_ml, int out_stride, int nq, int d,
-                                       int splits) {
-  const int t = blockIdx.x, h = blockIdx.y;
+                                       int splits, const int* __restrict__ items) {
+  const int t = items ? items[blockIdx.x] : blockIdx.x, h = blockIdx.y;
   const size_t idx0 = ((size_t)t * nq + h) * splits;
   float M = -INFINITY;
   for (int z = 0; z < splits; ++z) M = fmaxf(M, part_ml[(idx0 + z) * 2]);
@@ -159,10 +159,19 @@ int paged_attention_simt(void* out, const void* q, const void* cache, const int*
   if (splits > 1) {
     dim3 g2(tokens, nq);
     attention_merge_kernel<T><<<g2, d >= 128 ? 128 : (d >= 64 ? 64 : 32), 0, as_stream(stream)>>>(
-        (T*)out, part_acc, part_ml, out_stride, nq, d, splits);
+        (T*)out, part_acc, part_ml, out_stride, nq, d, splits, nullptr);
     rc = check_launch("attention_merge");
   }
   return rc;
+}
+
+// Merge for the tensor-core decode kernel: `items` (or 0..tokens-1) names the token rows.
+int attention_merge_bf16(void* out, const float* part_acc, const float* part_ml, int tokens, int out_stride,
+                         int nq, int d, int splits, const int* items, void* stream) {
+  dim3 grid(tokens, nq);
+  attention_merge_kernel<__nv_bfloat16><<<grid, d >= 128 ? 128 : (d >= 64 ? 64 : 32), 0, as_stream(stream)>>>(
+      (__nv_bfloat16*)out, part_acc, part_ml, out_stride, nq, d, splits, items);
+  return check_launch("attention_merge");
 }
 
 }  // namespace ptl

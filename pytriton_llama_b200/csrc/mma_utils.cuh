@@ -1,0 +1,57 @@
+// Warp-level tensor-core helpers for the bfloat16 attention kernels: mma.sync m16n8k16,
+// ldmatrix, cp.async with zero fill, and the shared-memory swizzle of [rows][D] tiles.
+//
+// Fragment layout of mma.sync.m16n8k16 (g = lane / 4, c = lane % 4):
+//   A (16x16): a0 (g, 2c..2c+1)   a1 (g+8, 2c..)   a2 (g, 2c+8..)   a3 (g+8, 2c+8..)
+//   B (16x8):  b0 (k 2c..2c+1, n g)   b1 (k 2c+8.., n g)
+//   C (16x8):  c0,c1 (g, 2c..2c+1)    c2,c3 (g+8, 2c..2c+1)
+#pragma once
+#include "common.cuh"
+
+namespace ptl {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// 16-byte asynchronous copy global -> shared; with valid == false the destination is zero-filled
+// and the source is not read.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// d += a * b, bfloat16 inputs, float32 accumulation
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` in a [rows][D] bfloat16 tile whose chunks are
+// XOR-swizzled with the row inside each 128-byte segment (conflict-free ldmatrix for D >= 64).
+template <int D> __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
+  static_assert(D % 64 == 0, "the swizzle is written for rows of whole 128-byte segments");
+  const int sw = (chunk & ~7) | ((chunk & 7) ^ (row & 7));
+  return static_cast<uint32_t>(row * (D * 2) + sw * 16);
+}
+
+}  // namespace ptl

@@ -41,6 +41,9 @@ class StepOutput:
     num_tokens: int = 0
 
 
+QUERY_TILE = 64   # query rows per block of the prompt attention kernel
+
+
 def _pad4(n: int) -> int:
     return (n + 3) & ~3
 
@@ -54,17 +57,30 @@ class _HostBatch:
         self.R = len(entries)
         self.T = sum(q_lens)
         self.max_q_len = max(q_lens)
+        # work lists of the attention kernels: single tokens, and tiles of up to 64 rows of longer portions
+        self.dec_items: List[int] = []
+        self.pf_tiles: List[int] = []
+        t0 = 0
+        for r, (n, s) in enumerate(zip(q_lens, starts)):
+            if n == 1:
+                self.dec_items.append(t0)
+            else:
+                for a in range(0, n, QUERY_TILE):
+                    self.pf_tiles += [r, t0 + a, min(QUERY_TILE, n - a), s + a]
+            t0 += n
 
 
 class _Layout:
     """Where each integer array of a step lies inside one packed int32 buffer (one copy per step)."""
 
-    def __init__(self, T: int, R: int, M: int, bt_width: int, groups: List[int], static_rows: bool = False):
+    def __init__(self, T: int, R: int, M: int, bt_width: int, groups: List[int], static_rows: bool = False,
+                 max_tiles: int = 0):
         self.T, self.R, self.M, self.bt_width, self.groups, self.static_rows = T, R, M, bt_width, groups, static_rows
+        self.max_tiles = max_tiles
         self.seg: Dict[str, tuple] = {}
         cursor = 0
         names = [("tokens", T), ("positions", T), ("tok_req", T), ("q_start", R + 1), ("ctx_len", R),
-                 ("state_slot", R), ("fresh", R), ("logit_rows", M)]
+                 ("state_slot", R), ("fresh", R), ("logit_rows", M), ("dec_items", T), ("pf_tiles", 4 * max_tiles)]
         for g in groups:
             names += [(f"slots{g}", T), (f"bt{g}", R * bt_width)]
         for name, n in names:
@@ -202,12 +218,14 @@ class Engine:
                 idx = torch.tensor(logit_rows, dtype=torch.long, device=self.device)
                 logits = logits.index_select(0, idx) if logit_rows else None
             return StepOutput(logits, rows, batch.T)
-        layout = _Layout(batch.T, batch.R, len(logit_rows), self._table_width(batch), self._paged_groups())
+        layout = _Layout(batch.T, batch.R, len(logit_rows), self._table_width(batch), self._paged_groups(),
+                         max_tiles=len(batch.pf_tiles) // 4)
         host = torch.empty(layout.size, dtype=torch.int32, pin_memory=self._pinned)
         self._fill(host.numpy(), layout, batch)
         dev = host.to(self.device, non_blocking=True)
         ctx, cache_view = self._context(dev, layout, batch.q_lens, [s + n for s, n in zip(starts, q_lens)],
-                                        self._choose_splits(batch.T, max(s + n for s, n in zip(starts, q_lens))))
+                                        self._choose_splits(batch.T, max(s + n for s, n in zip(starts, q_lens))),
+                                        n_decode=len(batch.dec_items), n_tiles=len(batch.pf_tiles) // 4)
         logits = self.model.forward(layout.view(dev, "tokens"), ctx, cache_view,
                                     layout.view(dev, "logit_rows") if logit_rows else None)
         return StepOutput(logits, rows, batch.T)
@@ -242,6 +260,13 @@ class Engine:
             h[lo:lo + n] = np.arange(n, dtype=np.int32)
         elif n:
             h[lo:lo + n] = b.logit_rows
+        if layout.static_rows:
+            lo, n = layout.seg["dec_items"]
+            h[lo:lo + n] = np.arange(n, dtype=np.int32)
+        else:
+            put("dec_items", b.dec_items)
+            if b.pf_tiles:
+                put("pf_tiles", b.pf_tiles)
         for g in layout.groups:
             put(f"slots{g}", b.slots_by_group[g], fill=-1)
             lo, n = layout.seg[f"bt{g}"]
@@ -251,7 +276,7 @@ class Engine:
                 t = self.cache.block_table(e.request, g)
                 bt[i, :len(t)] = t
 
-    def _context(self, dev: torch.Tensor, layout: "_Layout", q_lens, ctx_lens, splits: int):
+    def _context(self, dev: torch.Tensor, layout: "_Layout", q_lens, ctx_lens, splits: int, n_decode: int, n_tiles: int):
         cache = self.cache
         groups = {g: GroupStepView(page_size=cache.page_size,
                                    block_table=layout.view(dev, f"bt{g}").view(layout.R, layout.bt_width),
@@ -262,7 +287,9 @@ class Engine:
                           ctx_len=layout.view(dev, "ctx_len"), state_slot=layout.view(dev, "state_slot"),
                           fresh=layout.view(dev, "fresh"), groups=groups, q_lens=list(q_lens),
                           ctx_lens=list(ctx_lens), max_q_len=max(q_lens), max_ctx_len=max(ctx_lens),
-                          attn_splits=splits)
+                          attn_splits=splits, n_decode=n_decode, n_prefill_tiles=n_tiles,
+                          decode_items=layout.view(dev, "dec_items")[:n_decode],
+                          prefill_tiles=layout.view(dev, "pf_tiles"))
 
         def cache_view(entry: int, write: bool) -> LayerCacheView:
             g = cache.entry_group[entry]
@@ -316,11 +343,13 @@ class Engine:
         for name, fill in [("tok_req", -1)] + [(f"slots{g}", -1) for g in layout.groups] + [(f"bt{g}", -1) for g in layout.groups]:
             lo, n = layout.seg[name]
             h[lo:lo + n] = fill
-        lo, n = layout.seg["logit_rows"]
-        h[lo:lo + n] = np.arange(n, dtype=np.int32)
+        for name in ("logit_rows", "dec_items"):
+            lo, n = layout.seg[name]
+            h[lo:lo + n] = np.arange(n, dtype=np.int32)
         dev = host.to(self.device)
         splits = self._choose_splits(bucket, self.config.max_seq_len)
-        ctx, cache_view = self._context(dev, layout, [1] * bucket, [self.config.max_seq_len] * bucket, splits)
+        ctx, cache_view = self._context(dev, layout, [1] * bucket, [self.config.max_seq_len] * bucket, splits,
+                                        n_decode=bucket, n_tiles=0)
 
         def run():
             return self.model.forward(layout.view(dev, "tokens"), ctx, cache_view, layout.view(dev, "logit_rows"))

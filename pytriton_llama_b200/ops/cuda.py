@@ -55,6 +55,12 @@ def load_library() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = _GEMM_SIG
         fn.restype = _c_int
+    lib.ptl_decode_attention_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int,
+                                              _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _ptr]
+    lib.ptl_decode_attention_bf16.restype = _c_int
+    lib.ptl_prefill_attention_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                               _c_int, _c_int, _c_f, _c_int, _c_int, _ptr]
+    lib.ptl_prefill_attention_bf16.restype = _c_int
     lib.ptl_sample.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
     lib.ptl_sample.restype = _c_int
     lib.ptl_last_error.restype = ctypes.c_char_p
@@ -236,6 +242,11 @@ class CudaOps:
         self._want(positions, "positions", torch.int32)
         tokens = q.shape[0]
         out = self.empty((tokens, nq * d), q.dtype)
+        if (q.dtype == torch.bfloat16 and d in (64, 128) and nq // nkv <= 16 and hints is not None
+                and getattr(hints, "decode_items", None) is not None):
+            self._attention_tensor_cores(out, q, cache, block_table, tok_req, positions, nq, nkv, d, page_size, scale,
+                                         window, hints)
+            return out
         part_acc = part_ml = None
         if splits > 1:
             part_acc = self.empty((tokens, nq, splits, d), torch.float32)
@@ -246,6 +257,30 @@ class CudaOps:
                        float(scale), int(window), int(splits), cache.shape[0], self._stream()),
                     kernels=2 if splits > 1 else 1)
         return out
+
+    DECODE_BLOCKS = 592    # blocks the decode attention aims for: four per SM
+
+    def _attention_tensor_cores(self, out, q, cache, block_table, tok_req, positions, nq, nkv, d, page_size, scale,
+                                window, hints) -> None:
+        """bfloat16 attention on the tensor cores: single tokens through the split-key decode kernel,
+        longer portions through the tiled prompt kernel; both write their rows of ``out``."""
+        stream = self._stream()
+        num_pages = cache.shape[0]
+        if hints.n_decode:
+            longest = min(hints.max_ctx_len, window) if window else hints.max_ctx_len
+            splits = max(1, min(-(-self.DECODE_BLOCKS // (hints.n_decode * nkv)), -(-longest // 128)))
+            part_acc = part_ml = None
+            if splits > 1:
+                part_acc = self.empty((q.shape[0], nq, splits, d), torch.float32)
+                part_ml = self.empty((q.shape[0], nq, splits, 2), torch.float32)
+            self._check(self.lib.ptl_decode_attention_bf16(
+                _p(out), _p(part_acc), _p(part_ml), _p(q), _p(cache), _p(block_table), _p(hints.decode_items), _p(tok_req),
+                _p(positions), hints.n_decode, q.shape[1], nq * d, block_table.shape[1], nq, nkv, d, page_size,
+                float(scale), int(window), splits, num_pages, stream), kernels=2 if splits > 1 else 1)
+        if hints.n_prefill_tiles:
+            self._check(self.lib.ptl_prefill_attention_bf16(
+                _p(out), _p(q), _p(cache), _p(block_table), _p(hints.prefill_tiles), hints.n_prefill_tiles, q.shape[1],
+                nq * d, block_table.shape[1], nq, nkv, d, page_size, float(scale), int(window), num_pages, stream))
 
     def sample(self, logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Optional[torch.Tensor],
                u: Optional[torch.Tensor]) -> torch.Tensor:

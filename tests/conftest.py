@@ -60,9 +60,24 @@ FP32_TOL = 1e-4
 BF16_MAX_REL = 0.04
 BF16_MEAN_REL = 0.006
 
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-PAGE_SIZE = {"A": 4, "B": 8, "C": 16}
-NORM_INIT = {"A": "ones_jitter", "B": "ones", "C": "ones_jitter"}
+# head sizes 64 and 128: the sizes the tensor-core attention kernels take (groups of 4 and of 3)
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 256, "num_attention_heads": 8, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 384, "vocab_size": 512, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 128},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 4096,
+}
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 320, "num_attention_heads": 6, "num_key_value_heads": 2,
+    "head_dim": 128, "intermediate_size": 448, "vocab_size": 640, "rope_theta": 10000.0,
+    "rope_scaling": None, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 4096,
+}
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+PAGE_SIZE = {"A": 4, "B": 8, "C": 16, "D": 16, "E": 32}
+NORM_INIT = {"A": "ones_jitter", "B": "ones", "C": "ones_jitter", "D": "ones_jitter", "E": "ones"}
 
 
 def make_model_folder(folder, name, stored_dtype, seed=11, std=0.08, qk_gain=None):

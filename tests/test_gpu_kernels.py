@@ -173,6 +173,49 @@ def test_paged_attention_mixed_batch(ops, dtype, nq, nkv, d, page, window, split
     close(out, ref, dtype, "attention", scale=1.0 if dtype == "float32" else 4.0)
 
 
+def _hints(q_lens, ctx):
+    """The work lists the engine hands to the tensor-core attention kernels."""
+    from types import SimpleNamespace
+    dec, tiles, t0 = [], [], 0
+    for r, (n, c) in enumerate(zip(q_lens, ctx)):
+        if n == 1:
+            dec.append(t0)
+        else:
+            for a in range(0, n, 64):
+                tiles += [r, t0 + a, min(64, n - a), c - n + a]
+        t0 += n
+    i32 = lambda x: torch.tensor(x if x else [0], dtype=torch.int32).cuda()
+    return SimpleNamespace(n_decode=len(dec), decode_items=i32(dec)[:len(dec)], n_prefill_tiles=len(tiles) // 4,
+                           prefill_tiles=i32(tiles), max_ctx_len=max(ctx))
+
+
+@pytest.mark.parametrize("nq, nkv, d, page, window", [
+    (32, 8, 64, 16, 0), (8, 2, 128, 16, 0), (6, 2, 64, 8, 0), (16, 1, 64, 32, 0), (3, 3, 128, 4, 0),
+    (32, 8, 64, 16, 200), (4, 2, 128, 16, 33), (5, 1, 64, 1, 0)])
+def test_tensor_core_attention_mixed_batch(ops, nq, nkv, d, page, window):
+    """The bfloat16 tensor-core kernels (split-key decode, tiled prompt) on one mixed call: portions
+    of 150 (after 50 cached), 2 and 64 tokens, a whole 19-token prompt, and single tokens after 0,
+    63, 333 and 1500 cached tokens; against the plain statement and against the CUDA-core kernel."""
+    q_lens = [150, 1, 2, 1, 64, 1, 19, 1]
+    ctx = [200, 334, 66, 1, 128, 64, 19, 1501]
+    pages = sum(-(-c // page) for c in ctx) + 3
+    bt = _random_paging(len(ctx), ctx, page, pages, seed=d + nq + page)
+    cache = rnd((pages, 2, nkv, page, d), torch.bfloat16, 9)
+    T = sum(q_lens)
+    q = rnd((T, (nq + 2 * nkv) * d), torch.bfloat16, 10, 2.0)
+    tok_req = torch.repeat_interleave(torch.arange(len(ctx)), torch.tensor(q_lens)).int()
+    positions = torch.cat([torch.arange(c - n, c) for n, c in zip(q_lens, ctx)]).int()
+    scale = 1 / math.sqrt(d)
+    ref = REF.paged_attention(q, cache, bt, tok_req, positions, nq, nkv, d, page, scale, window=window)
+    args = (q.cuda(), cache.cuda(), bt.cuda(), tok_req.cuda(), positions.cuda(), nq, nkv, d, page, scale)
+    launches = ops.launches
+    out = ops.paged_attention(*args, window=window, hints=_hints(q_lens, ctx))
+    assert ops.launches - launches in (2, 3)                    # decode (+ merge) and prompt kernel, not the CUDA-core one
+    close(out, ref, "bfloat16", "tensor cores", scale=4.0)
+    simt = ops.paged_attention(*args, window=window, splits=2)
+    close(out, simt, "bfloat16", "against the CUDA-core kernel", scale=4.0)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("window", [0, 100])
 def test_attention_finds_one_far_key(ops, dtype, window):
@@ -207,10 +250,26 @@ def test_attention_finds_one_far_key(ops, dtype, window):
     out = ops.paged_attention(q.reshape(T, nq * d).to(DT[dtype]).cuda(), cache.cuda(), bt.cuda(),
                               torch.zeros(T, dtype=torch.int32).cuda(), positions.cuda(), nq, nkv, d, page,
                               1 / math.sqrt(d), window=window, splits=1 if window else 4).float().cpu().view(T, nq, d)
-    for t, key in enumerate(targets):
-        for h in range(nq):
-            want = cache[int(bt[0, key // page]), 1, h // 2, key % page].float()
-            assert (out[t, h] - want).abs().max() < 0.05, (t, h, key)
+    outs = [out]
+    if dtype == "bfloat16":
+        # the same queries as single decode tokens of six requests that share the pages, through the
+        # split-key tensor-core kernel, and as one-row "portions" through the prompt kernel
+        from types import SimpleNamespace
+        qd = q.reshape(T, nq * d).to(DT[dtype]).cuda()
+        bt6 = bt.repeat(T, 1).cuda()
+        req6 = torch.arange(T, dtype=torch.int32).cuda()
+        dec = SimpleNamespace(n_decode=T, decode_items=req6, n_prefill_tiles=0, prefill_tiles=req6, max_ctx_len=ctx)
+        outs.append(ops.paged_attention(qd, cache.cuda(), bt6, req6, positions.cuda(), nq, nkv, d, page, 1 / math.sqrt(d),
+                                        window=window, hints=dec).float().cpu().view(T, nq, d))
+        tiles = torch.tensor([[t, t, 1, int(positions[t])] for t in range(T)], dtype=torch.int32).reshape(-1).cuda()
+        pf = SimpleNamespace(n_decode=0, decode_items=req6[:0], n_prefill_tiles=T, prefill_tiles=tiles, max_ctx_len=ctx)
+        outs.append(ops.paged_attention(qd, cache.cuda(), bt6, req6, positions.cuda(), nq, nkv, d, page, 1 / math.sqrt(d),
+                                        window=window, hints=pf).float().cpu().view(T, nq, d))
+    for res in outs:
+        for t, key in enumerate(targets):
+            for h in range(nq):
+                want = cache[int(bt[0, key // page]), 1, h // 2, key % page].float()
+                assert (res[t, h] - want).abs().max() < 0.05, (t, h, key)
 
 
 @pytest.mark.parametrize("vocab", [1000, 128256, 37])

@@ -15,7 +15,8 @@ from gpu_common import assert_close, make_engine, reference_logits, stored_dtype
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 11, 17, 90, 47, 130], "B": [1, 9, 33, 70, 150, 41], "C": [40, 3, 100, 77, 260, 18]}
+LENGTHS = {"A": [5, 11, 17, 90, 47, 130], "B": [1, 9, 33, 70, 150, 41], "C": [40, 3, 100, 77, 260, 18],
+           "D": [70, 1, 200, 33, 129, 64], "E": [65, 140, 2, 90, 31, 128]}
 
 
 def _seqs(name):
@@ -44,7 +45,7 @@ FAMILIES = {
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("family", list(FAMILIES))
 def test_logits_do_not_depend_on_the_cut(model_folders, references, name, dtype, family):
     seqs = _seqs(name)
@@ -60,7 +61,7 @@ def test_logits_do_not_depend_on_the_cut(model_folders, references, name, dtype,
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_decode_steps_from_cuda_graphs(model_folders, references, name, dtype):
     """With ``compiled_model`` single-token steps replay captured graphs of padded batch sizes
     (1, 2, 4): the logits are those of the plain implementation all the same, also when the batch
