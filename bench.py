@@ -116,6 +116,7 @@ def main() -> int:
     ap.add_argument("--points", default="1,64", help="extra decode batch sizes, comma separated ('' for none)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill measurement (profiling runs)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -172,12 +173,12 @@ def main() -> int:
     # ------------------------------------------------------------------ prefill of 2,048 tokens
     prompt = tokens(PREFILL_TOKENS)
     times = []
-    for i in range(3 + 5):
+    for i in range(0 if args.no_prefill else 3 + 5):
         ms = event_time(lambda: engine.step([StepEntry("prefill", prompt, [PREFILL_TOKENS - 1])]), 1)
         engine.finish("prefill")
         if i >= 3:
             times.append(ms)
-    prefill_ms = statistics.median(times)
+    prefill_ms = statistics.median(times) if times else float("nan")
     matmul_params, head_params, weight_bytes, kv_per_token = model_bytes_and_flops(cfg, args.layers)
     nq, d = cfg["num_attention_heads"], cfg["head_dim"]
     attn_flops = args.layers * 4 * nq * d * (PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2)
