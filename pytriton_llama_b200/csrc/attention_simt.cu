@@ -112,27 +112,50 @@ paged_attention_simt_kernel(T* __restrict__ out, float* __restrict__ part_acc, f
 }
 
 // Merge of the per-split partial results: out = sum_z e^{m_z - M} acc_z / sum_z e^{m_z - M} l_z.
+// One warp per (token, head); the lanes share the weights of the splits and split the head's
+// dimensions among them.
+constexpr int kMergeWarps = 4;
 template <typename T>
-__global__ void attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
-                                       const float* __restrict__ part_ml, int out_stride, int nq, int d,
-                                       int splits, const int* __restrict__ items) {
-  const int t = items ? items[blockIdx.x] : blockIdx.x, h = blockIdx.y;
+__global__ void __launch_bounds__(kMergeWarps * 32)
+attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
+                       const float* __restrict__ part_ml, int out_stride, int nq, int d,
+                       int splits, const int* __restrict__ items, int n_rows) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pair = blockIdx.x * kMergeWarps + warp;       // (row, head) pair
+  if (pair >= n_rows * nq) return;
+  const int ti = pair / nq, h = pair % nq;
+  const int t = items ? items[ti] : ti;
   const size_t idx0 = ((size_t)t * nq + h) * splits;
+  // lanes read the (max, sum) pairs of up to 32 splits at a time
   float M = -INFINITY;
-  for (int z = 0; z < splits; ++z) M = fmaxf(M, part_ml[(idx0 + z) * 2]);
+  for (int z = lane; z < splits; z += 32) M = fmaxf(M, part_ml[(idx0 + z) * 2]);
+  M = warp_max(M);
   float L = 0.f;
-  for (int z = 0; z < splits; ++z) {
+  for (int z = lane; z < splits; z += 32) {
     const float mz = part_ml[(idx0 + z) * 2];
     if (mz > -INFINITY) L += expf(mz - M) * part_ml[(idx0 + z) * 2 + 1];
   }
+  L = warp_sum(L);
   const float inv = L > 0.f ? 1.0f / L : 0.f;
-  for (int dd = threadIdx.x; dd < d; dd += blockDim.x) {
-    float a = 0.f;
-    for (int z = 0; z < splits; ++z) {
-      const float mz = part_ml[(idx0 + z) * 2];
-      if (mz > -INFINITY) a = fmaf(expf(mz - M), part_acc[(idx0 + z) * d + dd], a);
+  float acc[kMaxDimPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxDimPerLane; ++i) acc[i] = 0.f;
+  for (int z = 0; z < splits; ++z) {
+    const float mz = part_ml[(idx0 + z) * 2];
+    if (!(mz > -INFINITY)) continue;                       // uniform over the warp
+    const float wz = expf(mz - M);
+    const float* pa = part_acc + (idx0 + z) * d;
+#pragma unroll
+    for (int i = 0; i < kMaxDimPerLane; ++i) {
+      const int dd = lane + 32 * i;
+      if (dd < d) acc[i] = fmaf(wz, pa[dd], acc[i]);
     }
-    out[(size_t)t * out_stride + (size_t)h * d + dd] = from_f32<T>(a * inv);
+  }
+  T* o = out + (size_t)t * out_stride + (size_t)h * d;
+#pragma unroll
+  for (int i = 0; i < kMaxDimPerLane; ++i) {
+    const int dd = lane + 32 * i;
+    if (dd < d) o[dd] = from_f32<T>(acc[i] * inv);
   }
 }
 
@@ -157,9 +180,9 @@ int paged_attention_simt(void* out, const void* q, const void* cache, const int*
   int rc = check_launch("paged_attention");
   if (rc) return rc;
   if (splits > 1) {
-    dim3 g2(tokens, nq);
-    attention_merge_kernel<T><<<g2, d >= 128 ? 128 : (d >= 64 ? 64 : 32), 0, as_stream(stream)>>>(
-        (T*)out, part_acc, part_ml, out_stride, nq, d, splits, nullptr);
+    const long long pairs = (long long)tokens * nq;
+    attention_merge_kernel<T><<<(unsigned)((pairs + kMergeWarps - 1) / kMergeWarps), kMergeWarps * 32, 0, as_stream(stream)>>>(
+        (T*)out, part_acc, part_ml, out_stride, nq, d, splits, nullptr, tokens);
     rc = check_launch("attention_merge");
   }
   return rc;
@@ -168,9 +191,9 @@ int paged_attention_simt(void* out, const void* q, const void* cache, const int*
 // Merge for the tensor-core decode kernel: `items` (or 0..tokens-1) names the token rows.
 int attention_merge_bf16(void* out, const float* part_acc, const float* part_ml, int tokens, int out_stride,
                          int nq, int d, int splits, const int* items, void* stream) {
-  dim3 grid(tokens, nq);
-  attention_merge_kernel<__nv_bfloat16><<<grid, d >= 128 ? 128 : (d >= 64 ? 64 : 32), 0, as_stream(stream)>>>(
-      (__nv_bfloat16*)out, part_acc, part_ml, out_stride, nq, d, splits, items);
+  const long long pairs = (long long)tokens * nq;
+  attention_merge_kernel<__nv_bfloat16><<<(unsigned)((pairs + kMergeWarps - 1) / kMergeWarps), kMergeWarps * 32, 0, as_stream(stream)>>>(
+      (__nv_bfloat16*)out, part_acc, part_ml, out_stride, nq, d, splits, items, tokens);
   return check_launch("attention_merge");
 }
 

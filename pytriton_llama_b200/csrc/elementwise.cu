@@ -42,14 +42,52 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ residual_out,
                                    const float* __restrict__ residual_in, const T* __restrict__ x,
                                    const float* __restrict__ w, const int* __restrict__ rows,
-                                   int hidden, float eps) {
+                                   int hidden, float eps, int vec_ok) {
   extern __shared__ float row[];
   __shared__ float red[33];
   const int m = blockIdx.x;
   const int r = rows ? rows[m] : m;
   const float* rin = residual_in ? residual_in + (size_t)r * hidden : nullptr;
   const T* xin = x ? x + (size_t)r * hidden : nullptr;
+  float* rout = residual_out ? residual_out + (size_t)m * hidden : nullptr;
+  T* yo = y + (size_t)m * hidden;
   float ss = 0.f;
+  if (vec_ok) {
+    // four elements per thread and turn: 16-byte packets of the float32 arrays, 8 or 16 bytes of T
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+      float4 s = rin ? *reinterpret_cast<const float4*>(rin + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      if (xin) {
+        if constexpr (sizeof(T) == 4) {
+          const float4 v = *reinterpret_cast<const float4*>(xin + i);
+          s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        } else {
+          const uint2 raw = *reinterpret_cast<const uint2*>(xin + i);
+          const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+          const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+          s.x += __bfloat162float(a.x); s.y += __bfloat162float(a.y);
+          s.z += __bfloat162float(b.x); s.w += __bfloat162float(b.y);
+        }
+      }
+      *reinterpret_cast<float4*>(row + i) = s;
+      if (rout) *reinterpret_cast<float4*>(rout + i) = s;
+      ss += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+    }
+    ss = block_sum(ss, red);
+    const float rrms = 1.0f / sqrtf(ss / (float)hidden + eps);
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+      const float4 s = *reinterpret_cast<const float4*>(row + i);
+      const float4 g = *reinterpret_cast<const float4*>(w + i);
+      if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(yo + i) = make_float4(s.x * rrms * g.x, s.y * rrms * g.y, s.z * rrms * g.z, s.w * rrms * g.w);
+      } else {
+        uint2 o;
+        *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(s.x * rrms * g.x, s.y * rrms * g.y);
+        *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(s.z * rrms * g.z, s.w * rrms * g.w);
+        *reinterpret_cast<uint2*>(yo + i) = o;
+      }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float s = rin ? rin[i] : 0.f;
     if (xin) s += to_f32(xin[i]);
@@ -58,8 +96,6 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ residu
   }
   ss = block_sum(ss, red);
   const float rrms = 1.0f / sqrtf(ss / (float)hidden + eps);
-  float* rout = residual_out ? residual_out + (size_t)m * hidden : nullptr;
-  T* yo = y + (size_t)m * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     const float s = row[i];
     if (rout) rout[i] = s;
@@ -126,9 +162,11 @@ int add_rmsnorm(void* y, float* residual_out, const float* residual_in, const vo
     PTL_REQUIRE(e == cudaSuccess, "add_rmsnorm: cannot raise shared memory: %s", cudaGetErrorString(e));
     raised[slot] = true;
   }
-  int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
+  const int vec_ok = hidden % 4 == 0 && aligned16(y) && aligned16(w) && (!x || aligned16(x)) &&
+                     (!residual_in || aligned16(residual_in)) && (!residual_out || aligned16(residual_out));
+  int threads = hidden >= 8192 ? 1024 : (hidden >= 2048 ? 512 : (hidden >= 1024 ? 256 : 128));
   add_rmsnorm_kernel<T><<<out_rows, threads, smem, as_stream(stream)>>>(
-      (T*)y, residual_out, residual_in, (const T*)x, w, rows, hidden, eps);
+      (T*)y, residual_out, residual_in, (const T*)x, w, rows, hidden, eps, vec_ok);
   return check_launch("add_rmsnorm");
 }
 

@@ -16,6 +16,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      const float* __restrict__ inv_freq, const int* __restrict__ slots,
                                      T* __restrict__ cache, int nq, int nkv, int d, int rot,
                                      int page_size, int write_cache, long long num_slots) {
+  extern __shared__ float cs[];            // cos[rot/2], sin[rot/2] of this token's angles
   const int t = blockIdx.x;
   const int row_len = (nq + 2 * nkv) * d;
   T* row = qkv + (size_t)t * row_len;
@@ -28,6 +29,15 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   T* kdst = cache ? cache + ((size_t)page * 2) * plane + (size_t)off * d : nullptr;
   T* vdst = cache ? kdst + plane : nullptr;
   const int half = rot / 2;
+  if (inv_freq) {
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+      float s, c;
+      sincosf(pos * inv_freq[j], &s, &c);   // the accurate version: angles reach thousands of radians
+      cs[j] = c;
+      cs[half + j] = s;
+    }
+    __syncthreads();
+  }
   const int pairs_per_head = d - half;  // `half` rotated pairs, then d - rot pass-through elements
   // q and k heads
   for (int e = threadIdx.x; e < (nq + nkv) * pairs_per_head; e += blockDim.x) {
@@ -37,17 +47,17 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
     const bool is_k = h >= nq;
     T* kd = (is_k && slot >= 0) ? kdst + (size_t)(h - nq) * page_size * d : nullptr;
     if (j < half) {
-      float x1 = to_f32(head[j]), x2 = to_f32(head[j + half]);
+      const float x1 = to_f32(head[j]), x2 = to_f32(head[j + half]);
       float o1 = x1, o2 = x2;
       if (inv_freq) {
-        float s, c;
-        sincosf(pos * inv_freq[j], &s, &c);
+        const float c = cs[j], s = cs[half + j];
         o1 = x1 * c - x2 * s;
         o2 = x2 * c + x1 * s;
       }
       const T r1 = from_f32<T>(o1), r2 = from_f32<T>(o2);
-      if (!is_k) { head[j] = r1; head[j + half] = r2; }
-      else { head[j] = r1; head[j + half] = r2; if (kd) { kd[j] = r1; kd[j + half] = r2; } }
+      head[j] = r1;
+      head[j + half] = r2;
+      if (kd) { kd[j] = r1; kd[j + half] = r2; }
     } else {
       const int i = rot + (j - half);  // untouched tail when rot < d
       if (kd) kd[i] = head[i];
@@ -71,7 +81,9 @@ int rope_kv_write(void* qkv, const int* positions, const float* inv_freq, const 
   PTL_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "rope_kv_write: rotary width %d must be even and <= head size %d", rot, d);
   PTL_REQUIRE(cache == nullptr || (page_size > 0 && slots != nullptr && num_slots > 0), "rope_kv_write: a cache needs slots and a page size");
   if (tokens == 0) return 0;
-  rope_kv_write_kernel<T><<<tokens, 128, 0, as_stream(stream)>>>(
+  const int work = (nq + nkv) * (d - rot / 2);
+  const int threads = work >= 1024 ? 512 : (work >= 256 ? 256 : 128);
+  rope_kv_write_kernel<T><<<tokens, threads, (size_t)rot * sizeof(float), as_stream(stream)>>>(
       (T*)qkv, positions, inv_freq, slots, (T*)cache, nq, nkv, d, rot, page_size, cache != nullptr, num_slots);
   return check_launch("rope_kv_write");
 }

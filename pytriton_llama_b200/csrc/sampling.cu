@@ -138,7 +138,62 @@ sample_kernel(int* __restrict__ tokens, const float* __restrict__ logits, float*
   }
 }
 
+// Greedy choice for whole batches in two stages, so that a few rows still use many SMs:
+// stage 1 finds the best (value, index) of each of `chunks` slices of a row, stage 2 the best of those.
+constexpr int kArgmaxChunks = 32;
+constexpr int kArgmaxThreads = 256;
+
+__global__ void __launch_bounds__(kArgmaxThreads)
+argmax_partial_kernel(float* __restrict__ part_val, int* __restrict__ part_idx, const float* __restrict__ logits,
+                      int vocab, long long ld) {
+  __shared__ float sv[33];
+  __shared__ int si[33];
+  const int row = blockIdx.y, chunk = blockIdx.x;
+  const int per = (vocab + kArgmaxChunks - 1) / kArgmaxChunks;
+  const int lo = chunk * per, hi = min(lo + per, vocab);
+  const float* x = logits + (size_t)row * ld;
+  float best = -INFINITY;
+  int besti = 0x7fffffff;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = x[i];
+    if (v > best || (v == best && i < besti)) { best = v; besti = i; }
+  }
+  block_argmax(best, besti, sv, si);
+  if (threadIdx.x == 0) {
+    part_val[row * kArgmaxChunks + chunk] = best;
+    part_idx[row * kArgmaxChunks + chunk] = besti;
+  }
+}
+
+__global__ void argmax_final_kernel(int* __restrict__ tokens, const float* __restrict__ part_val,
+                                    const int* __restrict__ part_idx) {
+  const int row = blockIdx.x, lane = threadIdx.x;
+  float v = part_val[row * kArgmaxChunks + lane];
+  int idx = part_idx[row * kArgmaxChunks + lane];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+  }
+  if (lane == 0) tokens[row] = idx;
+}
+
 }  // namespace ptl
+
+// scratch: rows * 32 floats and rows * 32 ints
+PTL_EXPORT int ptl_argmax(int* tokens, const float* logits, float* part_val, int* part_idx, int rows, int vocab,
+                          long long ld, void* stream) {
+  static_assert(ptl::kArgmaxChunks == 32, "the final stage is one warp");
+  PTL_REQUIRE(rows >= 0 && vocab > 0 && ld >= vocab && rows <= 65535, "argmax: bad sizes rows=%d vocab=%d", rows, vocab);
+  if (rows == 0) return 0;
+  dim3 grid(ptl::kArgmaxChunks, rows);
+  ptl::argmax_partial_kernel<<<grid, ptl::kArgmaxThreads, 0, ptl::as_stream(stream)>>>(part_val, part_idx, logits, vocab, ld);
+  int rc = ptl::check_launch("argmax_partial");
+  if (rc) return rc;
+  ptl::argmax_final_kernel<<<rows, 32, 0, ptl::as_stream(stream)>>>(tokens, part_val, part_idx);
+  return ptl::check_launch("argmax_final");
+}
 
 PTL_EXPORT int ptl_sample(int* tokens, const float* logits, float* probs, const float* temperature,
                           const float* top_p, const float* u, int rows, int vocab, long long ld,

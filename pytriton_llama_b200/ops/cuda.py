@@ -61,6 +61,8 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_prefill_attention_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                _c_int, _c_int, _c_f, _c_int, _c_int, _ptr]
     lib.ptl_prefill_attention_bf16.restype = _c_int
+    lib.ptl_argmax.argtypes = [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
+    lib.ptl_argmax.restype = _c_int
     lib.ptl_sample.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
     lib.ptl_sample.restype = _c_int
     lib.ptl_last_error.restype = ctypes.c_char_p
@@ -288,6 +290,11 @@ class CudaOps:
         self._want(logits, "logits", torch.float32)
         rows, vocab = logits.shape
         out = self.empty((rows,), torch.int32)
+        if temperature is None and rows <= 65535:
+            scratch = self.empty((2, rows, 32), torch.float32)   # per row 32 best values, and (as int32) their indices
+            self._check(self.lib.ptl_argmax(_p(out), _p(logits), _p(scratch[0]), _p(scratch[1]), rows, vocab, vocab,
+                                            self._stream()), kernels=2)
+            return out
         probs = None
         if temperature is not None:
             for name, t in (("temperature", temperature), ("top_p", top_p), ("u", u)):
