@@ -1,0 +1,556 @@
+// bfloat16 matrix product on the fifth-generation tensor cores: out = X[M,K] * W[N,K]^T with
+// float32 accumulation in tensor memory (TMEM), operands staged by TMA into 128-byte-swizzled
+// shared memory, `tcgen05.mma` issued by one thread, accumulators read back with `tcgen05.ld`
+// for a fused epilogue.
+//
+// One block computes one 128 x BN tile.  The 128 rows are the rows of the "row operand", the BN
+// columns the rows of the "column operand":
+//   * many tokens (M > 64): row operand = X (128 tokens), column operand = W (BN features);
+//   * few tokens (M <= 64, decoding): the operands are swapped -- row operand = W (128 features),
+//     column operand = X (tokens padded to 16/32/64) -- so the tensor core runs full rows while
+//     the kernel is a stream over the weights; the K range is split over the blocks of a thread-block
+//     cluster (blockIdx.y = rank in the cluster, up to 8); each block leaves its partial tile in its
+//     own shared memory, and after a cluster barrier every block adds one slice of the rows over
+//     all peers through distributed shared memory, in rank order, and runs the epilogue on it.
+//
+// Epilogues: 0 store bfloat16, 1 store float32, 2 add into a float32 residual [M,N] in place,
+// 3 SiLU(gate)*up where the rows of W alternate gate_j, up_j (out is [M, N/2] bfloat16).
+//
+// Warp roles (192 threads): warp 0 TMA producer, warp 1 TMEM allocation + MMA issue, warps 2..5
+// epilogue (warp w reads TMEM lanes 32*(w%4)..+31).  Every wait on an mbarrier gives up after a
+// bounded number of polls, records a code in *status, and the block drains and frees its TMEM.
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+#include "common.cuh"
+
+namespace ptl {
+
+constexpr int kTileRows = 128;     // rows of the row operand per block (MMA M)
+constexpr int kTileK = 64;         // K per stage: 64 bfloat16 = one 128-byte swizzle row
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kPollLimit = 1u << 22;
+
+struct GemmParams {
+  void* out;
+  int* status;           // set non-zero when a wait gave up
+  int rows;              // rows of the row operand (tokens, or features when swapped)
+  int cols;              // rows of the column operand
+  int K;
+  int ld_out;            // elements between tokens in `out`
+  int swapped;
+  int splits;
+  int kb_per_split;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false (and *abort = 1, *status = code) if the phase did not complete in time or
+// another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort, int* status, int code) {
+  for (uint32_t i = 0; i < kPollLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort) return false;
+    if (i > 64) __nanosleep(40);
+  }
+  *abort = 1;
+  if (status) atomicExch(status, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_load_16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16),
+// written by TMA with the 128-byte swizzle: groups of 8 rows are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);   // start address, bits 0-13
+  d |= (uint64_t)1 << 16;                     // leading byte offset (not used by swizzled K-major tiles)
+  d |= (uint64_t)(1024 >> 4) << 32;           // stride byte offset: 8 rows x 128 bytes
+  d |= (uint64_t)1 << 46;                     // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                     // 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major, M x N tile.
+__host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int BN> struct TcCfg {
+  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : 4);   // few tokens: small blocks, several per SM
+  static constexpr int kRowBytes = kTileRows * kTileK * 2;     // 16 KB
+  static constexpr int kColBytes = BN * kTileK * 2;
+  static constexpr int kStageBytes = kRowBytes + kColBytes;
+  static constexpr int kTmemCols = BN < 32 ? 32 : BN;          // power of two >= 32
+  static constexpr int kSmem = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+
+// ---------------------------------------------------------------- epilogue of one row's 16 accumulators
+// Normal mode: `row` is a token, columns c0..c0+15 are features.
+template <int EPI>
+__device__ __forceinline__ void store_normal(const GemmParams& p, int row, int c0, const float (&v)[16]) {
+  if (row >= p.rows) return;
+  const int n_total = p.cols;
+  if (EPI == 3) {
+    __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)row * p.ld_out + c0 / 2;
+    if (c0 + 16 <= n_total && (p.ld_out % 8 == 0)) {
+      uint4 pk;
+      uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 t = __floats2bfloat162_rn(silu_f(v[4 * j]) * v[4 * j + 1], silu_f(v[4 * j + 2]) * v[4 * j + 3]);
+        w[j] = *reinterpret_cast<uint32_t*>(&t);
+      }
+      *reinterpret_cast<uint4*>(o) = pk;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (c0 + 2 * j + 1 < n_total) o[j] = __float2bfloat16_rn(silu_f(v[2 * j]) * v[2 * j + 1]);
+    }
+    return;
+  }
+  const bool full = c0 + 16 <= n_total;
+  if (EPI == 0) {
+    __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)row * p.ld_out + c0;
+    if (full && p.ld_out % 8 == 0) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint4 pk;
+        uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __nv_bfloat162 t = __floats2bfloat162_rn(v[8 * h + 2 * j], v[8 * h + 2 * j + 1]);
+          w[j] = *reinterpret_cast<uint32_t*>(&t);
+        }
+        *reinterpret_cast<uint4*>(o + 8 * h) = pk;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (c0 + j < n_total) o[j] = __float2bfloat16_rn(v[j]);
+    }
+  } else {   // EPI 1 (store float32) or 2 (add into float32)
+    float* o = (float*)p.out + (size_t)row * p.ld_out + c0;
+    if (full && p.ld_out % 4 == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float4 t = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        if (EPI == 2) {
+          const float4 r = *reinterpret_cast<const float4*>(o + 4 * j);
+          t.x += r.x; t.y += r.y; t.z += r.z; t.w += r.w;
+        }
+        *reinterpret_cast<float4*>(o + 4 * j) = t;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (c0 + j < n_total) o[j] = EPI == 2 ? o[j] + v[j] : v[j];
+    }
+  }
+}
+
+// Swapped mode: `row` is a feature n, columns c0..c0+15 are tokens.
+template <int EPI>
+__device__ __forceinline__ void store_swapped(const GemmParams& p, int row, int c0, const float (&v)[16]) {
+  const int n = row;
+  const bool n_ok = n < p.rows;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const int tok = c0 + j;
+    if (EPI == 3) {
+      const float up = __shfl_down_sync(0xffffffffu, v[j], 1);   // odd rows hold up_j; all lanes take part
+      if (n_ok && tok < p.cols && (n & 1) == 0)
+        ((__nv_bfloat16*)p.out)[(size_t)tok * p.ld_out + n / 2] = __float2bfloat16_rn(silu_f(v[j]) * up);
+    } else if (n_ok && tok < p.cols) {
+      if (EPI == 0) ((__nv_bfloat16*)p.out)[(size_t)tok * p.ld_out + n] = __float2bfloat16_rn(v[j]);
+      else if (EPI == 1) ((float*)p.out)[(size_t)tok * p.ld_out + n] = v[j];
+      else ((float*)p.out)[(size_t)tok * p.ld_out + n] += v[j];
+    }
+  }
+}
+
+// One output element of the swapped mode after the cluster reduction: feature n, token tok.
+template <int EPI>
+__device__ __forceinline__ void store_swapped_one(const GemmParams& p, int n, int tok, float v, float up) {
+  if (n >= p.rows || tok >= p.cols) return;
+  if (EPI == 0) ((__nv_bfloat16*)p.out)[(size_t)tok * p.ld_out + n] = __float2bfloat16_rn(v);
+  else if (EPI == 1) ((float*)p.out)[(size_t)tok * p.ld_out + n] = v;
+  else if (EPI == 2) ((float*)p.out)[(size_t)tok * p.ld_out + n] += v;
+  else ((__nv_bfloat16*)p.out)[(size_t)tok * p.ld_out + n / 2] = __float2bfloat16_rn(silu_f(v) * up);
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(kGemmThreads)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col, const GemmParams p) {
+  using Cfg = TcCfg<BN>;
+  extern __shared__ unsigned char smem_raw[];
+  // tiles need 1024-byte alignment for the 128-byte swizzle pattern to start at row 0
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  // bars[0..S-1] full, bars[S..2S-1] empty, bars[2S] accumulator ready
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::kStages + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  volatile int* ok_flags = reinterpret_cast<volatile int*>(tmem_slot + 3);   // one per epilogue warp
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row_tile = p.swapped ? blockIdx.x : blockIdx.y;
+  const int col_tile = p.swapped ? 0 : blockIdx.x;
+  const int split = p.swapped ? blockIdx.y : 0;
+  const int num_kb = (p.K + kTileK - 1) / kTileK;
+  const int kb0 = split * p.kb_per_split;
+  const int kb1 = min(num_kb, kb0 + p.kb_per_split);
+  const int my_kb = max(0, kb1 - kb0);
+  const uint32_t smem_base = smem_addr(smem);
+  const uint32_t bar_base = smem_addr(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
+  const uint32_t accum_bar = bar_base + 8u * (2 * Cfg::kStages);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_row) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_col) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(Cfg::kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------ TMA producer
+    int issued = 0;
+    for (int i = 0; i < my_kb; ++i) {
+      const int s = i % Cfg::kStages;
+      const uint32_t ph = (i / Cfg::kStages) & 1;
+      if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, 1)) break;
+      mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
+      const uint32_t dst = smem_base + s * Cfg::kStageBytes;
+      tma_load_2d(dst, &map_row, full_bar(s), (kb0 + i) * kTileK, row_tile * kTileRows);
+      tma_load_2d(dst + Cfg::kRowBytes, &map_col, full_bar(s), (kb0 + i) * kTileK, col_tile * BN);
+      issued = i + 1;
+    }
+    if (*abort_flag) {
+      // leave no copy in flight behind: wait (bounded) for the stages that were requested
+      for (int i = max(0, issued - Cfg::kStages); i < issued; ++i) {
+        const int s = i % Cfg::kStages;
+        for (uint32_t t = 0; t < (1u << 16) && !mbar_try_wait(full_bar(s), (i / Cfg::kStages) & 1); ++t) __nanosleep(100);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc = instr_desc_bf16(kTileRows, BN);
+    bool ok = true;
+    for (int i = 0; i < my_kb && ok; ++i) {
+      const int s = i % Cfg::kStages;
+      const uint32_t ph = (i / Cfg::kStages) & 1;
+      ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 2);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const uint32_t a = smem_base + s * Cfg::kStageBytes;
+      const uint32_t b = a + Cfg::kRowBytes;
+#pragma unroll
+      for (int k = 0; k < kTileK / 16; ++k) {
+        tcgen05_mma_bf16(tmem_base, smem_desc_sw128(a + k * 32), smem_desc_sw128(b + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
+      }
+      tcgen05_commit(empty_bar(s));      // the stage is free once these MMAs have read it
+    }
+    tcgen05_commit(accum_bar);           // the accumulator is complete (also when there was nothing to do)
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------ epilogue
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    const int row = row_tile * kTileRows + row_in_tile;
+    const bool mine = mbar_wait(accum_bar, 0, abort_flag, p.status, 3);
+    tcgen05_fence_after();
+    // the four warps go on together or not at all (they meet at named barriers below)
+    if (lane == 0) ok_flags[quad] = mine ? 1 : 0;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const bool ok = ok_flags[0] && ok_flags[1] && ok_flags[2] && ok_flags[3];
+    if (ok) {
+      if (!p.swapped) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          uint32_t r[16];
+          tmem_load_16(tmem_base + ((uint32_t)(quad * 32) << 16) + c0, r);
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = my_kb > 0 ? __uint_as_float(r[j]) : 0.f;
+          store_normal<EPI>(p, row, col_tile * BN + c0, v);
+        }
+      } else if (p.splits == 1) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          uint32_t r[16];
+          tmem_load_16(tmem_base + ((uint32_t)(quad * 32) << 16) + c0, r);
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = my_kb > 0 ? __uint_as_float(r[j]) : 0.f;
+          store_swapped<EPI>(p, row, c0, v);
+        }
+      } else {
+        // partial tile -> own shared memory [column][128 rows] (the pipeline stages are idle by now)
+        float* part = reinterpret_cast<float*>(smem);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          uint32_t r[16];
+          tmem_load_16(tmem_base + ((uint32_t)(quad * 32) << 16) + c0, r);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) part[(c0 + j) * kTileRows + row_in_tile] = my_kb > 0 ? __uint_as_float(r[j]) : 0.f;
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (p.swapped && p.splits > 1) {
+    // every block of the cluster has its partial tile in place
+    cluster_sync_all();
+    if (warp >= 2 && !*abort_flag) {
+      const int S = p.splits;
+      const int rows_per = kTileRows / S;                    // rows this block finishes (S is 2, 4 or 8)
+      const uint32_t part_addr = smem_base;
+      const int t = threadIdx.x - 64;                        // 0..127
+      if (EPI == 3) {
+        const int pairs = rows_per / 2;
+        for (int idx = t; idx < pairs * BN; idx += 128) {
+          const int pr = idx % pairs, col = idx / pairs;
+          const int rl = split * rows_per + 2 * pr;
+          float g = 0.f, u = 0.f;
+          for (int z = 0; z < S; ++z) {
+            g += ld_peer_f32(part_addr + 4u * (col * kTileRows + rl), z);
+            u += ld_peer_f32(part_addr + 4u * (col * kTileRows + rl + 1), z);
+          }
+          store_swapped_one<EPI>(p, row_tile * kTileRows + rl, col, g, u);
+        }
+      } else {
+        for (int idx = t; idx < rows_per * BN; idx += 128) {
+          const int rl = split * rows_per + idx % rows_per, col = idx / rows_per;
+          float v = 0.f;
+#pragma unroll 4
+          for (int z = 0; z < S; ++z) v += ld_peer_f32(part_addr + 4u * (col * kTileRows + rl), z);
+          store_swapped_one<EPI>(p, row_tile * kTileRows + rl, col, v, 0.f);
+        }
+      }
+    }
+    cluster_sync_all();                                      // nobody leaves while a peer still reads its tile
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- host side
+static int encode_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows);
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// Tensor maps already encoded by this process: weights are asked for again every step.
+struct MapKey {
+  const void* base; int rows, K, box;
+  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && K == o.K && box == o.box; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    h ^= (size_t)k.rows * 0x9E3779B97F4A7C15ull + (size_t)k.K * 0xC2B2AE3D27D4EB4Full + (size_t)k.box * 0x165667B19E3779F9ull;
+    return h;
+  }
+};
+
+// A [rows, K] bfloat16 matrix, K contiguous, fetched in boxes of 64 (K) x box_rows with the 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex lock;
+  const MapKey key{base, rows, K, box_rows};
+  {
+    std::lock_guard<std::mutex> g(lock);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *map = it->second; return 0; }
+  }
+  int rc = encode_map(map, base, rows, K, box_rows);
+  if (rc) return rc;
+  std::lock_guard<std::mutex> g(lock);
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, *map);
+  return 0;
+}
+
+static int encode_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  PTL_REQUIRE(fn != nullptr, "gemm_tc: the driver has no cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  PTL_REQUIRE(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled failed with %d (rows=%d K=%d box=%d)", (int)r, rows, K, box_rows);
+  return 0;
+}
+
+template <int BN, int EPI>
+static int launch_tc(const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+  using Cfg = TcCfg<BN>;
+  static bool raised = false;
+  if (!raised) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
+    PTL_REQUIRE(e == cudaSuccess, "gemm_tc: cannot raise shared memory to %d: %s", Cfg::kSmem, cudaGetErrorString(e));
+    raised = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  int nattr = 0;
+  if (p.swapped && p.splits > 1) {
+    attr[nattr].id = cudaLaunchAttributeClusterDimension;
+    attr[nattr].val.clusterDim.x = 1;
+    attr[nattr].val.clusterDim.y = p.splits;
+    attr[nattr].val.clusterDim.z = 1;
+    ++nattr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = nattr;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI>, mr, mc, p);
+  if (e != cudaSuccess) return fail("gemm_tc: launch failed: %s", cudaGetErrorString(e));
+  return check_launch("gemm_tc");
+}
+
+template <int BN>
+static int launch_epi(int epi, const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& p, dim3 grid, cudaStream_t s) {
+  switch (epi) {
+    case 0: return launch_tc<BN, 0>(mr, mc, p, grid, s);
+    case 1: return launch_tc<BN, 1>(mr, mc, p, grid, s);
+    case 2: return launch_tc<BN, 2>(mr, mc, p, grid, s);
+    case 3: return launch_tc<BN, 3>(mr, mc, p, grid, s);
+  }
+  return fail("gemm_tc: unknown epilogue %d", epi);
+}
+
+}  // namespace ptl
+
+// out: epi 0 bf16 [M,N]; 1 float32 [M,N]; 2 float32 [M,N] added to in place; 3 bf16 [M,N/2].
+// Returns -2 when the sizes are not ones this kernel takes (K % 8 != 0 or K < 64), so that the caller
+// can use another product.  `splits_hint` > 0 forces the number of K splits when M <= 64 (1, 2, 4 or 8).
+PTL_EXPORT int ptl_gemm_tc_bf16(void* out, const void* X, const void* W, int M, int N, int K, int ld_out, int epi,
+                                int* status, int splits_hint, void* stream) {
+  using namespace ptl;
+  PTL_REQUIRE(M >= 0 && N > 0 && K > 0 && ld_out > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
+  if (K % 8 != 0 || K < kTileK) return -2;
+  PTL_REQUIRE(aligned16(X) && aligned16(W) && aligned16(out), "gemm_tc: operands must be 16-byte aligned");
+  PTL_REQUIRE(epi != 3 || N % 2 == 0, "gemm_tc: the SiLU*up epilogue needs an even number of weight rows");
+  if (M == 0) return 0;
+  GemmParams p{};
+  p.out = out; p.status = status;
+  p.K = K; p.ld_out = ld_out;
+  const int num_kb = (K + kTileK - 1) / kTileK;
+  CUtensorMap mr, mc;
+  cudaStream_t s = as_stream(stream);
+  if (M > 64) {
+    p.swapped = 0; p.rows = M; p.cols = N; p.splits = 1; p.kb_per_split = num_kb;
+    const bool wide = N % 256 == 0 || N >= 2048;
+    int rc = make_map(&mr, X, M, K, kTileRows);
+    if (rc) return rc;
+    rc = make_map(&mc, W, N, K, wide ? 256 : 128);
+    if (rc) return rc;
+    const int bn = wide ? 256 : 128;
+    dim3 grid((N + bn - 1) / bn, (M + kTileRows - 1) / kTileRows);
+    PTL_REQUIRE(grid.y <= 65535, "gemm_tc: too many rows");
+    return wide ? launch_epi<256>(epi, mr, mc, p, grid, s) : launch_epi<128>(epi, mr, mc, p, grid, s);
+  }
+  // few tokens: swapped operands; the K range is split over a cluster of 1, 2, 4 or 8 blocks so
+  // that about two blocks per SM stream the weights
+  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  const int row_tiles = (N + kTileRows - 1) / kTileRows;
+  int splits = 1;
+  if (splits_hint > 0) {
+    splits = splits_hint;
+  } else {
+    while (splits < 8 && row_tiles * splits * 2 <= 296 && num_kb / (splits * 2) >= 2) splits *= 2;
+  }
+  PTL_REQUIRE(splits == 1 || splits == 2 || splits == 4 || splits == 8, "gemm_tc: the K range splits 1, 2, 4 or 8 ways, not %d", splits);
+  const int kb_per = (num_kb + splits - 1) / splits;
+  p.swapped = 1; p.rows = N; p.cols = M; p.splits = splits; p.kb_per_split = kb_per;
+  int rc = make_map(&mr, W, N, K, kTileRows);
+  if (rc) return rc;
+  rc = make_map(&mc, X, M, K, bn);
+  if (rc) return rc;
+  dim3 grid(row_tiles, splits);
+  switch (bn) {
+    case 16: return launch_epi<16>(epi, mr, mc, p, grid, s);
+    case 32: return launch_epi<32>(epi, mr, mc, p, grid, s);
+    default: return launch_epi<64>(epi, mr, mc, p, grid, s);
+  }
+}

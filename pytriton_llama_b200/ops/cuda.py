@@ -61,6 +61,8 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_prefill_attention_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                _c_int, _c_int, _c_f, _c_int, _c_int, _ptr]
     lib.ptl_prefill_attention_bf16.restype = _c_int
+    lib.ptl_gemm_tc_bf16.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr]
+    lib.ptl_gemm_tc_bf16.restype = _c_int
     lib.ptl_argmax.argtypes = [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
     lib.ptl_argmax.restype = _c_int
     lib.ptl_sample.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
@@ -182,9 +184,81 @@ class CudaOps:
             out = self.empty((M, N), torch.float32)
             self._check(self.lib.ptl_gemm_simt_f32(_p(out), _p(x), _p(w), M, N, K, K, K, N, 0, self._stream()))
             return out
+        out = self.gemm_tc(x, w, self.EPI_F32 if out_dtype == torch.float32 else self.EPI_BF16)
+        if out is not None:
+            return out
+        # sizes the tensor-core kernel does not take (K no multiple of 8, or below 64): the library product
         if out_dtype == torch.float32:
             return torch.mm(x, w.t(), out_dtype=torch.float32)
         return torch.mm(x, w.t())
+
+    def linear_add(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor) -> Optional[torch.Tensor]:
+        """residual += x @ w^T in the product's epilogue (float32 residual, in place) and None; where
+        that is not possible the plain product, for the caller to add."""
+        if x.dtype == torch.bfloat16 and residual is not None:
+            if self.gemm_tc(x, w, self.EPI_ADD_F32, out=residual) is not None:
+                return None
+        return self.linear(x, w)
+
+    def fused_ffn_layout(self, dtype: torch.dtype, hidden: int, inter: int) -> bool:
+        """True if gate and up rows should alternate (gate_0, up_0, gate_1, ...) so that the
+        gate/up product can apply SiLU(gate)*up in its epilogue."""
+        return dtype == torch.bfloat16 and hidden % 8 == 0 and hidden >= 64
+
+    def gate_up_silu(self, x: torch.Tensor, w_alternating: torch.Tensor) -> torch.Tensor:
+        out = self.gemm_tc(x, w_alternating, self.EPI_SILU_MUL)
+        if out is None:
+            raise KernelError("gate_up_silu: sizes not taken; load the weights in the plain layout instead")
+        return out
+
+    # epilogues of the tensor-core product
+    EPI_BF16, EPI_F32, EPI_ADD_F32, EPI_SILU_MUL = 0, 1, 2, 3
+
+    def _tc_status_word(self):
+        if getattr(self, "_tc_status", None) is None:
+            self._tc_status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        return self._tc_status
+
+    def gemm_tc(self, x: torch.Tensor, w: torch.Tensor, epi: int = 0, out: Optional[torch.Tensor] = None,
+                splits: int = 0) -> Optional[torch.Tensor]:
+        """x[M,K] @ w[N,K]^T in bfloat16 on the tcgen05 tensor cores with a fused epilogue.
+        ``epi``: EPI_BF16 -> [M,N] bfloat16; EPI_F32 -> [M,N] float32; EPI_ADD_F32 adds into ``out``
+        (float32 [M,N], in place); EPI_SILU_MUL -> [M,N/2] bfloat16 for weights whose rows alternate
+        gate_j, up_j.  Returns None when the kernel does not take the sizes."""
+        self._want(x, "x", torch.bfloat16)
+        self._want(w, "w", torch.bfloat16)
+        M, K = x.shape
+        N = w.shape[0]
+        if w.shape[1] != K:
+            raise KernelError(f"gemm_tc: x is [{M},{K}] but w is {list(w.shape)}")
+        if K % 8 or K < 64:
+            return None
+        if epi == self.EPI_ADD_F32:
+            if out is None:
+                raise KernelError("gemm_tc: the add epilogue needs the float32 tensor to add into")
+            self._want(out, "out", torch.float32)
+            ld = N
+        elif epi == self.EPI_SILU_MUL:
+            out = self.empty((M, N // 2), torch.bfloat16)
+            ld = N // 2
+        else:
+            out = self.empty((M, N), torch.float32 if epi == self.EPI_F32 else torch.bfloat16)
+            ld = N
+        rc = self.lib.ptl_gemm_tc_bf16(_p(out), _p(x), _p(w), M, N, K, ld, epi, _p(self._tc_status_word()), splits,
+                                       self._stream())
+        if rc == -2:
+            return None
+        self._check(rc)
+        return out
+
+    def gemm_tc_status(self) -> int:
+        """0, or the code of the wait that gave up inside a tensor-core product since the last call (syncs)."""
+        if getattr(self, "_tc_status", None) is None:
+            return 0
+        code = int(self._tc_status.item())
+        if code:
+            self._tc_status.zero_()
+        return code
 
     def linear_simt(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """The CUDA-core product for any element type (checks of the tensor-core kernels)."""

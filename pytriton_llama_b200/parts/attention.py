@@ -62,7 +62,9 @@ class GQAttention(Part):
         return CacheNeed(kind="window" if self.window else "full", kv_heads=self.kv_heads,
                          head_dim=self.head_dim, window=self.window)
 
-    def forward(self, x, ctx, cache):
+    fuses_residual = True   # forward() may add its output into the residual itself and return None
+
+    def forward(self, x, ctx, cache, residual=None):
         ops = self.rt.ops
         qkv = ops.linear(x, self.w_qkv)
         inv_freq, rot = self.position.rotary_table()
@@ -75,4 +77,6 @@ class GQAttention(Part):
         o = ops.paged_attention(qkv, cache.kv, g.block_table, ctx.tok_req, ctx.positions, self.heads,
                                 self.kv_heads, self.head_dim, g.page_size, self.scale, window=self.window,
                                 splits=ctx.attn_splits, hints=ctx)
+        if residual is not None:
+            return ops.linear_add(o, self.w_o, residual)      # None when the product's epilogue did the add
         return ops.linear(o, self.w_o)

@@ -10,8 +10,9 @@ Contracts (``T`` = tokens of the step, all tensors on the runtime's device):
 
 * every part: ``tensor_specs() -> {local name: TensorSpec}``, ``load(tensors)`` with the same
   local names (tensors in the checkpoint's stored element type, on the CPU);
-* norm: ``forward(x, residual, rows=None) -> (y, residual)`` -- adds ``x`` ([T, H] or None) into
-  the float32 ``residual`` (None at the first layer), returns the normed sum in the compute type;
+* norm: ``forward(x, residual, rows=None) -> (y, residual)`` -- adds ``x`` ([T, H], or None when
+  the sub-layer before already added its output) into the float32 ``residual`` (None at the first
+  layer), returns the normed sum in the compute type;
 * position: ``rotary_table() -> (inv_freq float32 [rot/2], rot)`` or ``None`` when it is not a
   rotation of the (j, j + rot/2) pairs that the fused cache-write kernel can apply; and
   ``apply(qk, positions, heads, head_dim)`` for the general case (in place, [T, heads*head_dim]);
@@ -19,6 +20,8 @@ Contracts (``T`` = tokens of the step, all tensors on the runtime's device):
   step's ``StepContext`` and ``cache`` the ``LayerCacheView`` of the cache entry this run of the
   layer uses (``cache.write`` tells whether this run stores its keys and values);
 * ffn: ``forward(x) -> [T, H]``;
+* a mixer or ffn with the class attribute ``fuses_residual = True`` is called with
+  ``residual=<float32 [T, H]>`` as well and may add its output into it and return None;
 * block: ``forward(x, residual, ctx, cache) -> (x, residual)``.
 """
 from __future__ import annotations

@@ -28,7 +28,14 @@ class PreNormBlock(Part):
         return self.mixer.cache_need()
 
     def forward(self, x, residual, ctx, cache):
+        """``x`` may be None: the previous sub-layer then already added its output into ``residual``.
+        Mixers and feed-forwards that set ``fuses_residual`` get the residual and may do the same."""
         y, residual = self.norm1.forward(x, residual)
-        a = self.mixer.forward(y, ctx, cache)
+        if getattr(self.mixer, "fuses_residual", False):
+            a = self.mixer.forward(y, ctx, cache, residual=residual)
+        else:
+            a = self.mixer.forward(y, ctx, cache)
         y, residual = self.norm2.forward(a, residual)
+        if getattr(self.ffn, "fuses_residual", False):
+            return self.ffn.forward(y, residual=residual), residual
         return self.ffn.forward(y), residual

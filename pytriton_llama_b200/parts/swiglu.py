@@ -31,10 +31,27 @@ class SwiGLU(Part):
             "down": TensorSpec((self.hidden, self.inter)),
         }
 
+    fuses_residual = True   # forward() may add its output into the residual itself and return None
+
     def load(self, tensors) -> None:
-        self.w_gate_up = self._to_compute(torch.cat([tensors["gate"], tensors["up"]], dim=0))
+        ops = self.rt.ops
+        self.alternating = bool(ops is not None and hasattr(ops, "fused_ffn_layout")
+                                and ops.fused_ffn_layout(self.rt.dtype, self.hidden, self.inter))
+        if self.alternating:
+            # rows gate_0, up_0, gate_1, up_1, ...: each accumulator row/column pair of the product
+            # holds a gate and its up value, so the product's epilogue can apply SiLU(gate)*up
+            gu = torch.stack([tensors["gate"], tensors["up"]], dim=1).reshape(2 * self.inter, self.hidden)
+        else:
+            gu = torch.cat([tensors["gate"], tensors["up"]], dim=0)
+        self.w_gate_up = self._to_compute(gu)
         self.w_down = self._to_compute(tensors["down"])
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
         ops = self.rt.ops
-        return ops.linear(ops.silu_mul(ops.linear(x, self.w_gate_up)), self.w_down)
+        if self.alternating:
+            h = ops.gate_up_silu(x, self.w_gate_up)
+        else:
+            h = ops.silu_mul(ops.linear(x, self.w_gate_up))
+        if residual is not None:
+            return ops.linear_add(h, self.w_down, residual)   # None when the product's epilogue did the add
+        return ops.linear(h, self.w_down)

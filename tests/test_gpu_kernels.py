@@ -96,6 +96,42 @@ def test_linear_bfloat16(ops, M, N, K):
     assert (ops.linear_simt(x.cuda(), w.cuda(), out_dtype=torch.float32).double().cpu() - ref).abs().max() < 1e-4 * math.sqrt(K)
 
 
+@pytest.mark.parametrize("M, N, K", [
+    (128, 128, 64), (130, 264, 96), (200, 1000, 512), (300, 128, 4096), (1100, 768, 200),      # many tokens: 128-token tiles
+    (1, 304, 80), (8, 3072, 2048), (16, 2048, 2048), (17, 1000, 72), (33, 2048, 8192), (64, 1000, 512)])   # few: swapped, split K
+def test_tensor_core_product_and_its_epilogues(ops, M, N, K):
+    """The tcgen05/TMEM product against a float64 product: plain bfloat16 and float32 outputs, the
+    in-place add into a float32 residual, and SiLU(gate)*up on alternating weight rows."""
+    x, w = rnd((M, K), torch.bfloat16, 5), rnd((N, K), torch.bfloat16, 6, 0.5)
+    ref = x.double() @ w.double().T
+    scale = float(ref.abs().max())
+    out = ops.gemm_tc(x.cuda(), w.cuda(), ops.EPI_BF16)
+    assert out is not None and out.dtype == torch.bfloat16
+    assert (out.double().cpu() - ref).abs().max() <= 2 ** -8 * scale
+    out32 = ops.gemm_tc(x.cuda(), w.cuda(), ops.EPI_F32)
+    assert out32.dtype == torch.float32
+    assert (out32.double().cpu() - ref).abs().max() <= 2e-6 * math.sqrt(K) * scale / 10 + 1e-5
+    res = rnd((M, N), torch.float32, 7, 3.0)
+    acc = res.clone().cuda()
+    assert ops.gemm_tc(x.cuda(), w.cuda(), ops.EPI_ADD_F32, out=acc) is acc
+    assert (acc.double().cpu() - (ref + res.double())).abs().max() <= 2e-6 * math.sqrt(K) * scale / 10 + 1e-5
+    act = ops.gemm_tc(x.cuda(), w.cuda(), ops.EPI_SILU_MUL)
+    g, u = ref[:, 0::2], ref[:, 1::2]
+    want = g * torch.sigmoid(g) * u
+    assert act.shape == (M, N // 2)
+    assert (act.double().cpu() - want).abs().max() <= 2 ** -8 * float(want.abs().max())
+    assert ops.gemm_tc_status() == 0
+    # the same product twice gives the same bits (split partial sums are added in a fixed order)
+    assert torch.equal(ops.gemm_tc(x.cuda(), w.cuda(), ops.EPI_F32), out32)
+
+
+def test_tensor_core_product_leaves_other_sizes_to_the_library(ops):
+    x, w = rnd((4, 100), torch.bfloat16, 1), rnd((32, 100), torch.bfloat16, 2)    # K no multiple of 8
+    assert ops.gemm_tc(x.cuda(), w.cuda()) is None
+    assert ops.gemm_tc(x[:, :32].contiguous().cuda(), w[:, :32].contiguous().cuda()) is None   # K below one tile
+    close(ops.linear(x.cuda(), w.cuda()), x.double() @ w.double().T, "bfloat16")               # linear() still answers
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("rows, inter", [(3, 264), (2, 8192), (5, 101), (1, 24)])
 def test_silu_mul(ops, dtype, rows, inter):

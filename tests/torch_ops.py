@@ -46,6 +46,12 @@ class TorchOps:
 
     linear_simt = linear
 
+    def linear_add(self, x, w, residual):
+        return self.linear(x, w)          # never fused: the caller's norm adds it
+
+    def fused_ffn_layout(self, dtype, hidden, inter):
+        return False
+
     def silu_mul(self, gu):
         inter = gu.shape[1] // 2
         g, u = gu[:, :inter].float(), gu[:, inter:].float()
