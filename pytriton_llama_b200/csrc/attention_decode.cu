@@ -33,6 +33,8 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
                         int window, int splits, int num_pages) {
   using Cfg = DecodeCfg<D>;
   extern __shared__ __align__(128) unsigned char smem[];
+  pdl_wait();
+  pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
   const int split = blockIdx.x % splits;
@@ -227,11 +229,10 @@ int launch_decode(void* out, float* part_acc, float* part_ml, const void* q, con
   }
   const long long blocks = (long long)n_items * nkv * splits;
   PTL_REQUIRE(blocks <= 0x7fffffffLL, "decode_attention: too many blocks");
-  decode_attention_kernel<D><<<(unsigned)blocks, kDecWarps * 32, Cfg::kSmem, as_stream(stream)>>>(
-      (__nv_bfloat16*)out, part_acc, part_ml, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_table, items,
-      tok_req, positions, q_stride, out_stride, bt_stride, nq, nkv, page_size, scale * 1.4426950408889634f, window,
-      splits, num_pages);
-  int rc = check_launch("decode_attention");
+  int rc = launch_kernel("decode_attention", decode_attention_kernel<D>, dim3((unsigned)blocks), dim3(kDecWarps * 32),
+                         Cfg::kSmem, as_stream(stream), (__nv_bfloat16*)out, part_acc, part_ml, (const __nv_bfloat16*)q,
+                         (const __nv_bfloat16*)cache, block_table, items, tok_req, positions, q_stride, out_stride, bt_stride,
+                         nq, nkv, page_size, scale * 1.4426950408889634f, window, splits, num_pages);
   if (rc) return rc;
   if (splits > 1) rc = attention_merge_bf16(out, part_acc, part_ml, n_items, out_stride, nq, D, splits, items, stream);
   return rc;

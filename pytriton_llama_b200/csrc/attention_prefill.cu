@@ -32,6 +32,8 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
                          int nkv, int page_size, float scale_log2, int window, int num_pages) {
   using Cfg = PrefillCfg<D>;
   extern __shared__ __align__(128) unsigned char smem[];
+  pdl_wait();
+  pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
   const int* tl = tiles + 4 * blockIdx.x;
@@ -208,10 +210,10 @@ int launch_prefill(void* out, const void* q, const void* cache, const int* block
   }
   PTL_REQUIRE(nq <= 65535, "prefill_attention: at most 65535 query heads");
   dim3 grid(n_tiles, nq);
-  prefill_attention_kernel<D><<<grid, kPfWarps * 32, Cfg::kSmem, as_stream(stream)>>>(
-      (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_table, tiles, q_stride,
-      out_stride, bt_stride, nq, nkv, page_size, scale * 1.4426950408889634f, window, num_pages);
-  return check_launch("prefill_attention");
+  return launch_kernel("prefill_attention", prefill_attention_kernel<D>, grid, dim3(kPfWarps * 32), Cfg::kSmem,
+                       as_stream(stream), (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache,
+                       block_table, tiles, q_stride, out_stride, bt_stride, nq, nkv, page_size,
+                       scale * 1.4426950408889634f, window, num_pages);
 }
 
 }  // namespace ptl

@@ -24,6 +24,8 @@ paged_attention_simt_kernel(T* __restrict__ out, float* __restrict__ part_acc, f
                             int bt_stride, int nq, int nkv, int d, int page_size, float scale,
                             int window, int splits, int num_pages) {
   extern __shared__ float qs_all[];  // [warps][d] scaled query
+  pdl_wait();
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const int h = blockIdx.y * kWarpsPerBlock + warp;
@@ -120,37 +122,47 @@ __global__ void __launch_bounds__(kMergeWarps * 32)
 attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
                        const float* __restrict__ part_ml, int out_stride, int nq, int d,
                        int splits, const int* __restrict__ items, int n_rows) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pair = blockIdx.x * kMergeWarps + warp;       // (row, head) pair
   if (pair >= n_rows * nq) return;
   const int ti = pair / nq, h = pair % nq;
   const int t = items ? items[ti] : ti;
   const size_t idx0 = ((size_t)t * nq + h) * splits;
-  // lanes read the (max, sum) pairs of up to 32 splits at a time
+  // lane z holds the (max, sum) pair of split z, 32 splits at a time; the weights are then handed
+  // round by shuffles, so the loads of the partial accumulators below do not wait on one another
   float M = -INFINITY;
   for (int z = lane; z < splits; z += 32) M = fmaxf(M, part_ml[(idx0 + z) * 2]);
   M = warp_max(M);
   float L = 0.f;
-  for (int z = lane; z < splits; z += 32) {
-    const float mz = part_ml[(idx0 + z) * 2];
-    if (mz > -INFINITY) L += expf(mz - M) * part_ml[(idx0 + z) * 2 + 1];
-  }
-  L = warp_sum(L);
-  const float inv = L > 0.f ? 1.0f / L : 0.f;
   float acc[kMaxDimPerLane];
 #pragma unroll
   for (int i = 0; i < kMaxDimPerLane; ++i) acc[i] = 0.f;
-  for (int z = 0; z < splits; ++z) {
-    const float mz = part_ml[(idx0 + z) * 2];
-    if (!(mz > -INFINITY)) continue;                       // uniform over the warp
-    const float wz = expf(mz - M);
-    const float* pa = part_acc + (idx0 + z) * d;
+  for (int z0 = 0; z0 < splits; z0 += 32) {
+    const int z = z0 + lane;
+    float wz = 0.f;
+    if (z < splits) {
+      const float mz = part_ml[(idx0 + z) * 2];
+      if (mz > -INFINITY) {
+        wz = expf(mz - M);
+        L += wz * part_ml[(idx0 + z) * 2 + 1];
+      }
+    }
+    const int n = min(32, splits - z0);
+#pragma unroll 4
+    for (int j = 0; j < n; ++j) {
+      const float wj = __shfl_sync(0xffffffffu, wz, j);
+      const float* pa = part_acc + (idx0 + z0 + j) * d;      // an empty split wrote zeros here
 #pragma unroll
-    for (int i = 0; i < kMaxDimPerLane; ++i) {
-      const int dd = lane + 32 * i;
-      if (dd < d) acc[i] = fmaf(wz, pa[dd], acc[i]);
+      for (int i = 0; i < kMaxDimPerLane; ++i) {
+        const int dd = lane + 32 * i;
+        if (dd < d) acc[i] = fmaf(wj, pa[dd], acc[i]);
+      }
     }
   }
+  L = warp_sum(L);
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
   T* o = out + (size_t)t * out_stride + (size_t)h * d;
 #pragma unroll
   for (int i = 0; i < kMaxDimPerLane; ++i) {
@@ -174,16 +186,15 @@ int paged_attention_simt(void* out, const void* q, const void* cache, const int*
   if (tokens == 0) return 0;
   dim3 grid(tokens, (nq + kWarpsPerBlock - 1) / kWarpsPerBlock, splits);
   const size_t smem = (size_t)kWarpsPerBlock * d * sizeof(float);
-  paged_attention_simt_kernel<T><<<grid, kWarpsPerBlock * 32, smem, as_stream(stream)>>>(
-      (T*)out, part_acc, part_ml, (const T*)q, (const T*)cache, block_table, tok_req, positions,
-      q_stride, out_stride, bt_stride, nq, nkv, d, page_size, scale, window, splits, num_pages);
-  int rc = check_launch("paged_attention");
+  int rc = launch_kernel("paged_attention", paged_attention_simt_kernel<T>, grid, dim3(kWarpsPerBlock * 32), smem,
+                         as_stream(stream), (T*)out, part_acc, part_ml, (const T*)q, (const T*)cache, block_table, tok_req,
+                         positions, q_stride, out_stride, bt_stride, nq, nkv, d, page_size, scale, window, splits, num_pages);
   if (rc) return rc;
   if (splits > 1) {
     const long long pairs = (long long)tokens * nq;
-    attention_merge_kernel<T><<<(unsigned)((pairs + kMergeWarps - 1) / kMergeWarps), kMergeWarps * 32, 0, as_stream(stream)>>>(
-        (T*)out, part_acc, part_ml, out_stride, nq, d, splits, nullptr, tokens);
-    rc = check_launch("attention_merge");
+    rc = launch_kernel("attention_merge", attention_merge_kernel<T>, dim3((unsigned)((pairs + kMergeWarps - 1) / kMergeWarps)),
+                       dim3(kMergeWarps * 32), 0, as_stream(stream), (T*)out, (const float*)part_acc, (const float*)part_ml,
+                       out_stride, nq, d, splits, (const int*)nullptr, tokens);
   }
   return rc;
 }
@@ -192,9 +203,9 @@ int paged_attention_simt(void* out, const void* q, const void* cache, const int*
 int attention_merge_bf16(void* out, const float* part_acc, const float* part_ml, int tokens, int out_stride,
                          int nq, int d, int splits, const int* items, void* stream) {
   const long long pairs = (long long)tokens * nq;
-  attention_merge_kernel<__nv_bfloat16><<<(unsigned)((pairs + kMergeWarps - 1) / kMergeWarps), kMergeWarps * 32, 0, as_stream(stream)>>>(
-      (__nv_bfloat16*)out, part_acc, part_ml, out_stride, nq, d, splits, items, tokens);
-  return check_launch("attention_merge");
+  return launch_kernel("attention_merge", attention_merge_kernel<__nv_bfloat16>,
+                       dim3((unsigned)((pairs + kMergeWarps - 1) / kMergeWarps)), dim3(kMergeWarps * 32), 0, as_stream(stream),
+                       (__nv_bfloat16*)out, part_acc, part_ml, out_stride, nq, d, splits, items, tokens);
 }
 
 }  // namespace ptl

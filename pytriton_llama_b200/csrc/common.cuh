@@ -113,6 +113,40 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return scratch[32];
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Kernels of one step run back to back on one stream.  Launched with the attribute below, a kernel
+// may start while its predecessor is still running: its blocks get scheduled and do whatever does
+// not depend on earlier kernels (set-up, fetching weights), then `pdl_wait()` holds each thread
+// until every earlier kernel has finished and its writes are visible.  `pdl_launch_dependents()`
+// lets the successor start likewise.  Rule: no access to memory that another kernel of the step
+// writes, and no global write at all, before `pdl_wait()`.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline int& pdl_flag() {
+  static int enabled = 1;
+  return enabled;
+}
+
+// Launches `kernel` on `stream`, as a programmatic dependent of the kernel before it when enabled.
+template <typename... Params, typename... Args>
+inline int launch_kernel(const char* what, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                         cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_flag() ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+  if (e != cudaSuccess) return fail("%s: %s", what, cudaGetErrorString(e));
+  return check_launch(what);
+}
+
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -11,6 +11,8 @@ template <typename T>
 __global__ void embed_gather_kernel(T* __restrict__ out, const T* __restrict__ table,
                                     const int* __restrict__ ids, int hidden, int vocab,
                                     int vec_ok, int* __restrict__ status) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool bad = id < 0 || id >= vocab;
@@ -45,6 +47,8 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ residu
                                    int hidden, float eps, int vec_ok) {
   extern __shared__ float row[];
   __shared__ float red[33];
+  pdl_wait();
+  pdl_launch_dependents();
   const int m = blockIdx.x;
   const int r = rows ? rows[m] : m;
   const float* rin = residual_in ? residual_in + (size_t)r * hidden : nullptr;
@@ -107,6 +111,8 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ residu
 // gu is [T, 2*inter] (gate columns first); out[t, i] = g * sigmoid(g) * u in float32.
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, int vec_ok) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.y;
   const T* g = gu + (size_t)t * 2 * inter;
   const T* u = g + inter;
@@ -141,9 +147,8 @@ int embed_gather(void* out, const void* table, const int* ids, int tokens, int h
   if (tokens == 0) return 0;
   const int vec_ok = (hidden % Vec16<T>::N == 0) && aligned16(out) && aligned16(table);
   int threads = 128;
-  embed_gather_kernel<T><<<tokens, threads, 0, as_stream(stream)>>>(
-      (T*)out, (const T*)table, ids, hidden, vocab, vec_ok, status);
-  return check_launch("embed_gather");
+  return launch_kernel("embed_gather", embed_gather_kernel<T>, dim3(tokens), dim3(threads), 0, as_stream(stream),
+                       (T*)out, (const T*)table, ids, hidden, vocab, vec_ok, status);
 }
 
 template <typename T>
@@ -165,9 +170,8 @@ int add_rmsnorm(void* y, float* residual_out, const float* residual_in, const vo
   const int vec_ok = hidden % 4 == 0 && aligned16(y) && aligned16(w) && (!x || aligned16(x)) &&
                      (!residual_in || aligned16(residual_in)) && (!residual_out || aligned16(residual_out));
   int threads = hidden >= 8192 ? 1024 : (hidden >= 2048 ? 512 : (hidden >= 1024 ? 256 : 128));
-  add_rmsnorm_kernel<T><<<out_rows, threads, smem, as_stream(stream)>>>(
-      (T*)y, residual_out, residual_in, (const T*)x, w, rows, hidden, eps, vec_ok);
-  return check_launch("add_rmsnorm");
+  return launch_kernel("add_rmsnorm", add_rmsnorm_kernel<T>, dim3(out_rows), dim3(threads), smem, as_stream(stream),
+                       (T*)y, residual_out, residual_in, (const T*)x, w, rows, hidden, eps, vec_ok);
 }
 
 template <typename T>
@@ -179,8 +183,8 @@ int silu_mul(void* out, const void* gu, int tokens, int inter, void* stream) {
   const int vec_ok = (inter % VN == 0) && aligned16(out) && aligned16(gu);
   const int threads = 256;
   dim3 grid((inter + threads * VN - 1) / (threads * VN), tokens);
-  silu_mul_kernel<T><<<grid, threads, 0, as_stream(stream)>>>((T*)out, (const T*)gu, inter, vec_ok);
-  return check_launch("silu_mul");
+  return launch_kernel("silu_mul", silu_mul_kernel<T>, grid, dim3(threads), 0, as_stream(stream), (T*)out, (const T*)gu,
+                       inter, vec_ok);
 }
 
 }  // namespace ptl

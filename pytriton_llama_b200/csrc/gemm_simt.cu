@@ -11,6 +11,8 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_simt_kernel(TO* __restrict__ out, const TI* __restrict__ A, const TI* __restrict__ W,
                  int M, int N, int K, int lda, int ldw, int ldo, int accumulate) {
   constexpr int THREADS = (BM / TM) * (BN / TN);
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -76,15 +78,14 @@ int gemm_simt(void* out, const void* A, const void* W, int M, int N, int K, int 
     constexpr int BM = 128, BN = 64, BK = 16, TM = 8, TN = 4;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     PTL_REQUIRE(grid.y <= 65535, "gemm_simt: M=%d too large", M);
-    gemm_simt_kernel<TI, TO, BM, BN, BK, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, as_stream(stream)>>>(
-        (TO*)out, (const TI*)A, (const TI*)W, M, N, K, lda, ldw, ldo, accumulate);
+    return launch_kernel("gemm_simt", gemm_simt_kernel<TI, TO, BM, BN, BK, TM, TN>, grid, dim3((BM / TM) * (BN / TN)), 0,
+                         as_stream(stream), (TO*)out, (const TI*)A, (const TI*)W, M, N, K, lda, ldw, ldo, accumulate);
   } else {
     constexpr int BM = 32, BN = 64, BK = 32, TM = 2, TN = 4;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_simt_kernel<TI, TO, BM, BN, BK, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, as_stream(stream)>>>(
-        (TO*)out, (const TI*)A, (const TI*)W, M, N, K, lda, ldw, ldo, accumulate);
+    return launch_kernel("gemm_simt", gemm_simt_kernel<TI, TO, BM, BN, BK, TM, TN>, grid, dim3((BM / TM) * (BN / TN)), 0,
+                         as_stream(stream), (TO*)out, (const TI*)A, (const TI*)W, M, N, K, lda, ldw, ldo, accumulate);
   }
-  return check_launch("gemm_simt");
 }
 
 }  // namespace ptl

@@ -272,8 +272,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
 
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ TMA producer
+    // Weights do not depend on earlier kernels of the step: with swapped operands their tiles for
+    // the first ring of stages are requested before the wait on the predecessor, the tokens after.
     int issued = 0;
-    for (int i = 0; i < my_kb; ++i) {
+    int pre = 0;
+    if (p.swapped) {
+      pre = min(my_kb, Cfg::kStages);
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(full_bar(i), Cfg::kStageBytes);
+        tma_load_2d(smem_base + i * Cfg::kStageBytes, &map_row, full_bar(i), (kb0 + i) * kTileK, row_tile * kTileRows);
+      }
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int i = 0; i < pre; ++i)
+      tma_load_2d(smem_base + i * Cfg::kStageBytes + Cfg::kRowBytes, &map_col, full_bar(i), (kb0 + i) * kTileK, col_tile * BN);
+    issued = pre;
+    for (int i = pre; i < my_kb; ++i) {
       const int s = i % Cfg::kStages;
       const uint32_t ph = (i / Cfg::kStages) & 1;
       if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, 1)) break;
@@ -292,6 +307,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     }
   } else if (warp == 1 && lane == 0) {
     // ------------------------------------------------------------ MMA issuer
+    pdl_wait();
+    pdl_launch_dependents();
     constexpr uint32_t idesc = instr_desc_bf16(kTileRows, BN);
     bool ok = true;
     for (int i = 0; i < my_kb && ok; ++i) {
@@ -311,6 +328,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     tcgen05_commit(accum_bar);           // the accumulator is complete (also when there was nothing to do)
   } else if (warp >= 2) {
     // ------------------------------------------------------------ epilogue
+    pdl_wait();               // the epilogue reads and writes memory that earlier kernels touch
+    pdl_launch_dependents();
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
     const int row = row_tile * kTileRows + row_in_tile;
@@ -472,8 +491,13 @@ static int launch_tc(const CUtensorMap& mr, const CUtensorMap& mc, const GemmPar
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = Cfg::kSmem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   int nattr = 0;
+  if (pdl_flag()) {
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
   if (p.swapped && p.splits > 1) {
     attr[nattr].id = cudaLaunchAttributeClusterDimension;
     attr[nattr].val.clusterDim.x = 1;

@@ -17,6 +17,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      T* __restrict__ cache, int nq, int nkv, int d, int rot,
                                      int page_size, int write_cache, long long num_slots) {
   extern __shared__ float cs[];            // cos[rot/2], sin[rot/2] of this token's angles
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int row_len = (nq + 2 * nkv) * d;
   T* row = qkv + (size_t)t * row_len;
@@ -83,9 +85,9 @@ int rope_kv_write(void* qkv, const int* positions, const float* inv_freq, const 
   if (tokens == 0) return 0;
   const int work = (nq + nkv) * (d - rot / 2);
   const int threads = work >= 1024 ? 512 : (work >= 256 ? 256 : 128);
-  rope_kv_write_kernel<T><<<tokens, threads, (size_t)rot * sizeof(float), as_stream(stream)>>>(
-      (T*)qkv, positions, inv_freq, slots, (T*)cache, nq, nkv, d, rot, page_size, cache != nullptr, num_slots);
-  return check_launch("rope_kv_write");
+  return launch_kernel("rope_kv_write", rope_kv_write_kernel<T>, dim3(tokens), dim3(threads), (size_t)rot * sizeof(float),
+                       as_stream(stream), (T*)qkv, positions, inv_freq, slots, (T*)cache, nq, nkv, d, rot, page_size,
+                       (int)(cache != nullptr), num_slots);
 }
 
 }  // namespace ptl

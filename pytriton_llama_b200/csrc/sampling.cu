@@ -53,6 +53,8 @@ sample_kernel(int* __restrict__ tokens, const float* __restrict__ logits, float*
   __shared__ int si[33];
   __shared__ float red[33];
   __shared__ float chunk_sum[kSampleThreads];
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x;
   const float* x = logits + (size_t)row * ld;
   const int tid = threadIdx.x;
@@ -148,6 +150,8 @@ argmax_partial_kernel(float* __restrict__ part_val, int* __restrict__ part_idx, 
                       int vocab, long long ld) {
   __shared__ float sv[33];
   __shared__ int si[33];
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.y, chunk = blockIdx.x;
   const int per = (vocab + kArgmaxChunks - 1) / kArgmaxChunks;
   const int lo = chunk * per, hi = min(lo + per, vocab);
@@ -167,6 +171,8 @@ argmax_partial_kernel(float* __restrict__ part_val, int* __restrict__ part_idx, 
 
 __global__ void argmax_final_kernel(int* __restrict__ tokens, const float* __restrict__ part_val,
                                     const int* __restrict__ part_idx) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x, lane = threadIdx.x;
   float v = part_val[row * kArgmaxChunks + lane];
   int idx = part_idx[row * kArgmaxChunks + lane];
@@ -188,11 +194,11 @@ PTL_EXPORT int ptl_argmax(int* tokens, const float* logits, float* part_val, int
   PTL_REQUIRE(rows >= 0 && vocab > 0 && ld >= vocab && rows <= 65535, "argmax: bad sizes rows=%d vocab=%d", rows, vocab);
   if (rows == 0) return 0;
   dim3 grid(ptl::kArgmaxChunks, rows);
-  ptl::argmax_partial_kernel<<<grid, ptl::kArgmaxThreads, 0, ptl::as_stream(stream)>>>(part_val, part_idx, logits, vocab, ld);
-  int rc = ptl::check_launch("argmax_partial");
+  int rc = ptl::launch_kernel("argmax_partial", ptl::argmax_partial_kernel, grid, dim3(ptl::kArgmaxThreads), 0,
+                              ptl::as_stream(stream), part_val, part_idx, logits, vocab, ld);
   if (rc) return rc;
-  ptl::argmax_final_kernel<<<rows, 32, 0, ptl::as_stream(stream)>>>(tokens, part_val, part_idx);
-  return ptl::check_launch("argmax_final");
+  return ptl::launch_kernel("argmax_final", ptl::argmax_final_kernel, dim3(rows), dim3(32), 0, ptl::as_stream(stream), tokens,
+                            (const float*)part_val, (const int*)part_idx);
 }
 
 PTL_EXPORT int ptl_sample(int* tokens, const float* logits, float* probs, const float* temperature,
@@ -201,10 +207,12 @@ PTL_EXPORT int ptl_sample(int* tokens, const float* logits, float* probs, const 
   PTL_REQUIRE(rows >= 0 && vocab > 0 && ld >= vocab, "sample: bad sizes rows=%d vocab=%d ld=%lld", rows, vocab, ld);
   PTL_REQUIRE(temperature == nullptr || (probs && top_p && u), "sample: temperature sampling needs probs scratch, top_p and u");
   if (rows == 0) return 0;
-  ptl::sample_kernel<<<rows, ptl::kSampleThreads, 0, ptl::as_stream(stream)>>>(
-      tokens, logits, probs, temperature, top_p, u, vocab, ld);
-  return ptl::check_launch("sample");
+  return ptl::launch_kernel("sample", ptl::sample_kernel, dim3(rows), dim3(ptl::kSampleThreads), 0, ptl::as_stream(stream),
+                            tokens, logits, probs, temperature, top_p, u, vocab, ld);
 }
 
 PTL_EXPORT const char* ptl_last_error() { return ptl::error_buffer(); }
+// Switches programmatic dependent launch of the library's kernels on (default) or off.
+PTL_EXPORT void ptl_set_dependent_launch(int enabled) { ptl::pdl_flag() = enabled ? 1 : 0; }
+PTL_EXPORT int ptl_get_dependent_launch() { return ptl::pdl_flag(); }
 PTL_EXPORT int ptl_abi_version() { return 1; }

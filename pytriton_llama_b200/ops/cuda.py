@@ -10,6 +10,7 @@ or loaded, raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -68,6 +69,10 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_sample.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
     lib.ptl_sample.restype = _c_int
     lib.ptl_last_error.restype = ctypes.c_char_p
+    lib.ptl_set_dependent_launch.argtypes = [_c_int]
+    lib.ptl_get_dependent_launch.restype = _c_int
+    if os.environ.get("PTL_DEPENDENT_LAUNCH", "1") == "0":
+        lib.ptl_set_dependent_launch(0)
     _LIB = lib
     return lib
 
@@ -334,7 +339,7 @@ class CudaOps:
                     kernels=2 if splits > 1 else 1)
         return out
 
-    DECODE_BLOCKS = 592    # blocks the decode attention aims for: four per SM
+    DECODE_BLOCKS = 444    # blocks the decode attention aims for: the three per SM that fit at once
 
     def _attention_tensor_cores(self, out, q, cache, block_table, tok_req, positions, nq, nkv, d, page_size, scale,
                                 window, hints) -> None:
@@ -344,7 +349,7 @@ class CudaOps:
         num_pages = cache.shape[0]
         if hints.n_decode:
             longest = min(hints.max_ctx_len, window) if window else hints.max_ctx_len
-            splits = max(1, min(-(-self.DECODE_BLOCKS // (hints.n_decode * nkv)), -(-longest // 128)))
+            splits = max(1, min(self.DECODE_BLOCKS // (hints.n_decode * nkv), -(-longest // 128)))
             part_acc = part_ml = None
             if splits > 1:
                 part_acc = self.empty((q.shape[0], nq, splits, d), torch.float32)
