@@ -4,7 +4,8 @@
 // is a streaming read of the cache.  Four warps share 64-key tiles brought in by a ring of
 // cp.async stages (16 keys per warp and tile), keep their own running max / sum / accumulator in
 // float32 and are merged through shared memory at the end.  With splits > 1 the block writes an
-// unnormalised partial result that `attention_merge` (attention_simt.cu) combines.
+// unnormalised partial result; the block of a (token, kv head) that finishes last combines them
+// (or, without counters, the kernel `attention_merge` of attention_simt.cu does).
 //
 // The token list `items` names the tokens of the step that take this path (nullptr: tokens
 // 0..n-1).  Token t of request r = tok_req[t] at position p sees keys max(0, p-window+1)..p;
@@ -30,7 +31,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
                         const int* __restrict__ block_table, const int* __restrict__ items,
                         const int* __restrict__ tok_req, const int* __restrict__ positions, int q_stride,
                         int out_stride, int bt_stride, int nq, int nkv, int page_size, float scale_log2,
-                        int window, int splits, int num_pages) {
+                        int window, int splits, int num_pages, int page_shift, int* __restrict__ counters) {
   using Cfg = DecodeCfg<D>;
   extern __shared__ __align__(128) unsigned char smem[];
   pdl_wait();
@@ -69,22 +70,38 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     }
   }
 
-  // ---- loader: 64 keys x D of K and of V per tile, 16 bytes per cp.async, zero fill past the range
+  // ---- loader: 64 keys x D of K and of V per tile, 16 bytes per cp.async, zero fill past the range.
+  // Thread `tid` always copies chunk tid % kChunks of rows tid / kChunks + i * (128 / kChunks).
+  // When pages hold a power-of-two multiple of 16 keys and the range starts on a multiple of 16,
+  // each group of 16 consecutive rows lies in one page: one table entry per group, shifts instead
+  // of divisions.  Other page sizes take the general path.
+  constexpr int kRowsPerPass = kDecWarps * 32 / Cfg::kChunks;       // 16 for D = 64, 8 for D = 128
+  constexpr int kPasses = kDecKeys / kRowsPerPass;
+  const int my_row = tid / Cfg::kChunks, my_ch = tid % Cfg::kChunks;
+  const bool fast_pages = page_shift >= 4 && (k_begin & 15) == 0;
+  const size_t my_const = ((size_t)kvh * page_size) * D + my_ch * 8;
   auto load_tile = [&](int tile, int stage) {
     const uint32_t kbase = smem_base + stage * 2 * Cfg::kTileBytes;
     const uint32_t vbase = kbase + Cfg::kTileBytes;
+    const int k0 = k_begin + tile * kDecKeys;
 #pragma unroll
-    for (int i = 0; i < kDecKeys * Cfg::kChunks / (kDecWarps * 32); ++i) {
-      const int idx = tid + i * kDecWarps * 32;
-      const int row = idx / Cfg::kChunks, ch = idx % Cfg::kChunks;
-      const int key = k_begin + tile * kDecKeys + row;
+    for (int i = 0; i < kPasses; ++i) {
+      const int row = my_row + i * kRowsPerPass;
+      const int key = k0 + row;
       bool valid = key < k_end;
-      int page = valid ? bt[key / page_size] : 0;
+      int page, off;
+      if (fast_pages) {
+        page = valid ? bt[key >> page_shift] : 0;
+        off = key & (page_size - 1);
+      } else {
+        page = valid ? bt[key / page_size] : 0;
+        off = key % page_size;
+      }
       if (page < 0 || page >= num_pages) { valid = false; page = 0; }
-      const __nv_bfloat16* src = cache + ((size_t)page * 2) * plane + ((size_t)kvh * page_size + key % page_size) * D + ch * 8;
-      const uint32_t off = tile_offset<D>(row, ch);
-      cp_async_16(kbase + off, src, valid);
-      cp_async_16(vbase + off, src + plane, valid);
+      const __nv_bfloat16* src = cache + ((size_t)page * 2) * plane + (size_t)off * D + my_const;
+      const uint32_t dst = tile_offset<D>(row, my_ch);
+      cp_async_16(kbase + dst, src, valid);
+      cp_async_16(vbase + dst, src + plane, valid);
     }
   };
 
@@ -131,9 +148,10 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
       sv[1][e] = kk1 < k_end ? s1[e] * scale_log2 : -INFINITY;
     }
     // online softmax for rows g (e = 0,1) and g+8 (e = 2,3)
-    uint32_t pa[4];
+    uint32_t pa[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
+      if (h == 1 && G <= 8) break;          // rows 8..15 of the tile are padding for groups of up to 8 heads
       float mx = fmaxf(fmaxf(sv[0][2 * h], sv[0][2 * h + 1]), fmaxf(sv[1][2 * h], sv[1][2 * h + 1]));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
@@ -209,6 +227,76 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
       }
     }
   }
+  if (splits == 1 || counters == nullptr) return;   // one split is final; without counters a second kernel merges
+
+  // ---- the block that finishes last among the splits of this (token, kv head) merges them.
+  // Nobody waits: every block publishes its partial result, then takes a ticket.
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int ticket = atomicAdd(counters + (size_t)t * nkv + kvh, 1);
+    s_last = ticket == splits - 1;
+    if (s_last) counters[(size_t)t * nkv + kvh] = 0;          // ready for the next call
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // partial results of the group's heads are contiguous: [G][splits][D] and [G][splits][2]
+  const size_t idx0 = ((size_t)t * nq + (size_t)kvh * G) * splits;
+  float* w = reinterpret_cast<float*>(smem);                   // [G][splits] weights e^{m - M}
+  float* inv_l = w + G * splits;                               // [G]
+  float4* red = reinterpret_cast<float4*>(smem + (((size_t)(G * splits + 16) * 4 + 15) & ~(size_t)15));   // [z lanes][units of a pass]
+  for (int e = tid; e < G * splits; e += kDecWarps * 32) w[e] = __ldcg(part_ml + (idx0 + e) * 2);
+  __syncthreads();
+  if (tid < G) {
+    float M = -INFINITY;
+    for (int z = 0; z < splits; ++z) M = fmaxf(M, w[tid * splits + z]);
+    float L = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float mz = w[tid * splits + z];
+      const float wz = mz == -INFINITY ? 0.f : expf(mz - M);
+      L += wz * __ldcg(part_ml + (idx0 + tid * splits + z) * 2 + 1);
+      w[tid * splits + z] = wz;
+    }
+    inv_l[tid] = L > 0.f ? 1.0f / L : 0.f;
+  }
+  __syncthreads();
+  constexpr int kD4 = D / 4;
+  const int units = G * kD4;                                   // (head, 4 dimensions)
+  const int zlanes = units >= kDecWarps * 32 ? 1 : (kDecWarps * 32) / units;
+  const int per_pass = (kDecWarps * 32) / zlanes;
+  for (int u0 = 0; u0 < units; u0 += per_pass) {
+    const int ul = tid % per_pass, zl = tid / per_pass;
+    const int u = u0 + ul;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (u < units && zl < zlanes) {
+      const int gh = u / kD4, d4 = u % kD4;
+      const float4* src = reinterpret_cast<const float4*>(part_acc + (idx0 + (size_t)gh * splits) * D) + d4;
+#pragma unroll 8
+      for (int z = zl; z < splits; z += zlanes) {
+        const float wz = w[gh * splits + z];
+        const float4 v = __ldcg(src + (size_t)z * kD4);
+        a.x = fmaf(wz, v.x, a.x); a.y = fmaf(wz, v.y, a.y); a.z = fmaf(wz, v.z, a.z); a.w = fmaf(wz, v.w, a.w);
+      }
+    }
+    if (zl < zlanes) red[zl * per_pass + ul] = a;
+    __syncthreads();
+    if (zl == 0 && u < units) {
+      for (int z = 1; z < zlanes; ++z) {
+        const float4 b = red[z * per_pass + ul];
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+      }
+      const int gh = u / kD4, d4 = u % kD4;
+      const float il = inv_l[gh];
+      __nv_bfloat16* dst = out + (size_t)t * out_stride + (size_t)(kvh * G + gh) * D + d4 * 4;
+      uint2 pk;
+      pk.x = pack_bf16(a.x * il, a.y * il);
+      pk.y = pack_bf16(a.z * il, a.w * il);
+      *reinterpret_cast<uint2*>(dst) = pk;
+    }
+    __syncthreads();
+  }
 }
 
 // defined in attention_simt.cu
@@ -219,7 +307,7 @@ template <int D>
 int launch_decode(void* out, float* part_acc, float* part_ml, const void* q, const void* cache,
                   const int* block_table, const int* items, const int* tok_req, const int* positions, int n_items,
                   int q_stride, int out_stride, int bt_stride, int nq, int nkv, int page_size, float scale,
-                  int window, int splits, int num_pages, void* stream) {
+                  int window, int splits, int num_pages, int* counters, void* stream) {
   using Cfg = DecodeCfg<D>;
   static bool raised = false;
   if (!raised) {
@@ -227,36 +315,42 @@ int launch_decode(void* out, float* part_acc, float* part_ml, const void* q, con
     PTL_REQUIRE(e == cudaSuccess, "decode_attention: cannot raise shared memory: %s", cudaGetErrorString(e));
     raised = true;
   }
+  int page_shift = -1;                                   // log2(page_size) when it is a power of two
+  for (int b = 0; b < 20; ++b) if ((1 << b) == page_size) page_shift = b;
   const long long blocks = (long long)n_items * nkv * splits;
   PTL_REQUIRE(blocks <= 0x7fffffffLL, "decode_attention: too many blocks");
   int rc = launch_kernel("decode_attention", decode_attention_kernel<D>, dim3((unsigned)blocks), dim3(kDecWarps * 32),
                          Cfg::kSmem, as_stream(stream), (__nv_bfloat16*)out, part_acc, part_ml, (const __nv_bfloat16*)q,
                          (const __nv_bfloat16*)cache, block_table, items, tok_req, positions, q_stride, out_stride, bt_stride,
-                         nq, nkv, page_size, scale * 1.4426950408889634f, window, splits, num_pages);
+                         nq, nkv, page_size, scale * 1.4426950408889634f, window, splits, num_pages, page_shift, counters);
   if (rc) return rc;
-  if (splits > 1) rc = attention_merge_bf16(out, part_acc, part_ml, n_items, out_stride, nq, D, splits, items, stream);
+  if (splits > 1 && counters == nullptr)
+    rc = attention_merge_bf16(out, part_acc, part_ml, n_items, out_stride, nq, D, splits, items, stream);
   return rc;
 }
 
 }  // namespace ptl
 
 // Returns 0 on success; -2 if this kernel does not take the sizes (the caller then uses the
-// CUDA-core kernel); -1 on an error.
+// CUDA-core kernel); -1 on an error.  `counters` (one zeroed int per (token row, kv head), left
+// zeroed again) lets the last block of a token's splits merge them inside the kernel; with
+// nullptr a second kernel does the merge.  Splits are limited to 512 with counters.
 PTL_EXPORT int ptl_decode_attention_bf16(void* out, float* part_acc, float* part_ml, const void* q, const void* cache,
                                          const int* block_table, const int* items, const int* tok_req,
                                          const int* positions, int n_items, int q_stride, int out_stride,
                                          int bt_stride, int nq, int nkv, int d, int page_size, float scale, int window,
-                                         int splits, int num_pages, void* stream) {
+                                         int splits, int num_pages, int* counters, void* stream) {
   using namespace ptl;
   PTL_REQUIRE(n_items >= 0 && nq > 0 && nkv > 0 && page_size > 0 && num_pages > 0, "decode_attention: bad sizes");
   PTL_REQUIRE(nq % nkv == 0, "decode_attention: %d query heads are no multiple of %d kv heads", nq, nkv);
   if ((d != 64 && d != 128) || nq / nkv > 16) return -2;
   PTL_REQUIRE(splits >= 1 && (splits == 1 || (part_acc && part_ml)), "decode_attention: splits > 1 need scratch buffers");
+  PTL_REQUIRE(counters == nullptr || splits <= 512, "decode_attention: at most 512 splits with in-kernel merging");
   PTL_REQUIRE(aligned16(q) && aligned16(cache) && q_stride % 8 == 0, "decode_attention: q and cache must be 16-byte aligned");
   if (n_items == 0) return 0;
   if (d == 64)
     return launch_decode<64>(out, part_acc, part_ml, q, cache, block_table, items, tok_req, positions, n_items, q_stride,
-                             out_stride, bt_stride, nq, nkv, page_size, scale, window, splits, num_pages, stream);
+                             out_stride, bt_stride, nq, nkv, page_size, scale, window, splits, num_pages, counters, stream);
   return launch_decode<128>(out, part_acc, part_ml, q, cache, block_table, items, tok_req, positions, n_items, q_stride,
-                            out_stride, bt_stride, nq, nkv, page_size, scale, window, splits, num_pages, stream);
+                            out_stride, bt_stride, nq, nkv, page_size, scale, window, splits, num_pages, counters, stream);
 }

@@ -9,7 +9,7 @@ extern "C" int ptl_decode_attention_bf16(void* out, float* part_acc, float* part
                                          const int* block_table, const int* items, const int* tok_req,
                                          const int* positions, int n_items, int q_stride, int out_stride,
                                          int bt_stride, int nq, int nkv, int d, int page_size, float scale, int window,
-                                         int splits, int num_pages, void* stream);
+                                         int splits, int num_pages, int* counters, void* stream);
 
 namespace {
 
@@ -70,5 +70,5 @@ PTL_EXPORT int ptl_decode_attention_bf16_noalloc(void* out, const void* q, const
   }
   return ptl_decode_attention_bf16(out, part_acc, part_ml, q, cache, block_table, items, tok_req, positions, n_items,
                                    q_stride, out_stride, bt_stride, nq, nkv, d, page_size, scale, window, splits,
-                                   num_pages, stream);
+                                   num_pages, /*counters=*/nullptr, stream);
 }

@@ -288,6 +288,7 @@ class Engine:
                           fresh=layout.view(dev, "fresh"), groups=groups, q_lens=list(q_lens),
                           ctx_lens=list(ctx_lens), max_q_len=max(q_lens), max_ctx_len=max(ctx_lens),
                           attn_splits=splits, n_decode=n_decode, n_prefill_tiles=n_tiles,
+                          decode_in_order=(n_decode == layout.T),
                           decode_items=layout.view(dev, "dec_items")[:n_decode],
                           prefill_tiles=layout.view(dev, "pf_tiles"))
 

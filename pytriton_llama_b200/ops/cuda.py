@@ -57,7 +57,7 @@ def load_library() -> ctypes.CDLL:
         fn.argtypes = _GEMM_SIG
         fn.restype = _c_int
     lib.ptl_decode_attention_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int,
-                                              _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _ptr]
+                                              _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _ptr, _ptr]
     lib.ptl_decode_attention_bf16.restype = _c_int
     lib.ptl_prefill_attention_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                _c_int, _c_int, _c_f, _c_int, _c_int, _ptr]
@@ -339,7 +339,9 @@ class CudaOps:
                     kernels=2 if splits > 1 else 1)
         return out
 
-    DECODE_BLOCKS = 444    # blocks the decode attention aims for: the three per SM that fit at once
+    DECODE_BLOCKS = int(os.environ.get("PTL_DECODE_BLOCKS", "444"))    # blocks the decode attention aims for: the three per SM that fit at once
+
+    _DECODE_COUNTERS = 1 << 16
 
     def _attention_tensor_cores(self, out, q, cache, block_table, tok_req, positions, nq, nkv, d, page_size, scale,
                                 window, hints) -> None:
@@ -350,14 +352,21 @@ class CudaOps:
         if hints.n_decode:
             longest = min(hints.max_ctx_len, window) if window else hints.max_ctx_len
             splits = max(1, min(self.DECODE_BLOCKS // (hints.n_decode * nkv), -(-longest // 128)))
-            part_acc = part_ml = None
+            part_acc = part_ml = counters = None
             if splits > 1:
+                splits = min(splits, 512)
                 part_acc = self.empty((q.shape[0], nq, splits, d), torch.float32)
                 part_ml = self.empty((q.shape[0], nq, splits, 2), torch.float32)
+                if q.shape[0] * nkv <= self._DECODE_COUNTERS:
+                    if getattr(self, "_decode_counters", None) is None:
+                        self._decode_counters = torch.zeros(self._DECODE_COUNTERS, dtype=torch.int32, device=self.device)
+                    counters = self._decode_counters        # the last block of a token's splits merges them in the kernel
             self._check(self.lib.ptl_decode_attention_bf16(
-                _p(out), _p(part_acc), _p(part_ml), _p(q), _p(cache), _p(block_table), _p(hints.decode_items), _p(tok_req),
+                _p(out), _p(part_acc), _p(part_ml), _p(q), _p(cache), _p(block_table),
+                None if getattr(hints, "decode_in_order", False) else _p(hints.decode_items), _p(tok_req),
                 _p(positions), hints.n_decode, q.shape[1], nq * d, block_table.shape[1], nq, nkv, d, page_size,
-                float(scale), int(window), splits, num_pages, stream), kernels=2 if splits > 1 else 1)
+                float(scale), int(window), splits, num_pages, _p(counters), stream),
+                kernels=2 if splits > 1 and counters is None else 1)
         if hints.n_prefill_tiles:
             self._check(self.lib.ptl_prefill_attention_bf16(
                 _p(out), _p(q), _p(cache), _p(block_table), _p(hints.prefill_tiles), hints.n_prefill_tiles, q.shape[1],

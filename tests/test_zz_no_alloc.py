@@ -19,7 +19,7 @@ def _library():
     lib = ctypes.CDLL(str(build.library_path()))
     lib.ptl_decode_attention_bf16_noalloc.argtypes = [_ptr] * 7 + [_c_int] * 8 + [_c_f] + [_c_int] * 3 + [_ptr]
     lib.ptl_decode_attention_bf16_noalloc.restype = _c_int
-    lib.ptl_decode_attention_bf16.argtypes = [_ptr] * 9 + [_c_int] * 8 + [_c_f] + [_c_int] * 3 + [_ptr]
+    lib.ptl_decode_attention_bf16.argtypes = [_ptr] * 9 + [_c_int] * 8 + [_c_f] + [_c_int] * 3 + [_ptr, _ptr]
     lib.ptl_decode_attention_bf16.restype = _c_int
     lib.ptl_noalloc_scratch_bytes.restype = ctypes.c_ulonglong
     lib.ptl_last_error.restype = ctypes.c_char_p
@@ -53,7 +53,7 @@ def _run(lib, case, nq, nkv, d, page, splits, noalloc):
     else:
         acc = torch.empty((n, nq, splits, d), dtype=torch.float32, device="cuda")
         ml = torch.empty((n, nq, splits, 2), dtype=torch.float32, device="cuda")
-        rc = lib.ptl_decode_attention_bf16(out.data_ptr(), acc.data_ptr(), ml.data_ptr(), *common)
+        rc = lib.ptl_decode_attention_bf16(out.data_ptr(), acc.data_ptr(), ml.data_ptr(), *common[:-1], None, common[-1])
     assert rc == 0, lib.ptl_last_error().decode()
     torch.cuda.synchronize()
     return out.float().cpu()
