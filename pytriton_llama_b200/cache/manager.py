@@ -17,6 +17,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Tuple
 
+import numpy as np
 import torch
 
 from ..parts.base import CacheNeed
@@ -94,11 +95,45 @@ class CacheGroup:
         return 2 * n.kv_heads * n.head_dim * self.page_size * element_size * len(self.entries)
 
 
+class _Table:
+    """Block table of one request in one group: page of each block (-1: given back), kept in a
+    numpy array so that a step can copy it into its batch without a Python loop."""
+    __slots__ = ("pages", "n")
+
+    def __init__(self, capacity: int):
+        self.pages = np.full(capacity, -1, dtype=np.int32)
+        self.n = 0
+
+    def __len__(self) -> int:
+        return self.n
+
+    def __getitem__(self, i):
+        if isinstance(i, slice):
+            return self.pages[:self.n][i].tolist()
+        return int(self.pages[i])
+
+    def __setitem__(self, i: int, v: int) -> None:
+        self.pages[i] = v
+
+    def __iter__(self):
+        return iter(self.pages[:self.n].tolist())
+
+    def extend(self, pages: List[int]) -> None:
+        self.pages[self.n:self.n + len(pages)] = pages
+        self.n += len(pages)
+
+    def array(self) -> np.ndarray:
+        return self.pages[:self.n]
+
+    def held_below(self, block: int) -> int:
+        return int((self.pages[:min(block, self.n)] >= 0).sum()) if block > 0 else 0
+
+
 @dataclass
 class _Request:
     slot: int
     tokens: int = 0
-    tables: Dict[int, List[int]] = field(default_factory=dict)   # group -> page of each block (-1: given back)
+    tables: Dict[int, _Table] = field(default_factory=dict)   # group -> block table
 
 
 class CacheManager:
@@ -157,7 +192,12 @@ class CacheManager:
         return pool.free_pages if pool else 0
 
     def block_table(self, req: Hashable, group: int) -> List[int]:
-        return self._requests[req].tables.get(group, [])
+        t = self._requests[req].tables.get(group)
+        return [] if t is None else list(t)
+
+    def block_table_array(self, req: Hashable, group: int) -> np.ndarray:
+        """The same as an int32 array (a view: copy it before the next change of the request)."""
+        return self._requests[req].tables[group].array()
 
     def _first_needed_block(self, grp: CacheGroup, next_pos: int) -> int:
         """Blocks below this index hold no key that a query at ``next_pos`` or later can see."""
@@ -179,11 +219,10 @@ class CacheManager:
         for gi, grp in enumerate(self.groups):
             if not grp.paged:
                 continue
-            held = len(r.tables.get(gi, [])) if r else -(-have // self.page_size)
+            held = len(r.tables[gi]) if r else -(-have // self.page_size)
             need = total_blocks - held
-            if r is not None:
-                first = self._first_needed_block(grp, have)
-                need -= sum(1 for b in r.tables.get(gi, [])[:first] if b >= 0)
+            if r is not None and grp.need.kind == "window":
+                need -= r.tables[gi].held_below(self._first_needed_block(grp, have))
             out[gi] = need
         return out
 
@@ -207,7 +246,7 @@ class CacheManager:
         if not self._free_slots:
             raise OutOfSlots(f"all {self.max_requests} request slots are taken")
         slot = self._free_slots.pop()
-        self._requests[req] = _Request(slot=slot, tables={g: [] for g, grp in enumerate(self.groups) if grp.paged})
+        self._requests[req] = _Request(slot=slot, tables={g: _Table(self.max_blocks) for g, grp in enumerate(self.groups) if grp.paged})
         for grp in self.groups:
             for st in grp.state.values():
                 st[slot].zero_()
@@ -239,7 +278,12 @@ class CacheManager:
             total_blocks = -(-(r.tokens + new_tokens) // ps)
             if total_blocks > len(table):
                 table.extend(grp.pool.take(total_blocks - len(table)))
-            out[gi] = [table[p // ps] * ps + p % ps for p in range(r.tokens, r.tokens + new_tokens)]
+            if new_tokens == 1:
+                p = r.tokens
+                out[gi] = [table[p // ps] * ps + p % ps]
+            else:
+                pos = np.arange(r.tokens, r.tokens + new_tokens)
+                out[gi] = (table.pages[pos // ps].astype(np.int64) * ps + pos % ps).tolist()
         r.tokens += new_tokens
         return out
 

@@ -168,13 +168,15 @@ class Engine:
         return min(cap, fit)
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry]) -> StepOutput:
+    def step(self, entries: Sequence[StepEntry], validate: bool = True) -> StepOutput:
+        """``validate=False`` skips the checks of tokens, wanted places and free pages for callers
+        that made them already (the scheduler's plans)."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return StepOutput(None, [], 0)
         cache = self.cache
         seen = set()
-        for e in entries:
+        for e in entries if validate else ():
             if e.request in seen:
                 raise ValueError(f"request {e.request!r} appears twice in one step")
             seen.add(e.request)
@@ -187,7 +189,7 @@ class Engine:
             have = cache.tokens_of(e.request) if cache.has(e.request) else 0
             if have + len(e.tokens) > self.config.max_seq_len:
                 raise ValueError(f"request {e.request!r} would reach {have + len(e.tokens)} tokens; max_seq_len is {self.config.max_seq_len}")
-        if not cache.can_append([(e.request, len(e.tokens)) for e in entries]):
+        if validate and not cache.can_append([(e.request, len(e.tokens)) for e in entries]):
             raise OutOfPages("the cache cannot hold this step's tokens")
 
         q_lens = [len(e.tokens) for e in entries]
@@ -235,7 +237,7 @@ class Engine:
         return [g for g, grp in enumerate(self.cache.groups) if grp.paged]
 
     def _table_width(self, batch: "_HostBatch") -> int:
-        widths = [len(self.cache.block_table(e.request, g)) for g in self._paged_groups() for e in batch.entries]
+        widths = [len(self.cache.block_table_array(e.request, g)) for g in self._paged_groups() for e in batch.entries]
         return _pad4(max([1] + widths))
 
     def _fill(self, h: np.ndarray, layout: "_Layout", b: "_HostBatch") -> None:
@@ -273,7 +275,7 @@ class Engine:
             bt = h[lo:lo + n].reshape(layout.R, layout.bt_width)
             bt.fill(-1)
             for i, e in enumerate(b.entries):
-                t = self.cache.block_table(e.request, g)
+                t = self.cache.block_table_array(e.request, g)
                 bt[i, :len(t)] = t
 
     def _context(self, dev: torch.Tensor, layout: "_Layout", q_lens, ctx_lens, splits: int, n_decode: int, n_tiles: int):

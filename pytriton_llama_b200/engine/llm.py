@@ -37,7 +37,11 @@ class LLM:
         if request_id is None:
             request_id = f"req-{self._next_id}"
             self._next_id += 1
-        return self.scheduler.add(request_id, list(prompt), params)
+        prompt = [int(t) for t in prompt]
+        vocab = self.engine.vocab_size
+        if any(t < 0 or t >= vocab for t in prompt):
+            raise ValueError(f"the prompt has a token outside the vocabulary of {vocab}")
+        return self.scheduler.add(request_id, prompt, params)
 
     def has_work(self) -> bool:
         return self.scheduler.has_work()
@@ -52,9 +56,9 @@ class LLM:
             return {}, finished
         entries = []
         for p in plan.portions:
-            toks = p.request.all_tokens[p.start:p.start + p.length]
+            toks = p.request.tokens(p.start, p.length)
             entries.append(StepEntry(p.request.id, toks, [p.length - 1] if p.sample else []))
-        out = self.engine.step(entries)
+        out = self.engine.step(entries, validate=False)   # the plan was checked against the cache; tokens at intake
         sampled: Dict[Hashable, int] = {}
         if out.rows:
             reqs = [p.request for p in plan.portions if p.sample]

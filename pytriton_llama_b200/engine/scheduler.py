@@ -42,6 +42,15 @@ class Request:
     def pending(self) -> int:
         return len(self.prompt) + len(self.output) - self.computed
 
+    def tokens(self, start: int, length: int) -> List[int]:
+        """``all_tokens[start:start + length]`` without joining the two lists."""
+        n = len(self.prompt)
+        if start >= n:
+            return self.output[start - n:start - n + length]
+        if start + length <= n:
+            return self.prompt[start:start + length]
+        return self.prompt[start:] + self.output[:start + length - n]
+
 
 @dataclass
 class Portion:
@@ -95,8 +104,15 @@ class Scheduler:
         return bool(self.waiting or self.running)
 
     # ------------------------------------------------------------------ planning
-    def _pages_short(self, asks) -> bool:
-        return not self.cache.can_append(asks)
+    def _needs(self, req: Request, n: int):
+        """(pages per group, slots) that ``n`` more tokens of ``req`` take."""
+        live = self.cache.has(req.id)
+        return self.cache.pages_needed(req.id if live else None, n), 0 if live else 1
+
+    def _fits(self, needs, slots, reserved, reserved_slots) -> bool:
+        if slots + reserved_slots > self.cache.free_slots():
+            return False
+        return all(k + reserved.get(g, 0) <= self.cache.free_pages(g) for g, k in needs.items())
 
     def _fits_empty_cache(self, req: Request, n_tokens: int) -> bool:
         blocks = -(-n_tokens // self.cache.page_size)
@@ -118,7 +134,19 @@ class Scheduler:
     def schedule(self) -> StepPlan:
         plan = StepPlan()
         budget = self.max_batched_tokens
-        asks = []          # (request id, tokens) accepted so far, for the joint page check
+        reserved: Dict[int, int] = {}      # pages per group promised to portions accepted so far
+        reserved_slots = 0
+        accepted: Dict[Hashable, tuple] = {}   # request id -> (needs, slots) it reserved
+
+        def accept(req, n, needs, slots):
+            nonlocal budget, reserved_slots
+            plan.portions.append(Portion(req, req.computed, n, sample=(n == req.pending)))
+            for g, k in needs.items():
+                reserved[g] = reserved.get(g, 0) + k
+            reserved_slots += slots
+            accepted[req.id] = (needs, slots)
+            budget -= n
+
         # 1. running requests, oldest first: one token when decoding, else the next prompt portion
         for req in list(self.running):
             if req not in self.running:
@@ -126,14 +154,16 @@ class Scheduler:
             if budget <= 0:
                 break
             n = min(req.pending, budget, self.max_portion)
-            while self._pages_short(asks + [(req.id, n)]):
+            needs, slots = self._needs(req, n)
+            while not self._fits(needs, slots, reserved, reserved_slots):
                 victim = self.running[-1]
                 if victim is req:
                     # nothing younger to evict: shrink the portion, else give up this request
                     if n > 1:
                         n = max(1, n // 2)
+                        needs, slots = self._needs(req, n)
                         continue
-                    if len(self.running) == 1 and not asks:
+                    if len(self.running) == 1 and not accepted:
                         self.running.remove(req)
                         self.cache.release(req.id)
                         req.status, req.finish_reason = FINISHED, "cache_too_small"
@@ -142,15 +172,11 @@ class Scheduler:
                         self._preempt(req, plan)
                     n = 0
                     break
-                # a younger request gives way; drop anything already planned for it
-                plan.portions = [p for p in plan.portions if p.request is not victim]
-                asks = [(r, k) for r, k in asks if r != victim.id]
+                # a younger request gives way (it has nothing planned yet: older ones come first)
                 self._preempt(victim, plan)
             if n <= 0:
                 continue
-            plan.portions.append(Portion(req, req.computed, n, sample=(n == req.pending)))
-            asks.append((req.id, n))
-            budget -= n
+            accept(req, n, needs, slots)
         # 2. admissions, first come first served, not in a step that had to pre-empt
         while self.waiting and not plan.preempted and budget > 0 and len(self.running) < self.max_num_seqs:
             req = self.waiting[0]
@@ -161,14 +187,13 @@ class Scheduler:
                 plan.finished.append(req)
                 continue
             n = min(req.pending, budget, self.max_portion)
-            if self._pages_short(asks + [(req.id, n)]):
+            needs, slots = self._needs(req, n)
+            if not self._fits(needs, slots, reserved, reserved_slots):
                 break
             self.waiting.popleft()
             req.status = RUNNING
             self.running.append(req)
-            plan.portions.append(Portion(req, req.computed, n, sample=(n == req.pending)))
-            asks.append((req.id, n))
-            budget -= n
+            accept(req, n, needs, slots)
         return plan
 
     # ------------------------------------------------------------------ after the step
