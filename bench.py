@@ -117,6 +117,7 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill measurement (profiling runs)")
+    ap.add_argument("--only-prefill", action="store_true", help="measure the prefill only and print its numbers (profiling runs)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -185,6 +186,10 @@ def main() -> int:
     prefill_flops = 2 * matmul_params * PREFILL_TOKENS + attn_flops + 2 * head_params
     prefill = {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3),
                "frac": round(prefill_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+
+    if args.only_prefill:
+        print(json.dumps({"prefill": prefill}))
+        return 0
 
     # ------------------------------------------------------------------ decode, device-timed
     def decode_run(batch, steps, warmup, sample_clocks=False):
