@@ -16,9 +16,10 @@ namespace ptl {
 
 constexpr int kDecKeys = 64;      // keys per tile
 constexpr int kDecWarps = 4;
+constexpr int kDecStagedPages = 1024;   // block-table entries of a block's key range kept in shared memory
 
 template <int D> struct DecodeCfg {
-  static constexpr int kStages = D <= 64 ? 4 : 3;
+  static constexpr int kStages = 3;                            // 48 KB (D = 64): four blocks per SM
   static constexpr int kChunks = D / 8;                       // 16-byte chunks per row
   static constexpr int kTileBytes = kDecKeys * D * 2;          // one of K / V
   static constexpr int kSmem = kStages * 2 * kTileBytes;
@@ -52,9 +53,21 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   const int k_begin = lo + split * chunk_keys;
   const int k_end = r < 0 ? k_begin : min(k_begin + chunk_keys, p + 1);
   const int ntiles = k_end > k_begin ? (k_end - k_begin + kDecKeys - 1) / kDecKeys : 0;
-  const int* bt = block_table + (size_t)(r < 0 ? 0 : r) * bt_stride;
+  const int* bt_global = block_table + (size_t)(r < 0 ? 0 : r) * bt_stride;
   const size_t plane = (size_t)nkv * page_size * D;
   const uint32_t smem_base = smem_u32(smem);
+
+  // ---- the block-table entries of this block's key range go to shared memory once (when they
+  // fit), so that the copies of a tile never wait on a global load for their page
+  __shared__ int s_pages[kDecStagedPages];
+  const int first_block = ntiles > 0 ? k_begin / page_size : 0;
+  const int n_blocks = ntiles > 0 ? (k_end - 1) / page_size - first_block + 1 : 0;
+  const bool staged = n_blocks <= kDecStagedPages;
+  if (staged) {
+    for (int i = tid; i < n_blocks; i += kDecWarps * 32) s_pages[i] = bt_global[first_block + i];
+    __syncthreads();
+  }
+  const int* bt = staged ? s_pages - first_block : bt_global;
 
   // ---- query fragments: row g (and g+8) of the tile is query head kvh*G + g (zero beyond the group)
   uint32_t qa[D / 16][4];

@@ -339,7 +339,7 @@ class CudaOps:
                     kernels=2 if splits > 1 else 1)
         return out
 
-    DECODE_BLOCKS = int(os.environ.get("PTL_DECODE_BLOCKS", "444"))    # blocks the decode attention aims for: the three per SM that fit at once
+    DECODE_BLOCKS = int(os.environ.get("PTL_DECODE_BLOCKS", "592"))    # blocks the decode attention aims for: the four per SM that fit at once
 
     _DECODE_COUNTERS = 1 << 16
 
