@@ -16,8 +16,10 @@
 // Epilogues: 0 store bfloat16, 1 store float32, 2 add into a float32 residual [M,N] in place,
 // 3 SiLU(gate)*up where the rows of W alternate gate_j, up_j (out is [M, N/2] bfloat16).
 //
-// Warp roles (192 threads): warp 0 TMA producer, warp 1 TMEM allocation + MMA issue, warps 2..5
-// epilogue (warp w reads TMEM lanes 32*(w%4)..+31).  Every wait on an mbarrier gives up after a
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 TMEM allocation + MMA issue, warps 2..9
+// epilogue (warp w reads TMEM lanes 32*(w%4)..+31; with many tokens two warps share a lane quarter
+// and take half of the columns each).  With many tokens a block walks several tiles and keeps two
+// accumulators in TMEM, so the epilogue of one tile runs under the MMAs of the next.  Every wait on an mbarrier gives up after a
 // bounded number of polls, records a code in *status, and the block drains and frees its TMEM.
 #include <cuda.h>
 #include <mutex>
@@ -28,7 +30,7 @@ namespace ptl {
 
 constexpr int kTileRows = 128;     // rows of the row operand per block (MMA M)
 constexpr int kTileK = 64;         // K per stage: 64 bfloat16 = one 128-byte swizzle row
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, eight epilogue warps (two per TMEM lane quarter)
 constexpr uint32_t kPollLimit = 1u << 22;
 
 struct GemmParams {
@@ -41,6 +43,8 @@ struct GemmParams {
   int swapped;
   int splits;
   int kb_per_split;
+  int tiles_m;           // normal mode: tiles along the tokens and along the features
+  int tiles_n;
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -51,6 +55,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -91,6 +98,15 @@ __device__ __forceinline__ void tmem_load_16(uint32_t taddr, uint32_t (&r)[16]) 
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -124,11 +140,14 @@ template <int BN> struct TcCfg {
   static constexpr int kRowBytes = kTileRows * kTileK * 2;     // 16 KB
   static constexpr int kColBytes = BN * kTileK * 2;
   static constexpr int kStageBytes = kRowBytes + kColBytes;
-  static constexpr int kTmemCols = BN < 32 ? 32 : BN;          // power of two >= 32
+  static constexpr int kAccBufs = BN >= 128 ? 2 : 1;           // many tokens: the epilogue of a tile overlaps the next tile's MMAs
+  static constexpr int kTmemCols = BN < 32 ? 32 : BN * kAccBufs;   // power of two >= 32
   static constexpr int kSmem = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
-__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+// SiLU for the bfloat16 path: the result is rounded to 8 bits of mantissa, so the fast
+// exponential and reciprocal (about 2 ulp of float32) cost no accuracy that survives.
+__device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
 // ---------------------------------------------------------------- epilogue of one row's 16 accumulators
 // Normal mode: `row` is a token, columns c0..c0+15 are features.
@@ -232,17 +251,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
   // tiles need 1024-byte alignment for the 128-byte swizzle pattern to start at row 0
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
-  // bars[0..S-1] full, bars[S..2S-1] empty, bars[2S] accumulator ready
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::kStages + 1);
+  // bars: [0,S) stage full, [S,2S) stage empty, then accumulator full[2], accumulator empty[2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
-  volatile int* ok_flags = reinterpret_cast<volatile int*>(tmem_slot + 3);   // one per epilogue warp
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row_tile = p.swapped ? blockIdx.x : blockIdx.y;
-  const int col_tile = p.swapped ? 0 : blockIdx.x;
-  const int split = p.swapped ? blockIdx.y : 0;
   const int num_kb = (p.K + kTileK - 1) / kTileK;
+  // swapped mode: one tile per block (blockIdx.x = row tile, blockIdx.y = K split);
+  // normal mode: the block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (token tiles fastest)
+  const int total_tiles = p.swapped ? 1 : p.tiles_m * p.tiles_n;
+  const int first_tile = p.swapped ? 0 : blockIdx.x;
+  const int tile_step = p.swapped ? 1 : gridDim.x;
+  const int split = p.swapped ? blockIdx.y : 0;
   const int kb0 = split * p.kb_per_split;
   const int kb1 = min(num_kb, kb0 + p.kb_per_split);
   const int my_kb = max(0, kb1 - kb0);
@@ -250,13 +270,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
   const uint32_t bar_base = smem_addr(bars);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
-  const uint32_t accum_bar = bar_base + 8u * (2 * Cfg::kStages);
+  auto acc_full = [&](int b) { return bar_base + 8u * (2 * Cfg::kStages + b); };
+  auto acc_empty = [&](int b) { return bar_base + 8u * (2 * Cfg::kStages + 2 + b); };
+  auto tile_rows_cols = [&](int tile, int& row_tile, int& col_tile) {
+    if (p.swapped) { row_tile = blockIdx.x; col_tile = 0; }
+    else { row_tile = tile % p.tiles_m; col_tile = tile / p.tiles_m; }
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 8); }
     *abort_flag = 0;
-    *last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_row) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_col) : "memory");
@@ -274,33 +298,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     // ------------------------------------------------------------ TMA producer
     // Weights do not depend on earlier kernels of the step: with swapped operands their tiles for
     // the first ring of stages are requested before the wait on the predecessor, the tokens after.
-    int issued = 0;
+    int it = 0;          // stage uses so far, over all tiles of this block
     int pre = 0;
     if (p.swapped) {
       pre = min(my_kb, Cfg::kStages);
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(full_bar(i), Cfg::kStageBytes);
-        tma_load_2d(smem_base + i * Cfg::kStageBytes, &map_row, full_bar(i), (kb0 + i) * kTileK, row_tile * kTileRows);
+        tma_load_2d(smem_base + i * Cfg::kStageBytes, &map_row, full_bar(i), (kb0 + i) * kTileK, blockIdx.x * kTileRows);
       }
     }
     pdl_wait();
     pdl_launch_dependents();
     for (int i = 0; i < pre; ++i)
-      tma_load_2d(smem_base + i * Cfg::kStageBytes + Cfg::kRowBytes, &map_col, full_bar(i), (kb0 + i) * kTileK, col_tile * BN);
-    issued = pre;
-    for (int i = pre; i < my_kb; ++i) {
-      const int s = i % Cfg::kStages;
-      const uint32_t ph = (i / Cfg::kStages) & 1;
-      if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, 1)) break;
-      mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
-      const uint32_t dst = smem_base + s * Cfg::kStageBytes;
-      tma_load_2d(dst, &map_row, full_bar(s), (kb0 + i) * kTileK, row_tile * kTileRows);
-      tma_load_2d(dst + Cfg::kRowBytes, &map_col, full_bar(s), (kb0 + i) * kTileK, col_tile * BN);
-      issued = i + 1;
+      tma_load_2d(smem_base + i * Cfg::kStageBytes + Cfg::kRowBytes, &map_col, full_bar(i), (kb0 + i) * kTileK, 0);
+    it = pre;
+    bool ok = true;
+    for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
+      int row_tile, col_tile;
+      tile_rows_cols(tile, row_tile, col_tile);
+      for (int i = (tile == first_tile ? pre : 0); i < my_kb; ++i, ++it) {
+        const int s = it % Cfg::kStages;
+        const uint32_t ph = (it / Cfg::kStages) & 1;
+        if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+        mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
+        const uint32_t dst = smem_base + s * Cfg::kStageBytes;
+        tma_load_2d(dst, &map_row, full_bar(s), (kb0 + i) * kTileK, row_tile * kTileRows);
+        tma_load_2d(dst + Cfg::kRowBytes, &map_col, full_bar(s), (kb0 + i) * kTileK, col_tile * BN);
+      }
     }
     if (*abort_flag) {
-      // leave no copy in flight behind: wait (bounded) for the stages that were requested
-      for (int i = max(0, issued - Cfg::kStages); i < issued; ++i) {
+      // leave no copy in flight behind: wait (bounded) for the stages that were requested last
+      for (int i = max(0, it - Cfg::kStages); i < it; ++i) {
         const int s = i % Cfg::kStages;
         for (uint32_t t = 0; t < (1u << 16) && !mbar_try_wait(full_bar(s), (i / Cfg::kStages) & 1); ++t) __nanosleep(100);
       }
@@ -310,51 +338,97 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     pdl_wait();
     pdl_launch_dependents();
     constexpr uint32_t idesc = instr_desc_bf16(kTileRows, BN);
+    int it = 0;
     bool ok = true;
-    for (int i = 0; i < my_kb && ok; ++i) {
-      const int s = i % Cfg::kStages;
-      const uint32_t ph = (i / Cfg::kStages) & 1;
-      ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 2);
+    int lt = 0;          // tiles of this block so far
+    for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++lt) {
+      const int buf = Cfg::kAccBufs == 2 ? (lt & 1) : 0;
+      const int use = Cfg::kAccBufs == 2 ? (lt >> 1) : lt;            // how often this buffer was used before
+      ok = mbar_wait(acc_empty(buf), (use & 1) ^ 1, abort_flag, p.status, 4);    // the epilogue has drained it
       if (!ok) break;
       tcgen05_fence_after();
-      const uint32_t a = smem_base + s * Cfg::kStageBytes;
-      const uint32_t b = a + Cfg::kRowBytes;
+      const uint32_t acc = tmem_base + buf * BN;
+      for (int i = 0; i < my_kb; ++i, ++it) {
+        const int s = it % Cfg::kStages;
+        const uint32_t ph = (it / Cfg::kStages) & 1;
+        ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 2);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t a = smem_base + s * Cfg::kStageBytes;
+        const uint32_t b = a + Cfg::kRowBytes;
 #pragma unroll
-      for (int k = 0; k < kTileK / 16; ++k) {
-        tcgen05_mma_bf16(tmem_base, smem_desc_sw128(a + k * 32), smem_desc_sw128(b + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < kTileK / 16; ++k) {
+          tcgen05_mma_bf16(acc, smem_desc_sw128(a + k * 32), smem_desc_sw128(b + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        tcgen05_commit(empty_bar(s));      // the stage is free once these MMAs have read it
       }
-      tcgen05_commit(empty_bar(s));      // the stage is free once these MMAs have read it
+      tcgen05_commit(acc_full(buf));       // the accumulator is complete (also when there was nothing to do)
     }
-    tcgen05_commit(accum_bar);           // the accumulator is complete (also when there was nothing to do)
   } else if (warp >= 2) {
     // ------------------------------------------------------------ epilogue
     pdl_wait();               // the epilogue reads and writes memory that earlier kernels touch
     pdl_launch_dependents();
-    const int quad = warp & 3;
+    const int quad = warp & 3;                 // TMEM lanes 32*quad.. belong to this warp
+    const int half = (warp - 2) >> 2;          // with many tokens, which half of the tile's columns it handles
     const int row_in_tile = quad * 32 + lane;
-    const int row = row_tile * kTileRows + row_in_tile;
-    const bool mine = mbar_wait(accum_bar, 0, abort_flag, p.status, 3);
-    tcgen05_fence_after();
-    // the four warps go on together or not at all (they meet at named barriers below)
-    if (lane == 0) ok_flags[quad] = mine ? 1 : 0;
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    const bool ok = ok_flags[0] && ok_flags[1] && ok_flags[2] && ok_flags[3];
-    if (ok) {
+    int lt = 0;
+    for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++lt) {
+      int row_tile, col_tile;
+      tile_rows_cols(tile, row_tile, col_tile);
+      const int buf = Cfg::kAccBufs == 2 ? (lt & 1) : 0;
+      const int use = Cfg::kAccBufs == 2 ? (lt >> 1) : lt;
+      const int row = row_tile * kTileRows + row_in_tile;
+      // the add epilogue fetches what it adds to ahead of time: 32 columns before the accumulator
+      // is even complete, then the next 32 while the current ones are being written
+      constexpr int kHalfCols = BN / 2 >= 32 ? BN / 2 : 32;
+      float4 ahead[8];
+      const bool can_prefetch = EPI == 2 && !p.swapped && row < p.rows && p.ld_out % 4 == 0 && p.cols % 32 == 0;
+      auto prefetch = [&](int c0) {
+        const float4* src = reinterpret_cast<const float4*>((const float*)p.out + (size_t)row * p.ld_out + col_tile * BN + c0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ahead[j] = col_tile * BN + c0 + 4 * j < p.cols ? __ldcg(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+      };
+      if (can_prefetch) prefetch(half * kHalfCols);
+      if (!mbar_wait(acc_full(buf), use & 1, abort_flag, p.status, 3)) break;
+      tcgen05_fence_after();
+      const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
       if (!p.swapped) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 16) {
-          uint32_t r[16];
-          tmem_load_16(tmem_base + ((uint32_t)(quad * 32) << 16) + c0, r);
+        for (int c0 = half * kHalfCols; c0 < (half + 1) * kHalfCols && c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_load_32(acc + c0, r);
           float v[16];
+          if (can_prefetch) {
+            float4 cur[8];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = my_kb > 0 ? __uint_as_float(r[j]) : 0.f;
-          store_normal<EPI>(p, row, col_tile * BN + c0, v);
+            for (int j = 0; j < 8; ++j) cur[j] = ahead[j];
+            if (c0 + 32 < (half + 1) * kHalfCols) prefetch(c0 + 32);
+            float* o = (float*)p.out + (size_t)row * p.ld_out + col_tile * BN + c0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (col_tile * BN + c0 + 4 * j < p.cols) {
+                float4 t = cur[j];
+                t.x += __uint_as_float(r[4 * j]); t.y += __uint_as_float(r[4 * j + 1]);
+                t.z += __uint_as_float(r[4 * j + 2]); t.w += __uint_as_float(r[4 * j + 3]);
+                *reinterpret_cast<float4*>(o + 4 * j) = t;
+              }
+            }
+            continue;
+          }
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = my_kb > 0 ? __uint_as_float(r[16 * h + j]) : 0.f;
+            store_normal<EPI>(p, row, col_tile * BN + c0 + 16 * h, v);
+          }
         }
+      } else if (half == 1) {
+        // few tokens: the tile has at most 64 columns, one warp per lane quarter does it all
       } else if (p.splits == 1) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
           uint32_t r[16];
-          tmem_load_16(tmem_base + ((uint32_t)(quad * 32) << 16) + c0, r);
+          tmem_load_16(acc + c0, r);
           float v[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = my_kb > 0 ? __uint_as_float(r[j]) : 0.f;
@@ -366,11 +440,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
           uint32_t r[16];
-          tmem_load_16(tmem_base + ((uint32_t)(quad * 32) << 16) + c0, r);
+          tmem_load_16(acc + c0, r);
 #pragma unroll
           for (int j = 0; j < 16; ++j) part[(c0 + j) * kTileRows + row_in_tile] = my_kb > 0 ? __uint_as_float(r[j]) : 0.f;
         }
       }
+      // this warp has read its share of the buffer: one of the eight arrivals that free it
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty(buf));
     }
   }
   tcgen05_fence_before();
@@ -379,13 +457,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     // every block of the cluster has its partial tile in place
     cluster_sync_all();
     if (warp >= 2 && !*abort_flag) {
+      const int row_tile = blockIdx.x;
       const int S = p.splits;
       const int rows_per = kTileRows / S;                    // rows this block finishes (S is 2, 4 or 8)
       const uint32_t part_addr = smem_base;
-      const int t = threadIdx.x - 64;                        // 0..127
+      const int t = threadIdx.x - 64;                        // 0..255
       if (EPI == 3) {
         const int pairs = rows_per / 2;
-        for (int idx = t; idx < pairs * BN; idx += 128) {
+        for (int idx = t; idx < pairs * BN; idx += 256) {
           const int pr = idx % pairs, col = idx / pairs;
           const int rl = split * rows_per + 2 * pr;
           float g = 0.f, u = 0.f;
@@ -396,7 +475,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
           store_swapped_one<EPI>(p, row_tile * kTileRows + rl, col, g, u);
         }
       } else {
-        for (int idx = t; idx < rows_per * BN; idx += 128) {
+        for (int idx = t; idx < rows_per * BN; idx += 256) {
           const int rl = split * rows_per + idx % rows_per, col = idx / rows_per;
           float v = 0.f;
 #pragma unroll 4
@@ -407,8 +486,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     }
     cluster_sync_all();                                      // nobody leaves while a peer still reads its tile
   }
-  tcgen05_fence_before();
-  __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols) : "memory");
   }
@@ -550,8 +627,17 @@ PTL_EXPORT int ptl_gemm_tc_bf16(void* out, const void* X, const void* W, int M, 
     rc = make_map(&mc, W, N, K, wide ? 256 : 128);
     if (rc) return rc;
     const int bn = wide ? 256 : 128;
-    dim3 grid((N + bn - 1) / bn, (M + kTileRows - 1) / kTileRows);
-    PTL_REQUIRE(grid.y <= 65535, "gemm_tc: too many rows");
+    p.tiles_m = (M + kTileRows - 1) / kTileRows;
+    p.tiles_n = (N + bn - 1) / bn;
+    static int sm_count = 0;
+    if (!sm_count) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+      if (sm_count <= 0) sm_count = 148;
+    }
+    const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    dim3 grid((unsigned)(tiles < sm_count ? tiles : sm_count));
     return wide ? launch_epi<256>(epi, mr, mc, p, grid, s) : launch_epi<128>(epi, mr, mc, p, grid, s);
   }
   // few tokens: swapped operands; the K range is split over a cluster of 1, 2, 4 or 8 blocks so
