@@ -41,7 +41,7 @@ class StepOutput:
     num_tokens: int = 0
 
 
-QUERY_TILE = 64   # query rows per block of the prompt attention kernel
+QUERY_TILE = 128   # query rows per block of the prompt attention kernel
 
 
 def _pad4(n: int) -> int:

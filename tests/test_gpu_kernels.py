@@ -217,8 +217,8 @@ def _hints(q_lens, ctx):
         if n == 1:
             dec.append(t0)
         else:
-            for a in range(0, n, 64):
-                tiles += [r, t0 + a, min(64, n - a), c - n + a]
+            for a in range(0, n, 128):
+                tiles += [r, t0 + a, min(128, n - a), c - n + a]
         t0 += n
     i32 = lambda x: torch.tensor(x if x else [0], dtype=torch.int32).cuda()
     return SimpleNamespace(n_decode=len(dec), decode_items=i32(dec)[:len(dec)], n_prefill_tiles=len(tiles) // 4,
