@@ -21,17 +21,13 @@
 // and take half of the columns each).  With many tokens a block walks several tiles and keeps two
 // accumulators in TMEM, so the epilogue of one tile runs under the MMAs of the next.  Every wait on an mbarrier gives up after a
 // bounded number of polls, records a code in *status, and the block drains and frees its TMEM.
-#include <cuda.h>
-#include <mutex>
-#include <unordered_map>
-#include "common.cuh"
+#include "tcgen05_utils.cuh"
 
 namespace ptl {
 
 constexpr int kTileRows = 128;     // rows of the row operand per block (MMA M)
 constexpr int kTileK = 64;         // K per stage: 64 bfloat16 = one 128-byte swizzle row
 constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, eight epilogue warps (two per TMEM lane quarter)
-constexpr uint32_t kPollLimit = 1u << 22;
 
 struct GemmParams {
   void* out;
@@ -46,94 +42,6 @@ struct GemmParams {
   int tiles_m;           // normal mode: tiles along the tokens and along the features
   int tiles_n;
 };
-
-// ---------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
-               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait: false (and *abort = 1, *status = code) if the phase did not complete in time or
-// another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort, int* status, int code) {
-  for (uint32_t i = 0; i < kPollLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort) return false;
-    if (i > 64) __nanosleep(40);
-  }
-  *abort = 1;
-  if (status) atomicExch(status, code);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tmem_load_16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-               : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-               : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank) {
-  uint32_t remote;
-  float v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-  return v;
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16),
-// written by TMA with the 128-byte swizzle: groups of 8 rows are 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);   // start address, bits 0-13
-  d |= (uint64_t)1 << 16;                     // leading byte offset (not used by swizzled K-major tiles)
-  d |= (uint64_t)(1024 >> 4) << 32;           // stride byte offset: 8 rows x 128 bytes
-  d |= (uint64_t)1 << 46;                     // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                     // 128-byte swizzle
-  return d;
-}
-// Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major, M x N tile.
-__host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
 
 template <int BN> struct TcCfg {
   static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : 4);   // few tokens: small blocks, several per SM
@@ -492,68 +400,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
 }
 
 // ---------------------------------------------------------------- host side
-static int encode_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows);
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
-// Tensor maps already encoded by this process: weights are asked for again every step.
-struct MapKey {
-  const void* base; int rows, K, box;
-  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && K == o.K && box == o.box; }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& k) const {
-    size_t h = reinterpret_cast<size_t>(k.base);
-    h ^= (size_t)k.rows * 0x9E3779B97F4A7C15ull + (size_t)k.K * 0xC2B2AE3D27D4EB4Full + (size_t)k.box * 0x165667B19E3779F9ull;
-    return h;
-  }
-};
-
-// A [rows, K] bfloat16 matrix, K contiguous, fetched in boxes of 64 (K) x box_rows with the 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  static std::mutex lock;
-  const MapKey key{base, rows, K, box_rows};
-  {
-    std::lock_guard<std::mutex> g(lock);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *map = it->second; return 0; }
-  }
-  int rc = encode_map(map, base, rows, K, box_rows);
-  if (rc) return rc;
-  std::lock_guard<std::mutex> g(lock);
-  if (cache.size() > 8192) cache.clear();
-  cache.emplace(key, *map);
-  return 0;
-}
-
-static int encode_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  PTL_REQUIRE(fn != nullptr, "gemm_tc: the driver has no cuTensorMapEncodeTiled");
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  PTL_REQUIRE(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled failed with %d (rows=%d K=%d box=%d)", (int)r, rows, K, box_rows);
-  return 0;
-}
-
 template <int BN, int EPI>
 static int launch_tc(const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& p, dim3 grid, cudaStream_t stream) {
   using Cfg = TcCfg<BN>;

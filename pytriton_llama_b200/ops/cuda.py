@@ -64,6 +64,9 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_prefill_attention_bf16.restype = _c_int
     lib.ptl_gemm_tc_bf16.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr]
     lib.ptl_gemm_tc_bf16.restype = _c_int
+    lib.ptl_prefill_attention_tc_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                                  _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _ptr, _ptr]
+    lib.ptl_prefill_attention_tc_bf16.restype = _c_int
     lib.ptl_argmax.argtypes = [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
     lib.ptl_argmax.restype = _c_int
     lib.ptl_sample.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
@@ -368,6 +371,14 @@ class CudaOps:
                 float(scale), int(window), splits, num_pages, _p(counters), stream),
                 kernels=2 if splits > 1 and counters is None else 1)
         if hints.n_prefill_tiles:
+            if os.environ.get("PTL_PREFILL_TC", "1") != "0":
+                rc = self.lib.ptl_prefill_attention_tc_bf16(
+                    _p(out), _p(q), _p(cache), _p(block_table), _p(hints.prefill_tiles), hints.n_prefill_tiles, q.shape[0],
+                    q.shape[1], nq * d, block_table.shape[1], nq, nkv, d, page_size, float(scale), int(window), num_pages,
+                    _p(self._tc_status_word()), stream)
+                if rc != -2:          # -2: sizes the tcgen05 kernel leaves to the warp-level one
+                    self._check(rc)
+                    return
             self._check(self.lib.ptl_prefill_attention_bf16(
                 _p(out), _p(q), _p(cache), _p(block_table), _p(hints.prefill_tiles), hints.n_prefill_tiles, q.shape[1],
                 nq * d, block_table.shape[1], nq, nkv, d, page_size, float(scale), int(window), num_pages, stream))
