@@ -180,9 +180,9 @@ class Engine:
             if e.request in seen:
                 raise ValueError(f"request {e.request!r} appears twice in one step")
             seen.add(e.request)
-            for t in e.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise ValueError(f"token {t} of request {e.request!r} is outside the vocabulary of {self.vocab_size}")
+            toks = np.asarray(e.tokens)
+            if toks.size and (int(toks.min()) < 0 or int(toks.max()) >= self.vocab_size):
+                raise ValueError(f"a token of request {e.request!r} is outside the vocabulary of {self.vocab_size}")
             for w in e.want:
                 if not 0 <= int(w) < len(e.tokens):
                     raise ValueError(f"request {e.request!r} wants logits at {w} but brings {len(e.tokens)} tokens")

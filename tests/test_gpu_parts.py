@@ -275,3 +275,67 @@ def test_run_order_may_repeat_a_layer_and_share_a_cache_entry(tmp_path):
         return plain_llama.rms_norm(h, w2["model.norm.weight"], eps) @ w2["model.embed_tokens.weight"].T
     for r, s in seqs.items():
         assert_close(got2[r], shared_forward(s), "float32", r)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_with_a_window_get_pages_of_their_own(tmp_path, dtype):
+    """A toy architecture whose second layer attends over a window of 24 keys while the first sees
+    everything: two cache groups with their own pools and block tables; the windowed group gives
+    pages back as decoding moves on, and the logits still equal the plain implementation's."""
+    import traces
+    from conftest import make_model_folder
+    from pytriton_llama_b200.config import EngineConfig, LlamaConfig, register_architecture
+    from pytriton_llama_b200.engine.engine import Engine, StepEntry
+    from pytriton_llama_b200.models.llama import llama_spec
+    from pytriton_llama_b200.weights import read_folder, write_file, write_random_model
+    from conftest import TINY_D
+    window = 24
+    cfg = dict(TINY_D, architectures=["WindowedForCausalLM"])
+
+    def spec(c, norm_init="ones"):
+        sp = llama_spec(c, norm_init=norm_init)
+        sp.layers[1].parts["mixer"].params["window"] = window
+        return sp
+    register_architecture("WindowedForCausalLM", LlamaConfig.from_dict, spec)
+    stored = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = write_random_model(tmp_path / "windowed", cfg, seed=9, dtype=torch.float32, std=0.08, norm_init="ones_jitter")
+    tensors = {k: v.clone() for k, v in read_folder(folder).items()}
+    gain = 2.0 if dtype == "float32" else 1.0
+    for k in tensors:
+        if k.endswith("q_proj.weight") or k.endswith("k_proj.weight"):
+            tensors[k] = tensors[k] * gain
+    tensors = {k: v.to(stored) for k, v in tensors.items()}
+    write_file(folder / "model.safetensors", tensors)
+    w = {k: v.double() for k, v in tensors.items()}
+
+    def plain(tokens):
+        tokens = torch.as_tensor(tokens)
+        pos = torch.arange(len(tokens))
+        h = w["model.embed_tokens.weight"][tokens]
+        eps = cfg["rms_norm_eps"]
+        for layer in (0, 1):
+            pre = f"model.layers.{layer}."
+            x = plain_llama.rms_norm(h, w[pre + "input_layernorm.weight"], eps)
+            h = h + plain_llama.attention_block(x, pos, cfg, w, pre, window=window if layer == 1 else None)
+            h = h + plain_llama.swiglu_ffn(plain_llama.rms_norm(h, w[pre + "post_attention_layernorm.weight"], eps),
+                                           w[pre + "mlp.gate_proj.weight"], w[pre + "mlp.up_proj.weight"], w[pre + "mlp.down_proj.weight"])
+        return plain_llama.rms_norm(h, w["model.norm.weight"], eps) @ w["model.embed_tokens.weight"].T
+
+    eng = Engine(folder, EngineConfig(dtype=dtype, page_size=16, max_gpu_num_blocks=40, max_seq_len=320, max_num_seqs=3))
+    assert len(eng.cache.groups) == 2
+    kinds = sorted((g.need.kind, g.need.window) for g in eng.cache.groups)
+    assert kinds == [("full", 0), ("window", window)]
+    seqs = {f"w{i}": random_tokens(n, 512, 90 + i) for i, n in enumerate([150, 70, 300, 40])}
+    got = traces.replay(eng, traces.mixed(seqs, live=3, sizes=(40, 7, 130, 2, 19), decode_tail=40))
+    for r, s_ in seqs.items():
+        assert_close(got[r], plain(s_), dtype, r)
+    # the windowed group really gives pages back: a long request holds few of its pages
+    win_group = [i for i, g in enumerate(eng.cache.groups) if g.need.kind == "window"][0]
+    full_group = 1 - win_group
+    eng.step([StepEntry("long", random_tokens(200, 512, 1), [])])
+    for i in range(60):
+        eng.step([StepEntry("long", [i % 512], [])])
+    held_window = sum(1 for p_ in eng.cache.block_table("long", win_group) if p_ >= 0)
+    held_full = sum(1 for p_ in eng.cache.block_table("long", full_group) if p_ >= 0)
+    assert held_full == -(-260 // 16) and held_window <= -(-window // 16) + 1
+    eng.cache.check_invariants()
