@@ -73,7 +73,7 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ residu
         }
       }
       *reinterpret_cast<float4*>(row + i) = s;
-      if (rout) *reinterpret_cast<float4*>(rout + i) = s;
+      if (rout && (xin || rout != rin)) *reinterpret_cast<float4*>(rout + i) = s;   // unchanged rows are not rewritten
       ss += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
     }
     ss = block_sum(ss, red);
@@ -102,7 +102,7 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ residu
   const float rrms = 1.0f / sqrtf(ss / (float)hidden + eps);
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     const float s = row[i];
-    if (rout) rout[i] = s;
+    if (rout && (xin || rout != rin)) rout[i] = s;
     yo[i] = from_f32<T>(s * rrms * w[i]);
   }
 }

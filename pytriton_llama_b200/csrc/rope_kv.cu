@@ -11,11 +11,15 @@
 
 namespace ptl {
 
+template <typename T> struct Pair;
+template <> struct Pair<float> { using type = float2; };
+template <> struct Pair<__nv_bfloat16> { using type = __nv_bfloat162; };
+
 template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                                      const float* __restrict__ inv_freq, const int* __restrict__ slots,
                                      T* __restrict__ cache, int nq, int nkv, int d, int rot,
-                                     int page_size, int write_cache, long long num_slots) {
+                                     int page_size, int write_cache, long long num_slots, int vec2_ok) {
   extern __shared__ float cs[];            // cos[rot/2], sin[rot/2] of this token's angles
   pdl_wait();
   pdl_launch_dependents();
@@ -41,6 +45,44 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
     __syncthreads();
   }
   const int pairs_per_head = d - half;  // `half` rotated pairs, then d - rot pass-through elements
+  if (vec2_ok) {
+    // two neighbouring frequencies per thread: 4-byte (bfloat16) or 8-byte (float32) accesses
+    using V2 = typename Pair<T>::type;
+    const int half2 = half / 2;
+    for (int e = threadIdx.x; e < (nq + nkv) * half2; e += blockDim.x) {
+      const int h = e / half2;
+      const int j = (e % half2) * 2;
+      T* head = row + (size_t)h * d;
+      const V2 a = *reinterpret_cast<const V2*>(head + j), b = *reinterpret_cast<const V2*>(head + j + half);
+      float x1a = to_f32(a.x), x1b = to_f32(a.y), x2a = to_f32(b.x), x2b = to_f32(b.y);
+      float o1a = x1a, o1b = x1b, o2a = x2a, o2b = x2b;
+      if (inv_freq) {
+        const float ca = cs[j], cb = cs[j + 1], sa = cs[half + j], sb = cs[half + j + 1];
+        o1a = x1a * ca - x2a * sa; o2a = x2a * ca + x1a * sa;
+        o1b = x1b * cb - x2b * sb; o2b = x2b * cb + x1b * sb;
+      }
+      V2 r1, r2;
+      r1.x = from_f32<T>(o1a); r1.y = from_f32<T>(o1b);
+      r2.x = from_f32<T>(o2a); r2.y = from_f32<T>(o2b);
+      *reinterpret_cast<V2*>(head + j) = r1;
+      *reinterpret_cast<V2*>(head + j + half) = r2;
+      if (h >= nq && slot >= 0) {
+        T* kd = kdst + (size_t)(h - nq) * page_size * d;
+        *reinterpret_cast<V2*>(kd + j) = r1;
+        *reinterpret_cast<V2*>(kd + j + half) = r2;
+      }
+    }
+    if (slot >= 0 && vdst) {
+      // values: 16-byte packets
+      constexpr int VN = Vec16<T>::N;
+      const T* vsrc = row + (size_t)(nq + nkv) * d;
+      for (int e = threadIdx.x * VN; e < nkv * d; e += blockDim.x * VN) {
+        const int h = e / d, i = e % d;
+        store16(vdst + (size_t)h * page_size * d + i, load16(vsrc + e));
+      }
+    }
+    return;
+  }
   // q and k heads
   for (int e = threadIdx.x; e < (nq + nkv) * pairs_per_head; e += blockDim.x) {
     const int h = e / pairs_per_head;
@@ -83,11 +125,14 @@ int rope_kv_write(void* qkv, const int* positions, const float* inv_freq, const 
   PTL_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "rope_kv_write: rotary width %d must be even and <= head size %d", rot, d);
   PTL_REQUIRE(cache == nullptr || (page_size > 0 && slots != nullptr && num_slots > 0), "rope_kv_write: a cache needs slots and a page size");
   if (tokens == 0) return 0;
-  const int work = (nq + nkv) * (d - rot / 2);
-  const int threads = work >= 1024 ? 512 : (work >= 256 ? 256 : 128);
+  // the paired path needs the whole head rotated, whole 16-byte packets per head and aligned rows
+  const int vec2_ok = rot == d && d % 16 == 0 && aligned16(qkv) && (cache == nullptr || aligned16(cache)) &&
+                      ((size_t)(nq + 2 * nkv) * d * sizeof(T)) % 16 == 0;
+  const int work = vec2_ok ? (nq + nkv) * (d / 4) : (nq + nkv) * (d - rot / 2);
+  const int threads = work >= 2048 ? 256 : 128;
   return launch_kernel("rope_kv_write", rope_kv_write_kernel<T>, dim3(tokens), dim3(threads), (size_t)rot * sizeof(float),
                        as_stream(stream), (T*)qkv, positions, inv_freq, slots, (T*)cache, nq, nkv, d, rot, page_size,
-                       (int)(cache != nullptr), num_slots);
+                       (int)(cache != nullptr), num_slots, vec2_ok);
 }
 
 }  // namespace ptl
