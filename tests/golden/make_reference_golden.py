@@ -130,7 +130,9 @@ def run_reference(root, name):
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_reference_golden.py /path/to/lite_llama_checkout")
+    root = sys.argv[1]
     for name in CONFIGS:
         out = run_reference(root, name)
         torch.save(out, HERE / f"reference_tiny_{name}.pt")

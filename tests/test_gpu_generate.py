@@ -28,7 +28,7 @@ def _plain_greedy(folder, prompts, n, stop=()):
 
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_greedy_generation_float32_equals_plain(model_folders, name):
-    """BASELINE workload of the tiny models: prompts 5/11/17 (A) and 1/9/33/70 (B), 8 new tokens."""
+    """The tiny models' generation workload: prompts of 5/11/17 (A) and 1/9/33/70 (B) tokens, 8 new tokens each."""
     from pytriton_llama_b200.sampling import SamplingParams
     folder = model_folders(name)
     vocab = TINY[name]["vocab_size"]
@@ -78,7 +78,7 @@ def test_greedy_generation_bfloat16(model_folders):
 
 
 def test_sampling_is_seeded_and_independent_of_batching(model_folders):
-    """Temperature 0.8 from a fixed seed (BASELINE config B): the float32 engine draws exactly the
+    """Temperature 0.8 from a fixed seed (configuration B): the float32 engine draws exactly the
     tokens the plain implementation draws from the same uniform numbers, whether the requests run
     together in portions of 16 or one at a time."""
     from pytriton_llama_b200.sampling import SamplingParams, uniform
