@@ -226,8 +226,10 @@ def main() -> int:
     # ------------------------------------------------------------------ decode through the Python entry point
     e2e = None
     if not args.no_e2e:
-        ctx0 = CONTEXT - K - W
-        params = SamplingParams(temperature=0.0, max_gen_len=K + W + 4, stop_token_ids=[])
+        # Prompts are cut into 2,048-token portions, so requests reach decoding a few steps apart;
+        # they are sized so that none ends (and the batch never shrinks) inside the timed steps.
+        ctx0 = CONTEXT - K - W - 3 * B
+        params = SamplingParams(temperature=0.0, max_gen_len=None, stop_token_ids=[])
         reqs = [llm.add_request(tokens(ctx0), params) for _ in range(B)]
         while any(r.computed < len(r.prompt) for r in reqs):
             llm.step()
@@ -245,6 +247,8 @@ def main() -> int:
         h2d = 4 * graph.layout.size if graph else 4 * (8 * B + B * (-(-CONTEXT // 16)))
         e2e = {"value": round(produced / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": 4 * B, "ms_per_step": round(dt / K * 1e3, 4)}
+        for r in reqs:                      # stop them: the measurement is over
+            r.params.max_gen_len = len(r.output) + 1
         while llm.has_work():
             llm.step()
 
