@@ -371,6 +371,11 @@ class Engine:
         staging = [(torch.empty(layout.size, dtype=torch.int32, pin_memory=True), torch.cuda.Event()) for _ in range(4)]
         return _DecodeGraph(graph, layout, staging, dev, logits, launches)
 
+    def check_device_status(self) -> None:
+        """Raises if a kernel reported a problem (synchronises the device; call it off the hot path)."""
+        if hasattr(self.ops, "check_status"):
+            self.ops.check_status()
+
     # ------------------------------------------------------------------ requests
     def finish(self, request: Hashable) -> None:
         """Gives back everything the request holds."""

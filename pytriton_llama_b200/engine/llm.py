@@ -76,6 +76,7 @@ class LLM:
         reqs = [self.add_request(p, sp) for p, sp in zip(prompt_tokens, plist)]
         while self.scheduler.has_work():
             self.step()
+        self.engine.check_device_status()
         return [list(r.output) for r in reqs]
 
     def generate_stream(self, prompt_tokens: Sequence[Sequence[int]],

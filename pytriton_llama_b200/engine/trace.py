@@ -64,6 +64,7 @@ def main(argv=None) -> int:
         for rid in msg.get("end", []):
             engine.finish(rid)
         print(f"done {step}", flush=True)
+    engine.check_device_status()
     return 0
 
 

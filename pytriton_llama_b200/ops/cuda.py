@@ -259,6 +259,15 @@ class CudaOps:
         self._check(rc)
         return out
 
+    def check_status(self) -> None:
+        """Raises if a kernel flagged a problem since the last call: a token outside the vocabulary
+        reached the embedding, or a wait inside a tensor-core kernel gave up (synchronises)."""
+        if self.bad_token_seen():
+            raise KernelError("a token id outside the vocabulary reached the embedding kernel")
+        code = self.gemm_tc_status()
+        if code:
+            raise KernelError(f"a wait inside a tcgen05 kernel gave up (code {code}); results since the last check are invalid")
+
     def gemm_tc_status(self) -> int:
         """0, or the code of the wait that gave up inside a tensor-core product since the last call (syncs)."""
         if getattr(self, "_tc_status", None) is None:
