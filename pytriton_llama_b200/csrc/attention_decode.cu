@@ -14,18 +14,26 @@
 
 namespace ptl {
 
-constexpr int kDecKeys = 64;      // keys per tile
 constexpr int kDecWarps = 4;
+
+__device__ __forceinline__ float dec_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));   // 0 for -inf; P is rounded to bfloat16 anyway
+  return y;
+}
 constexpr int kDecStagedPages = 1024;   // block-table entries of a block's key range kept in shared memory
 
-template <int D> struct DecodeCfg {
+// KP = groups of 16 keys per warp and tile: 1 (64-key tiles, four blocks per SM) for large batches,
+// 2 (128-key tiles, two blocks per SM, fewer barriers per key) when few blocks are in flight.
+template <int D, int KP> struct DecodeCfg {
+  static constexpr int kKeys = 64 * KP;
   static constexpr int kStages = 3;                            // 48 KB (D = 64): four blocks per SM
   static constexpr int kChunks = D / 8;                       // 16-byte chunks per row
-  static constexpr int kTileBytes = kDecKeys * D * 2;          // one of K / V
+  static constexpr int kTileBytes = kKeys * D * 2;             // one of K / V
   static constexpr int kSmem = kStages * 2 * kTileBytes;
 };
 
-template <int D>
+template <int D, int KP>
 __global__ void __launch_bounds__(kDecWarps * 32)
 decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
                         const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
@@ -33,7 +41,9 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
                         const int* __restrict__ tok_req, const int* __restrict__ positions, int q_stride,
                         int out_stride, int bt_stride, int nq, int nkv, int page_size, float scale_log2,
                         int window, int splits, int num_pages, int page_shift, int* __restrict__ counters) {
-  using Cfg = DecodeCfg<D>;
+  using Cfg = DecodeCfg<D, KP>;
+  constexpr int kDecKeys = Cfg::kKeys;
+  constexpr int kDecKP = KP;
   extern __shared__ __align__(128) unsigned char smem[];
   pdl_wait();
   pdl_launch_dependents();
@@ -139,59 +149,79 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     const int stage = tile % Cfg::kStages;
     const uint32_t kbase = smem_base + stage * 2 * Cfg::kTileBytes;
     const uint32_t vbase = kbase + Cfg::kTileBytes;
-    const int row0 = warp * 16;                               // this warp's 16 keys of the tile
-    // S = Q K^T for 16 keys: two n-tiles of 8
-    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+    const int row0 = warp * 16 * kDecKP;                      // this warp's keys of the tile
+    // S = Q K^T: two n-tiles of 8 keys per group of 16
+    float sc[kDecKP][2][4];
+#pragma unroll
+    for (int kp = 0; kp < kDecKP; ++kp)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { sc[kp][0][e] = 0.f; sc[kp][1][e] = 0.f; }
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
-      uint32_t kb[4];
-      const int id = lane >> 3;
-      const int krow = row0 + (id >> 1) * 8 + (lane & 7);
-      ldmatrix_x4(kb, kbase + tile_offset<D>(krow, 2 * ks + (id & 1)));
-      mma_bf16_16816(s0, qa[ks], kb[0], kb[1]);
-      mma_bf16_16816(s1, qa[ks], kb[2], kb[3]);
+#pragma unroll
+      for (int kp = 0; kp < kDecKP; ++kp) {
+        uint32_t kb[4];
+        const int id = lane >> 3;
+        const int krow = row0 + kp * 16 + (id >> 1) * 8 + (lane & 7);
+        ldmatrix_x4(kb, kbase + tile_offset<D>(krow, 2 * ks + (id & 1)));
+        mma_bf16_16816(sc[kp][0], qa[ks], kb[0], kb[1]);
+        mma_bf16_16816(sc[kp][1], qa[ks], kb[2], kb[3]);
+      }
     }
     // mask keys past the range, scale into log2 units
     const int key0 = k_begin + tile * kDecKeys + row0 + 2 * c;
-    float sv[2][4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int kk0 = key0 + (e & 1), kk1 = key0 + 8 + (e & 1);
-      sv[0][e] = kk0 < k_end ? s0[e] * scale_log2 : -INFINITY;
-      sv[1][e] = kk1 < k_end ? s1[e] * scale_log2 : -INFINITY;
-    }
+    for (int kp = 0; kp < kDecKP; ++kp)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int kk0 = key0 + kp * 16 + (e & 1), kk1 = kk0 + 8;
+        sc[kp][0][e] = kk0 < k_end ? sc[kp][0][e] * scale_log2 : -INFINITY;
+        sc[kp][1][e] = kk1 < k_end ? sc[kp][1][e] * scale_log2 : -INFINITY;
+      }
     // online softmax for rows g (e = 0,1) and g+8 (e = 2,3)
-    uint32_t pa[4] = {0u, 0u, 0u, 0u};
+    uint32_t pa[kDecKP][4];
+#pragma unroll
+    for (int kp = 0; kp < kDecKP; ++kp) { pa[kp][0] = pa[kp][1] = pa[kp][2] = pa[kp][3] = 0u; }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       if (h == 1 && G <= 8) break;          // rows 8..15 of the tile are padding for groups of up to 8 heads
-      float mx = fmaxf(fmaxf(sv[0][2 * h], sv[0][2 * h + 1]), fmaxf(sv[1][2 * h], sv[1][2 * h + 1]));
+      float mx = -INFINITY;
+#pragma unroll
+      for (int kp = 0; kp < kDecKP; ++kp)
+        mx = fmaxf(mx, fmaxf(fmaxf(sc[kp][0][2 * h], sc[kp][0][2 * h + 1]), fmaxf(sc[kp][1][2 * h], sc[kp][1][2 * h + 1])));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
       const float m_new = fmaxf(m_run[h], mx);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = exp2f(m_run[h] - m_use);
-      const float p00 = exp2f(sv[0][2 * h] - m_use), p01 = exp2f(sv[0][2 * h + 1] - m_use);
-      const float p10 = exp2f(sv[1][2 * h] - m_use), p11 = exp2f(sv[1][2 * h + 1] - m_use);
-      float sum = p00 + p01 + p10 + p11;
+      const float alpha = dec_exp2(m_run[h] - m_use);
+      float sum = 0.f;
+#pragma unroll
+      for (int kp = 0; kp < kDecKP; ++kp) {
+        const float p00 = dec_exp2(sc[kp][0][2 * h] - m_use), p01 = dec_exp2(sc[kp][0][2 * h + 1] - m_use);
+        const float p10 = dec_exp2(sc[kp][1][2 * h] - m_use), p11 = dec_exp2(sc[kp][1][2 * h + 1] - m_use);
+        sum += p00 + p01 + p10 + p11;
+        pa[kp][h] = pack_bf16(p00, p01);          // a0 / a1: keys 2c..2c+1
+        pa[kp][2 + h] = pack_bf16(p10, p11);      // a2 / a3: keys 8+2c..
+      }
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
       sum += __shfl_xor_sync(0xffffffffu, sum, 2);
       l_run[h] = l_run[h] * alpha + sum;
       m_run[h] = m_new;
 #pragma unroll
       for (int i = 0; i < D / 8; ++i) { o[i][2 * h] *= alpha; o[i][2 * h + 1] *= alpha; }
-      pa[h] = pack_bf16(p00, p01);          // a0 / a1: keys 2c..2c+1
-      pa[2 + h] = pack_bf16(p10, p11);      // a2 / a3: keys 8+2c..
     }
-    // O += P V over this warp's 16 keys
+    // O += P V over this warp's keys
 #pragma unroll
-    for (int nt = 0; nt < D / 8; nt += 2) {
-      uint32_t vb[4];
-      const int id = lane >> 3;
-      const int vrow = row0 + (id & 1) * 8 + (lane & 7);
-      ldmatrix_x4_trans(vb, vbase + tile_offset<D>(vrow, nt + (id >> 1)));
-      mma_bf16_16816(o[nt], pa, vb[0], vb[1]);
-      mma_bf16_16816(o[nt + 1], pa, vb[2], vb[3]);
+    for (int kp = 0; kp < kDecKP; ++kp) {
+#pragma unroll
+      for (int nt = 0; nt < D / 8; nt += 2) {
+        uint32_t vb[4];
+        const int id = lane >> 3;
+        const int vrow = row0 + kp * 16 + (id & 1) * 8 + (lane & 7);
+        ldmatrix_x4_trans(vb, vbase + tile_offset<D>(vrow, nt + (id >> 1)));
+        mma_bf16_16816(o[nt], pa[kp], vb[0], vb[1]);
+        mma_bf16_16816(o[nt + 1], pa[kp], vb[2], vb[3]);
+      }
     }
   }
   cp_async_wait<0>();
@@ -224,7 +254,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
 #pragma unroll
     for (int w = 0; w < kDecWarps; ++w) {
       const float mw = mml[(w * 16 + row) * 2];
-      const float wgt = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      const float wgt = mw == -INFINITY ? 0.f : dec_exp2(mw - M);
       L += wgt * mml[(w * 16 + row) * 2 + 1];
       acc += wgt * mo[(w * 16 + row) * D + col];
     }
@@ -316,15 +346,15 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
 int attention_merge_bf16(void* out, const float* part_acc, const float* part_ml, int tokens, int out_stride,
                          int nq, int d, int splits, const int* items, void* stream);
 
-template <int D>
+template <int D, int KP>
 int launch_decode(void* out, float* part_acc, float* part_ml, const void* q, const void* cache,
                   const int* block_table, const int* items, const int* tok_req, const int* positions, int n_items,
                   int q_stride, int out_stride, int bt_stride, int nq, int nkv, int page_size, float scale,
                   int window, int splits, int num_pages, int* counters, void* stream) {
-  using Cfg = DecodeCfg<D>;
+  using Cfg = DecodeCfg<D, KP>;
   static bool raised = false;
   if (!raised) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D, KP>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
     PTL_REQUIRE(e == cudaSuccess, "decode_attention: cannot raise shared memory: %s", cudaGetErrorString(e));
     raised = true;
   }
@@ -332,7 +362,7 @@ int launch_decode(void* out, float* part_acc, float* part_ml, const void* q, con
   for (int b = 0; b < 20; ++b) if ((1 << b) == page_size) page_shift = b;
   const long long blocks = (long long)n_items * nkv * splits;
   PTL_REQUIRE(blocks <= 0x7fffffffLL, "decode_attention: too many blocks");
-  int rc = launch_kernel("decode_attention", decode_attention_kernel<D>, dim3((unsigned)blocks), dim3(kDecWarps * 32),
+  int rc = launch_kernel("decode_attention", decode_attention_kernel<D, KP>, dim3((unsigned)blocks), dim3(kDecWarps * 32),
                          Cfg::kSmem, as_stream(stream), (__nv_bfloat16*)out, part_acc, part_ml, (const __nv_bfloat16*)q,
                          (const __nv_bfloat16*)cache, block_table, items, tok_req, positions, q_stride, out_stride, bt_stride,
                          nq, nkv, page_size, scale * 1.4426950408889634f, window, splits, num_pages, page_shift, counters);
@@ -361,9 +391,11 @@ PTL_EXPORT int ptl_decode_attention_bf16(void* out, float* part_acc, float* part
   PTL_REQUIRE(counters == nullptr || splits <= 512, "decode_attention: at most 512 splits with in-kernel merging");
   PTL_REQUIRE(aligned16(q) && aligned16(cache) && q_stride % 8 == 0, "decode_attention: q and cache must be 16-byte aligned");
   if (n_items == 0) return 0;
-  if (d == 64)
-    return launch_decode<64>(out, part_acc, part_ml, q, cache, block_table, items, tok_req, positions, n_items, q_stride,
-                             out_stride, bt_stride, nq, nkv, page_size, scale, window, splits, num_pages, counters, stream);
-  return launch_decode<128>(out, part_acc, part_ml, q, cache, block_table, items, tok_req, positions, n_items, q_stride,
-                            out_stride, bt_stride, nq, nkv, page_size, scale, window, splits, num_pages, counters, stream);
+  // few blocks in flight: 128-key tiles; many: 64-key tiles and twice the blocks per SM
+  const bool wide = (long long)n_items * nkv * splits <= 296;
+#define PTL_DECODE_ARGS out, part_acc, part_ml, q, cache, block_table, items, tok_req, positions, n_items, q_stride, \
+                        out_stride, bt_stride, nq, nkv, page_size, scale, window, splits, num_pages, counters, stream
+  if (d == 64) return wide ? launch_decode<64, 2>(PTL_DECODE_ARGS) : launch_decode<64, 1>(PTL_DECODE_ARGS);
+  return wide ? launch_decode<128, 2>(PTL_DECODE_ARGS) : launch_decode<128, 1>(PTL_DECODE_ARGS);
+#undef PTL_DECODE_ARGS
 }

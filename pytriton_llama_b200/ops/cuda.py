@@ -363,7 +363,10 @@ class CudaOps:
         num_pages = cache.shape[0]
         if hints.n_decode:
             longest = min(hints.max_ctx_len, window) if window else hints.max_ctx_len
-            splits = max(1, min(self.DECODE_BLOCKS // (hints.n_decode * nkv), -(-longest // 128)))
+            pairs = hints.n_decode * nkv
+            # small batches: 128-key tiles at two blocks per SM (296 in flight); large ones: 64-key tiles, four per SM
+            target = 296 if pairs <= 148 else self.DECODE_BLOCKS
+            splits = max(1, min(target // pairs, -(-longest // 128)))
             part_acc = part_ml = counters = None
             if splits > 1:
                 splits = min(splits, 512)
