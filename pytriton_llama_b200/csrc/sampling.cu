@@ -140,6 +140,28 @@ sample_kernel(int* __restrict__ tokens, const float* __restrict__ logits, float*
   }
 }
 
+// log softmax(logits[row])[tokens[row]] of the unscaled logits, one block per row
+// (lite_llama/generete_with_probs.py:154-165 takes the same quantity with log_softmax + gather).
+__global__ void __launch_bounds__(kSampleThreads)
+token_logprob_kernel(float* __restrict__ out, const float* __restrict__ logits, const int* __restrict__ tokens,
+                     int vocab, long long ld) {
+  __shared__ float red[33];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int row = blockIdx.x;
+  const float* x = logits + (size_t)row * ld;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, x[i]);
+  mx = block_max(mx, red);
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) sum += expf(x[i] - mx);
+  sum = block_sum(sum, red);
+  if (threadIdx.x == 0) {
+    const int t = tokens[row];
+    out[row] = (t >= 0 && t < vocab) ? x[t] - mx - logf(sum) : -INFINITY;
+  }
+}
+
 // Greedy choice for whole batches in two stages, so that a few rows still use many SMs:
 // stage 1 finds the best (value, index) of each of `chunks` slices of a row, stage 2 the best of those.
 constexpr int kArgmaxChunks = 32;
@@ -199,6 +221,14 @@ PTL_EXPORT int ptl_argmax(int* tokens, const float* logits, float* part_val, int
   if (rc) return rc;
   return ptl::launch_kernel("argmax_final", ptl::argmax_final_kernel, dim3(rows), dim3(32), 0, ptl::as_stream(stream), tokens,
                             (const float*)part_val, (const int*)part_idx);
+}
+
+PTL_EXPORT int ptl_token_logprob(float* out, const float* logits, const int* tokens, int rows, int vocab, long long ld,
+                                 void* stream) {
+  PTL_REQUIRE(rows >= 0 && vocab > 0 && ld >= vocab, "token_logprob: bad sizes rows=%d vocab=%d", rows, vocab);
+  if (rows == 0) return 0;
+  return ptl::launch_kernel("token_logprob", ptl::token_logprob_kernel, dim3(rows), dim3(ptl::kSampleThreads), 0,
+                            ptl::as_stream(stream), out, logits, tokens, vocab, ld);
 }
 
 PTL_EXPORT int ptl_sample(int* tokens, const float* logits, float* probs, const float* temperature,

@@ -60,12 +60,14 @@ class LLM:
             entries.append(StepEntry(p.request.id, toks, [p.length - 1] if p.sample else []))
         out = self.engine.step(entries, validate=False)   # the plan was checked against the cache; tokens at intake
         sampled: Dict[Hashable, int] = {}
+        logprobs: Dict[Hashable, Optional[float]] = {}
         if out.rows:
             reqs = [p.request for p in plan.portions if p.sample]
-            toks = self.sampler.sample(out.logits, [r.params for r in reqs], [r.number for r in reqs],
-                                       [len(r.output) for r in reqs])
+            toks, lps = self.sampler.sample_with_logprobs(out.logits, [r.params for r in reqs], [r.number for r in reqs],
+                                                          [len(r.output) for r in reqs])
             sampled = {r.id: t for r, t in zip(reqs, toks)}
-        finished += self.scheduler.update(plan, sampled)
+            logprobs = {r.id: lp for r, lp in zip(reqs, lps)}
+        finished += self.scheduler.update(plan, sampled, logprobs)
         return sampled, finished
 
     # ------------------------------------------------------------------ whole runs
@@ -145,12 +147,22 @@ class GenerateText(_TextMixin):
         self.device = dev
 
     def generate(self, prompt_tokens: List[List[int]], max_gen_len: Optional[int], temperature: float = 0.6,
-                 top_p: float = 0.9, echo: bool = False) -> List[List[int]]:
+                 top_p: float = 0.9, echo: bool = False, logprobs: bool = False):
         """Token ids generated for each prompt, cut before the first end-of-sequence token
-        (lite_llama/generate.py:192-204); with ``echo`` the prompt is put in front."""
-        params = SamplingParams(temperature=temperature, top_p=top_p, max_gen_len=max_gen_len)
-        outs = self.llm.generate(prompt_tokens, params)
-        return [_trim(p, o, echo, self.llm.engine.eos_token_ids) for p, o in zip(prompt_tokens, outs)]
+        (lite_llama/generate.py:192-204); with ``echo`` the prompt is put in front.  With ``logprobs``
+        the result is (tokens, log-probabilities of the generated tokens), as in
+        lite_llama/generete_with_probs.py:87-96,154-165."""
+        params = SamplingParams(temperature=temperature, top_p=top_p, max_gen_len=max_gen_len, logprobs=logprobs)
+        reqs = [self.llm.add_request(p, params) for p in prompt_tokens]
+        while self.llm.has_work():
+            self.llm.step()
+        self.llm.engine.check_device_status()
+        eos = self.llm.engine.eos_token_ids
+        toks = [_trim(p, r.output, echo, eos) for p, r in zip(prompt_tokens, reqs)]
+        if not logprobs:
+            return toks
+        kept = [len(_trim(p, r.output, False, eos)) for p, r in zip(prompt_tokens, reqs)]
+        return toks, [r.logprobs[:n] for r, n in zip(reqs, kept)]
 
     def text_completion(self, prompts: List[str], temperature: float = 0.6, top_p: float = 0.9,
                         max_gen_len: Optional[int] = None, echo: bool = False) -> List[str]:

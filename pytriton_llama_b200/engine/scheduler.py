@@ -29,6 +29,7 @@ class Request:
     params: SamplingParams
     number: int = 0                    # arrival number; also feeds the sampling counters
     output: List[int] = field(default_factory=list)
+    logprobs: List[float] = field(default_factory=list)   # of the generated tokens, when asked for
     computed: int = 0                  # tokens of prompt + output that are in the cache
     status: str = WAITING
     finish_reason: Optional[str] = None
@@ -197,7 +198,8 @@ class Scheduler:
         return plan
 
     # ------------------------------------------------------------------ after the step
-    def update(self, plan: StepPlan, sampled: Dict[Hashable, int]) -> List[Request]:
+    def update(self, plan: StepPlan, sampled: Dict[Hashable, int],
+               logprobs: Optional[Dict[Hashable, Optional[float]]] = None) -> List[Request]:
         """Records the step's progress; ``sampled`` has the new token of every portion with
         ``sample`` set.  Returns the requests that finished (their pages are given back here)."""
         done: List[Request] = []
@@ -208,6 +210,8 @@ class Scheduler:
                 continue
             tok = int(sampled[req.id])
             req.output.append(tok)
+            if logprobs is not None and logprobs.get(req.id) is not None:
+                req.logprobs.append(float(logprobs[req.id]))
             stop = self.eos_token_ids | set(req.params.stop_token_ids)
             limit = req.params.max_gen_len
             if tok in stop:

@@ -69,6 +69,8 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_prefill_attention_tc_bf16.restype = _c_int
     lib.ptl_argmax.argtypes = [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
     lib.ptl_argmax.restype = _c_int
+    lib.ptl_token_logprob.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
+    lib.ptl_token_logprob.restype = _c_int
     lib.ptl_sample.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
     lib.ptl_sample.restype = _c_int
     lib.ptl_last_error.restype = ctypes.c_char_p
@@ -394,6 +396,15 @@ class CudaOps:
             self._check(self.lib.ptl_prefill_attention_bf16(
                 _p(out), _p(q), _p(cache), _p(block_table), _p(hints.prefill_tiles), hints.n_prefill_tiles, q.shape[1],
                 nq * d, block_table.shape[1], nq, nkv, d, page_size, float(scale), int(window), num_pages, stream))
+
+    def token_logprobs(self, logits: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+        """log softmax(logits[row])[tokens[row]] as float32 [rows]."""
+        self._want(logits, "logits", torch.float32)
+        self._want(tokens, "tokens", torch.int32)
+        rows, vocab = logits.shape
+        out = self.empty((rows,), torch.float32)
+        self._check(self.lib.ptl_token_logprob(_p(out), _p(logits), _p(tokens), rows, vocab, vocab, self._stream()))
+        return out
 
     def sample(self, logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Optional[torch.Tensor],
                u: Optional[torch.Tensor]) -> torch.Tensor:

@@ -13,6 +13,7 @@ class SamplingParams:
     max_gen_len: Optional[int] = None  # None: up to the engine's max_seq_len (generate_stream.py:198-199)
     stop_token_ids: List[int] = field(default_factory=list)
     seed: Optional[int] = None        # None: the engine's seed
+    logprobs: bool = False            # also report log softmax(logits)[token] of every generated token
 
     def __post_init__(self):
         if self.temperature < 0:

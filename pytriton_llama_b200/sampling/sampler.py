@@ -25,11 +25,26 @@ class Sampler:
                token_indices: Sequence[int]) -> List[int]:
         """One token per logits row.  ``request_numbers`` and ``token_indices`` feed the counter-based
         uniform numbers (the index is the count of tokens the request has generated so far)."""
+        return self.sample_with_logprobs(logits, params, request_numbers, token_indices)[0]
+
+    def sample_with_logprobs(self, logits, params, request_numbers, token_indices):
+        """(tokens, logprobs): ``logprobs[i]`` is log softmax(logits[i])[tokens[i]] of the unscaled
+        logits (lite_llama/generete_with_probs.py:154-165) where ``params[i].logprobs`` is set, else None."""
+        tokens = self._sample_device(logits, params, request_numbers, token_indices)
+        if tokens is None:
+            return [], []
+        if any(p.logprobs for p in params):
+            lp = self.ops.token_logprobs(logits, tokens)
+            both = torch.stack([tokens.to(torch.float32), lp]).tolist()     # one read-back for both
+            return [int(t) for t in both[0]], [v if p.logprobs else None for v, p in zip(both[1], params)]
+        return tokens.tolist(), [None] * len(params)
+
+    def _sample_device(self, logits, params, request_numbers, token_indices):
         rows = logits.shape[0]
         if rows == 0:
-            return []
+            return None
         if all(p.temperature <= 0 for p in params):
-            return self.ops.sample(logits, None, None, None).tolist()
+            return self.ops.sample(logits, None, None, None)
         host = torch.empty((3, rows), dtype=torch.float32, pin_memory=self.device.type == "cuda")
         for i, p in enumerate(params):
             host[0, i] = p.temperature
@@ -37,4 +52,4 @@ class Sampler:
             seed = self.seed if p.seed is None else p.seed
             host[2, i] = uniform(seed, request_numbers[i], token_indices[i])
         dev = host.to(self.device, non_blocking=True)
-        return self.ops.sample(logits, dev[0], dev[1], dev[2]).tolist()
+        return self.ops.sample(logits, dev[0], dev[1], dev[2])

@@ -48,6 +48,16 @@ def test_greedy_generation_float32_equals_plain(model_folders, name):
     trimmed = [w[: next((i for i, t in enumerate(w) if t in stop), len(w))] for w in want]
     assert out == trimmed
     assert gen.generate(prompts[:1], max_gen_len=8, temperature=0.0, echo=True) == [prompts[0] + trimmed[0]]
+    # log-probabilities of the generated tokens, as lite_llama's logprobs variant reports them
+    toks, lps = gen.generate(prompts, max_gen_len=8, temperature=0.0, logprobs=True)
+    assert toks == trimmed
+    cfg64, w64 = plain_llama.load_model_folder(folder, dtype=torch.float64)
+    for p_, out_, lp_ in zip(prompts, toks, lps):
+        assert len(lp_) == len(out_)
+        if out_:
+            ref_lp = torch.log_softmax(plain_llama.forward(cfg64, w64, p_ + out_), -1)
+            for i, (tok, got_lp) in enumerate(zip(out_, lp_)):
+                assert abs(got_lp - float(ref_lp[len(p_) + i - 1, tok])) < 2e-4
     stream = GenerateStreamText(str(folder), None, max_gpu_num_blocks=60, max_seq_len=128, dtype="float32", page_size=PAGE_SIZE[name])
     pieces = [[] for _ in prompts]
     for batch in stream.generate_stream(prompts, max_gen_len=8, temperature=0.0):

@@ -335,6 +335,16 @@ def test_sampling(ops, vocab):
     assert torch.equal(greedy[1:].long(), torch.argmax(logits[1:], -1))
 
 
+@pytest.mark.parametrize("vocab", [1000, 128256, 37])
+def test_token_logprobs(ops, vocab):
+    g = torch.Generator().manual_seed(vocab + 1)
+    logits = 4.0 * torch.randn(6, vocab, generator=g)
+    tokens = torch.tensor([0, vocab - 1, 5, 7, vocab // 2, 3], dtype=torch.int32)
+    want = torch.log_softmax(logits.double(), -1).gather(1, tokens.long().view(-1, 1)).view(-1)
+    got = ops.token_logprobs(logits.cuda(), tokens.cuda()).double().cpu()
+    assert (got - want).abs().max() < 1e-4
+
+
 def test_sampling_follows_the_distribution(ops):
     """Many draws with different uniform numbers reproduce the filtered probabilities."""
     vocab, n = 50, 4000

@@ -118,5 +118,9 @@ class TorchOps:
             out[i] = min(tok, int(torch.nonzero(keep)[-1]))
         return out.to(logits.device)
 
+    def token_logprobs(self, logits, tokens):
+        lp = torch.log_softmax(logits.double(), dim=-1)
+        return lp.gather(1, tokens.long().view(-1, 1)).view(-1).float()
+
     def bad_token_seen(self):
         return False
