@@ -231,15 +231,18 @@ def main() -> int:
         ctx0 = CONTEXT - K - W - 3 * B
         params = SamplingParams(temperature=0.0, max_gen_len=None, stop_token_ids=[])
         reqs = [llm.add_request(tokens(ctx0), params) for _ in range(B)]
+        # ``LLM.run`` is the loop behind ``generate``: it yields every step's tokens as host
+        # integers; each step's integers (tokens, positions, block tables) go up from pinned memory
+        steps = llm.run()
         while any(r.computed < len(r.prompt) for r in reqs):
-            llm.step()
+            next(steps)
         for _ in range(W - 1):
-            llm.step()
+            next(steps)
         torch.cuda.synchronize(dev)
         t0 = time.perf_counter()
         produced = 0
         for _ in range(K):
-            sampled, _ = llm.step()
+            sampled, _ = next(steps)
             produced += len(sampled)
         torch.cuda.synchronize(dev)
         dt = time.perf_counter() - t0
@@ -249,8 +252,8 @@ def main() -> int:
                "d2h_bytes_per_step": 4 * B, "ms_per_step": round(dt / K * 1e3, 4)}
         for r in reqs:                      # stop them: the measurement is over
             r.params.max_gen_len = len(r.output) + 1
-        while llm.has_work():
-            llm.step()
+        for _ in steps:
+            pass
 
     pts = {}
     for pb in points:

@@ -140,6 +140,18 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
   }
 }
 
+// tokens[i] = sampled[src[i]] where src[i] >= 0: a step whose input token is the one the previous
+// step sampled takes it on the device, before the host has read it.
+__global__ void take_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ src,
+                                   const int* __restrict__ sampled, int n, int n_sampled) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int s = src[i];
+  if (s >= 0 && s < n_sampled) tokens[i] = sampled[s];
+}
+
 template <typename T>
 int embed_gather(void* out, const void* table, const int* ids, int tokens, int hidden, int vocab,
                  int* status, void* stream) {
@@ -188,6 +200,13 @@ int silu_mul(void* out, const void* gu, int tokens, int inter, void* stream) {
 }
 
 }  // namespace ptl
+
+PTL_EXPORT int ptl_take_tokens(int* tokens, const int* src, const int* sampled, int n, int n_sampled, void* stream) {
+  PTL_REQUIRE(n >= 0 && n_sampled >= 0, "take_tokens: bad sizes n=%d sampled=%d", n, n_sampled);
+  if (n == 0) return 0;
+  return ptl::launch_kernel("take_tokens", ptl::take_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0,
+                            ptl::as_stream(stream), tokens, src, sampled, n, n_sampled);
+}
 
 PTL_EXPORT int ptl_embed_gather_f32(void* out, const void* table, const int* ids, int tokens, int hidden, int vocab, int* status, void* stream) {
   return ptl::embed_gather<float>(out, table, ids, tokens, hidden, vocab, status, stream);

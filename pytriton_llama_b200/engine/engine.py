@@ -32,6 +32,7 @@ class StepEntry:
     request: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    from_row: Optional[int] = None    # the single token is ``Engine.sampled[from_row]``, read on the device
 
 
 @dataclass
@@ -54,6 +55,7 @@ class _HostBatch:
     def __init__(self, entries, q_lens, starts, fresh, state_slots, slots_by_group, logit_rows):
         self.entries, self.q_lens, self.starts, self.fresh = entries, q_lens, starts, fresh
         self.state_slots, self.slots_by_group, self.logit_rows = state_slots, slots_by_group, logit_rows
+        self.takes_sampled = any(e.from_row is not None for e in entries)
         self.R = len(entries)
         self.T = sum(q_lens)
         self.max_q_len = max(q_lens)
@@ -79,7 +81,7 @@ class _Layout:
         self.max_tiles = max_tiles
         self.seg: Dict[str, tuple] = {}
         cursor = 0
-        names = [("tokens", T), ("positions", T), ("tok_req", T), ("q_start", R + 1), ("ctx_len", R),
+        names = [("tokens", T), ("token_src", T), ("positions", T), ("tok_req", T), ("q_start", R + 1), ("ctx_len", R),
                  ("state_slot", R), ("fresh", R), ("logit_rows", M), ("dec_items", T), ("pf_tiles", 4 * max_tiles)]
         for g in groups:
             names += [(f"slots{g}", T), (f"bt{g}", R * bt_width)]
@@ -140,6 +142,10 @@ class Engine:
         self.cache = CacheManager(entries, self.config.page_size, num_pages, self.config.max_num_seqs,
                                   self.config.max_seq_len, self.device, self.config.dtype)
         self._pinned = self.device.type == "cuda"
+        # Tokens sampled from the last step's logits rows, for callers that sample on the device and
+        # launch the next step before they have read them: an entry with ``from_row`` takes its
+        # token from here.
+        self.sampled = torch.zeros(max(1, self.config.max_num_seqs), dtype=torch.int32, device=self.device)
         self.steps_run = 0
         self._graphs = {}
 
@@ -181,7 +187,10 @@ class Engine:
                 raise ValueError(f"request {e.request!r} appears twice in one step")
             seen.add(e.request)
             toks = np.asarray(e.tokens)
-            if toks.size and (int(toks.min()) < 0 or int(toks.max()) >= self.vocab_size):
+            if e.from_row is not None:
+                if len(e.tokens) != 1 or not 0 <= int(e.from_row) < self.sampled.shape[0]:
+                    raise ValueError(f"request {e.request!r}: from_row names one sampled token, row 0..{self.sampled.shape[0] - 1}")
+            elif toks.size and (int(toks.min()) < 0 or int(toks.max()) >= self.vocab_size):
                 raise ValueError(f"a token of request {e.request!r} is outside the vocabulary of {self.vocab_size}")
             for w in e.want:
                 if not 0 <= int(w) < len(e.tokens):
@@ -225,6 +234,8 @@ class Engine:
         host = torch.empty(layout.size, dtype=torch.int32, pin_memory=self._pinned)
         self._fill(host.numpy(), layout, batch)
         dev = host.to(self.device, non_blocking=True)
+        if batch.takes_sampled:
+            self.ops.take_tokens(layout.view(dev, "tokens"), layout.view(dev, "token_src"), self.sampled)
         ctx, cache_view = self._context(dev, layout, batch.q_lens, [s + n for s, n in zip(starts, q_lens)],
                                         self._choose_splits(batch.T, max(s + n for s, n in zip(starts, q_lens))),
                                         n_decode=len(batch.dec_items), n_tiles=len(batch.pf_tiles) // 4)
@@ -251,6 +262,15 @@ class Engine:
             h[lo + len(values):lo + n] = fill
 
         put("tokens", np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in b.entries]))
+        lo, n = layout.seg["token_src"]
+        h[lo:lo + n] = -1
+        if b.takes_sampled:
+            t0 = 0
+            for e, k in zip(b.entries, b.q_lens):
+                if e.from_row is not None:
+                    h[lo + t0] = e.from_row
+                    h[layout.seg["tokens"][0] + t0] = 0
+                t0 += k
         put("positions", np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(b.starts, b.q_lens)]))
         put("tok_req", np.repeat(np.arange(R, dtype=np.int32), b.q_lens), fill=-1)
         put("q_start", np.concatenate([[0], np.cumsum(b.q_lens)]).astype(np.int32), fill=T)
@@ -343,7 +363,7 @@ class Engine:
         host = torch.empty(layout.size, dtype=torch.int32, pin_memory=True)
         h = host.numpy()
         h.fill(0)
-        for name, fill in [("tok_req", -1)] + [(f"slots{g}", -1) for g in layout.groups] + [(f"bt{g}", -1) for g in layout.groups]:
+        for name, fill in [("tok_req", -1), ("token_src", -1)] + [(f"slots{g}", -1) for g in layout.groups] + [(f"bt{g}", -1) for g in layout.groups]:
             lo, n = layout.seg[name]
             h[lo:lo + n] = fill
         for name in ("logit_rows", "dec_items"):
@@ -355,6 +375,7 @@ class Engine:
                                         n_decode=bucket, n_tiles=0)
 
         def run():
+            self.ops.take_tokens(layout.view(dev, "tokens"), layout.view(dev, "token_src"), self.sampled)
             return self.model.forward(layout.view(dev, "tokens"), ctx, cache_view, layout.view(dev, "logit_rows"))
         side = torch.cuda.Stream(self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))

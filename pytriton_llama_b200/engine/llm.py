@@ -10,6 +10,7 @@ safetensors files and there are no Triton kernels.
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Dict, Generator, Hashable, Iterable, List, Optional, Sequence, Tuple, Union
 
 import torch
@@ -18,7 +19,17 @@ from ..config.engine import EngineConfig
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .engine import Engine, StepEntry
-from .scheduler import Request, Scheduler
+from .scheduler import PENDING, Request, Scheduler, StepPlan
+
+
+@dataclass
+class _Launched:
+    """A step that runs on the device, and where its tokens will arrive on the host."""
+    plan: StepPlan
+    requests: List[Request]              # one per sampled row, in row order
+    host: Optional[torch.Tensor] = None  # int32 [2, rows]: tokens, bit patterns of the log-probabilities
+    event: object = None
+    logprobs: bool = False
 
 
 class LLM:
@@ -30,6 +41,13 @@ class LLM:
                                    cfg.max_seq_len, eos_token_ids=self.engine.eos_token_ids)
         self.sampler = Sampler(self.engine.ops, self.engine.device, seed=cfg.seed)
         self._next_id = 0
+        self._rows: Dict[Hashable, int] = {}     # request -> its row among the tokens sampled by the last launched step
+        self._turn = 0
+        self._staging = []
+        if self.engine.device.type == "cuda":
+            # where sampled tokens arrive on the host; a buffer is read before the launch after next reuses it
+            self._staging = [(torch.empty((2, cfg.max_num_seqs), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+                             for _ in range(3)]
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -47,28 +65,85 @@ class LLM:
         return self.scheduler.has_work()
 
     def step(self) -> Tuple[Dict[Hashable, int], List[Request]]:
-        """Runs one scheduled step.  Returns (request id -> new token, requests that finished)."""
-        plan = self.scheduler.schedule()
-        finished = list(plan.finished)
-        if not plan.portions:
-            if not finished and self.scheduler.has_work():
+        """Runs one scheduled step and reads its tokens.  Returns (request id -> new token, requests
+        that finished)."""
+        launched = self._launch()
+        if launched is None:
+            if self.scheduler.has_work():
                 raise RuntimeError("the scheduler found nothing to run although requests are pending")
-            return {}, finished
+            return {}, []
+        return self._collect(launched)
+
+    def run(self) -> Generator[Tuple[Dict[Hashable, int], List[Request]], None, None]:
+        """Steps until no request is left, yielding what ``step`` returns for every step.  With
+        ``overlap_steps`` the next step is planned and launched before the tokens of the last one are
+        read: a request that goes on takes its token on the device (``StepEntry.from_row``), so the
+        host's work runs beside the device's.  The tokens are the same either way; a request that a
+        stop token ends has by then run one step more, whose token is dropped."""
+        overlap = self.engine.config.overlap_steps
+        waiting_for: Optional[_Launched] = None
+        while waiting_for is not None or self.scheduler.has_work():
+            launched = self._launch()
+            if launched is None and waiting_for is None:
+                raise RuntimeError("the scheduler found nothing to run although requests are pending")
+            if waiting_for is not None:
+                yield self._collect(waiting_for)
+                waiting_for = None
+            if launched is not None and not overlap:
+                yield self._collect(launched)
+            else:
+                waiting_for = launched
+
+    def _launch(self) -> Optional[_Launched]:
+        plan = self.scheduler.schedule()
+        if not plan.portions:
+            return _Launched(plan, []) if plan.finished else None
         entries = []
         for p in plan.portions:
-            toks = p.request.tokens(p.start, p.length)
-            entries.append(StepEntry(p.request.id, toks, [p.length - 1] if p.sample else []))
+            req = p.request
+            if req.output and req.output[-1] == PENDING and p.start + p.length == len(req.prompt) + len(req.output):
+                if p.length != 1:
+                    raise RuntimeError(f"request {req.id!r}: a token that has not been read yet lies inside a longer portion")
+                entries.append(StepEntry(req.id, [0], [0], from_row=self._rows[req.id]))
+            else:
+                entries.append(StepEntry(req.id, req.tokens(p.start, p.length), [p.length - 1] if p.sample else []))
         out = self.engine.step(entries, validate=False)   # the plan was checked against the cache; tokens at intake
-        sampled: Dict[Hashable, int] = {}
-        logprobs: Dict[Hashable, Optional[float]] = {}
-        if out.rows:
-            reqs = [p.request for p in plan.portions if p.sample]
-            toks, lps = self.sampler.sample_with_logprobs(out.logits, [r.params for r in reqs], [r.number for r in reqs],
-                                                          [len(r.output) for r in reqs])
-            sampled = {r.id: t for r, t in zip(reqs, toks)}
-            logprobs = {r.id: lp for r, lp in zip(reqs, lps)}
-        finished += self.scheduler.update(plan, sampled, logprobs)
-        return sampled, finished
+        reqs = [p.request for p in plan.portions if p.sample]
+        launched = _Launched(plan, reqs)
+        if reqs:
+            n = len(reqs)
+            tokens, lp = self.sampler.sample_device(out.logits, [r.params for r in reqs], [r.number for r in reqs],
+                                                    [len(r.output) for r in reqs], out=self.engine.sampled[:n])
+            launched.logprobs = lp is not None
+            if self.engine.device.type == "cuda":
+                launched.host, launched.event = self._staging[self._turn % len(self._staging)]
+                self._turn += 1
+                launched.host[0, :n].copy_(tokens, non_blocking=True)
+                if lp is not None:
+                    launched.host[1, :n].view(torch.float32).copy_(lp, non_blocking=True)
+                launched.event.record(torch.cuda.current_stream(self.engine.device))
+            else:
+                launched.host = torch.stack([tokens.cpu(), (lp if lp is not None else torch.zeros(n)).cpu().view(torch.int32)])
+        self._rows = {r.id: i for i, r in enumerate(reqs)}
+        self.scheduler.advance(plan)
+        return launched
+
+    def _collect(self, launched: _Launched) -> Tuple[Dict[Hashable, int], List[Request]]:
+        finished = list(launched.plan.finished)
+        reqs = launched.requests
+        if not reqs:
+            return {}, finished + self.scheduler.resolve(launched.plan, {})[1]
+        if launched.event is not None:
+            launched.event.synchronize()
+        n = len(reqs)
+        tokens = launched.host[0, :n].tolist()
+        sampled = {r.id: t for r, t in zip(reqs, tokens)}
+        logprobs = None
+        if launched.logprobs:
+            values = launched.host[1, :n].view(torch.float32).tolist()
+            logprobs = {r.id: (v if r.params.logprobs else None) for r, v in zip(reqs, values)}
+        accepted, done = self.scheduler.resolve(launched.plan, sampled, logprobs)
+        return accepted, finished + done
 
     # ------------------------------------------------------------------ whole runs
     def generate(self, prompt_tokens: Sequence[Sequence[int]],
@@ -76,8 +151,8 @@ class LLM:
         """Generated token ids of every prompt (without the prompt), in the order given."""
         plist = self._params_list(params, len(prompt_tokens))
         reqs = [self.add_request(p, sp) for p, sp in zip(prompt_tokens, plist)]
-        while self.scheduler.has_work():
-            self.step()
+        for _ in self.run():
+            pass
         self.engine.check_device_status()
         return [list(r.output) for r in reqs]
 
@@ -92,8 +167,7 @@ class LLM:
         early = [(index[r.id], [], True) for r in reqs if r.status == "finished"]
         if early:
             yield early
-        while self.scheduler.has_work():
-            sampled, finished = self.step()
+        for sampled, finished in self.run():
             done = {r.id for r in finished}
             events = [(index[rid], [tok], rid in done) for rid, tok in sampled.items() if rid in index]
             events += [(index[r.id], [], True) for r in finished if r.id in index and r.id not in sampled]
@@ -154,8 +228,8 @@ class GenerateText(_TextMixin):
         lite_llama/generete_with_probs.py:87-96,154-165."""
         params = SamplingParams(temperature=temperature, top_p=top_p, max_gen_len=max_gen_len, logprobs=logprobs)
         reqs = [self.llm.add_request(p, params) for p in prompt_tokens]
-        while self.llm.has_work():
-            self.llm.step()
+        for _ in self.llm.run():
+            pass
         self.llm.engine.check_device_status()
         eos = self.llm.engine.eos_token_ids
         toks = [_trim(p, r.output, echo, eos) for p, r in zip(prompt_tokens, reqs)]

@@ -10,6 +10,14 @@ When pages run out for a request that is already running, the request admitted l
 pre-empted: its pages are given back, it returns to the front of the queue and later recomputes
 its prompt together with the tokens it had generated.  A request that could not fit even into an
 empty cache is finished with reason "cache_too_small" instead of waiting for ever.
+
+A step's outcome is recorded in two halves so that the next step can be planned and launched
+while the first one's tokens are still on the device: ``advance`` (right after the launch) counts
+the tokens as computed and puts a placeholder where the sampled token will go; ``resolve`` (once
+the token has been read) fills it in and ends the request if it was a stop token.  A request that
+is known to end with the token in flight (length limits) is set aside and not planned again; one
+that ends by a stop token may have run one more step by then, whose token is dropped.
+``update`` does both at once.
 """
 from __future__ import annotations
 
@@ -19,7 +27,8 @@ from typing import Deque, Dict, Hashable, List, Optional
 
 from ..sampling.params import SamplingParams
 
-WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+WAITING, RUNNING, DRAINING, FINISHED = "waiting", "running", "draining", "finished"
+PENDING = -1     # stands in ``Request.output`` for a token that was sampled but not read yet
 
 
 @dataclass
@@ -59,6 +68,7 @@ class Portion:
     start: int            # index into all_tokens
     length: int
     sample: bool          # True when the portion ends at the request's last token
+    out_index: int = -1   # where in ``request.output`` the sampled token goes (set by ``advance``)
 
 
 @dataclass
@@ -86,6 +96,7 @@ class Scheduler:
         self.eos_token_ids = set(eos_token_ids)
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []      # in admission order
+        self.draining: List[Request] = []     # their last token is in flight
         self._counter = 0
 
     # ------------------------------------------------------------------ intake
@@ -102,7 +113,7 @@ class Scheduler:
         return req
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self.draining)
 
     # ------------------------------------------------------------------ planning
     def _needs(self, req: Request, n: int):
@@ -164,7 +175,9 @@ class Scheduler:
                         n = max(1, n // 2)
                         needs, slots = self._needs(req, n)
                         continue
-                    if len(self.running) == 1 and not accepted:
+                    if self.draining:
+                        pass       # pages come back as soon as the tokens in flight have been read: wait a step
+                    elif len(self.running) == 1 and not accepted:
                         self.running.remove(req)
                         self.cache.release(req.id)
                         req.status, req.finish_reason = FINISHED, "cache_too_small"
@@ -198,32 +211,63 @@ class Scheduler:
         return plan
 
     # ------------------------------------------------------------------ after the step
-    def update(self, plan: StepPlan, sampled: Dict[Hashable, int],
-               logprobs: Optional[Dict[Hashable, Optional[float]]] = None) -> List[Request]:
-        """Records the step's progress; ``sampled`` has the new token of every portion with
-        ``sample`` set.  Returns the requests that finished (their pages are given back here)."""
-        done: List[Request] = []
+    def advance(self, plan: StepPlan) -> None:
+        """The plan has been launched: its tokens count as computed, and every portion with
+        ``sample`` set gets a placeholder for its token.  Requests that end with that token for a
+        reason known now (``max_gen_len``, ``max_seq_len``) are not planned again."""
         for p in plan.portions:
             req = p.request
             req.computed += p.length
             if not p.sample:
                 continue
-            tok = int(sampled[req.id])
-            req.output.append(tok)
-            if logprobs is not None and logprobs.get(req.id) is not None:
-                req.logprobs.append(float(logprobs[req.id]))
-            stop = self.eos_token_ids | set(req.params.stop_token_ids)
+            p.out_index = len(req.output)
+            req.output.append(PENDING)
             limit = req.params.max_gen_len
-            if tok in stop:
-                req.finish_reason = "stop"
-            elif limit is not None and len(req.output) >= limit:
+            if limit is not None and len(req.output) >= limit:
                 req.finish_reason = "length"
             elif len(req.prompt) + len(req.output) >= self.max_seq_len:
                 req.finish_reason = "max_seq_len"
             if req.finish_reason:
-                req.status = FINISHED
+                req.status = DRAINING
                 self.running.remove(req)
-                if self.cache.has(req.id):
-                    self.cache.release(req.id)
-                done.append(req)
-        return done
+                self.draining.append(req)
+
+    def resolve(self, plan: StepPlan, sampled: Dict[Hashable, int],
+                logprobs: Optional[Dict[Hashable, Optional[float]]] = None):
+        """The plan's tokens have been read: ``sampled`` has the new token of every portion with
+        ``sample`` set.  Returns (request id -> token for the tokens that count, requests that
+        finished); the pages of finished requests are given back here."""
+        accepted: Dict[Hashable, int] = {}
+        done: List[Request] = []
+        for p in plan.portions:
+            req = p.request
+            if not p.sample or req.status == FINISHED:
+                continue            # a request that a stop token ended one step earlier: the extra token is dropped
+            tok = int(sampled[req.id])
+            req.output[p.out_index] = tok
+            accepted[req.id] = tok
+            if logprobs is not None and logprobs.get(req.id) is not None:
+                req.logprobs.append(float(logprobs[req.id]))
+            if tok in self.eos_token_ids or tok in req.params.stop_token_ids:
+                req.finish_reason = "stop"
+                del req.output[p.out_index + 1:]
+            elif not (req.status == DRAINING and p.out_index == len(req.output) - 1):
+                continue
+            if req.status == DRAINING:
+                self.draining.remove(req)
+            elif req.status == RUNNING:
+                self.running.remove(req)
+            else:
+                self.waiting.remove(req)        # pre-empted while its token was in flight
+            req.status = FINISHED
+            if self.cache.has(req.id):
+                self.cache.release(req.id)
+            done.append(req)
+        return accepted, done
+
+    def update(self, plan: StepPlan, sampled: Dict[Hashable, int],
+               logprobs: Optional[Dict[Hashable, Optional[float]]] = None) -> List[Request]:
+        """``advance`` and ``resolve`` in one go, for callers that read the tokens before they plan
+        the next step.  Returns the requests that finished."""
+        self.advance(plan)
+        return self.resolve(plan, sampled, logprobs)[1]

@@ -69,6 +69,8 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_prefill_attention_tc_bf16.restype = _c_int
     lib.ptl_argmax.argtypes = [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
     lib.ptl_argmax.restype = _c_int
+    lib.ptl_take_tokens.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _ptr]
+    lib.ptl_take_tokens.restype = _c_int
     lib.ptl_token_logprob.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
     lib.ptl_token_logprob.restype = _c_int
     lib.ptl_sample.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
@@ -142,6 +144,13 @@ class CudaOps:
         self._check(fn(_p(out), _p(table), _p(ids), ids.shape[0], table.shape[1], table.shape[0],
                        _p(self._status), self._stream()))
         return out
+
+    def take_tokens(self, tokens: torch.Tensor, src: torch.Tensor, sampled: torch.Tensor) -> None:
+        """tokens[i] = sampled[src[i]] where src[i] >= 0, in place."""
+        for name, t in (("tokens", tokens), ("src", src), ("sampled", sampled)):
+            self._want(t, name, torch.int32)
+        self._check(self.lib.ptl_take_tokens(_p(tokens), _p(src), _p(sampled), tokens.shape[0], sampled.shape[0],
+                                             self._stream()))
 
     def bad_token_seen(self) -> bool:
         """True if an embedding lookup met an id outside the vocabulary since the last call (syncs)."""
@@ -407,11 +416,17 @@ class CudaOps:
         return out
 
     def sample(self, logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Optional[torch.Tensor],
-               u: Optional[torch.Tensor]) -> torch.Tensor:
-        """int32 token per row; rows with temperature <= 0 (or temperature None) take the argmax."""
+               u: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """int32 token per row (written to ``out`` if given); rows with temperature <= 0 (or
+        temperature None) take the argmax."""
         self._want(logits, "logits", torch.float32)
         rows, vocab = logits.shape
-        out = self.empty((rows,), torch.int32)
+        if out is None:
+            out = self.empty((rows,), torch.int32)
+        else:
+            self._want(out, "out", torch.int32)
+            if out.shape[0] != rows:
+                raise KernelError(f"sample: out has {out.shape[0]} rows, the logits {rows}")
         if temperature is None and rows <= 65535:
             scratch = self.empty((2, rows, 32), torch.float32)   # per row 32 best values, and (as int32) their indices
             self._check(self.lib.ptl_argmax(_p(out), _p(logits), _p(scratch[0]), _p(scratch[1]), rows, vocab, vocab,

@@ -30,26 +30,27 @@ class Sampler:
     def sample_with_logprobs(self, logits, params, request_numbers, token_indices):
         """(tokens, logprobs): ``logprobs[i]`` is log softmax(logits[i])[tokens[i]] of the unscaled
         logits (lite_llama/generete_with_probs.py:154-165) where ``params[i].logprobs`` is set, else None."""
-        tokens = self._sample_device(logits, params, request_numbers, token_indices)
-        if tokens is None:
+        if logits is None or logits.shape[0] == 0:
             return [], []
-        if any(p.logprobs for p in params):
-            lp = self.ops.token_logprobs(logits, tokens)
+        tokens, lp = self.sample_device(logits, params, request_numbers, token_indices)
+        if lp is not None:
             both = torch.stack([tokens.to(torch.float32), lp]).tolist()     # one read-back for both
             return [int(t) for t in both[0]], [v if p.logprobs else None for v, p in zip(both[1], params)]
         return tokens.tolist(), [None] * len(params)
 
-    def _sample_device(self, logits, params, request_numbers, token_indices):
+    def sample_device(self, logits, params, request_numbers, token_indices, out=None):
+        """The same without reading anything back: (int32 tokens on the device, written to ``out``
+        if given; float32 log-probabilities on the device, or None if no row asks for them)."""
         rows = logits.shape[0]
-        if rows == 0:
-            return None
         if all(p.temperature <= 0 for p in params):
-            return self.ops.sample(logits, None, None, None)
-        host = torch.empty((3, rows), dtype=torch.float32, pin_memory=self.device.type == "cuda")
-        for i, p in enumerate(params):
-            host[0, i] = p.temperature
-            host[1, i] = p.top_p
-            seed = self.seed if p.seed is None else p.seed
-            host[2, i] = uniform(seed, request_numbers[i], token_indices[i])
-        dev = host.to(self.device, non_blocking=True)
-        return self.ops.sample(logits, dev[0], dev[1], dev[2])
+            tokens = self.ops.sample(logits, None, None, None, out=out)
+        else:
+            host = torch.empty((3, rows), dtype=torch.float32, pin_memory=self.device.type == "cuda")
+            h = host.numpy()
+            for i, p in enumerate(params):
+                seed = self.seed if p.seed is None else p.seed
+                h[0, i], h[1, i], h[2, i] = p.temperature, p.top_p, uniform(seed, request_numbers[i], token_indices[i])
+            dev = host.to(self.device, non_blocking=True)
+            tokens = self.ops.sample(logits, dev[0], dev[1], dev[2], out=out)
+        lp = self.ops.token_logprobs(logits, tokens) if any(p.logprobs for p in params) else None
+        return tokens, lp

@@ -54,3 +54,50 @@ def test_step_refuses_bad_input_and_leaves_the_cache_alone(model_folders):
     assert out.logits is None and out.num_tokens == 3
     out = eng.step([StepEntry("a", [4], want=[0]), StepEntry("b", [], want=[])])
     assert out.logits.shape == (1, 256) and out.rows == [("a", 0)]
+
+
+def _llm(folder, name, pages, overlap, max_seq_len=96, max_num_seqs=4, budget=24):
+    from pytriton_llama_b200.engine.llm import LLM
+    cfg = EngineConfig(dtype="float32", page_size=PAGE_SIZE[name], max_gpu_num_blocks=pages, max_seq_len=max_seq_len,
+                       max_num_seqs=max_num_seqs, max_batched_tokens=budget, overlap_steps=overlap, seed=3)
+    return LLM(folder, cfg, device="cpu", ops=TorchOps())
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_overlapped_steps_generate_the_same_tokens(model_folders, name):
+    """Launching the next step before the last one's tokens are read changes nothing in what is
+    generated: greedy and sampled, with stop tokens that end requests early, limits known in
+    advance, and so few pages that requests are pre-empted and recomputed."""
+    from pytriton_llama_b200.sampling.params import SamplingParams
+    folder = model_folders(name)
+    vocab = TINY[name]["vocab_size"]
+    prompts = [random_tokens(n, vocab, 300 + i) for i, n in enumerate([7, 30, 3, 18, 11, 26])]
+    ps = PAGE_SIZE[name]
+    # greedy first, to find tokens that do occur and use them as stop tokens
+    base = _llm(folder, name, 64, overlap=False).generate(prompts, SamplingParams(temperature=0.0, max_gen_len=12))
+    stops = sorted({o[5] for o in base} | {base[0][2]})
+    settings = [SamplingParams(temperature=0.0, max_gen_len=12, stop_token_ids=stops),
+                SamplingParams(temperature=0.9, top_p=0.8, max_gen_len=9, stop_token_ids=stops[:1], logprobs=True),
+                SamplingParams(temperature=0.0, max_gen_len=1),
+                SamplingParams(temperature=0.0, max_gen_len=None)]           # runs into max_seq_len
+    preempted = 0
+    for pages in (64, -(-(30 + 12) // ps) + 3):                              # roomy; tight enough to pre-empt
+        for sp in settings:
+            runs = []
+            for overlap in (False, True):
+                llm = _llm(folder, name, pages, overlap, max_seq_len=48 if sp.max_gen_len is None else 96)
+                reqs = [llm.add_request(p, sp) for p in prompts]
+                steps = sum(1 for _ in llm.run())
+                runs.append(([list(r.output) for r in reqs], [r.finish_reason for r in reqs],
+                             [list(r.logprobs) for r in reqs], sum(r.preemptions for r in reqs)))
+                llm.engine.cache.check_invariants()
+                assert llm.engine.cache.free_pages() == pages and not llm.scheduler.has_work() and steps > 0
+                assert all(-1 not in r.output for r in reqs)
+            assert runs[0][:2] == runs[1][:2], (pages, sp)
+            for a, b in zip(runs[0][2], runs[1][2]):         # what else is in a batch moves the last bits of a logit
+                assert len(a) == len(b) and all(abs(x - y) < 1e-4 for x, y in zip(a, b)), (pages, sp)
+            if sp.logprobs:
+                assert [len(lp) for lp in runs[1][2]] == [len(o) for o in runs[1][0]]
+            preempted += runs[1][3] if pages < 64 else 0
+    assert preempted > 0, "the tight cache pre-empted nothing"
+    assert any(len(o) < 12 for o in _llm(folder, name, 64, True).generate(prompts, settings[0])), "no stop token ended a request"

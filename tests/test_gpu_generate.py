@@ -74,7 +74,7 @@ def test_greedy_generation_bfloat16(model_folders):
     folder = model_folders(name, torch.bfloat16)
     cfg, w = plain_llama.load_model_folder(folder, dtype=torch.float64)
     prompts = [random_tokens(n, 384, 400 + n) for n in (9, 33, 70)]
-    llm = _llm(folder, name, "bfloat16", pages=60)
+    llm = _llm(folder, name, "bfloat16", pages=60, compiled_model=True)     # overlapped steps, captured decode graphs
     got = llm.generate(prompts, SamplingParams(temperature=0.0, max_gen_len=8, stop_token_ids=[]))
     agree = 0
     for p, out in zip(prompts, got):
@@ -143,6 +143,38 @@ def test_generation_under_page_pressure_preempts_and_still_matches(model_folders
     while llm.has_work():
         llm.step()
     assert too_big.finish_reason == "cache_too_small"
+
+
+@pytest.mark.parametrize("dtype,name", [("float32", "A"), ("float32", "B")])
+def test_overlapped_steps_and_captured_graphs_change_no_token(model_folders, dtype, name):
+    """The next step launched before the last one's tokens are read (tokens handed over on the
+    device), with and without captured decode graphs, roomy and under page pressure: the same
+    tokens and finish reasons as stepping one at a time.  Stop tokens are ones that do occur."""
+    from pytriton_llama_b200.sampling import SamplingParams
+    folder = model_folders(name, stored_dtype(dtype))
+    vocab = TINY[name]["vocab_size"]
+    prompts = [random_tokens(n, vocab, 800 + n) for n in (17, 3, 29, 8, 12, 21)]
+    ps = PAGE_SIZE[name]
+    base = _llm(folder, name, dtype, pages=80, overlap_steps=False).generate(
+        prompts, SamplingParams(temperature=0.0, max_gen_len=14, stop_token_ids=[]))
+    stops = sorted({o[6] for o in base[:3]})
+    settings = [SamplingParams(temperature=0.0, max_gen_len=14, stop_token_ids=stops),
+                SamplingParams(temperature=0.7, top_p=0.9, max_gen_len=10, stop_token_ids=stops[:1], seed=5)]
+    for pages in (80, -(-(29 + 14) // ps) + 3):
+        for sp in settings:
+            runs = []
+            for overlap, graphs in ((False, False), (True, False), (True, True)):
+                llm = _llm(folder, name, dtype, pages=pages, overlap_steps=overlap, compiled_model=graphs)
+                reqs = [llm.add_request(p, sp) for p in prompts]
+                for _ in llm.run():
+                    pass
+                llm.engine.check_device_status()
+                llm.engine.cache.check_invariants()
+                assert llm.engine.cache.free_pages() == pages
+                runs.append(([list(r.output) for r in reqs], [r.finish_reason for r in reqs]))
+            assert runs[0] == runs[1] == runs[2], (pages, sp)
+            if sp.temperature == 0.0:
+                assert any(r == "stop" for r in runs[0][1])
 
 
 def test_command_line(model_folders, tmp_path):

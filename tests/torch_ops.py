@@ -98,9 +98,9 @@ class TorchOps:
                 out[t, h * d:(h + 1) * d] = torch.softmax(s, dim=0) @ v[:, h // group]
         return out.to(q.dtype)
 
-    def sample(self, logits, temperature, top_p, u):
+    def sample(self, logits, temperature, top_p, u, out=None):
         rows = logits.shape[0]
-        out = torch.empty(rows, dtype=torch.int32)
+        given, out = out, torch.empty(rows, dtype=torch.int32)
         for i in range(rows):
             t = 0.0 if temperature is None else float(temperature[i])
             x = logits[i].double()
@@ -116,7 +116,14 @@ class TorchOps:
             cdf = torch.cumsum(kept, 0)
             tok = int(torch.searchsorted(cdf, torch.tensor(float(u[i]) * float(cdf[-1]), dtype=cdf.dtype), right=True))
             out[i] = min(tok, int(torch.nonzero(keep)[-1]))
+        if given is not None:
+            given.copy_(out)
+            return given
         return out.to(logits.device)
+
+    def take_tokens(self, tokens, src, sampled):
+        pick = src >= 0
+        tokens[pick] = sampled[src[pick].long()]
 
     def token_logprobs(self, logits, tokens):
         lp = torch.log_softmax(logits.double(), dim=-1)
