@@ -45,17 +45,18 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   constexpr int kDecKeys = Cfg::kKeys;
   constexpr int kDecKP = KP;
   extern __shared__ __align__(128) unsigned char smem[];
-  pdl_wait();
-  pdl_launch_dependents();
+  // Everything up to the wait below reads only what the kernel directly before this one does not
+  // write: the step's integers, the block table, and keys and values of earlier positions (the
+  // predecessor writes q and the slot of position p).  So it runs under the predecessor's tail.
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
   const int split = blockIdx.x % splits;
   const int kvh = (blockIdx.x / splits) % nkv;
   const int ti = blockIdx.x / (splits * nkv);
-  const int t = items ? items[ti] : ti;
+  const int t = items ? __ldcg(items + ti) : ti;
   const int G = nq / nkv;
-  const int r = tok_req[t];
-  const int p = positions[t];
+  const int r = __ldcg(tok_req + t);
+  const int p = __ldcg(positions + t);
   const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   const int nkeys = r < 0 ? 0 : p - lo + 1;
   int chunk_keys = (nkeys + splits - 1) / splits;
@@ -74,24 +75,10 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   const int n_blocks = ntiles > 0 ? (k_end - 1) / page_size - first_block + 1 : 0;
   const bool staged = n_blocks <= kDecStagedPages;
   if (staged) {
-    for (int i = tid; i < n_blocks; i += kDecWarps * 32) s_pages[i] = bt_global[first_block + i];
+    for (int i = tid; i < n_blocks; i += kDecWarps * 32) s_pages[i] = __ldcg(bt_global + first_block + i);
     __syncthreads();
   }
   const int* bt = staged ? s_pages - first_block : bt_global;
-
-  // ---- query fragments: row g (and g+8) of the tile is query head kvh*G + g (zero beyond the group)
-  uint32_t qa[D / 16][4];
-  {
-    const __nv_bfloat16* qrow = q + (size_t)t * q_stride + (size_t)kvh * G * D;
-#pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-      const int col = ks * 16 + 2 * c;
-      qa[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col) : 0u;
-      qa[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col) : 0u;
-      qa[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col + 8) : 0u;
-      qa[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col + 8) : 0u;
-    }
-  }
 
   // ---- loader: 64 keys x D of K and of V per tile, 16 bytes per cp.async, zero fill past the range.
   // Thread `tid` always copies chunk tid % kChunks of rows tid / kChunks + i * (128 / kChunks).
@@ -133,10 +120,38 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
 
+  // the first tiles are requested before the wait when none of them holds position p
+  const int first_tiles = min(ntiles, Cfg::kStages - 1);
+  const bool early = first_tiles > 0 && k_begin + first_tiles * kDecKeys <= p;
+  if (early) {
 #pragma unroll
-  for (int s = 0; s < Cfg::kStages - 1; ++s) {
-    if (s < ntiles) load_tile(s, s);
-    cp_async_commit();
+    for (int s = 0; s < Cfg::kStages - 1; ++s) {
+      if (s < ntiles) load_tile(s, s);
+      cp_async_commit();
+    }
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+  // ---- query fragments: row g (and g+8) of the tile is query head kvh*G + g (zero beyond the group)
+  uint32_t qa[D / 16][4];
+  {
+    const __nv_bfloat16* qrow = q + (size_t)t * q_stride + (size_t)kvh * G * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int col = ks * 16 + 2 * c;
+      qa[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col) : 0u;
+      qa[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col) : 0u;
+      qa[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col + 8) : 0u;
+      qa[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col + 8) : 0u;
+    }
+  }
+
+  if (!early) {
+#pragma unroll
+    for (int s = 0; s < Cfg::kStages - 1; ++s) {
+      if (s < ntiles) load_tile(s, s);
+      cp_async_commit();
+    }
   }
   for (int tile = 0; tile < ntiles; ++tile) {
     cp_async_wait<Cfg::kStages - 2>();

@@ -9,14 +9,16 @@
 //   * few tokens (M <= 64, decoding): the operands are swapped -- row operand = W (128 features),
 //     column operand = X (tokens padded to 16/32/64) -- so the tensor core runs full rows while
 //     the kernel is a stream over the weights; the K range is split over the blocks of a thread-block
-//     cluster (blockIdx.y = rank in the cluster, up to 8); each block leaves its partial tile in its
-//     own shared memory, and after a cluster barrier every block adds one slice of the rows over
-//     all peers through distributed shared memory, in rank order, and runs the epilogue on it.
+//     cluster (blockIdx.y = rank in the cluster, up to 8); block z owns the rows z*128/S.. of the
+//     tile: every block sends its partial sums of those rows into the owner's shared memory
+//     (distributed shared memory stores), and after one cluster barrier the owner adds them up in
+//     rank order and runs the epilogue on them.
 //
 // Epilogues: 0 store bfloat16, 1 store float32, 2 add into a float32 residual [M,N] in place,
 // 3 SiLU(gate)*up where the rows of W alternate gate_j, up_j (out is [M, N/2] bfloat16).
 //
-// Warp roles (320 threads): warp 0 TMA producer, warp 1 TMEM allocation + MMA issue, warps 2..9
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 TMEM allocation + MMA issue (with few tokens
+// warps 6..8 issue too), warps 2..9
 // epilogue (warp w reads TMEM lanes 32*(w%4)..+31; with many tokens two warps share a lane quarter
 // and take half of the columns each).  With many tokens a block walks several tiles and keeps two
 // accumulators in TMEM, so the epilogue of one tile runs under the MMAs of the next.  Every wait on an mbarrier gives up after a
@@ -44,13 +46,25 @@ struct GemmParams {
 };
 
 template <int BN> struct TcCfg {
-  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : 4);   // few tokens: small blocks, several per SM
+  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN == 64 ? 3 : 4));   // few tokens: small blocks, two or three per SM
   static constexpr int kRowBytes = kTileRows * kTileK * 2;     // 16 KB
   static constexpr int kColBytes = BN * kTileK * 2;
   static constexpr int kStageBytes = kRowBytes + kColBytes;
   static constexpr int kAccBufs = BN >= 128 ? 2 : 1;           // many tokens: the epilogue of a tile overlaps the next tile's MMAs
-  static constexpr int kTmemCols = BN < 32 ? 32 : BN * kAccBufs;   // power of two >= 32
-  static constexpr int kSmem = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  // few tokens: an MMA of 128 x BN x 16 is short, and one thread that waits for a stage, issues its
+  // four MMAs and commits spends about 130 cycles per MMA, most of it on the wait; the tensor core
+  // takes 40.  So several warps issue: issuer j takes the stages j, j + ways, ... and has an
+  // accumulator of its own, and the epilogue adds the accumulators up.
+  // A stage must always be waited for by the same issuer: a wait for the second filling of a
+  // stage, made before its first filling has completed, would return at once (only the parity of
+  // the phase is compared).  Hence as many issuers as stages, or a divisor of their number.
+  static constexpr int kAccWays = BN >= 128 ? 1 : (BN == 64 ? 3 : 4);
+  static_assert(kStages % kAccWays == 0, "every stage belongs to one issuer");
+  static constexpr int kTmemCols = BN >= 128 ? BN * kAccBufs : (BN == 64 ? 256 : (BN * kAccWays < 32 ? 32 : BN * kAccWays));   // power of two >= 32
+  static constexpr int kPipeSmem = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  // few tokens, K split over a cluster: where the peers' partial sums of this block's rows arrive
+  static constexpr int kRecvBytes = BN < 128 ? BN * kTileRows * 4 : 0;
+  static constexpr int kSmem = kPipeSmem + kRecvBytes;
 };
 
 // SiLU for the bfloat16 path: the result is rounded to 8 bits of mantissa, so the fast
@@ -151,6 +165,23 @@ __device__ __forceinline__ void store_swapped_one(const GemmParams& p, int n, in
   else ((__nv_bfloat16*)p.out)[(size_t)tok * p.ld_out + n / 2] = __float2bfloat16_rn(silu_f(v) * up);
 }
 
+// 16 columns of this thread's TMEM lane, added over the issuers' accumulators; an issuer that had
+// no stage (fewer stages than issuers) left its accumulator unwritten.
+template <int BN, int WAYS>
+__device__ __forceinline__ void load_ways(uint32_t taddr, int stages, float (&v)[16]) {
+  uint32_t r[WAYS][16];
+#pragma unroll
+  for (int w = 0; w < WAYS; ++w) tmem_load_16_nowait(taddr + w * BN, r[w]);
+  tmem_wait_ld();
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < WAYS; ++w) acc += w < stages ? __uint_as_float(r[w][j]) : 0.f;
+    v[j] = acc;
+  }
+}
+
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col, const GemmParams p) {
@@ -187,7 +218,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 8); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), p.swapped ? Cfg::kAccWays : 1); mbar_init(acc_empty(b), 8); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_row) : "memory");
@@ -201,6 +232,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // blocks of a cluster write into each other's shared memory later on; none may do so before all
+  // of them run, which the wait that matches this arrival establishes
+  if (p.swapped && p.splits > 1) cluster_arrive();
 
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -215,10 +249,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
         tma_load_2d(smem_base + i * Cfg::kStageBytes, &map_row, full_bar(i), (kb0 + i) * kTileK, blockIdx.x * kTileRows);
       }
     }
-    pdl_wait();
+    pdl_wait();                // (the tokens of those stages are requested by the MMA issuers, each for its own stages)
     pdl_launch_dependents();
-    for (int i = 0; i < pre; ++i)
-      tma_load_2d(smem_base + i * Cfg::kStageBytes + Cfg::kRowBytes, &map_col, full_bar(i), (kb0 + i) * kTileK, 0);
     it = pre;
     bool ok = true;
     for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
@@ -241,8 +273,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
         for (uint32_t t = 0; t < (1u << 16) && !mbar_try_wait(full_bar(s), (i / Cfg::kStages) & 1); ++t) __nanosleep(100);
       }
     }
+  } else if (p.swapped && (warp == 1 || (warp >= 6 && warp - 5 < Cfg::kAccWays))) {
+    // ------------------------------------------------------------ MMA issuers, few tokens
+    pdl_wait();
+    pdl_launch_dependents();
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc_bf16(kTileRows, BN);
+      const int issuer = warp == 1 ? 0 : warp - 5;
+      const uint32_t acc = tmem_base + issuer * BN;
+      // the weights of the first ring of stages are on their way since before the wait; their tokens follow now
+      for (int i = issuer; i < min(my_kb, Cfg::kStages); i += Cfg::kAccWays)
+        tma_load_2d(smem_base + i * Cfg::kStageBytes + Cfg::kRowBytes, &map_col, full_bar(i), (kb0 + i) * kTileK, 0);
+      for (int i = issuer; i < my_kb; i += Cfg::kAccWays) {
+        const int s = i % Cfg::kStages;
+        if (!mbar_wait(full_bar(s), (i / Cfg::kStages) & 1, abort_flag, p.status, 2)) break;
+        tcgen05_fence_after();
+        const uint32_t a = smem_base + s * Cfg::kStageBytes;
+        const uint32_t b = a + Cfg::kRowBytes;
+#pragma unroll
+        for (int k = 0; k < kTileK / 16; ++k)
+          tcgen05_mma_bf16(acc, smem_desc_sw128(a + k * 32), smem_desc_sw128(b + k * 32), idesc, (i >= Cfg::kAccWays || k > 0) ? 1u : 0u);
+        tcgen05_commit(empty_bar(s));      // the stage is free once these MMAs have read it
+      }
+      tcgen05_commit(acc_full(0));         // this issuer's accumulator is complete (also when it had nothing to do)
+    }
   } else if (warp == 1 && lane == 0) {
-    // ------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------ MMA issuer, many tokens
     pdl_wait();
     pdl_launch_dependents();
     constexpr uint32_t idesc = instr_desc_bf16(kTileRows, BN);
@@ -332,26 +388,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
         }
       } else if (half == 1) {
         // few tokens: the tile has at most 64 columns, one warp per lane quarter does it all
+        // (warps 6.. issue MMAs instead; a warp that gets here only waits for the tile)
       } else if (p.splits == 1) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
-          uint32_t r[16];
-          tmem_load_16(acc + c0, r);
           float v[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = my_kb > 0 ? __uint_as_float(r[j]) : 0.f;
+          load_ways<BN, Cfg::kAccWays>(acc + c0, my_kb, v);
           store_swapped<EPI>(p, row, c0, v);
         }
       } else {
-        // partial tile -> own shared memory [column][128 rows] (the pipeline stages are idle by now)
-        float* part = reinterpret_cast<float*>(smem);
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 16) {
-          uint32_t r[16];
-          tmem_load_16(acc + c0, r);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) part[(c0 + j) * kTileRows + row_in_tile] = my_kb > 0 ? __uint_as_float(r[j]) : 0.f;
-        }
+        // K split over the cluster: the tile is sent to the owners of its rows below
       }
       // this warp has read its share of the buffer: one of the eight arrivals that free it
       tcgen05_fence_before();
@@ -359,40 +405,71 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       if (lane == 0) mbar_arrive(acc_empty(buf));
     }
   }
-  tcgen05_fence_before();
-  __syncthreads();
   if (p.swapped && p.splits > 1) {
-    // every block of the cluster has its partial tile in place
-    cluster_sync_all();
-    if (warp >= 2 && !*abort_flag) {
-      const int row_tile = blockIdx.x;
-      const int S = p.splits;
-      const int rows_per = kTileRows / S;                    // rows this block finishes (S is 2, 4 or 8)
-      const uint32_t part_addr = smem_base;
-      const int t = threadIdx.x - 64;                        // 0..255
-      if (EPI == 3) {
-        const int pairs = rows_per / 2;
-        for (int idx = t; idx < pairs * BN; idx += 256) {
-          const int pr = idx % pairs, col = idx / pairs;
-          const int rl = split * rows_per + 2 * pr;
-          float g = 0.f, u = 0.f;
-          for (int z = 0; z < S; ++z) {
-            g += ld_peer_f32(part_addr + 4u * (col * kTileRows + rl), z);
-            u += ld_peer_f32(part_addr + 4u * (col * kTileRows + rl + 1), z);
-          }
-          store_swapped_one<EPI>(p, row_tile * kTileRows + rl, col, g, u);
-        }
-      } else {
-        for (int idx = t; idx < rows_per * BN; idx += 256) {
-          const int rl = split * rows_per + idx % rows_per, col = idx / rows_per;
-          float v = 0.f;
-#pragma unroll 4
-          for (int z = 0; z < S; ++z) v += ld_peer_f32(part_addr + 4u * (col * kTileRows + rl), z);
-          store_swapped_one<EPI>(p, row_tile * kTileRows + rl, col, v, 0.f);
+    const int row_tile = blockIdx.x;
+    const int S = p.splits;
+    const int rows_per = kTileRows / S;                    // rows of the tile that each block owns (S is 2, 4 or 8)
+    float* recv = reinterpret_cast<float*>(smem + Cfg::kPipeSmem - 1024);      // [S sources][BN columns][rows_per]
+    cluster_wait();                                        // every block of the cluster runs
+    if (warp >= 2 && warp < 6 && !*abort_flag) {
+      // this thread's row of the tile goes to the block that owns it (neighbouring lanes write
+      // neighbouring words: wider stores of a row's columns would collide in the banks)
+      const int rl = (warp & 3) * 32 + lane;
+      const uint32_t acc = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+      const uint32_t dst = map_to_peer(smem_addr(recv) + 4u * ((split * BN) * rows_per + rl % rows_per), rl / rows_per);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        load_ways<BN, Cfg::kAccWays>(acc + c0, my_kb, v);
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) st_peer_f32(dst + 4u * ((c0 + jj) * rows_per), v[jj]);
+      }
+    }
+    tcgen05_fence_before();
+    const int group = EPI == 3 ? rows_per / 2 : rows_per;  // items per column: rows, or gate/up pairs
+    const int items = group * BN;
+    const int t = threadIdx.x - 64;                        // 0..255 in the epilogue warps
+    const bool worker = warp >= 2;
+    auto item_pos = [&](int idx, int& r, int& col) {
+      col = idx / group;
+      r = EPI == 3 ? 2 * (idx % group) : idx % group;
+    };
+    cluster_arrive();
+    float res0 = 0.f;                                      // what the add epilogue adds to, fetched under the barrier
+    if (EPI == 2 && worker && t < items) {
+      int r, col;
+      item_pos(t, r, col);
+      const int n = row_tile * kTileRows + split * rows_per + r;
+      if (n < p.rows && col < p.cols) res0 = __ldcg((const float*)p.out + (size_t)col * p.ld_out + n);
+    }
+    cluster_wait();                                        // the partial sums of this block's rows have arrived
+    if (worker && !*abort_flag) {
+      auto sum_sources = [&](int r, int col) {
+        float a[8];
+#pragma unroll
+        for (int z = 0; z < 8; ++z) a[z] = z < S ? recv[(z * BN + col) * rows_per + r] : 0.f;
+        float v = a[0];
+#pragma unroll
+        for (int z = 1; z < 8; ++z) v += a[z];
+        return v;
+      };
+      for (int idx = t; idx < items; idx += 256) {
+        int r, col;
+        item_pos(idx, r, col);
+        const int n = row_tile * kTileRows + split * rows_per + r;
+        const float v = sum_sources(r, col);
+        if (n >= p.rows || col >= p.cols) continue;
+        if (EPI == 2) {
+          float* o = (float*)p.out + (size_t)col * p.ld_out + n;
+          *o = (idx == t ? res0 : __ldcg(o)) + v;
+        } else {
+          store_swapped_one<EPI>(p, n, col, v, EPI == 3 ? sum_sources(r + 1, col) : 0.f);
         }
       }
     }
-    cluster_sync_all();                                      // nobody leaves while a peer still reads its tile
+  } else {
+    tcgen05_fence_before();
+    __syncthreads();
   }
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols) : "memory");
@@ -412,7 +489,7 @@ static int launch_tc(const CUtensorMap& mr, const CUtensorMap& mc, const GemmPar
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kGemmThreads);
-  cfg.dynamicSmemBytes = Cfg::kSmem;
+  cfg.dynamicSmemBytes = (p.swapped && p.splits > 1) ? Cfg::kSmem : Cfg::kPipeSmem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   int nattr = 0;

@@ -21,13 +21,13 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      T* __restrict__ cache, int nq, int nkv, int d, int rot,
                                      int page_size, int write_cache, long long num_slots, int vec2_ok) {
   extern __shared__ float cs[];            // cos[rot/2], sin[rot/2] of this token's angles
-  pdl_wait();
-  pdl_launch_dependents();
+  // positions, slots and frequencies are inputs of the step, not results of the kernel before this
+  // one: the angles are worked out while that kernel still runs
   const int t = blockIdx.x;
   const int row_len = (nq + 2 * nkv) * d;
   T* row = qkv + (size_t)t * row_len;
-  const float pos = (float)positions[t];
-  int slot = write_cache ? slots[t] : -1;
+  const float pos = (float)__ldcg(positions + t);
+  int slot = write_cache ? __ldcg(slots + t) : -1;
   if (slot >= num_slots) slot = -1;  // never write outside the pool
   const int page = slot >= 0 ? slot / page_size : 0;
   const int off = slot >= 0 ? slot % page_size : 0;
@@ -42,8 +42,10 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
       cs[j] = c;
       cs[half + j] = s;
     }
-    __syncthreads();
   }
+  pdl_wait();
+  pdl_launch_dependents();
+  __syncthreads();
   const int pairs_per_head = d - half;  // `half` rotated pairs, then d - rot pass-through elements
   if (vec2_ok) {
     // two neighbouring frequencies per thread: 4-byte (bfloat16) or 8-byte (float32) accesses
