@@ -3,9 +3,13 @@
 // m16n8k16 tile, so each key and value is fetched from HBM once for the whole group; the kernel
 // is a streaming read of the cache.  Four warps share 64-key tiles brought in by a ring of
 // cp.async stages (16 keys per warp and tile), keep their own running max / sum / accumulator in
-// float32 and are merged through shared memory at the end.  With splits > 1 the block writes an
-// unnormalised partial result; the block of a (token, kv head) that finishes last combines them
-// (or, without counters, the kernel `attention_merge` of attention_simt.cu does).
+// float32 and are merged through shared memory at the end.  With splits > 1 the partial results of
+// a (token, kv head) are combined in one of three ways: up to 8 splits with 128-key tiles form a
+// thread-block cluster, every warp sends its partial rows into the shared memory of the block
+// that owns the row (distributed shared memory), and after one cluster barrier the owners
+// finish them; otherwise the block writes an unnormalised partial result to global memory and
+// the block that finishes last combines them (or, without counters, the kernel `attention_merge`
+// of attention_simt.cu does).
 //
 // The token list `items` names the tokens of the step that take this path (nullptr: tokens
 // 0..n-1).  Token t of request r = tok_req[t] at position p sees keys max(0, p-window+1)..p;
@@ -40,11 +44,15 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
                         const int* __restrict__ block_table, const int* __restrict__ items,
                         const int* __restrict__ tok_req, const int* __restrict__ positions, int q_stride,
                         int out_stride, int bt_stride, int nq, int nkv, int page_size, float scale_log2,
-                        int window, int splits, int num_pages, int page_shift, int* __restrict__ counters) {
+                        int window, int splits, int num_pages, int page_shift, int* __restrict__ counters,
+                        int cluster_merge) {
   using Cfg = DecodeCfg<D, KP>;
   constexpr int kDecKeys = Cfg::kKeys;
   constexpr int kDecKP = KP;
   extern __shared__ __align__(128) unsigned char smem[];
+  // with a cluster, peers write into this block's shared memory later on: none may do so before
+  // every block runs, which the wait that matches this arrival establishes
+  if (cluster_merge) cluster_arrive();
   // Everything up to the wait below reads only what the kernel directly before this one does not
   // write: the step's integers, the block table, and keys and values of earlier positions (the
   // predecessor writes q and the slot of position p).  So it runs under the predecessor's tail.
@@ -242,6 +250,46 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   cp_async_wait<0>();
   __syncthreads();
 
+  if (cluster_merge) {
+    // ---- the splits of this (token, kv head) are the blocks of a cluster.  Row r of the group
+    // belongs to block r % splits; every warp of every block sends its partial row there:
+    // [splits * warps sources][rows owned][D accumulators, max, sum]
+    float* recv = reinterpret_cast<float*>(smem + Cfg::kSmem);
+    const int rows_own = (G + splits - 1) / splits;
+    constexpr int kRow = D + 2;
+    cluster_wait();
+    const int src = split * kDecWarps + warp;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = g + 8 * h;
+      if (row < G) {
+        const uint32_t dst = map_to_peer(smem_u32(recv) + 4u * ((src * rows_own + row / splits) * kRow), row % splits);
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) st_peer_f32x2(dst + 4u * (i * 8 + 2 * c), o[i][2 * h], o[i][2 * h + 1]);
+        if (c == 0) st_peer_f32x2(dst + 4u * D, m_run[h], l_run[h]);
+      }
+    }
+    cluster_arrive();
+    cluster_wait();
+    const int nsrc = splits * kDecWarps;
+    for (int e = tid; e < rows_own * D; e += kDecWarps * 32) {
+      const int rloc = e / D, col = e % D;
+      const int row = rloc * splits + split;
+      if (row >= G) continue;
+      float M = -INFINITY;
+      for (int sidx = 0; sidx < nsrc; ++sidx) M = fmaxf(M, recv[(sidx * rows_own + rloc) * kRow + D]);
+      float L = 0.f, acc = 0.f;
+      for (int sidx = 0; sidx < nsrc; ++sidx) {
+        const float* part = recv + (sidx * rows_own + rloc) * kRow;
+        const float wgt = part[D] == -INFINITY ? 0.f : dec_exp2(part[D] - M);
+        L += wgt * part[D + 1];
+        acc += wgt * part[col];
+      }
+      out[(size_t)t * out_stride + (size_t)(kvh * G + row) * D + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    }
+    return;
+  }
+
   // ---- merge the four warps through shared memory
   float* mo = reinterpret_cast<float*>(smem);                  // [warps][16][D]
   float* mml = mo + kDecWarps * 16 * D;                        // [warps][16][2]
@@ -302,10 +350,33 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   __threadfence();
   // partial results of the group's heads are contiguous: [G][splits][D] and [G][splits][2]
   const size_t idx0 = ((size_t)t * nq + (size_t)kvh * G) * splits;
-  float* w = reinterpret_cast<float*>(smem);                   // [G][splits] weights e^{m - M}
-  float* inv_l = w + G * splits;                               // [G]
-  float4* red = reinterpret_cast<float4*>(smem + (((size_t)(G * splits + 16) * 4 + 15) & ~(size_t)15));   // [z lanes][units of a pass]
-  for (int e = tid; e < G * splits; e += kDecWarps * 32) w[e] = __ldcg(part_ml + (idx0 + e) * 2);
+  float* w = reinterpret_cast<float*>(smem);                   // [G][splits] maxima m, then weights e^{m - M}
+  float* lz = w + G * splits;                                  // [G][splits] sums l
+  float* inv_l = lz + G * splits;                              // [G]
+  float4* red = reinterpret_cast<float4*>(smem + (((size_t)(2 * G * splits + 16) * 4 + 15) & ~(size_t)15));   // [z lanes][units of a pass]
+  constexpr int kD4 = D / 4;
+  const int units = G * kD4;                                   // (head, 4 dimensions)
+  const int zlanes = units >= kDecWarps * 32 ? 1 : (kDecWarps * 32) / units;
+  const int per_pass = (kDecWarps * 32) / zlanes;
+  const int ul = tid % per_pass, zl = tid / per_pass;
+  // every load of the merge that needs no weight is issued before anything is computed: the
+  // maxima and sums, and this thread's first partial accumulators (one round trip to L2, not several)
+  constexpr int kAhead = 4;
+  float4 ahead[kAhead];
+  {
+    const int gh = ul / kD4, d4 = ul % kD4;
+    const float4* src = reinterpret_cast<const float4*>(part_acc + (idx0 + (size_t)gh * splits) * D) + d4;
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i) {
+      const int z = zl + i * zlanes;
+      ahead[i] = (ul < units && zl < zlanes && z < splits) ? __ldcg(src + (size_t)z * kD4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  for (int e = tid; e < G * splits; e += kDecWarps * 32) {
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (idx0 + e) * 2));
+    w[e] = ml.x;
+    lz[e] = ml.y;
+  }
   __syncthreads();
   if (tid < G) {
     float M = -INFINITY;
@@ -314,25 +385,29 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     for (int z = 0; z < splits; ++z) {
       const float mz = w[tid * splits + z];
       const float wz = mz == -INFINITY ? 0.f : expf(mz - M);
-      L += wz * __ldcg(part_ml + (idx0 + tid * splits + z) * 2 + 1);
+      L += wz * lz[tid * splits + z];
       w[tid * splits + z] = wz;
     }
     inv_l[tid] = L > 0.f ? 1.0f / L : 0.f;
   }
   __syncthreads();
-  constexpr int kD4 = D / 4;
-  const int units = G * kD4;                                   // (head, 4 dimensions)
-  const int zlanes = units >= kDecWarps * 32 ? 1 : (kDecWarps * 32) / units;
-  const int per_pass = (kDecWarps * 32) / zlanes;
   for (int u0 = 0; u0 < units; u0 += per_pass) {
-    const int ul = tid % per_pass, zl = tid / per_pass;
     const int u = u0 + ul;
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
     if (u < units && zl < zlanes) {
       const int gh = u / kD4, d4 = u % kD4;
       const float4* src = reinterpret_cast<const float4*>(part_acc + (idx0 + (size_t)gh * splits) * D) + d4;
+      int z = zl;
+      if (u0 == 0) {
+#pragma unroll
+        for (int i = 0; i < kAhead; ++i, z += zlanes) {
+          if (z >= splits) break;
+          const float wz = w[gh * splits + z];
+          a.x = fmaf(wz, ahead[i].x, a.x); a.y = fmaf(wz, ahead[i].y, a.y); a.z = fmaf(wz, ahead[i].z, a.z); a.w = fmaf(wz, ahead[i].w, a.w);
+        }
+      }
 #pragma unroll 8
-      for (int z = zl; z < splits; z += zlanes) {
+      for (; z < splits; z += zlanes) {
         const float wz = w[gh * splits + z];
         const float4 v = __ldcg(src + (size_t)z * kD4);
         a.x = fmaf(wz, v.x, a.x); a.y = fmaf(wz, v.y, a.y); a.z = fmaf(wz, v.z, a.z); a.w = fmaf(wz, v.w, a.w);
@@ -377,11 +452,25 @@ int launch_decode(void* out, float* part_acc, float* part_ml, const void* q, con
   for (int b = 0; b < 20; ++b) if ((1 << b) == page_size) page_shift = b;
   const long long blocks = (long long)n_items * nkv * splits;
   PTL_REQUIRE(blocks <= 0x7fffffffLL, "decode_attention: too many blocks");
-  int rc = launch_kernel("decode_attention", decode_attention_kernel<D, KP>, dim3((unsigned)blocks), dim3(kDecWarps * 32),
-                         Cfg::kSmem, as_stream(stream), (__nv_bfloat16*)out, part_acc, part_ml, (const __nv_bfloat16*)q,
-                         (const __nv_bfloat16*)cache, block_table, items, tok_req, positions, q_stride, out_stride, bt_stride,
-                         nq, nkv, page_size, scale * 1.4426950408889634f, window, splits, num_pages, page_shift, counters);
+  // a cluster per (token, kv head) when its splits fit one and the rows they exchange are small
+  const int G = nq / nkv;
+  const size_t recv_bytes = (size_t)splits * kDecWarps * ((G + splits - 1) / splits) * (D + 2) * sizeof(float);
+  const bool cluster = KP == 2 && splits >= 2 && splits <= 8 && recv_bytes <= 16 * 1024;
+  static bool raised_cluster = false;
+  if (cluster && !raised_cluster) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D, KP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmem + 16 * 1024);
+    PTL_REQUIRE(e == cudaSuccess, "decode_attention: cannot raise shared memory: %s", cudaGetErrorString(e));
+    raised_cluster = true;
+  }
+  int rc = launch_kernel_cluster("decode_attention", decode_attention_kernel<D, KP>, dim3((unsigned)blocks), dim3(kDecWarps * 32),
+                                 Cfg::kSmem + (cluster ? recv_bytes : 0), as_stream(stream), cluster ? splits : 1,
+                                 (__nv_bfloat16*)out, part_acc, part_ml, (const __nv_bfloat16*)q,
+                                 (const __nv_bfloat16*)cache, block_table, items, tok_req, positions, q_stride, out_stride, bt_stride,
+                                 nq, nkv, page_size, scale * 1.4426950408889634f, window, splits, num_pages, page_shift, counters,
+                                 cluster ? 1 : 0);
   if (rc) return rc;
+  if (cluster) return 0;
   if (splits > 1 && counters == nullptr)
     rc = attention_merge_bf16(out, part_acc, part_ml, n_items, out_stride, nq, D, splits, items, stream);
   return rc;
@@ -406,6 +495,8 @@ PTL_EXPORT int ptl_decode_attention_bf16(void* out, float* part_acc, float* part
   PTL_REQUIRE(counters == nullptr || splits <= 512, "decode_attention: at most 512 splits with in-kernel merging");
   PTL_REQUIRE(aligned16(q) && aligned16(cache) && q_stride % 8 == 0, "decode_attention: q and cache must be 16-byte aligned");
   if (n_items == 0) return 0;
+  // the in-kernel merge keeps a maximum and a sum per (head of the group, split) in shared memory
+  if ((long long)(nq / nkv) * splits > 4096) counters = nullptr;
   // few blocks in flight: 128-key tiles; many: 64-key tiles and twice the blocks per SM
   const bool wide = (long long)n_items * nkv * splits <= 296;
 #define PTL_DECODE_ARGS out, part_acc, part_ml, q, cache, block_table, items, tok_req, positions, n_items, q_stride, \

@@ -128,23 +128,62 @@ inline int& pdl_flag() {
   return enabled;
 }
 
+// ---------------------------------------------------------------- thread-block clusters
+// Arrive and wait of the cluster barrier (every thread of every block takes part), the address of
+// a peer block's shared memory, and stores into it.
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_peer(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void st_peer_f32(uint32_t remote_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void st_peer_f32x2(uint32_t remote_addr, float a, float b) {
+  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(remote_addr), "f"(a), "f"(b) : "memory");
+}
+
 // Launches `kernel` on `stream`, as a programmatic dependent of the kernel before it when enabled.
+// `cluster_x` > 1 groups that many consecutive blocks (along x) into a thread-block cluster.
 template <typename... Params, typename... Args>
-inline int launch_kernel(const char* what, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
-                         cudaStream_t stream, Args&&... args) {
+inline int launch_kernel_cluster(const char* what, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, int cluster_x, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (pdl_flag()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_flag() ? 1 : 0;
+  cfg.numAttrs = n;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
   if (e != cudaSuccess) return fail("%s: %s", what, cudaGetErrorString(e));
   return check_launch(what);
+}
+
+template <typename... Params, typename... Args>
+inline int launch_kernel(const char* what, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                         cudaStream_t stream, Args&&... args) {
+  return launch_kernel_cluster(what, kernel, grid, block, smem, stream, 1, static_cast<Args&&>(args)...);
 }
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }

@@ -71,21 +71,6 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) 
                : "r"(taddr) : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void cluster_arrive() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void cluster_wait() {
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t map_to_peer(uint32_t local_addr, uint32_t rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  return remote;
-}
-__device__ __forceinline__ void st_peer_f32(uint32_t remote_addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_addr), "f"(v) : "memory");
-}
-
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16),
 // written by TMA with the 128-byte swizzle: groups of 8 rows are 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
