@@ -45,7 +45,8 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
                         const int* __restrict__ tok_req, const int* __restrict__ positions, int q_stride,
                         int out_stride, int bt_stride, int nq, int nkv, int page_size, float scale_log2,
                         int window, int splits, int num_pages, int page_shift, int* __restrict__ counters,
-                        int cluster_merge) {
+                        int cluster_merge, int fused, const float* __restrict__ inv_freq,
+                        const int* __restrict__ slots) {
   using Cfg = DecodeCfg<D, KP>;
   constexpr int kDecKeys = Cfg::kKeys;
   constexpr int kDecKP = KP;
@@ -87,6 +88,16 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     __syncthreads();
   }
   const int* bt = staged ? s_pages - first_block : bt_global;
+
+  // ---- with `fused` the kernel does the work of rope_kv_write for its single tokens itself: q is
+  // the unrotated projection; the angles of position p depend on nothing the predecessor writes
+  __shared__ float s_cs[D];                                   // cos[D/2], sin[D/2]
+  if (fused && inv_freq && tid < D / 2) {
+    float sn, cs;
+    sincosf((float)p * inv_freq[tid], &sn, &cs);             // as rope_kv_write_kernel does
+    s_cs[tid] = cs;
+    s_cs[D / 2 + tid] = sn;
+  }
 
   // ---- loader: 64 keys x D of K and of V per tile, 16 bytes per cp.async, zero fill past the range.
   // Thread `tid` always copies chunk tid % kChunks of rows tid / kChunks + i * (128 / kChunks).
@@ -140,6 +151,37 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   }
   pdl_wait();
   pdl_launch_dependents();
+  // With `fused`, the block whose key range ends at position p owns the token's new key and
+  // value: it rotates the key, sends both to the cache (for later steps; nothing in this step waits
+  // for that) and keeps them in shared memory to put them into its last tile, whose copy from the
+  // cache still holds what was in the slot before.
+  __shared__ __align__(16) __nv_bfloat16 s_new[2 * D];
+  bool owner = fused && slots && r >= 0 && ntiles > 0 && k_end == p + 1;
+  if (fused) __syncthreads();                                 // the angles are in place
+  if (owner) {
+    const int slot = __ldcg(slots + t);                       // the same for every thread of the block
+    owner = slot >= 0 && slot < (long long)num_pages * page_size;   // a layer that does not write reads the cache as it is
+    if (owner) {
+    const bool store = true;
+    const __nv_bfloat16* ksrc = q + (size_t)t * q_stride + (size_t)(nq + kvh) * D;
+    __nv_bfloat16* kdst = const_cast<__nv_bfloat16*>(cache) + ((size_t)(slot / page_size) * 2) * plane +
+                          ((size_t)kvh * page_size + slot % page_size) * D;
+    if (tid < D / 2) {
+      const float x1 = __bfloat162float(ksrc[tid]), x2 = __bfloat162float(ksrc[tid + D / 2]);
+      float o1 = x1, o2 = x2;
+      if (inv_freq) rope_rotate(x1, x2, s_cs[tid], s_cs[D / 2 + tid], o1, o2);
+      const __nv_bfloat16 b1 = __float2bfloat16_rn(o1), b2 = __float2bfloat16_rn(o2);
+      s_new[tid] = b1;
+      s_new[tid + D / 2] = b2;
+      if (store) { kdst[tid] = b1; kdst[tid + D / 2] = b2; }
+    } else if (tid - D / 2 < D / 8) {
+      const int ch = tid - D / 2;
+      const uint4 v = *reinterpret_cast<const uint4*>(ksrc + (size_t)nkv * D + ch * 8);
+      *reinterpret_cast<uint4*>(s_new + D + ch * 8) = v;
+      if (store) *reinterpret_cast<uint4*>(kdst + plane + ch * 8) = v;
+    }
+    }
+  }
   // ---- query fragments: row g (and g+8) of the tile is query head kvh*G + g (zero beyond the group)
   uint32_t qa[D / 16][4];
   {
@@ -151,6 +193,23 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
       qa[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col) : 0u;
       qa[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col + 8) : 0u;
       qa[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col + 8) : 0u;
+    }
+    if (fused && inv_freq) {
+      // element pairs (j, j + D/2) lie in the same thread: fragments ks and ks + D/32
+      constexpr int KH = D / 32;
+#pragma unroll
+      for (int ks = 0; ks < KH; ++ks) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int j = ks * 16 + (i >= 2 ? 8 : 0) + 2 * c;
+          const float2 a = unpack_bf16(qa[ks][i]), b = unpack_bf16(qa[ks + KH][i]);
+          float o1x, o2x, o1y, o2y;
+          rope_rotate(a.x, b.x, s_cs[j], s_cs[D / 2 + j], o1x, o2x);
+          rope_rotate(a.y, b.y, s_cs[j + 1], s_cs[D / 2 + j + 1], o1y, o2y);
+          qa[ks][i] = pack_bf16(o1x, o1y);
+          qa[ks + KH][i] = pack_bf16(o2x, o2y);
+        }
+      }
     }
   }
 
@@ -172,6 +231,16 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     const int stage = tile % Cfg::kStages;
     const uint32_t kbase = smem_base + stage * 2 * Cfg::kTileBytes;
     const uint32_t vbase = kbase + Cfg::kTileBytes;
+    if (owner && tile == ntiles - 1) {
+      // the token's own key and value take their place in the tile (row p of the range)
+      const int prow = p - (k_begin + tile * kDecKeys);
+      if (tid < 2 * Cfg::kChunks) {
+        const int ch = tid % Cfg::kChunks;
+        const uint4 v = *reinterpret_cast<const uint4*>(s_new + (tid / Cfg::kChunks) * D + ch * 8);
+        st_shared_16((tid < Cfg::kChunks ? kbase : vbase) + tile_offset<D>(prow, ch), v);
+      }
+      __syncthreads();
+    }
     const int row0 = warp * 16 * kDecKP;                      // this warp's keys of the tile
     // S = Q K^T: two n-tiles of 8 keys per group of 16
     float sc[kDecKP][2][4];
@@ -440,7 +509,8 @@ template <int D, int KP>
 int launch_decode(void* out, float* part_acc, float* part_ml, const void* q, const void* cache,
                   const int* block_table, const int* items, const int* tok_req, const int* positions, int n_items,
                   int q_stride, int out_stride, int bt_stride, int nq, int nkv, int page_size, float scale,
-                  int window, int splits, int num_pages, int* counters, void* stream) {
+                  int window, int splits, int num_pages, int* counters, void* stream, int fused,
+                  const float* inv_freq, const int* slots) {
   using Cfg = DecodeCfg<D, KP>;
   static bool raised = false;
   if (!raised) {
@@ -468,12 +538,41 @@ int launch_decode(void* out, float* part_acc, float* part_ml, const void* q, con
                                  (__nv_bfloat16*)out, part_acc, part_ml, (const __nv_bfloat16*)q,
                                  (const __nv_bfloat16*)cache, block_table, items, tok_req, positions, q_stride, out_stride, bt_stride,
                                  nq, nkv, page_size, scale * 1.4426950408889634f, window, splits, num_pages, page_shift, counters,
-                                 cluster ? 1 : 0);
+                                 cluster ? 1 : 0, fused, inv_freq, slots);
   if (rc) return rc;
   if (cluster) return 0;
   if (splits > 1 && counters == nullptr)
     rc = attention_merge_bf16(out, part_acc, part_ml, n_items, out_stride, nq, D, splits, items, stream);
   return rc;
+}
+
+}  // namespace ptl
+
+namespace ptl {
+
+static int decode_attention_entry(void* out, float* part_acc, float* part_ml, const void* q, const void* cache,
+                                  const int* block_table, const int* items, const int* tok_req, const int* positions,
+                                  int n_items, int q_stride, int out_stride, int bt_stride, int nq, int nkv, int d,
+                                  int page_size, float scale, int window, int splits, int num_pages, int* counters,
+                                  void* stream, int fused, const float* inv_freq, const int* slots) {
+  PTL_REQUIRE(n_items >= 0 && nq > 0 && nkv > 0 && page_size > 0 && num_pages > 0, "decode_attention: bad sizes");
+  PTL_REQUIRE(nq % nkv == 0, "decode_attention: %d query heads are no multiple of %d kv heads", nq, nkv);
+  if ((d != 64 && d != 128) || nq / nkv > 16) return -2;
+  PTL_REQUIRE(splits >= 1 && (splits == 1 || (part_acc && part_ml)), "decode_attention: splits > 1 need scratch buffers");
+  PTL_REQUIRE(counters == nullptr || splits <= 512, "decode_attention: at most 512 splits with in-kernel merging");
+  PTL_REQUIRE(aligned16(q) && aligned16(cache) && q_stride % 8 == 0, "decode_attention: q and cache must be 16-byte aligned");
+  PTL_REQUIRE(!fused || q_stride >= (nq + 2 * nkv) * d, "decode_attention: the fused form needs the whole q|k|v row, %d < %d", q_stride, (nq + 2 * nkv) * d);
+  if (n_items == 0) return 0;
+  // the in-kernel merge keeps a maximum and a sum per (head of the group, split) in shared memory
+  if ((long long)(nq / nkv) * splits > 4096) counters = nullptr;
+  // few blocks in flight: 128-key tiles; many: 64-key tiles and twice the blocks per SM
+  const bool wide = (long long)n_items * nkv * splits <= 296;
+#define PTL_DECODE_ARGS out, part_acc, part_ml, q, cache, block_table, items, tok_req, positions, n_items, q_stride, \
+                        out_stride, bt_stride, nq, nkv, page_size, scale, window, splits, num_pages, counters, stream, \
+                        fused, inv_freq, slots
+  if (d == 64) return wide ? launch_decode<64, 2>(PTL_DECODE_ARGS) : launch_decode<64, 1>(PTL_DECODE_ARGS);
+  return wide ? launch_decode<128, 2>(PTL_DECODE_ARGS) : launch_decode<128, 1>(PTL_DECODE_ARGS);
+#undef PTL_DECODE_ARGS
 }
 
 }  // namespace ptl
@@ -487,21 +586,23 @@ PTL_EXPORT int ptl_decode_attention_bf16(void* out, float* part_acc, float* part
                                          const int* positions, int n_items, int q_stride, int out_stride,
                                          int bt_stride, int nq, int nkv, int d, int page_size, float scale, int window,
                                          int splits, int num_pages, int* counters, void* stream) {
-  using namespace ptl;
-  PTL_REQUIRE(n_items >= 0 && nq > 0 && nkv > 0 && page_size > 0 && num_pages > 0, "decode_attention: bad sizes");
-  PTL_REQUIRE(nq % nkv == 0, "decode_attention: %d query heads are no multiple of %d kv heads", nq, nkv);
-  if ((d != 64 && d != 128) || nq / nkv > 16) return -2;
-  PTL_REQUIRE(splits >= 1 && (splits == 1 || (part_acc && part_ml)), "decode_attention: splits > 1 need scratch buffers");
-  PTL_REQUIRE(counters == nullptr || splits <= 512, "decode_attention: at most 512 splits with in-kernel merging");
-  PTL_REQUIRE(aligned16(q) && aligned16(cache) && q_stride % 8 == 0, "decode_attention: q and cache must be 16-byte aligned");
-  if (n_items == 0) return 0;
-  // the in-kernel merge keeps a maximum and a sum per (head of the group, split) in shared memory
-  if ((long long)(nq / nkv) * splits > 4096) counters = nullptr;
-  // few blocks in flight: 128-key tiles; many: 64-key tiles and twice the blocks per SM
-  const bool wide = (long long)n_items * nkv * splits <= 296;
-#define PTL_DECODE_ARGS out, part_acc, part_ml, q, cache, block_table, items, tok_req, positions, n_items, q_stride, \
-                        out_stride, bt_stride, nq, nkv, page_size, scale, window, splits, num_pages, counters, stream
-  if (d == 64) return wide ? launch_decode<64, 2>(PTL_DECODE_ARGS) : launch_decode<64, 1>(PTL_DECODE_ARGS);
-  return wide ? launch_decode<128, 2>(PTL_DECODE_ARGS) : launch_decode<128, 1>(PTL_DECODE_ARGS);
-#undef PTL_DECODE_ARGS
+  return ptl::decode_attention_entry(out, part_acc, part_ml, q, cache, block_table, items, tok_req, positions, n_items,
+                                     q_stride, out_stride, bt_stride, nq, nkv, d, page_size, scale, window, splits,
+                                     num_pages, counters, stream, 0, nullptr, nullptr);
+}
+
+// The same for steps of single tokens only, with the work of ptl_rope_kv_write folded in: `qkv` is
+// the unrotated projection [rows, (nq + 2 nkv) d]; every token's q and k are rotated by the angles
+// position * inv_freq[j] over the whole head (inv_freq == nullptr: not at all), and its k and v
+// are written to cache slot slots[row] before they are read (slots == nullptr or a negative slot:
+// not written).  The q part of `qkv` is left as it was.
+PTL_EXPORT int ptl_decode_attention_rope_bf16(void* out, float* part_acc, float* part_ml, const void* qkv, void* cache,
+                                              const int* block_table, const int* items, const int* tok_req,
+                                              const int* positions, int n_items, int q_stride, int out_stride,
+                                              int bt_stride, int nq, int nkv, int d, int page_size, float scale,
+                                              int window, int splits, int num_pages, int* counters,
+                                              const float* inv_freq, const int* slots, void* stream) {
+  return ptl::decode_attention_entry(out, part_acc, part_ml, qkv, cache, block_table, items, tok_req, positions, n_items,
+                                     q_stride, out_stride, bt_stride, nq, nkv, d, page_size, scale, window, splits,
+                                     num_pages, counters, stream, 1, inv_freq, slots);
 }

@@ -128,6 +128,13 @@ inline int& pdl_flag() {
   return enabled;
 }
 
+// One rotary pair: (x1, x2) turned by the angle whose cosine and sine are given.  Products and sums
+// are rounded one by one (no fused multiply-add), so that every kernel that rotates gets the same bits.
+__device__ __forceinline__ void rope_rotate(float x1, float x2, float c, float s, float& o1, float& o2) {
+  o1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
+  o2 = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
+}
+
 // ---------------------------------------------------------------- thread-block clusters
 // Arrive and wait of the cluster barrier (every thread of every block takes part), the address of
 // a peer block's shared memory, and stores into it.

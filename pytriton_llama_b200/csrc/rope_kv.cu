@@ -60,8 +60,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
       float o1a = x1a, o1b = x1b, o2a = x2a, o2b = x2b;
       if (inv_freq) {
         const float ca = cs[j], cb = cs[j + 1], sa = cs[half + j], sb = cs[half + j + 1];
-        o1a = x1a * ca - x2a * sa; o2a = x2a * ca + x1a * sa;
-        o1b = x1b * cb - x2b * sb; o2b = x2b * cb + x1b * sb;
+        rope_rotate(x1a, x2a, ca, sa, o1a, o2a);
+        rope_rotate(x1b, x2b, cb, sb, o1b, o2b);
       }
       V2 r1, r2;
       r1.x = from_f32<T>(o1a); r1.y = from_f32<T>(o1b);
@@ -96,9 +96,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
       const float x1 = to_f32(head[j]), x2 = to_f32(head[j + half]);
       float o1 = x1, o2 = x2;
       if (inv_freq) {
-        const float c = cs[j], s = cs[half + j];
-        o1 = x1 * c - x2 * s;
-        o2 = x2 * c + x1 * s;
+        rope_rotate(x1, x2, cs[j], cs[half + j], o1, o2);
       }
       const T r1 = from_f32<T>(o1), r2 = from_f32<T>(o2);
       head[j] = r1;

@@ -59,6 +59,10 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_decode_attention_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int,
                                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _ptr, _ptr]
     lib.ptl_decode_attention_bf16.restype = _c_int
+    lib.ptl_decode_attention_rope_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int,
+                                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _ptr,
+                                                   _ptr, _ptr, _ptr]
+    lib.ptl_decode_attention_rope_bf16.restype = _c_int
     lib.ptl_prefill_attention_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                _c_int, _c_int, _c_f, _c_int, _c_int, _ptr]
     lib.ptl_prefill_attention_bf16.restype = _c_int
@@ -362,12 +366,41 @@ class CudaOps:
                     kernels=2 if splits > 1 else 1)
         return out
 
+    def rope_attention(self, qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: int,
+                       slots: Optional[torch.Tensor], cache: torch.Tensor, block_table: torch.Tensor,
+                       tok_req: torch.Tensor, nq: int, nkv: int, d: int, page_size: int, scale: float,
+                       window: int = 0, splits: int = 1, hints=None, write: bool = True) -> torch.Tensor:
+        """``rope_kv_write`` followed by ``paged_attention``.  A bfloat16 step of single tokens only
+        runs both in the decode attention kernel (rotation over the whole head, head sizes 64 and
+        128); everything else takes the two kernels."""
+        fused = (os.environ.get("PTL_FUSED_ROPE", "1") != "0" and qkv.dtype == torch.bfloat16 and d in (64, 128)
+                 and nq // nkv <= 16 and hints is not None and getattr(hints, "decode_items", None) is not None
+                 and getattr(hints, "n_decode", 0) == qkv.shape[0] and not getattr(hints, "n_prefill_tiles", 0)
+                 and (inv_freq is None or rot == d) and qkv.shape[1] >= (nq + 2 * nkv) * d)
+        if not fused:
+            self.rope_kv_write(qkv, positions, inv_freq, rot, slots if write else None, cache if write else None,
+                               nq, nkv, d, page_size)
+            return self.paged_attention(qkv, cache, block_table, tok_req, positions, nq, nkv, d, page_size, scale,
+                                        window=window, splits=splits, hints=hints)
+        for name, t in (("qkv", qkv), ("cache", cache)):
+            self._want(t, name, torch.bfloat16)
+        for name, t in (("block_table", block_table), ("tok_req", tok_req), ("positions", positions)):
+            self._want(t, name, torch.int32)
+        if inv_freq is not None:
+            self._want(inv_freq, "inv_freq", torch.float32)
+        if write:
+            self._want(slots, "slots", torch.int32)
+        out = self.empty((qkv.shape[0], nq * d), qkv.dtype)
+        self._attention_tensor_cores(out, qkv, cache, block_table, tok_req, positions, nq, nkv, d, page_size, scale,
+                                     window, hints, rope=(inv_freq, slots if write else None))
+        return out
+
     DECODE_BLOCKS = int(os.environ.get("PTL_DECODE_BLOCKS", "592"))    # blocks the decode attention aims for: the four per SM that fit at once
 
     _DECODE_COUNTERS = 1 << 16
 
     def _attention_tensor_cores(self, out, q, cache, block_table, tok_req, positions, nq, nkv, d, page_size, scale,
-                                window, hints) -> None:
+                                window, hints, rope=None) -> None:
         """bfloat16 attention on the tensor cores: single tokens through the split-key decode kernel,
         longer portions through the tiled prompt kernel; both write their rows of ``out``."""
         stream = self._stream()
@@ -387,12 +420,18 @@ class CudaOps:
                     if getattr(self, "_decode_counters", None) is None:
                         self._decode_counters = torch.zeros(self._DECODE_COUNTERS, dtype=torch.int32, device=self.device)
                     counters = self._decode_counters        # the last block of a token's splits merges them in the kernel
-            self._check(self.lib.ptl_decode_attention_bf16(
-                _p(out), _p(part_acc), _p(part_ml), _p(q), _p(cache), _p(block_table),
-                None if getattr(hints, "decode_in_order", False) else _p(hints.decode_items), _p(tok_req),
-                _p(positions), hints.n_decode, q.shape[1], nq * d, block_table.shape[1], nq, nkv, d, page_size,
-                float(scale), int(window), splits, num_pages, _p(counters), stream),
-                kernels=2 if splits > 1 and counters is None else 1)
+            items = None if getattr(hints, "decode_in_order", False) else _p(hints.decode_items)
+            if rope is not None:
+                rc = self.lib.ptl_decode_attention_rope_bf16(
+                    _p(out), _p(part_acc), _p(part_ml), _p(q), _p(cache), _p(block_table), items, _p(tok_req),
+                    _p(positions), hints.n_decode, q.shape[1], nq * d, block_table.shape[1], nq, nkv, d, page_size,
+                    float(scale), int(window), splits, num_pages, _p(counters), _p(rope[0]), _p(rope[1]), stream)
+            else:
+                rc = self.lib.ptl_decode_attention_bf16(
+                    _p(out), _p(part_acc), _p(part_ml), _p(q), _p(cache), _p(block_table), items, _p(tok_req),
+                    _p(positions), hints.n_decode, q.shape[1], nq * d, block_table.shape[1], nq, nkv, d, page_size,
+                    float(scale), int(window), splits, num_pages, _p(counters), stream)
+            self._check(rc, kernels=2 if splits > 1 and counters is None and not (2 <= splits <= 8) else 1)
         if hints.n_prefill_tiles:
             if os.environ.get("PTL_PREFILL_TC", "1") != "0":
                 rc = self.lib.ptl_prefill_attention_tc_bf16(

@@ -71,12 +71,18 @@ class GQAttention(Part):
         if inv_freq is None and rot != 0:
             raise NotImplementedError("a position encoding without a rotary table must rotate q and k itself")
         g = cache.group
-        ops.rope_kv_write(qkv, ctx.positions, inv_freq, rot, g.slots if cache.write else None,
-                          cache.kv if cache.write else None, self.heads, self.kv_heads, self.head_dim,
-                          g.page_size)
-        o = ops.paged_attention(qkv, cache.kv, g.block_table, ctx.tok_req, ctx.positions, self.heads,
-                                self.kv_heads, self.head_dim, g.page_size, self.scale, window=self.window,
-                                splits=ctx.attn_splits, hints=ctx)
+        both = getattr(ops, "rope_attention", None)      # an operator set may run the two steps as one
+        if both is not None:
+            o = both(qkv, ctx.positions, inv_freq, rot, g.slots, cache.kv, g.block_table, ctx.tok_req, self.heads,
+                     self.kv_heads, self.head_dim, g.page_size, self.scale, window=self.window,
+                     splits=ctx.attn_splits, hints=ctx, write=cache.write)
+        else:
+            ops.rope_kv_write(qkv, ctx.positions, inv_freq, rot, g.slots if cache.write else None,
+                              cache.kv if cache.write else None, self.heads, self.kv_heads, self.head_dim,
+                              g.page_size)
+            o = ops.paged_attention(qkv, cache.kv, g.block_table, ctx.tok_req, ctx.positions, self.heads,
+                                    self.kv_heads, self.head_dim, g.page_size, self.scale, window=self.window,
+                                    splits=ctx.attn_splits, hints=ctx)
         if residual is not None:
             return ops.linear_add(o, self.w_o, residual)      # None when the product's epilogue did the add
         return ops.linear(o, self.w_o)

@@ -376,3 +376,44 @@ def test_kernels_refuse_sizes_they_cannot_take(ops):
         ops.embed(torch.zeros(2, dtype=torch.int32), torch.zeros(4, 4))       # CPU tensors: there is no CPU path
     with pytest.raises(KernelError, match="row buffer"):
         ops.add_rmsnorm(torch.zeros(1, 60000, device="cuda"), None, torch.ones(60000, device="cuda"), 1e-5)
+
+
+@pytest.mark.parametrize("nq, nkv, d, page, window, rotate", [(32, 8, 64, 16, 0, True), (8, 2, 128, 32, 0, True),
+                                                              (6, 3, 64, 8, 40, True), (4, 4, 64, 16, 0, False)])
+def test_decode_attention_with_rope_and_cache_write_folded_in(ops, nq, nkv, d, page, window, rotate):
+    """Single-token steps: the decode kernel that rotates q and k itself and writes k and v to the
+    cache gives the same output and the same cache as rope_kv_write followed by paged_attention,
+    for contexts that end at the start, in the middle and at the end of a page and of a key tile."""
+    from types import SimpleNamespace
+    lens = [1, 2, page, page + 1, 127, 128, 129, 300, 1025]
+    B = len(lens)
+    g = torch.Generator().manual_seed(d + nq)
+    pages_per = max(-(-n // page) for n in lens)
+    num_pages = B * pages_per + 3
+    bt = _random_paging(B, lens, page, num_pages, 5).cuda()
+    cache0 = (torch.randn(num_pages, 2, nkv, page, d, generator=g) * 0.5).bfloat16()
+    qkv0 = (torch.randn(B, (nq + 2 * nkv) * d, generator=g) * 0.7).bfloat16()
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32).cuda()
+    slots = torch.tensor([int(bt[i, (n - 1) // page]) * page + (n - 1) % page for i, n in enumerate(lens)], dtype=torch.int32).cuda()
+    tok_req = torch.arange(B, dtype=torch.int32).cuda()
+    inv = (1.0 / (10000.0 ** (torch.arange(0, d, 2).float() / d))).cuda() if rotate else None
+    hints = SimpleNamespace(n_decode=B, decode_items=tok_req, decode_in_order=True, n_prefill_tiles=0,
+                            prefill_tiles=tok_req, max_ctx_len=max(lens))
+    # the two kernels
+    qkv_a, cache_a = qkv0.clone().cuda(), cache0.clone().cuda()
+    ops.rope_kv_write(qkv_a, pos, inv, d if rotate else 0, slots, cache_a, nq, nkv, d, page)
+    want = ops.paged_attention(qkv_a, cache_a, bt, tok_req, pos, nq, nkv, d, page, d ** -0.5, window=window, hints=hints)
+    # one kernel
+    qkv_b, cache_b = qkv0.clone().cuda(), cache0.clone().cuda()
+    got = ops.rope_attention(qkv_b, pos, inv, d if rotate else 0, slots, cache_b, bt, tok_req, nq, nkv, d, page,
+                             d ** -0.5, window=window, hints=hints)
+    torch.cuda.synchronize()
+    assert torch.equal(cache_a, cache_b), "the cache differs"
+    assert torch.equal(qkv_b, qkv0.cuda()), "the fused form leaves the projection as it was"
+    assert (got.float() - want.float()).abs().max() <= 2 ** -7 * float(want.float().abs().max())
+    # a layer that only reads the cache (write=False) rotates q but writes nothing
+    cache_c = cache_a.clone()
+    got2 = ops.rope_attention(qkv0.clone().cuda(), pos, inv, d if rotate else 0, slots, cache_c, bt, tok_req, nq, nkv, d,
+                              page, d ** -0.5, window=window, hints=hints, write=False)
+    assert torch.equal(cache_c, cache_a)
+    assert (got2.float() - want.float()).abs().max() <= 2 ** -7 * float(want.float().abs().max())
