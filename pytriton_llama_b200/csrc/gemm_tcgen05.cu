@@ -43,6 +43,21 @@ struct GemmParams {
   int kb_per_split;
   int tiles_m;           // normal mode: tiles along the tokens and along the features
   int tiles_n;
+  // The add epilogue can prepare the RMS norm that follows it (all null otherwise): with r the
+  // new residual, xs = bfloat16(r * norm_w) [tokens, xs_ld] and sums of r^2 over slices of the
+  // row, sumsq [tokens, sumsq_ld]: a slot per 16 features with few tokens, per half tile with many.
+  __nv_bfloat16* xs;
+  const float* norm_w;
+  float* sumsq;
+  int xs_ld;
+  int sumsq_ld;
+  // A product whose token operand is such an xs finishes the norm: every output row is scaled by
+  // rsqrt(sum of the row's scale_slots slots * scale_inv_n + scale_eps) before the epilogue.
+  const float* scale_sumsq;
+  int scale_slots;
+  int scale_ld;
+  float scale_eps;
+  float scale_inv_n;
 };
 
 template <int BN> struct TcCfg {
@@ -61,7 +76,8 @@ template <int BN> struct TcCfg {
   static constexpr int kAccWays = BN >= 128 ? 1 : (BN == 64 ? 3 : 4);
   static_assert(kStages % kAccWays == 0, "every stage belongs to one issuer");
   static constexpr int kTmemCols = BN >= 128 ? BN * kAccBufs : (BN == 64 ? 256 : (BN * kAccWays < 32 ? 32 : BN * kAccWays));   // power of two >= 32
-  static constexpr int kPipeSmem = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int kBarBytes = 512;                        // barriers and TMEM slot, then 64 per-token scales
+  static constexpr int kPipeSmem = kStages * kStageBytes + 1024 /* alignment slack */ + kBarBytes;
   // few tokens, K split over a cluster: where the peers' partial sums of this block's rows arrive
   static constexpr int kRecvBytes = BN < 128 ? BN * kTileRows * 4 : 0;
   static constexpr int kSmem = kPipeSmem + kRecvBytes;
@@ -135,6 +151,33 @@ __device__ __forceinline__ void store_normal(const GemmParams& p, int row, int c
   }
 }
 
+// The sum over the 16 lanes of a half warp (all lanes of the warp take part).
+__device__ __forceinline__ float half_warp_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 8);
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v;
+}
+
+// The add epilogue for one feature n and token tok with few tokens; `have` is what the residual
+// held if the caller fetched it already.  With p.xs the next norm's input goes out too; every lane of the
+// warp must call this, the lanes of a half warp with the same token and 16 consecutive features.
+__device__ __forceinline__ void add_and_emit(const GemmParams& p, int n, int tok, float v, bool fetched, float have, int lane) {
+  const bool valid = n < p.rows && tok < p.cols;
+  float r = 0.f;
+  if (valid) {
+    float* o = (float*)p.out + (size_t)tok * p.ld_out + n;
+    r = (fetched ? have : __ldcg(o)) + v;
+    *o = r;
+    if (p.xs) p.xs[(size_t)tok * p.xs_ld + n] = __float2bfloat16_rn(r * __ldg(p.norm_w + n));
+  }
+  if (p.xs) {
+    const float sq = half_warp_sum(r * r);
+    if ((lane & 15) == 0 && valid) p.sumsq[(size_t)tok * p.sumsq_ld + n / 16] = sq;
+  }
+}
+
 // Swapped mode: `row` is a feature n, columns c0..c0+15 are tokens.
 template <int EPI>
 __device__ __forceinline__ void store_swapped(const GemmParams& p, int row, int c0, const float (&v)[16]) {
@@ -147,10 +190,11 @@ __device__ __forceinline__ void store_swapped(const GemmParams& p, int row, int 
       const float up = __shfl_down_sync(0xffffffffu, v[j], 1);   // odd rows hold up_j; all lanes take part
       if (n_ok && tok < p.cols && (n & 1) == 0)
         ((__nv_bfloat16*)p.out)[(size_t)tok * p.ld_out + n / 2] = __float2bfloat16_rn(silu_f(v[j]) * up);
+    } else if (EPI == 2) {
+      add_and_emit(p, n, tok, v[j], false, 0.f, threadIdx.x & 31);
     } else if (n_ok && tok < p.cols) {
       if (EPI == 0) ((__nv_bfloat16*)p.out)[(size_t)tok * p.ld_out + n] = __float2bfloat16_rn(v[j]);
-      else if (EPI == 1) ((float*)p.out)[(size_t)tok * p.ld_out + n] = v[j];
-      else ((float*)p.out)[(size_t)tok * p.ld_out + n] += v[j];
+      else ((float*)p.out)[(size_t)tok * p.ld_out + n] = v[j];
     }
   }
 }
@@ -193,6 +237,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
   // bars: [0,S) stage full, [S,2S) stage empty, then accumulator full[2], accumulator empty[2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* s_scale = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes + 256);   // few tokens: scale of each token
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (p.K + kTileK - 1) / kTileK;
@@ -335,6 +380,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     const int quad = warp & 3;                 // TMEM lanes 32*quad.. belong to this warp
     const int half = (warp - 2) >> 2;          // with many tokens, which half of the tile's columns it handles
     const int row_in_tile = quad * 32 + lane;
+    if (BN < 128 && p.swapped && p.scale_sumsq && half == 0) {
+      // few tokens: the scale of every token, summed over its slots by 128 / BN threads each
+      constexpr int kPer = BN < 128 ? 128 / BN : 1;
+      const int tok = row_in_tile / kPer, part = row_in_tile % kPer;
+      float sum = 0.f;
+      if (tok < p.cols) {
+        const float* src = p.scale_sumsq + (size_t)tok * p.scale_ld;
+        if (p.scale_ld % 4 == 0 && p.scale_slots % 4 == 0) {
+          const float4* src4 = reinterpret_cast<const float4*>(src);
+#pragma unroll 4
+          for (int k = part; k < p.scale_slots / 4; k += kPer) {
+            const float4 q4 = __ldcg(src4 + k);
+            sum += (q4.x + q4.y) + (q4.z + q4.w);
+          }
+        } else {
+          for (int k = part; k < p.scale_slots; k += kPer) sum += __ldcg(src + k);
+        }
+      }
+#pragma unroll
+      for (int o = kPer / 2; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (part == 0) s_scale[tok] = tok < p.cols ? rsqrtf(sum * p.scale_inv_n + p.scale_eps) : 0.f;
+      asm volatile("bar.sync 1, 128;" ::: "memory");           // the four warps that read the table
+    }
     int lt = 0;
     for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++lt) {
       int row_tile, col_tile;
@@ -353,6 +421,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
         for (int j = 0; j < 8; ++j) ahead[j] = col_tile * BN + c0 + 4 * j < p.cols ? __ldcg(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
       };
       if (can_prefetch) prefetch(half * kHalfCols);
+      float row_scale = 1.f;                   // many tokens: this thread's token
+      if (!p.swapped && p.scale_sumsq && row < p.rows) {
+        float sum = 0.f;
+        for (int k = 0; k < p.scale_slots; ++k) sum += __ldcg(p.scale_sumsq + (size_t)row * p.scale_ld + k);
+        row_scale = rsqrtf(sum * p.scale_inv_n + p.scale_eps);
+      }
+      float ss = 0.f;                          // sum of squares of this thread's share of its row (add epilogue, emitting)
       if (!mbar_wait(acc_full(buf), use & 1, abort_flag, p.status, 3)) break;
       tcgen05_fence_after();
       const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
@@ -375,6 +450,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
                 t.x += __uint_as_float(r[4 * j]); t.y += __uint_as_float(r[4 * j + 1]);
                 t.z += __uint_as_float(r[4 * j + 2]); t.w += __uint_as_float(r[4 * j + 3]);
                 *reinterpret_cast<float4*>(o + 4 * j) = t;
+                if (p.xs) {
+                  const float4 w4 = __ldg(reinterpret_cast<const float4*>(p.norm_w + col_tile * BN + c0) + j);
+                  uint2 pk;
+                  __nv_bfloat162 lo = __floats2bfloat162_rn(t.x * w4.x, t.y * w4.y), hi = __floats2bfloat162_rn(t.z * w4.z, t.w * w4.w);
+                  pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                  pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                  *reinterpret_cast<uint2*>(p.xs + (size_t)row * p.xs_ld + col_tile * BN + c0 + 4 * j) = pk;
+                  ss += t.x * t.x; ss += t.y * t.y; ss += t.z * t.z; ss += t.w * t.w;
+                }
               }
             }
             continue;
@@ -382,10 +466,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = my_kb > 0 ? __uint_as_float(r[16 * h + j]) : 0.f;
+            for (int j = 0; j < 16; ++j) v[j] = my_kb > 0 ? __uint_as_float(r[16 * h + j]) * row_scale : 0.f;
             store_normal<EPI>(p, row, col_tile * BN + c0 + 16 * h, v);
           }
         }
+        if (can_prefetch && p.xs) p.sumsq[(size_t)row * p.sumsq_ld + col_tile * 2 + half] = ss;
       } else if (half == 1) {
         // few tokens: the tile has at most 64 columns, one warp per lane quarter does it all
         // (warps 6.. issue MMAs instead; a warp that gets here only waits for the tile)
@@ -394,6 +479,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
         for (int c0 = 0; c0 < BN; c0 += 16) {
           float v[16];
           load_ways<BN, Cfg::kAccWays>(acc + c0, my_kb, v);
+          if (p.scale_sumsq) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] *= s_scale[c0 + j];
+          }
           store_swapped<EPI>(p, row, c0, v);
         }
       } else {
@@ -457,13 +546,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
         int r, col;
         item_pos(idx, r, col);
         const int n = row_tile * kTileRows + split * rows_per + r;
-        const float v = sum_sources(r, col);
-        if (n >= p.rows || col >= p.cols) continue;
+        const float sc = p.scale_sumsq ? s_scale[col] : 1.f;
+        const float v = sum_sources(r, col) * sc;
         if (EPI == 2) {
-          float* o = (float*)p.out + (size_t)col * p.ld_out + n;
-          *o = (idx == t ? res0 : __ldcg(o)) + v;
+          add_and_emit(p, n, col, v, idx == t, res0, lane);     // (every lane: the sums of squares are added over half warps)
         } else {
-          store_swapped_one<EPI>(p, n, col, v, EPI == 3 ? sum_sources(r + 1, col) : 0.f);
+          store_swapped_one<EPI>(p, n, col, v, EPI == 3 ? sum_sources(r + 1, col) * sc : 0.f);
         }
       }
     }
@@ -528,8 +616,18 @@ static int launch_epi(int epi, const CUtensorMap& mr, const CUtensorMap& mc, con
 // out: epi 0 bf16 [M,N]; 1 float32 [M,N]; 2 float32 [M,N] added to in place; 3 bf16 [M,N/2].
 // Returns -2 when the sizes are not ones this kernel takes (K % 8 != 0 or K < 64), so that the caller
 // can use another product.  `splits_hint` > 0 forces the number of K splits when M <= 64 (1, 2, 4 or 8).
-PTL_EXPORT int ptl_gemm_tc_bf16(void* out, const void* X, const void* W, int M, int N, int K, int ld_out, int epi,
-                                int* status, int splits_hint, void* stream) {
+//
+// Around an RMS norm: with `xs` (bf16 [M,N]), `norm_w` (float32 [N]) and `sumsq` (float32 [M, sumsq_ld],
+// sumsq_ld >= ceil(N/16)) the add epilogue also writes the next norm's input, xs = bfloat16(new
+// residual * norm_w), and sums of squares of the new residual over slices of each row; *slots_out
+// says how many slots a row got.  A later product that takes this xs as X and is given `scale_sumsq`
+// (that array), `scale_slots`, `scale_ld` and `scale_eps` multiplies every output row by
+// rsqrt(sum of the row's slots / K + eps), which completes the norm (epi 0, 1 and 3).  -2 is also
+// returned when what was asked for around the norm cannot be done for these sizes.
+PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, int M, int N, int K, int ld_out, int epi,
+                                     int* status, int splits_hint, void* xs, const float* norm_w, float* sumsq,
+                                     int sumsq_ld, int* slots_out, const float* scale_sumsq, int scale_slots,
+                                     int scale_ld, float scale_eps, void* stream) {
   using namespace ptl;
   PTL_REQUIRE(M >= 0 && N > 0 && K > 0 && ld_out > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
   if (K % 8 != 0 || K < kTileK) return -2;
@@ -539,6 +637,18 @@ PTL_EXPORT int ptl_gemm_tc_bf16(void* out, const void* X, const void* W, int M, 
   GemmParams p{};
   p.out = out; p.status = status;
   p.K = K; p.ld_out = ld_out;
+  if (xs) {
+    if (epi != 2 || N % 32 != 0 || ld_out % 4 != 0) return -2;
+    PTL_REQUIRE(norm_w && sumsq && slots_out, "gemm_tc: the next norm's input needs its weight, the sums and a place for their count");
+    PTL_REQUIRE(aligned16(xs) && aligned16(norm_w) && sumsq_ld >= (N + 15) / 16, "gemm_tc: xs and norm_w must be 16-byte aligned, sumsq_ld >= N/16");
+    p.xs = (__nv_bfloat16*)xs; p.norm_w = norm_w; p.sumsq = sumsq; p.xs_ld = N; p.sumsq_ld = sumsq_ld;
+  }
+  if (scale_sumsq) {
+    if (epi == 2) return -2;
+    PTL_REQUIRE(scale_slots > 0 && scale_ld >= scale_slots && scale_eps > 0.f, "gemm_tc: bad row scale arguments");
+    p.scale_sumsq = scale_sumsq; p.scale_slots = scale_slots; p.scale_ld = scale_ld; p.scale_eps = scale_eps;
+    p.scale_inv_n = 1.0f / (float)K;
+  }
   const int num_kb = (K + kTileK - 1) / kTileK;
   CUtensorMap mr, mc;
   cudaStream_t s = as_stream(stream);
@@ -552,6 +662,7 @@ PTL_EXPORT int ptl_gemm_tc_bf16(void* out, const void* X, const void* W, int M, 
     const int bn = wide ? 256 : 128;
     p.tiles_m = (M + kTileRows - 1) / kTileRows;
     p.tiles_n = (N + bn - 1) / bn;
+    if (slots_out) *slots_out = p.tiles_n * 2;
     static int sm_count = 0;
     if (!sm_count) {
       int dev = 0;
@@ -581,9 +692,16 @@ PTL_EXPORT int ptl_gemm_tc_bf16(void* out, const void* X, const void* W, int M, 
   rc = make_map(&mc, X, M, K, bn);
   if (rc) return rc;
   dim3 grid(row_tiles, splits);
+  if (slots_out) *slots_out = (N + 15) / 16;
   switch (bn) {
     case 16: return launch_epi<16>(epi, mr, mc, p, grid, s);
     case 32: return launch_epi<32>(epi, mr, mc, p, grid, s);
     default: return launch_epi<64>(epi, mr, mc, p, grid, s);
   }
+}
+
+PTL_EXPORT int ptl_gemm_tc_bf16(void* out, const void* X, const void* W, int M, int N, int K, int ld_out, int epi,
+                                int* status, int splits_hint, void* stream) {
+  return ptl_gemm_tc_bf16_norm(out, X, W, M, N, K, ld_out, epi, status, splits_hint, nullptr, nullptr, nullptr, 0, nullptr,
+                               nullptr, 0, 0, 0.f, stream);
 }

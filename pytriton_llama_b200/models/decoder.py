@@ -79,8 +79,14 @@ class DecoderModel:
         ops = self.rt.ops
         x = ops.embed(token_ids, self.embedding)
         residual = None
-        for e in self.spec.run_order:
-            x, residual = self.blocks[e.layer].forward(x, residual, ctx, cache_views(e.cache, e.write))
+        run = self.spec.run_order
+        for i, e in enumerate(run):
+            block = self.blocks[e.layer]
+            kw = {}
+            if i + 1 < len(run) and getattr(block, "takes_next_norm", False):
+                # the norm that reads the residual after this block (the final norm selects rows and does its own work)
+                kw["next_norm"] = getattr(self.blocks[run[i + 1].layer], "norm1", None)
+            x, residual = block.forward(x, residual, ctx, cache_views(e.cache, e.write), **kw)
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         y, _ = self.final_norm.forward(x, residual, rows=logit_rows)

@@ -33,6 +33,29 @@ _SIGNATURES = {
 _GEMM_SIG = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr]
 
 
+class NormedActivation:
+    """The input of an RMS norm whose normalisation is still to be done by the product that reads it:
+    ``xs`` = bfloat16(residual * weight) [tokens, width] and, per token, ``slots`` partial sums of
+    residual^2 in ``sumsq``.  The row scale rsqrt(sum / width + eps) is applied by the consumer."""
+    __slots__ = ("xs", "sumsq", "slots", "eps", "weight")
+
+    def __init__(self, xs, sumsq, slots, eps, weight):
+        self.xs, self.sumsq, self.slots, self.eps, self.weight = xs, sumsq, slots, eps, weight
+
+    @property
+    def shape(self):
+        return self.xs.shape
+
+    @property
+    def dtype(self):
+        return self.xs.dtype
+
+    def materialise(self) -> torch.Tensor:
+        """The normed activation as a plain tensor (for consumers that cannot apply the scale)."""
+        scale = torch.rsqrt(self.sumsq[:, :self.slots].sum(dim=1) / self.xs.shape[1] + self.eps)
+        return (self.xs.float() * scale[:, None]).to(self.xs.dtype)
+
+
 class KernelError(RuntimeError):
     """A launcher refused its arguments or CUDA reported an error."""
 
@@ -68,6 +91,9 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_prefill_attention_bf16.restype = _c_int
     lib.ptl_gemm_tc_bf16.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr]
     lib.ptl_gemm_tc_bf16.restype = _c_int
+    lib.ptl_gemm_tc_bf16_norm.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int,
+                                          _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _c_int, _c_int, _c_f, _ptr]
+    lib.ptl_gemm_tc_bf16_norm.restype = _c_int
     lib.ptl_prefill_attention_tc_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                   _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _ptr, _ptr]
     lib.ptl_prefill_attention_tc_bf16.restype = _c_int
@@ -195,7 +221,13 @@ class CudaOps:
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """x[T, K] @ w[N, K]^T.  float32: the library's own FFMA kernel (true 32-bit);
-        bfloat16: a cuBLAS product with float32 accumulation."""
+        bfloat16: the tensor-core product of this library (a cuBLAS product for sizes it leaves out).
+        ``x`` may be a ``NormedActivation``."""
+        if isinstance(x, NormedActivation):
+            out = self.gemm_tc(x, w, self.EPI_F32 if out_dtype == torch.float32 else self.EPI_BF16)
+            if out is not None:
+                return out
+            x = x.materialise()
         self._want(x, "x")
         self._want(w, "w", x.dtype)
         out_dtype = out_dtype or x.dtype
@@ -215,10 +247,22 @@ class CudaOps:
             return torch.mm(x, w.t(), out_dtype=torch.float32)
         return torch.mm(x, w.t())
 
-    def linear_add(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor) -> Optional[torch.Tensor]:
+    fuses_next_norm = os.environ.get("PTL_FUSED_NORM", "1") != "0"
+    # Steps of up to this many tokens fold the norms into the products around them.  With more
+    # tokens a step is no longer bound by the number of kernels, and the add epilogue of the
+    # products with a short K range has no time to spare for the extra stores.
+    FUSED_NORM_MAX_TOKENS = int(os.environ.get("PTL_FUSED_NORM_MAX", "64"))
+
+    def linear_add(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, next_norm=None):
         """residual += x @ w^T in the product's epilogue (float32 residual, in place) and None; where
-        that is not possible the plain product, for the caller to add."""
+        that is not possible the plain product, for the caller to add.  With ``next_norm`` = (weight,
+        eps) of the RMS norm that reads the residual next, the epilogue prepares that norm's input
+        as well and a ``NormedActivation`` is returned instead of None (where the sizes allow it)."""
         if x.dtype == torch.bfloat16 and residual is not None:
+            if next_norm is not None and self.fuses_next_norm and x.shape[0] <= self.FUSED_NORM_MAX_TOKENS:
+                normed = self.gemm_tc(x, w, self.EPI_ADD_F32, out=residual, emit_norm=next_norm)
+                if normed is not None:
+                    return normed
             if self.gemm_tc(x, w, self.EPI_ADD_F32, out=residual) is not None:
                 return None
         return self.linear(x, w)
@@ -228,8 +272,10 @@ class CudaOps:
         gate/up product can apply SiLU(gate)*up in its epilogue."""
         return dtype == torch.bfloat16 and hidden % 8 == 0 and hidden >= 64
 
-    def gate_up_silu(self, x: torch.Tensor, w_alternating: torch.Tensor) -> torch.Tensor:
+    def gate_up_silu(self, x, w_alternating: torch.Tensor) -> torch.Tensor:
         out = self.gemm_tc(x, w_alternating, self.EPI_SILU_MUL)
+        if out is None and isinstance(x, NormedActivation):
+            out = self.gemm_tc(x.materialise(), w_alternating, self.EPI_SILU_MUL)
         if out is None:
             raise KernelError("gate_up_silu: sizes not taken; load the weights in the plain layout instead")
         return out
@@ -242,12 +288,17 @@ class CudaOps:
             self._tc_status = torch.zeros(1, dtype=torch.int32, device=self.device)
         return self._tc_status
 
-    def gemm_tc(self, x: torch.Tensor, w: torch.Tensor, epi: int = 0, out: Optional[torch.Tensor] = None,
-                splits: int = 0) -> Optional[torch.Tensor]:
+    def gemm_tc(self, x, w: torch.Tensor, epi: int = 0, out: Optional[torch.Tensor] = None,
+                splits: int = 0, emit_norm=None):
         """x[M,K] @ w[N,K]^T in bfloat16 on the tcgen05 tensor cores with a fused epilogue.
         ``epi``: EPI_BF16 -> [M,N] bfloat16; EPI_F32 -> [M,N] float32; EPI_ADD_F32 adds into ``out``
         (float32 [M,N], in place); EPI_SILU_MUL -> [M,N/2] bfloat16 for weights whose rows alternate
-        gate_j, up_j.  Returns None when the kernel does not take the sizes."""
+        gate_j, up_j.  ``x`` may be a ``NormedActivation``: its row scale is applied before the
+        epilogue.  ``emit_norm`` = (weight, eps) with EPI_ADD_F32 returns the ``NormedActivation`` of the
+        norm that follows.  Returns None when the kernel does not take the sizes."""
+        scale = None
+        if isinstance(x, NormedActivation):
+            scale, x = x, x.xs
         self._want(x, "x", torch.bfloat16)
         self._want(w, "w", torch.bfloat16)
         M, K = x.shape
@@ -267,11 +318,34 @@ class CudaOps:
         else:
             out = self.empty((M, N), torch.float32 if epi == self.EPI_F32 else torch.bfloat16)
             ld = N
-        rc = self.lib.ptl_gemm_tc_bf16(_p(out), _p(x), _p(w), M, N, K, ld, epi, _p(self._tc_status_word()), splits,
-                                       self._stream())
+        if scale is None and emit_norm is None:
+            rc = self.lib.ptl_gemm_tc_bf16(_p(out), _p(x), _p(w), M, N, K, ld, epi, _p(self._tc_status_word()), splits,
+                                           self._stream())
+            if rc == -2:
+                return None
+            self._check(rc)
+            return out
+        normed = slots = None
+        if emit_norm is not None:
+            weight, eps = emit_norm
+            self._want(weight, "norm weight", torch.float32)
+            width = (N + 15) // 16
+            normed = NormedActivation(self.empty((M, N), torch.bfloat16), self.empty((M, width), torch.float32), 0,
+                                      float(eps), weight)
+            slots = ctypes.c_int(0)
+        rc = self.lib.ptl_gemm_tc_bf16_norm(
+            _p(out), _p(x), _p(w), M, N, K, ld, epi, _p(self._tc_status_word()), splits,
+            _p(normed.xs) if normed else None, _p(normed.weight) if normed else None,
+            _p(normed.sumsq) if normed else None, normed.sumsq.shape[1] if normed else 0,
+            ctypes.byref(slots) if normed else None,
+            _p(scale.sumsq) if scale else None, scale.slots if scale else 0, scale.sumsq.shape[1] if scale else 0,
+            scale.eps if scale else 0.0, self._stream())
         if rc == -2:
             return None
         self._check(rc)
+        if normed is not None:
+            normed.slots = slots.value
+            return normed
         return out
 
     def check_status(self) -> None:

@@ -63,8 +63,10 @@ class GQAttention(Part):
                          head_dim=self.head_dim, window=self.window)
 
     fuses_residual = True   # forward() may add its output into the residual itself and return None
+    accepts_normed = True   # x may be a norm's prepared input (the q|k|v product finishes the norm)
+    emits_normed = True     # the output product may prepare the input of the norm that follows
 
-    def forward(self, x, ctx, cache, residual=None):
+    def forward(self, x, ctx, cache, residual=None, next_norm=None):
         ops = self.rt.ops
         qkv = ops.linear(x, self.w_qkv)
         inv_freq, rot = self.position.rotary_table()
@@ -84,5 +86,7 @@ class GQAttention(Part):
                                     self.kv_heads, self.head_dim, g.page_size, self.scale, window=self.window,
                                     splits=ctx.attn_splits, hints=ctx)
         if residual is not None:
+            if next_norm is not None and getattr(ops, "fuses_next_norm", False):
+                return ops.linear_add(o, self.w_o, residual, next_norm=next_norm)
             return ops.linear_add(o, self.w_o, residual)      # None when the product's epilogue did the add
         return ops.linear(o, self.w_o)

@@ -21,21 +21,32 @@ class PreNormBlock(Part):
         self.norm2 = build_part("norm", spec.parts["norm2"], runtime)
         self.ffn = build_part("ffn", spec.parts["ffn"], runtime)
 
+    takes_next_norm = True   # forward() accepts the norm part that follows the block
+
     def children(self):
         return {"norm1": self.norm1, "mixer": self.mixer, "norm2": self.norm2, "ffn": self.ffn}
 
     def cache_need(self):
         return self.mixer.cache_need()
 
-    def forward(self, x, residual, ctx, cache):
+    def forward(self, x, residual, ctx, cache, next_norm=None):
         """``x`` may be None: the previous sub-layer then already added its output into ``residual``.
-        Mixers and feed-forwards that set ``fuses_residual`` get the residual and may do the same."""
+        Mixers and feed-forwards that set ``fuses_residual`` get the residual and may do the same.
+        Those that also set ``emits_normed`` are told which norm reads the residual next
+        (``next_norm``: the norm part that follows this block, if any) and may return that norm's
+        prepared input; a sub-layer reads such an input only if it sets ``accepts_normed``."""
         y, residual = self.norm1.forward(x, residual)
-        if getattr(self.mixer, "fuses_residual", False):
-            a = self.mixer.forward(y, ctx, cache, residual=residual)
-        else:
-            a = self.mixer.forward(y, ctx, cache)
+        a = self._run(self.mixer, y, residual, self.norm2, ctx, cache)
         y, residual = self.norm2.forward(a, residual)
-        if getattr(self.ffn, "fuses_residual", False):
-            return self.ffn.forward(y, residual=residual), residual
-        return self.ffn.forward(y), residual
+        return self._run(self.ffn, y, residual, next_norm), residual
+
+    @staticmethod
+    def _run(part, y, residual, following_norm, *args):
+        if hasattr(y, "materialise") and not getattr(part, "accepts_normed", False):
+            y = y.materialise()
+        kw = {}
+        if getattr(part, "fuses_residual", False):
+            kw["residual"] = residual
+            if getattr(part, "emits_normed", False) and getattr(following_norm, "deferrable", False):
+                kw["next_norm"] = (following_norm.weight, following_norm.eps)
+        return part.forward(y, *args, **kw)

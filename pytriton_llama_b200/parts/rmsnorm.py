@@ -30,5 +30,15 @@ class RMSNorm(Part):
     def load(self, tensors) -> None:
         self.weight = self._to_f32(tensors["weight"])  # norm weights stay 32-bit in every compute type
 
+    deferrable = True   # the product before this norm may prepare its input, the product after it finish it
+
     def forward(self, x, residual, rows=None):
+        """``x`` may be the prepared input that a product's epilogue made for this very norm (it has
+        ``materialise``): the sum is in ``residual`` already, and it is handed on as it is for the
+        next product to finish.  One made for another norm, or with ``rows``, only means that
+        nothing is left to add."""
+        if hasattr(x, "materialise"):
+            if x.weight is self.weight and rows is None:
+                return x, residual
+            x = None
         return self.rt.ops.add_rmsnorm(x, residual, self.weight, self.eps, rows=rows, dtype=self.rt.dtype)

@@ -32,6 +32,8 @@ class SwiGLU(Part):
         }
 
     fuses_residual = True   # forward() may add its output into the residual itself and return None
+    accepts_normed = True   # x may be a norm's prepared input (the gate/up product finishes the norm)
+    emits_normed = True     # the down product may prepare the input of the norm that follows
 
     def load(self, tensors) -> None:
         ops = self.rt.ops
@@ -46,12 +48,14 @@ class SwiGLU(Part):
         self.w_gate_up = self._to_compute(gu)
         self.w_down = self._to_compute(tensors["down"])
 
-    def forward(self, x, residual=None):
+    def forward(self, x, residual=None, next_norm=None):
         ops = self.rt.ops
         if self.alternating:
             h = ops.gate_up_silu(x, self.w_gate_up)
         else:
             h = ops.silu_mul(ops.linear(x, self.w_gate_up))
         if residual is not None:
+            if next_norm is not None and getattr(ops, "fuses_next_norm", False):
+                return ops.linear_add(h, self.w_down, residual, next_norm=next_norm)
             return ops.linear_add(h, self.w_down, residual)   # None when the product's epilogue did the add
         return ops.linear(h, self.w_down)

@@ -417,3 +417,42 @@ def test_decode_attention_with_rope_and_cache_write_folded_in(ops, nq, nkv, d, p
                               page, d ** -0.5, window=window, hints=hints, write=False)
     assert torch.equal(cache_c, cache_a)
     assert (got2.float() - want.float()).abs().max() <= 2 ** -7 * float(want.float().abs().max())
+
+
+@pytest.mark.parametrize("M, H, K, N2", [(8, 2048, 2048, 3072), (1, 64, 128, 96), (16, 192, 320, 640), (40, 2048, 8192, 256),
+                                         (64, 9600, 512, 128), (200, 256, 512, 1000), (1100, 2048, 256, 512),
+                                         (130, 192, 64, 384)])
+def test_product_prepares_the_next_norm_and_the_next_product_finishes_it(ops, M, H, K, N2):
+    """residual += a @ w1^T with the norm that follows prepared in the epilogue (unnormalised
+    bfloat16 input and partial sums of squares), then products that take that input and apply the
+    row scale: against residual -> RMS norm -> product in float64."""
+    a, w1 = rnd((M, K), torch.bfloat16, 1), rnd((H, K), torch.bfloat16, 2, 0.3)
+    res0 = rnd((M, H), torch.float32, 3, 2.0)
+    nw = (1.0 + 0.2 * torch.randn(H, generator=torch.Generator().manual_seed(4))).float()
+    eps = 1e-5
+    res = res0.clone().cuda()
+    normed = ops.gemm_tc(a.cuda(), w1.cuda(), ops.EPI_ADD_F32, out=res, emit_norm=(nw.cuda(), eps))
+    assert normed is not None and normed.slots > 0
+    want_res = res0.double() + a.double() @ w1.double().T
+    assert (res.double().cpu() - want_res).abs().max() <= 1e-5 * math.sqrt(K) * float(want_res.abs().max())
+    got_sq = normed.sumsq[:, :normed.slots].double().sum(1).cpu()
+    assert ((got_sq - (want_res ** 2).sum(1)).abs() / (want_res ** 2).sum(1)).max() < 1e-5
+    slack = 1e-5 * math.sqrt(K) * float(want_res.abs().max())          # what float32 accumulation may move the residual by
+    assert ((normed.xs.double().cpu() - want_res * nw.double()).abs() <= 2 ** -8 * (want_res * nw.double()).abs() + 2 * slack).all()
+    y = want_res * torch.rsqrt((want_res ** 2).mean(1, keepdim=True) + eps) * nw.double()
+    assert (normed.materialise().double().cpu() - y).abs().max() <= 2 ** -7 * float(y.abs().max())
+    # consumers
+    w2 = rnd((N2, H), torch.bfloat16, 5, 0.3)
+    ref = y @ w2.double().T
+    out = ops.gemm_tc(normed, w2.cuda(), ops.EPI_BF16)
+    assert (out.double().cpu() - ref).abs().max() <= 2 ** -6 * float(ref.abs().max())
+    out32 = ops.gemm_tc(normed, w2.cuda(), ops.EPI_F32)
+    plain = ops.gemm_tc(normed.materialise(), w2.cuda(), ops.EPI_F32)
+    assert (out32.double().cpu() - ref).abs().max() <= 2 ** -7 * float(ref.abs().max())
+    assert (out32 - plain).abs().max() <= 2 ** -7 * float(ref.abs().max())      # the two ways agree to the activation's rounding
+    act = ops.gemm_tc(normed, w2.cuda(), ops.EPI_SILU_MUL)
+    g, u = ref[:, 0::2], ref[:, 1::2]
+    want = g * torch.sigmoid(g) * u
+    assert (act.double().cpu() - want).abs().max() <= 2 ** -5 * float(want.abs().max())
+    assert (ops.linear(normed, w2.cuda()).double().cpu() - ref).abs().max() <= 2 ** -6 * float(ref.abs().max())
+    assert ops.gemm_tc_status() == 0
