@@ -8,7 +8,7 @@
 // alike.  Scores, running max and sum, and the accumulator are float32; P is rounded to bfloat16
 // for the second product, as lite_llama's kernel does (lite_llama/kernels/flashattentionv2.py:55).
 //
-// tiles[i] = {request row, first token index, rows (1..128), position of the first token}.
+// tiles[i] = {request row, first token index, rows (0..128; 0: nothing to do), position of the first token}.
 #include "mma_utils.cuh"
 
 namespace ptl {
@@ -52,6 +52,7 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   const int g = lane >> 2, c = lane & 3;
   const int* tl = tiles + 4 * (gridDim.x - 1 - blockIdx.x);   // later tiles see more keys: start them first
   const int req = tl[0], tok0 = tl[1], rows = tl[2], pos0 = tl[3];
+  if (rows <= 0) return;                          // an empty second half of a pair of tiles
   const int h = blockIdx.y;
   const int kvh = h / (nq / nkv);
   const int k_lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;

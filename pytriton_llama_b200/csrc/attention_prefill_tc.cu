@@ -1,47 +1,59 @@
 // Attention of prompt portions over the paged cache on the fifth-generation tensor cores
-// (head size 64, bfloat16).  One block per (tile of up to 128 query tokens of one request, query
-// head):
-//   S = Q K^T       tcgen05.mma 128 x 128 x 64 into TMEM (float32), K tile fetched page by page
-//                   with TMA into 128-byte-swizzled shared memory;
-//   softmax         four warps, one thread per query row: tcgen05.ld of the row's 128 scores,
-//                   running max and sum in float32 (base-2 exponentials), P rounded to bfloat16
-//                   and written to shared memory in the layout of a K-major MMA operand, the
-//                   output accumulator in TMEM rescaled by the change of the maximum;
+// (head size 64, bfloat16).  One block per (pair of tiles of up to 128 query tokens each, query
+// head); the pair are consecutive rows of one request (tile B continues tile A; B may be absent),
+// so both walk the same keys and every key/value tile is fetched once for 256 query rows:
+//   S = Q K^T       tcgen05.mma 128 x 128 x 64 into TMEM (float32), per tile of the pair; the K
+//                   tile is fetched page by page with TMA into 128-byte-swizzled shared memory;
+//   softmax         a group of four warps per tile of the pair, one thread per query row:
+//                   tcgen05.ld of the row's 128 scores, running max and sum in float32 (base-2
+//                   exponentials), P rounded to bfloat16 and written to shared memory in the
+//                   layout of a K-major MMA operand, the output accumulator in TMEM rescaled by
+//                   the change of the maximum;
 //   O += P V        tcgen05.mma 128 x 64 x 128; V stays as the cache has it ([key][dim], the
 //                   "MN-major" operand form), so nothing is transposed;
 //   epilogue        O / sum -> bfloat16.
-// Two blocks fit on an SM (112 KB of shared memory, 256 TMEM columns each), so one block's
-// softmax runs under the other's MMAs.  Queries attend over the pages up to their own position
-// (the step's own keys were written before), optionally within a window.
+// The two tiles of the pair take turns: while group A works on the scores of a key tile, the
+// tensor core computes those of group B, then A's P V while B is in its softmax, and so on -- the
+// exponentials of one tile run under the matrix products of the other inside one block (one
+// block per SM: 193 KB of shared memory, 384 TMEM columns).  Queries attend over the pages up to
+// their own position (the step's own keys were written before), optionally within a window.
 //
-// Warp roles (192 threads): warp 0 TMA producer, warp 1 TMEM allocation + MMA issue, warps 2..5
-// softmax and epilogue (warp w owns TMEM lanes 32*(w%4)..+31).  Waits are bounded as in the
-// matrix product: a wait that gives up records a code in *status and the block drains.
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 TMEM allocation + MMA issue, warps 2..5
+// softmax and epilogue of tile A, warps 6..9 of tile B (warp w owns TMEM lanes 32*(w%4)..+31).
+// Waits are bounded as in the matrix product: a wait that gives up records a code in *status and
+// the block drains.
+//
+// tiles[2j], tiles[2j+1] = {request row, first token index, rows, position of the first token};
+// the second entry either continues the first (same request, first token and position + 128) or
+// has rows == 0.
 #include "tcgen05_utils.cuh"
 
 namespace ptl {
 
-constexpr int kTcRows = 128;       // query rows per block
+constexpr int kTcRows = 128;       // query rows per tile of the pair
 constexpr int kTcKeys = 128;       // keys per tile
 constexpr int kTcD = 64;           // head size
-constexpr int kTcThreads = 192;
-constexpr int kTcStages = 2;
+constexpr int kTcThreads = 320;
+constexpr int kTcStages = 3;
 constexpr int kTcTileBytes = kTcKeys * kTcD * 2;           // one of K / V: 16 KB
-constexpr int kTcQBytes = kTcRows * kTcD * 2;              // 16 KB
-constexpr int kTcPBytes = kTcRows * kTcKeys * 2;           // 32 KB: two 64-key blocks of [128 rows][128 B]
-constexpr int kTcStagedPages = 128;    // block-table entries kept in shared memory (2,048 keys with pages of 16)
-// Two blocks per SM need each to stay below ~113 KB: tiles, 128 bytes of barriers, the staged table.
-constexpr int kTcSmem = kTcQBytes + kTcStages * 2 * kTcTileBytes + kTcPBytes + 128 + kTcStagedPages * 4;
-constexpr int kTcTmemCols = 256;   // S: columns 0..127, O: columns 128..191
+constexpr int kTcQBytes = kTcRows * kTcD * 2;              // 16 KB per tile of the pair
+constexpr int kTcPBytes = kTcRows * kTcKeys * 2;           // 32 KB per tile of the pair: two 64-key blocks of [128 rows][128 B]
+constexpr int kTcStagedPages = 264;    // block-table entries kept in shared memory (4,096 + 128 keys with pages of 16)
+constexpr int kTcBarBytes = 256;
+constexpr int kTcSmem = 2 * kTcQBytes + kTcStages * 2 * kTcTileBytes + 2 * kTcPBytes + kTcBarBytes + kTcStagedPages * 4;
+constexpr int kTcTmemCols = 512;   // S of A and B: columns 0..127, 128..255; O of A and B: 256..319, 320..383
 
 struct PrefillTcParams {
   __nv_bfloat16* out;
   const int* block_table;
-  const int* tiles;          // {request row, first token, rows, first position} per block
+  const int* tiles;
   int* status;
   int out_stride, bt_stride, nq, nkv, page_size, window, num_pages;
   float scale_log2;
 };
+
+// Barriers (8 bytes each): q_full, kv_full[3], kv_empty[3], then per tile of the pair s_full, p_full, o_done, s_free.
+enum : int { kBarQ = 0, kBarKvFull = 1, kBarKvEmpty = 4, kBarSFull = 7, kBarPFull = 9, kBarODone = 11, kBarSFree = 13, kBarCount = 15 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -54,38 +66,54 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const PrefillTcParams p) {
   extern __shared__ __align__(1024) unsigned char smem[];     // swizzled tiles need 1024-byte alignment
   const uint32_t q_smem = smem_addr(smem);
-  const uint32_t kv_smem = q_smem + kTcQBytes;
+  const uint32_t kv_smem = q_smem + 2 * kTcQBytes;
   const uint32_t p_smem = kv_smem + kTcStages * 2 * kTcTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kTcQBytes + kTcStages * 2 * kTcTileBytes + kTcPBytes);
-  // bars: 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5 s_full | 6 p_full | 7 o_done
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * kTcQBytes + kTcStages * 2 * kTcTileBytes + 2 * kTcPBytes);
   const uint32_t bar_base = smem_addr(bars);
   auto bar = [&](int i) { return bar_base + 8u * i; };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kBarCount);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* s_pages = reinterpret_cast<int*>(bars + 16);
+  int* s_pages = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(bars) + kTcBarBytes);
   if (q_smem & 1023u) {                                        // never expected; refuse rather than compute garbage
     if (threadIdx.x == 0 && p.status) atomicExch(p.status, 99);
     return;
   }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int* tl = p.tiles + 4 * (gridDim.x - 1 - blockIdx.x);     // later tiles see more keys: start them first
-  const int req = tl[0], tok0 = tl[1], rows = tl[2], pos0 = tl[3];
-  const int h = blockIdx.y;
+  // Blocks are handed out with x running fastest: heads along x and pairs along y, last pair
+  // first, start the pairs that see the most keys first on every SM (longest work first).
+  const int pair = gridDim.y - 1 - blockIdx.y;
+  const int* tl = p.tiles + 8 * pair;
+  const int req = tl[0], tok0 = tl[1], pos0 = tl[3];
+  const int rows_g[2] = {tl[2], tl[6]};                        // rows of tile A and of tile B (0: absent)
+  const int h = blockIdx.x;
   const int kvh = h / (p.nq / p.nkv);
-  const int k_lo_raw = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
-  const int k_lo = k_lo_raw / p.page_size * p.page_size;        // tiles start on a page boundary
-  const int k_end = pos0 + rows;
-  const int ntiles = (k_end - k_lo + kTcKeys - 1) / kTcKeys;
+  // Per tile of the pair: first key it may see (window), one past the last, and the range of key
+  // tiles it takes part in.  Key tiles are counted from tile A's first page.
+  int lo_raw[2], k_end[2], t_first[2], t_last[2], pos_g[2];
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    pos_g[g] = pos0 + g * kTcRows;
+    lo_raw[g] = (p.window > 0 && pos_g[g] - p.window + 1 > 0) ? pos_g[g] - p.window + 1 : 0;
+    k_end[g] = pos_g[g] + rows_g[g];
+  }
+  const int k_base = lo_raw[0] / p.page_size * p.page_size;    // tiles start on a page boundary
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    t_first[g] = (lo_raw[g] - k_base) / kTcKeys;
+    t_last[g] = rows_g[g] > 0 ? (k_end[g] - k_base + kTcKeys - 1) / kTcKeys : 0;     // one past the last
+  }
+  const int ntiles = max(t_last[0], t_last[1]);
   const int pages_per_tile = kTcKeys / p.page_size;
   const int* bt_global = p.block_table + (size_t)req * p.bt_stride;
+  auto takes_part = [&](int g, int t) { return rows_g[g] > 0 && t >= t_first[g] && t < t_last[g]; };
 
   if (threadIdx.x == 0) {
-    mbar_init(bar(0), 1);
-    for (int s = 0; s < kTcStages; ++s) { mbar_init(bar(1 + s), 1); mbar_init(bar(3 + s), 1); }
-    mbar_init(bar(5), 1);
-    mbar_init(bar(6), 4);
-    mbar_init(bar(7), 1);
+    mbar_init(bar(kBarQ), 1);
+    for (int s = 0; s < kTcStages; ++s) { mbar_init(bar(kBarKvFull + s), 1); mbar_init(bar(kBarKvEmpty + s), 1); }
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(bar(kBarSFull + g), 1); mbar_init(bar(kBarPFull + g), 4); mbar_init(bar(kBarODone + g), 1); mbar_init(bar(kBarSFree + g), 4);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -98,9 +126,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   pdl_wait();                 // everything below reads what earlier kernels of the step wrote
   pdl_launch_dependents();
   // block-table entries of the key range, staged once (the producer thread reads them)
-  const int first_block = k_lo / p.page_size;
+  const int first_block = k_base / p.page_size;
   const int n_blocks = ntiles * pages_per_tile;
-  const int have_blocks = (k_end - 1) / p.page_size - first_block + 1;     // entries that exist for this request
+  const int have_blocks = (max(k_end[0], k_end[1]) - 1) / p.page_size - first_block + 1;   // entries that exist for this request
   const bool staged = n_blocks <= kTcStagedPages;
   if (staged)
     for (int i = threadIdx.x; i < n_blocks; i += kTcThreads) s_pages[i] = i < have_blocks ? bt_global[first_block + i] : -1;
@@ -108,18 +136,18 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
 
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ TMA producer
-    mbar_expect_tx(bar(0), kTcQBytes);
-    tma_load_2d(q_smem, &map_q, bar(0), h * kTcD, tok0);           // rows past the step's tokens arrive as zeros
+    mbar_expect_tx(bar(kBarQ), (rows_g[1] > 0 ? 2 : 1) * kTcQBytes);
+    tma_load_2d(q_smem, &map_q, bar(kBarQ), h * kTcD, tok0);       // rows past the step's tokens arrive as zeros
+    if (rows_g[1] > 0) tma_load_2d(q_smem + kTcQBytes, &map_q, bar(kBarQ), h * kTcD, tok0 + kTcRows);
     const int rows_per_page_group = p.nkv * p.page_size;           // cache rows between the k and v planes of a page
     for (int t = 0; t < ntiles; ++t) {
       const int s = t % kTcStages;
       const uint32_t ph = (t / kTcStages) & 1;
-      if (!mbar_wait(bar(3 + s), ph ^ 1, abort_flag, p.status, 11)) break;
-      mbar_expect_tx(bar(1 + s), 2 * kTcTileBytes);
+      if (!mbar_wait(bar(kBarKvEmpty + s), ph ^ 1, abort_flag, p.status, 11)) break;
+      mbar_expect_tx(bar(kBarKvFull + s), 2 * kTcTileBytes);
       const uint32_t kdst = kv_smem + s * 2 * kTcTileBytes, vdst = kdst + kTcTileBytes;
       for (int i = 0; i < pages_per_tile; ++i) {
         const int bi = t * pages_per_tile + i;
@@ -127,60 +155,114 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (page < 0 || page >= p.num_pages) page = 0;             // beyond the request: any page, its keys get masked
         const int krow = (page * 2 * p.nkv + kvh) * p.page_size;
         const uint32_t off = (uint32_t)i * p.page_size * 128u;
-        tma_load_2d(kdst + off, &map_kv, bar(1 + s), 0, krow);
-        tma_load_2d(vdst + off, &map_kv, bar(1 + s), 0, krow + rows_per_page_group);
+        tma_load_2d(kdst + off, &map_kv, bar(kBarKvFull + s), 0, krow);
+        tma_load_2d(vdst + off, &map_kv, bar(kBarKvFull + s), 0, krow + rows_per_page_group);
       }
     }
   } else if (warp == 1 && lane == 0) {
     // ------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc_s = instr_desc_bf16(kTcRows, kTcKeys);                    // Q, K both K-major
     constexpr uint32_t idesc_o = instr_desc_bf16(kTcRows, kTcD) | (1u << 16);          // V is MN-major
-    bool ok = mbar_wait(bar(0), 0, abort_flag, p.status, 12);
-    for (int t = 0; t < ntiles && ok; ++t) {
-      const int s = t % kTcStages;
-      const uint32_t ph = (t / kTcStages) & 1;
-      ok = mbar_wait(bar(1 + s), ph, abort_flag, p.status, 13);
-      if (!ok) break;
-      // the previous tile's softmax has read S (it arrives on p_full only after that), so S is free
-      tcgen05_fence_after();
-      const uint32_t kb = kv_smem + s * 2 * kTcTileBytes, vb = kb + kTcTileBytes;
+    bool ok = mbar_wait(bar(kBarQ), 0, abort_flag, p.status, 12);
+    int n_g[2] = {0, 0};                                          // P V products issued so far for each tile of the pair
+    auto stage_of = [&](int t) { return t % kTcStages; };
+    auto issue_s = [&](int g, int t) {
+      const uint32_t kb = kv_smem + stage_of(t) * 2 * kTcTileBytes;
 #pragma unroll
       for (int k = 0; k < kTcD / 16; ++k)
-        tcgen05_mma_bf16(tmem_s, smem_desc_sw128(q_smem + k * 32), smem_desc_sw128(kb + k * 32), idesc_s, k > 0 ? 1u : 0u);
-      tcgen05_commit(bar(5));                                     // S complete
-      ok = mbar_wait(bar(6), t & 1, abort_flag, p.status, 14);   // P written, O rescaled
-      if (!ok) break;
-      tcgen05_fence_after();
+        tcgen05_mma_bf16(tmem_base + g * kTcKeys, smem_desc_sw128(q_smem + g * kTcQBytes + k * 32), smem_desc_sw128(kb + k * 32),
+                         idesc_s, k > 0 ? 1u : 0u);
+      tcgen05_commit(bar(kBarSFull + g));                           // S of this tile complete
+    };
+    auto issue_pv = [&](int g, int t) {
+      const uint32_t vb = kv_smem + stage_of(t) * 2 * kTcTileBytes + kTcTileBytes;
 #pragma unroll
       for (int k = 0; k < kTcKeys / 16; ++k) {
         // A: P, K-major, 64-key blocks of 16 KB; B: V rows = keys, 16 keys = 2 KB per step
-        const uint64_t adesc = smem_desc_sw128(p_smem + (k >> 2) * (kTcRows * 128) + (k & 3) * 32);
+        const uint64_t adesc = smem_desc_sw128(p_smem + g * kTcPBytes + (k >> 2) * (kTcRows * 128) + (k & 3) * 32);
         const uint64_t bdesc = smem_desc_sw128(vb + k * 2048);
-        tcgen05_mma_bf16(tmem_o, adesc, bdesc, idesc_o, (t > 0 || k > 0) ? 1u : 0u);
+        tcgen05_mma_bf16(tmem_base + 2 * kTcKeys + g * kTcD, adesc, bdesc, idesc_o, (n_g[g] > 0 || k > 0) ? 1u : 0u);
       }
-      tcgen05_commit(bar(3 + s));                                 // K/V stage free
-      tcgen05_commit(bar(7));                                     // O updated, P free
+      tcgen05_commit(bar(kBarODone + g));                           // O of this tile updated, its P free
+      ++n_g[g];
+    };
+    // This thread serves whichever of the two groups is ready: the scores of a group's next key
+    // tile are issued as soon as the group has taken the previous ones out of TMEM (s_free), long
+    // before its softmax is done, so a group does not wait for its scores; its P V product follows
+    // when it hands over P.  Barriers are tested without suspending; a key tile's stage is given
+    // back once every product that reads it has been issued.
+    int next_s[2] = {t_first[0], t_first[1]}, next_pv[2] = {t_first[0], t_first[1]};
+    int kv_ready = 0, released = 0;
+    uint32_t idle = 0;
+    while (ok && released < ntiles) {
+      bool progress = false;
+      if (kv_ready < ntiles && mbar_test_wait(bar(kBarKvFull + stage_of(kv_ready)), (kv_ready / kTcStages) & 1)) {
+        ++kv_ready;
+        progress = true;
+      }
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        if (rows_g[g] <= 0) continue;
+        const int issued = next_s[g] - t_first[g];
+        if (next_s[g] < t_last[g] && next_s[g] < kv_ready &&
+            (issued == 0 || mbar_test_wait(bar(kBarSFree + g), (issued - 1) & 1))) {
+          tcgen05_fence_after();
+          issue_s(g, next_s[g]);
+          ++next_s[g];
+          progress = true;
+        }
+        if (next_pv[g] < next_s[g] && mbar_test_wait(bar(kBarPFull + g), n_g[g] & 1)) {     // P written, O rescaled
+          tcgen05_fence_after();
+          issue_pv(g, next_pv[g]);
+          ++next_pv[g];
+          progress = true;
+        }
+      }
+      while (released < ntiles && (!takes_part(0, released) || next_pv[0] > released) &&
+             (!takes_part(1, released) || next_pv[1] > released)) {
+        tcgen05_commit(bar(kBarKvEmpty + stage_of(released)));
+        ++released;
+        progress = true;
+      }
+      if (progress) {
+        idle = 0;
+      } else if (*abort_flag || ++idle > kPollLimit) {
+        if (!*abort_flag) { *abort_flag = 1; if (p.status) atomicExch(p.status, 14); }
+        ok = false;
+      } else if (idle > 256) {
+        __nanosleep(32);
+      }
     }
   } else if (warp >= 2) {
     // ------------------------------------------------------------ softmax, correction, epilogue
+    const int g = (warp - 2) >> 2;                                // which tile of the pair
     const int quad = warp & 3;
-    const int r = quad * 32 + lane;                               // query row of this thread
-    const int qpos = pos0 + r;
+    const int r = quad * 32 + lane;                               // query row of this thread within its tile
+    const int rows = rows_g[g];
+    const int tile_pos0 = pos_g[g];
+    const int qpos = tile_pos0 + r;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    const uint32_t tmem_s = tmem_base + g * kTcKeys, tmem_o = tmem_base + 2 * kTcKeys + g * kTcD;
+    const uint32_t my_p = p_smem + g * kTcPBytes;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
-    for (int t = 0; t < ntiles && ok; ++t) {
-      ok = mbar_wait(bar(5), t & 1, abort_flag, p.status, 15);
+    int n = 0;                                                    // key tiles taken so far
+    for (int t = t_first[g]; t < t_last[g] && ok; ++t, ++n) {
+      ok = mbar_wait(bar(kBarSFull + g), n & 1, abort_flag, p.status, 15);
       if (!ok) break;
       tcgen05_fence_after();
-      const int key0 = k_lo + t * kTcKeys;
-      const bool need_mask = key0 + kTcKeys - 1 > pos0 || key0 < k_lo_raw ||
-                             (p.window > 0 && key0 < pos0 + kTcRows - 1 - p.window + 1);
+      const int key0 = k_base + t * kTcKeys;
+      const bool need_mask = key0 + kTcKeys - 1 > tile_pos0 || key0 < lo_raw[g] ||
+                             (p.window > 0 && key0 < tile_pos0 + kTcRows - 1 - p.window + 1);
       // the row's 128 scores come out of TMEM once and stay in registers
       uint32_t v[kTcKeys];
 #pragma unroll
       for (int c0 = 0; c0 < kTcKeys; c0 += 32) tmem_load_32_nowait(tmem_s + lane_addr + c0, v + c0);
       tmem_wait_ld();
+      // the scores are in registers: the next key tile's may be written
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kBarSFree + g));
       float mx = -INFINITY;
       if (need_mask) {
 #pragma unroll
@@ -196,12 +278,16 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int j = 0; j < kTcKeys; ++j) mx = fmaxf(mx, __uint_as_float(v[j]));
       }
       mx *= p.scale_log2;                                       // the scale is positive: max and scaling commute
-      const float m_new = fmaxf(m_run, mx);
+      // The reference maximum only moves when the row's maximum has grown by more than 8 (a factor of
+      // 256 in P, which bfloat16 and the float32 sums take): rescaling the accumulator becomes rare.
+      const float m_top = fmaxf(m_run, mx);
+      const bool moved = m_top > m_run + 8.0f;
+      const float m_new = moved ? m_top : m_run;
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = ex2_approx(m_run - m_use);
+      const float alpha = moved ? ex2_approx(m_run - m_use) : 1.0f;
       // the previous P V product must be complete before P is overwritten and O rescaled
-      if (t > 0) {
-        ok = mbar_wait(bar(7), (t - 1) & 1, abort_flag, p.status, 16);
+      if (n > 0) {
+        ok = mbar_wait(bar(kBarODone + g), (n - 1) & 1, abort_flag, p.status, 16);
         if (!ok) break;
         tcgen05_fence_after();
       }
@@ -219,14 +305,14 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           packed[j >> 1] = *reinterpret_cast<uint32_t*>(&pk);
         }
         // keys c0..c0+7 are 16-byte chunk (c0 % 64) / 8 of this row inside 64-key block c0 / 64
-        const uint32_t dst = p_smem + (c0 >> 6) * (kTcRows * 128) + r * 128 + (((((c0 & 63) >> 3)) ^ (r & 7)) << 4);
+        const uint32_t dst = my_p + (c0 >> 6) * (kTcRows * 128) + r * 128 + (((((c0 & 63) >> 3)) ^ (r & 7)) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(packed[0]), "r"(packed[1]), "r"(packed[2]),
                      "r"(packed[3]) : "memory");
       }
       l_run = l_run * alpha + sum;
       m_run = m_new;
       // rescale the output accumulator where the maximum moved (never on the first tile: O is overwritten there)
-      if (t > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+      if (n > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
         for (int c0 = 0; c0 < kTcD; c0 += 32) {
           uint32_t o[32];
@@ -240,11 +326,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(6));
+      if (lane == 0) mbar_arrive(bar(kBarPFull + g));
     }
     // epilogue: wait for the last P V product, then O / sum
-    if (ok && ntiles > 0) ok = mbar_wait(bar(7), (ntiles - 1) & 1, abort_flag, p.status, 17);
-    if (ok) {
+    if (ok && n > 0) ok = mbar_wait(bar(kBarODone + g), (n - 1) & 1, abort_flag, p.status, 17);
+    if (ok && n > 0) {
       tcgen05_fence_after();
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
 #pragma unroll 1
@@ -252,7 +338,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         uint32_t v[32];
         tmem_load_32(tmem_o + lane_addr + c0, v);
         if (r < rows) {
-          __nv_bfloat16* dst = p.out + (size_t)(tok0 + r) * p.out_stride + (size_t)h * kTcD + c0;
+          __nv_bfloat16* dst = p.out + (size_t)(tok0 + g * kTcRows + r) * p.out_stride + (size_t)h * kTcD + c0;
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
             uint4 pk;
@@ -279,16 +365,17 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
 // Returns 0 on success; -2 if this kernel does not take the sizes (the caller then uses the
 // warp-level kernel): head size 64 only, pages of 8..128 keys that divide 128, 16-byte aligned
-// rows; -1 on an error.
+// rows; -1 on an error.  `tiles` holds n_tiles entries in pairs (n_tiles is even): see the top of the file.
 PTL_EXPORT int ptl_prefill_attention_tc_bf16(void* out, const void* q, const void* cache, const int* block_table,
                                              const int* tiles, int n_tiles, int n_tokens, int q_stride, int out_stride,
                                              int bt_stride, int nq, int nkv, int d, int page_size, float scale,
                                              int window, int num_pages, int* status, void* stream) {
   using namespace ptl;
   PTL_REQUIRE(n_tiles >= 0 && nq > 0 && nkv > 0 && page_size > 0 && num_pages > 0, "prefill_attention_tc: bad sizes");
+  PTL_REQUIRE(n_tiles % 2 == 0, "prefill_attention_tc: tiles come in pairs, %d is odd", n_tiles);
   PTL_REQUIRE(nq % nkv == 0, "prefill_attention_tc: %d query heads are no multiple of %d kv heads", nq, nkv);
   if (d != kTcD || page_size < 8 || page_size > kTcKeys || kTcKeys % page_size != 0 || q_stride % 8 != 0 ||
-      out_stride % 8 != 0 || nq > 65535)
+      out_stride % 8 != 0 || n_tiles / 2 > 65535)
     return -2;
   PTL_REQUIRE(aligned16(q) && aligned16(cache) && aligned16(out), "prefill_attention_tc: q, cache and out must be 16-byte aligned");
   if (n_tiles == 0) return 0;
@@ -307,6 +394,6 @@ PTL_EXPORT int ptl_prefill_attention_tc_bf16(void* out, const void* q, const voi
   p.out = (__nv_bfloat16*)out; p.block_table = block_table; p.tiles = tiles; p.status = status;
   p.out_stride = out_stride; p.bt_stride = bt_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size;
   p.window = window; p.num_pages = num_pages; p.scale_log2 = scale * 1.4426950408889634f;
-  return launch_kernel("prefill_attention_tc", prefill_attention_tc_kernel, dim3(n_tiles, nq), dim3(kTcThreads), kTcSmem,
+  return launch_kernel("prefill_attention_tc", prefill_attention_tc_kernel, dim3(nq, n_tiles / 2), dim3(kTcThreads), kTcSmem,
                        as_stream(stream), mq, mkv, p);
 }

@@ -50,5 +50,5 @@ class StepContext:
     n_decode: int = 0                                  # tokens that are the only new token of their request
     decode_items: Optional[torch.Tensor] = None        # int32 [n_decode] their token indices
     decode_in_order: bool = False                      # True when they are simply tokens 0..n_decode-1
-    n_prefill_tiles: int = 0                           # tiles of up to 128 rows of longer portions
+    n_prefill_tiles: int = 0                           # tiles of up to 128 rows of longer portions, in pairs (the second continues the first or has 0 rows)
     prefill_tiles: Optional[torch.Tensor] = None       # int32 [4 * tiles]: request row, first token, rows, first position

@@ -59,7 +59,7 @@ class _HostBatch:
         self.R = len(entries)
         self.T = sum(q_lens)
         self.max_q_len = max(q_lens)
-        # work lists of the attention kernels: single tokens, and tiles of up to 64 rows of longer portions
+        # work lists of the attention kernels: single tokens, and tiles of up to 128 rows of longer portions
         self.dec_items: List[int] = []
         self.pf_tiles: List[int] = []
         t0 = 0
@@ -67,8 +67,12 @@ class _HostBatch:
             if n == 1:
                 self.dec_items.append(t0)
             else:
-                for a in range(0, n, QUERY_TILE):
+                # tiles come in pairs: the second continues the first or is empty (the prompt
+                # attention kernel fetches every key once for both)
+                for a in range(0, n, 2 * QUERY_TILE):
                     self.pf_tiles += [r, t0 + a, min(QUERY_TILE, n - a), s + a]
+                    b = a + QUERY_TILE
+                    self.pf_tiles += [r, t0 + b, max(0, min(QUERY_TILE, n - b)), s + b]
             t0 += n
 
 

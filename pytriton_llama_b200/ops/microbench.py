@@ -71,7 +71,7 @@ def run(case: str, reps: int) -> dict:
         rows = torch.zeros(tokens, dtype=torch.int32, device=dev)
         pos = torch.arange(tokens, dtype=torch.int32, device=dev)
         qkv = torch.randn(tokens, (nq + 2 * nkv) * d, device=dev).bfloat16()
-        tiles = torch.tensor([[0, a, 128, a] for a in range(0, tokens, 128)], dtype=torch.int32, device=dev).reshape(-1)
+        tiles = torch.tensor([[0, a, 128, a] for a in range(0, tokens, 128)], dtype=torch.int32, device=dev).reshape(-1)   # pairs of consecutive tiles
         hints = SimpleNamespace(n_decode=0, decode_items=rows[:0], n_prefill_tiles=tokens // 128, prefill_tiles=tiles,
                                 max_ctx_len=tokens, decode_in_order=False)
         sec = _time(lambda: ops.paged_attention(qkv, cache, table, rows, pos, nq, nkv, d, page, d ** -0.5, hints=hints), reps)

@@ -218,8 +218,9 @@ def _hints(q_lens, ctx):
         if n == 1:
             dec.append(t0)
         else:
-            for a in range(0, n, 128):
+            for a in range(0, n, 256):                    # pairs: the second tile continues the first or is empty
                 tiles += [r, t0 + a, min(128, n - a), c - n + a]
+                tiles += [r, t0 + a + 128, max(0, min(128, n - a - 128)), c - n + a + 128]
         t0 += n
     i32 = lambda x: torch.tensor(x if x else [0], dtype=torch.int32).cuda()
     return SimpleNamespace(n_decode=len(dec), decode_items=i32(dec)[:len(dec)], n_prefill_tiles=len(tiles) // 4,
@@ -298,8 +299,9 @@ def test_attention_finds_one_far_key(ops, dtype, window):
         dec = SimpleNamespace(n_decode=T, decode_items=req6, n_prefill_tiles=0, prefill_tiles=req6, max_ctx_len=ctx)
         outs.append(ops.paged_attention(qd, cache.cuda(), bt6, req6, positions.cuda(), nq, nkv, d, page, 1 / math.sqrt(d),
                                         window=window, hints=dec).float().cpu().view(T, nq, d))
-        tiles = torch.tensor([[t, t, 1, int(positions[t])] for t in range(T)], dtype=torch.int32).reshape(-1).cuda()
-        pf = SimpleNamespace(n_decode=0, decode_items=req6[:0], n_prefill_tiles=T, prefill_tiles=tiles, max_ctx_len=ctx)
+        tiles = torch.tensor([[t, t, 1, int(positions[t]), t, t + 128, 0, int(positions[t]) + 128] for t in range(T)],
+                             dtype=torch.int32).reshape(-1).cuda()          # pairs whose second tile is empty
+        pf = SimpleNamespace(n_decode=0, decode_items=req6[:0], n_prefill_tiles=2 * T, prefill_tiles=tiles, max_ctx_len=ctx)
         outs.append(ops.paged_attention(qd, cache.cuda(), bt6, req6, positions.cuda(), nq, nkv, d, page, 1 / math.sqrt(d),
                                         window=window, hints=pf).float().cpu().view(T, nq, d))
     for res in outs:
