@@ -107,6 +107,64 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ residu
   }
 }
 
+// The same for many rows of a width of N4 * 128: one warp per row, the row in registers (N4 packets
+// of four per lane), no shared memory and no block-wide barrier.
+template <typename T, int N4>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_warp_kernel(T* __restrict__ y, float* __restrict__ residual_out, const float* __restrict__ residual_in,
+                        const T* __restrict__ x, const float* __restrict__ w, const int* __restrict__ rows, int out_rows,
+                        float eps) {
+  pdl_wait();
+  pdl_launch_dependents();
+  constexpr int hidden = N4 * 128;
+  const int lane = threadIdx.x & 31;
+  const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (m >= out_rows) return;
+  const int r = rows ? rows[m] : m;
+  const float* rin = residual_in ? residual_in + (size_t)r * hidden : nullptr;
+  const T* xin = x ? x + (size_t)r * hidden : nullptr;
+  float* rout = residual_out ? residual_out + (size_t)m * hidden : nullptr;
+  T* yo = y + (size_t)m * hidden;
+  float4 s[N4];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < N4; ++k) {
+    const int i = (k * 32 + lane) * 4;
+    s[k] = rin ? __ldcg(reinterpret_cast<const float4*>(rin + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (xin) {
+      if constexpr (sizeof(T) == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(xin + i);
+        s[k].x += v.x; s[k].y += v.y; s[k].z += v.z; s[k].w += v.w;
+      } else {
+        const uint2 raw = *reinterpret_cast<const uint2*>(xin + i);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        s[k].x += __bfloat162float(a.x); s[k].y += __bfloat162float(a.y);
+        s[k].z += __bfloat162float(b.x); s[k].w += __bfloat162float(b.y);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < N4; ++k) ss += s[k].x * s[k].x + s[k].y * s[k].y + s[k].z * s[k].z + s[k].w * s[k].w;
+  ss = warp_sum(ss);
+  const float rrms = 1.0f / sqrtf(ss / (float)hidden + eps);
+  const bool write_back = rout && (xin || rout != rin);      // unchanged rows are not rewritten
+#pragma unroll
+  for (int k = 0; k < N4; ++k) {
+    const int i = (k * 32 + lane) * 4;
+    if (write_back) *reinterpret_cast<float4*>(rout + i) = s[k];
+    const float4 g = __ldg(reinterpret_cast<const float4*>(w + i));
+    if constexpr (sizeof(T) == 4) {
+      *reinterpret_cast<float4*>(yo + i) = make_float4(s[k].x * rrms * g.x, s[k].y * rrms * g.y, s[k].z * rrms * g.z, s[k].w * rrms * g.w);
+    } else {
+      uint2 o;
+      *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(s[k].x * rrms * g.x, s[k].y * rrms * g.y);
+      *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(s[k].z * rrms * g.z, s[k].w * rrms * g.w);
+      *reinterpret_cast<uint2*>(yo + i) = o;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ SiLU(gate) * up
 // gu is [T, 2*inter] (gate columns first); out[t, i] = g * sigmoid(g) * u in float32.
 template <typename T>
@@ -181,6 +239,19 @@ int add_rmsnorm(void* y, float* residual_out, const float* residual_in, const vo
   }
   const int vec_ok = hidden % 4 == 0 && aligned16(y) && aligned16(w) && (!x || aligned16(x)) &&
                      (!residual_in || aligned16(residual_in)) && (!residual_out || aligned16(residual_out));
+  // many rows of a common width: a warp per row
+  if (vec_ok && out_rows >= 256 && (hidden == 512 || hidden == 1024 || hidden == 2048 || hidden == 4096)) {
+    const dim3 grid((out_rows + 7) / 8), block(256);
+#define PTL_NORM_ROWS(N4) launch_kernel("add_rmsnorm", add_rmsnorm_warp_kernel<T, N4>, grid, block, 0, as_stream(stream), \
+                                        (T*)y, residual_out, residual_in, (const T*)x, w, rows, out_rows, eps)
+    switch (hidden) {
+      case 512: return PTL_NORM_ROWS(4);
+      case 1024: return PTL_NORM_ROWS(8);
+      case 2048: return PTL_NORM_ROWS(16);
+      default: return PTL_NORM_ROWS(32);
+    }
+#undef PTL_NORM_ROWS
+  }
   int threads = hidden >= 8192 ? 1024 : (hidden >= 2048 ? 512 : (hidden >= 1024 ? 256 : 128));
   return launch_kernel("add_rmsnorm", add_rmsnorm_kernel<T>, dim3(out_rows), dim3(threads), smem, as_stream(stream),
                        (T*)y, residual_out, residual_in, (const T*)x, w, rows, hidden, eps, vec_ok);

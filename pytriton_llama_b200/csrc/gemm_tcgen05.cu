@@ -58,6 +58,7 @@ struct GemmParams {
   int scale_ld;
   float scale_eps;
   float scale_inv_n;
+  int tma_add;           // many tokens, add epilogue: the accumulator tiles are added into `out` by TMA (map_out)
 };
 
 template <int BN> struct TcCfg {
@@ -80,7 +81,9 @@ template <int BN> struct TcCfg {
   static constexpr int kPipeSmem = kStages * kStageBytes + 1024 /* alignment slack */ + kBarBytes;
   // few tokens, K split over a cluster: where the peers' partial sums of this block's rows arrive
   static constexpr int kRecvBytes = BN < 128 ? BN * kTileRows * 4 : 0;
-  static constexpr int kSmem = kPipeSmem + kRecvBytes;
+  // many tokens, add epilogue: two tiles of 128 rows x 32 float32 from which TMA adds into the residual
+  static constexpr int kAddStageBytes = BN >= 128 ? 2 * kTileRows * 128 + 512 : 0;   // (+512: the tiles start 1024-byte aligned behind the barriers)
+  static constexpr int kSmem = kPipeSmem + kRecvBytes + kAddStageBytes;
 };
 
 // SiLU for the bfloat16 path: the result is rounded to 8 bits of mantissa, so the fast
@@ -228,7 +231,8 @@ __device__ __forceinline__ void load_ways(uint32_t taddr, int stages, float (&v)
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kGemmThreads)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col, const GemmParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col,
+               const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
   using Cfg = TcCfg<BN>;
   extern __shared__ unsigned char smem_raw[];
   // tiles need 1024-byte alignment for the 128-byte swizzle pattern to start at row 0
@@ -268,6 +272,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_row) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_col) : "memory");
+    if (EPI == 2 && p.tma_add) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_out) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(Cfg::kTmemCols) : "memory");
@@ -431,7 +436,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       if (!mbar_wait(acc_full(buf), use & 1, abort_flag, p.status, 3)) break;
       tcgen05_fence_after();
       const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
-      if (!p.swapped) {
+      if (EPI == 2 && !p.swapped && p.tma_add) {
+        // The accumulator goes out through shared memory, 32 columns at a time, and TMA adds it into
+        // the residual: nothing of the residual is read here, and global memory sees whole rows of 128 bytes.
+        const uint32_t buf = smem_base + Cfg::kStages * Cfg::kStageBytes + 1024 + half * (kTileRows * 128);
+        const bool issuer = quad == 0 && lane == 0;
+#pragma unroll 1
+        for (int c0 = half * kHalfCols; c0 < (half + 1) * kHalfCols && c0 < BN && col_tile * BN + c0 < p.cols; c0 += 32) {
+          uint32_t r[32];
+          tmem_load_32(acc + c0, r);
+          if (issuer) bulk_wait_read_all();                      // the tile sent before has left the buffer
+          asm volatile("bar.sync %0, 128;" ::"r"(2 + half) : "memory");
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + row_in_tile * 128 + ((j ^ (row_in_tile & 7)) << 4)),
+                         "r"(r[4 * j]), "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3]) : "memory");
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("bar.sync %0, 128;" ::"r"(2 + half) : "memory");
+          if (issuer) tma_reduce_add_2d(&map_out, buf, col_tile * BN + c0, row_tile * kTileRows);
+        }
+      } else if (!p.swapped) {
 #pragma unroll 1
         for (int c0 = half * kHalfCols; c0 < (half + 1) * kHalfCols && c0 < BN; c0 += 32) {
           uint32_t r[32];
@@ -493,6 +517,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty(buf));
     }
+    if (EPI == 2 && !p.swapped && p.tma_add && quad == 0 && lane == 0) bulk_wait_all();   // the adds have landed
   }
   if (p.swapped && p.splits > 1) {
     const int row_tile = blockIdx.x;
@@ -566,7 +591,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
 
 // ---------------------------------------------------------------- host side
 template <int BN, int EPI>
-static int launch_tc(const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+static int launch_tc(const CUtensorMap& mr, const CUtensorMap& mc, const CUtensorMap& mo, const GemmParams& p, dim3 grid,
+                     cudaStream_t stream) {
   using Cfg = TcCfg<BN>;
   static bool raised = false;
   if (!raised) {
@@ -577,7 +603,7 @@ static int launch_tc(const CUtensorMap& mr, const CUtensorMap& mc, const GemmPar
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kGemmThreads);
-  cfg.dynamicSmemBytes = (p.swapped && p.splits > 1) ? Cfg::kSmem : Cfg::kPipeSmem;
+  cfg.dynamicSmemBytes = ((p.swapped && p.splits > 1) || p.tma_add) ? Cfg::kSmem : Cfg::kPipeSmem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   int nattr = 0;
@@ -595,18 +621,19 @@ static int launch_tc(const CUtensorMap& mr, const CUtensorMap& mc, const GemmPar
   }
   cfg.attrs = attr;
   cfg.numAttrs = nattr;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI>, mr, mc, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI>, mr, mc, mo, p);
   if (e != cudaSuccess) return fail("gemm_tc: launch failed: %s", cudaGetErrorString(e));
   return check_launch("gemm_tc");
 }
 
 template <int BN>
-static int launch_epi(int epi, const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& p, dim3 grid, cudaStream_t s) {
+static int launch_epi(int epi, const CUtensorMap& mr, const CUtensorMap& mc, const CUtensorMap& mo, const GemmParams& p, dim3 grid,
+                      cudaStream_t s) {
   switch (epi) {
-    case 0: return launch_tc<BN, 0>(mr, mc, p, grid, s);
-    case 1: return launch_tc<BN, 1>(mr, mc, p, grid, s);
-    case 2: return launch_tc<BN, 2>(mr, mc, p, grid, s);
-    case 3: return launch_tc<BN, 3>(mr, mc, p, grid, s);
+    case 0: return launch_tc<BN, 0>(mr, mc, mo, p, grid, s);
+    case 1: return launch_tc<BN, 1>(mr, mc, mo, p, grid, s);
+    case 2: return launch_tc<BN, 2>(mr, mc, mo, p, grid, s);
+    case 3: return launch_tc<BN, 3>(mr, mc, mo, p, grid, s);
   }
   return fail("gemm_tc: unknown epilogue %d", epi);
 }
@@ -672,7 +699,14 @@ PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, in
     }
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
     dim3 grid((unsigned)(tiles < sm_count ? tiles : sm_count));
-    return wide ? launch_epi<256>(epi, mr, mc, p, grid, s) : launch_epi<128>(epi, mr, mc, p, grid, s);
+    // the add epilogue hands its tiles to TMA, which adds them into the residual (unless the next norm's input is wanted too)
+    CUtensorMap mo = mr;
+    if (epi == 2 && !xs && N % 32 == 0 && ld_out % 4 == 0) {
+      rc = encode_map_f32(&mo, out, M, N, ld_out, kTileRows);
+      if (rc) return rc;
+      p.tma_add = 1;
+    }
+    return wide ? launch_epi<256>(epi, mr, mc, mo, p, grid, s) : launch_epi<128>(epi, mr, mc, mo, p, grid, s);
   }
   // few tokens: swapped operands; the K range is split over a cluster of 1, 2, 4 or 8 blocks so
   // that about two blocks per SM stream the weights
@@ -694,9 +728,9 @@ PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, in
   dim3 grid(row_tiles, splits);
   if (slots_out) *slots_out = (N + 15) / 16;
   switch (bn) {
-    case 16: return launch_epi<16>(epi, mr, mc, p, grid, s);
-    case 32: return launch_epi<32>(epi, mr, mc, p, grid, s);
-    default: return launch_epi<64>(epi, mr, mc, p, grid, s);
+    case 16: return launch_epi<16>(epi, mr, mc, mr, p, grid, s);
+    case 32: return launch_epi<32>(epi, mr, mc, mr, p, grid, s);
+    default: return launch_epi<64>(epi, mr, mc, mr, p, grid, s);
   }
 }
 

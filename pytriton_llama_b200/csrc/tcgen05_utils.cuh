@@ -52,6 +52,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+// Adds a tile of float32 in shared memory (rows of 128 bytes, 128-byte swizzle) into global memory:
+// the sum is formed in L2, the block reads nothing.  Issue, commit, and the two waits of the
+// issuing thread: for the tile to have been read out of shared memory, and for everything to be done.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
@@ -167,6 +177,22 @@ inline int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
   std::lock_guard<std::mutex> g(lock);
   if (cache.size() > 8192) cache.clear();
   cache.emplace(key, *map);
+  return 0;
+}
+
+// A [rows, cols] float32 matrix with `ld` elements between rows, written in boxes of 32 (cols) x
+// box_rows with the 128-byte swizzle (for tma_reduce_add_2d).  Not cached: the residual moves.
+inline int encode_map_f32(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  PTL_REQUIRE(fn != nullptr, "gemm_tc: the driver has no cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {32u, (cuuint32_t)box_rows};   // 32 float32 = one 128-byte swizzle row
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  PTL_REQUIRE(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled (float32) failed with %d (rows=%d cols=%d ld=%d)", (int)r, rows, cols, ld);
   return 0;
 }
 
