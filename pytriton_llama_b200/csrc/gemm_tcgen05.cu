@@ -62,7 +62,7 @@ struct GemmParams {
 };
 
 template <int BN> struct TcCfg {
-  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN == 64 ? 3 : 4));   // few tokens: small blocks, two or three per SM
+  static constexpr int kStages = BN >= 192 ? 4 : (BN >= 128 ? 6 : (BN == 64 ? 3 : 4));   // few tokens: small blocks, two or three per SM
   static constexpr int kRowBytes = kTileRows * kTileK * 2;     // 16 KB
   static constexpr int kColBytes = BN * kTileK * 2;
   static constexpr int kStageBytes = kRowBytes + kColBytes;
@@ -76,7 +76,7 @@ template <int BN> struct TcCfg {
   // the phase is compared).  Hence as many issuers as stages, or a divisor of their number.
   static constexpr int kAccWays = BN >= 128 ? 1 : (BN == 64 ? 3 : 4);
   static_assert(kStages % kAccWays == 0, "every stage belongs to one issuer");
-  static constexpr int kTmemCols = BN >= 128 ? BN * kAccBufs : (BN == 64 ? 256 : (BN * kAccWays < 32 ? 32 : BN * kAccWays));   // power of two >= 32
+  static constexpr int kTmemCols = BN == 192 ? 512 : (BN >= 128 ? BN * kAccBufs : (BN == 64 ? 256 : (BN * kAccWays < 32 ? 32 : BN * kAccWays)));   // power of two >= 32
   static constexpr int kBarBytes = 512;                        // barriers and TMEM slot, then 64 per-token scales
   static constexpr int kPipeSmem = kStages * kStageBytes + 1024 /* alignment slack */ + kBarBytes;
   // few tokens, K split over a cluster: where the peers' partial sums of this block's rows arrive
@@ -681,15 +681,6 @@ PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, in
   cudaStream_t s = as_stream(stream);
   if (M > 64) {
     p.swapped = 0; p.rows = M; p.cols = N; p.splits = 1; p.kb_per_split = num_kb;
-    const bool wide = N % 256 == 0 || N >= 2048;
-    int rc = make_map(&mr, X, M, K, kTileRows);
-    if (rc) return rc;
-    rc = make_map(&mc, W, N, K, wide ? 256 : 128);
-    if (rc) return rc;
-    const int bn = wide ? 256 : 128;
-    p.tiles_m = (M + kTileRows - 1) / kTileRows;
-    p.tiles_n = (N + bn - 1) / bn;
-    if (slots_out) *slots_out = p.tiles_n * 2;
     static int sm_count = 0;
     if (!sm_count) {
       int dev = 0;
@@ -697,6 +688,23 @@ PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, in
       cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
       if (sm_count <= 0) sm_count = 148;
     }
+    // 256 features per tile; 192 where N is a multiple of it and the tiles then fill the rounds of
+    // the SMs better (16 x 12 tiles of 256 take two rounds of 148, 16 x 16 of 192 take two cheaper
+    // ones); 128 for narrow products
+    const long long tm = (M + kTileRows - 1) / kTileRows;
+    int bn = (N % 256 == 0 || N >= 2048) ? 256 : 128;
+    if (bn == 256 && N % 192 == 0) {
+      const long long cost256 = (tm * ((N + 255) / 256) + sm_count - 1) / sm_count * 256;
+      const long long cost192 = (tm * (N / 192) + sm_count - 1) / sm_count * 192;
+      if (cost192 < cost256) bn = 192;
+    }
+    int rc = make_map(&mr, X, M, K, kTileRows);
+    if (rc) return rc;
+    rc = make_map(&mc, W, N, K, bn);
+    if (rc) return rc;
+    p.tiles_m = (M + kTileRows - 1) / kTileRows;
+    p.tiles_n = (N + bn - 1) / bn;
+    if (slots_out) *slots_out = p.tiles_n * 2;
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
     dim3 grid((unsigned)(tiles < sm_count ? tiles : sm_count));
     // the add epilogue hands its tiles to TMA, which adds them into the residual (unless the next norm's input is wanted too)
@@ -706,7 +714,9 @@ PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, in
       if (rc) return rc;
       p.tma_add = 1;
     }
-    return wide ? launch_epi<256>(epi, mr, mc, mo, p, grid, s) : launch_epi<128>(epi, mr, mc, mo, p, grid, s);
+    if (bn == 256) return launch_epi<256>(epi, mr, mc, mo, p, grid, s);
+    if (bn == 192) return launch_epi<192>(epi, mr, mc, mo, p, grid, s);
+    return launch_epi<128>(epi, mr, mc, mo, p, grid, s);
   }
   // few tokens: swapped operands; the K range is split over a cluster of 1, 2, 4 or 8 blocks so
   // that about two blocks per SM stream the weights
