@@ -3,6 +3,7 @@
     python -m pytriton_llama_b200.ops.microbench <case> [--reps N]
 
 Cases: ``decode_attention`` (32 requests x 4,096 cached tokens, 268 MB of keys and values),
+``decode_step_attention`` (8 requests x 4,096 tokens with rotary encoding and cache write folded in),
 ``gemm_decode`` (8 tokens x a [65536, 2048] weight, 268 MB), ``gemm_prefill`` (2,048 tokens x the
 gate/up weight [16384, 2048] with the SiLU*up epilogue), ``prefill_attention`` (one 2,048-token
 prompt, 32 query heads).  Inputs are larger than the 126 MB L2 where the kernel is a stream, so
@@ -51,6 +52,24 @@ def run(case: str, reps: int) -> dict:
                                 max_ctx_len=ctx, decode_in_order=True)
         sec = _time(lambda: ops.paged_attention(qkv, cache, table, rows, pos, nq, nkv, d, page, d ** -0.5, hints=hints), reps)
         return {"case": case, "us": sec * 1e6, "bytes": cache.numel() * 2, "GB/s": cache.numel() * 2 / sec / 1e9}
+    if case == "decode_step_attention":
+        # the attention of one layer of a decode step at batch 8: q|k|v unrotated, rotary encoding and
+        # the cache write inside the kernel, the four splits of a token merged over a cluster
+        batch, ctx = 8, 4096
+        per = ctx // page
+        cache = torch.randn(batch * per, 2, nkv, page, d, device=dev).bfloat16()
+        table = torch.arange(batch * per, dtype=torch.int32, device=dev).view(batch, per)
+        rows = torch.arange(batch, dtype=torch.int32, device=dev)
+        pos = torch.full((batch,), ctx - 1, dtype=torch.int32, device=dev)
+        slots = (rows * per * page + ctx - 1).int()
+        inv = (1.0 / (500000.0 ** (torch.arange(0, d, 2, device=dev).float() / d))).contiguous()
+        qkv = torch.randn(batch, (nq + 2 * nkv) * d, device=dev).bfloat16()
+        hints = SimpleNamespace(n_decode=batch, decode_items=rows, n_prefill_tiles=0, prefill_tiles=rows,
+                                max_ctx_len=ctx, decode_in_order=True)
+        sec = _time(lambda: ops.rope_attention(qkv, pos, inv, d, slots, cache, table, rows, nq, nkv, d, page, d ** -0.5,
+                                               hints=hints), reps)
+        nbytes = cache.numel() * 2
+        return {"case": case, "us": sec * 1e6, "bytes": nbytes, "GB/s": nbytes / sec / 1e9}
     if case == "gemm_decode":
         m, n, k = 8, 65536, 2048
         x = torch.randn(m, k, device=dev).bfloat16()
@@ -82,7 +101,7 @@ def run(case: str, reps: int) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("case", choices=["decode_attention", "gemm_decode", "gemm_prefill", "prefill_attention"])
+    ap.add_argument("case", choices=["decode_attention", "decode_step_attention", "gemm_decode", "gemm_prefill", "prefill_attention"])
     ap.add_argument("--reps", type=int, default=10)
     args = ap.parse_args()
     print(json.dumps(run(args.case, args.reps)))
