@@ -339,3 +339,136 @@ def test_layers_with_a_window_get_pages_of_their_own(tmp_path, dtype):
     held_full = sum(1 for p_ in eng.cache.block_table("long", full_group) if p_ >= 0)
     assert held_full == -(-260 // 16) and held_window <= -(-window // 16) + 1
     eng.cache.check_invariants()
+
+
+# ---------------------------------------------------------------------------------------------
+# A toy feed-forward with routing and a toy position encoding, both defined here and registered
+# from outside the package: layer 0 keeps the dense feed-forward, layer 1 routes every token to
+# one of three small experts; attention rotates only half of every head, with frequencies of its own.
+
+def _register_toy_routed_ffn_and_position():
+    from pytriton_llama_b200.parts import Part, TensorSpec, register_part
+
+    @register_part("ffn", "toy_top1_experts")
+    class ToyTop1Experts(Part):
+        """y = p_e * W2_e relu(W1_e x) for the expert e with the largest router logit, p = softmax(logits)."""
+
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            self.hidden, self.inter, self.experts = spec.params["hidden"], spec.params["inter"], spec.params["experts"]
+
+        def tensor_specs(self):
+            return {"router": TensorSpec((self.experts, self.hidden)),
+                    "w1": TensorSpec((self.experts * self.inter, self.hidden)),
+                    "w2": TensorSpec((self.experts * self.hidden, self.inter))}
+
+        def load(self, tensors):
+            self.router = self._to_f32(tensors["router"])
+            self.w1 = self._to_f32(tensors["w1"]).view(self.experts, self.inter, self.hidden)
+            self.w2 = self._to_f32(tensors["w2"]).view(self.experts, self.hidden, self.inter)
+
+        def forward(self, x):
+            xf = x.float()
+            logits = xf @ self.router.T                       # router logits in float32
+            probs = torch.softmax(logits, dim=-1)
+            choice = logits.argmax(dim=-1)
+            out = torch.zeros_like(xf)
+            for e in range(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    h = torch.relu(xf[rows] @ self.w1[e].T) @ self.w2[e].T
+                    out[rows] = probs[rows, e:e + 1] * h
+            return out.to(x.dtype)
+
+    @register_part("position", "toy_half_rotary")
+    class ToyHalfRotary(Part):
+        """Rotates the first half of every head only, with frequencies 0.3 / (j + 1)."""
+
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            self.rot = spec.params["head_dim"] // 2
+            self.inv_freq = (0.3 / (torch.arange(self.rot // 2, dtype=torch.float32) + 1.0)).to(runtime.device)
+
+        def rotary_table(self):
+            return self.inv_freq, self.rot
+
+        def apply(self, qk, positions, heads, head_dim):
+            raise NotImplementedError
+
+
+def _plain_routed_forward(cfg, w, tokens, experts, inter):
+    """Float64, whole sequence, from the plain implementation's pieces."""
+    tokens = torch.as_tensor(tokens)
+    S = len(tokens)
+    pos = torch.arange(S)
+    nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    d = plain_llama.head_dim_of(cfg)
+    rot = d // 2
+    inv_freq = 0.3 / (torch.arange(rot // 2, dtype=torch.float32) + 1.0)
+    cos, sin = plain_llama.rope_cos_sin(inv_freq, pos, torch.float64)      # [S, rot]
+
+    def half_rotary(x):                                                    # x [S, heads, d]
+        return torch.cat((plain_llama.apply_rope(x[..., :rot], cos, sin), x[..., rot:]), dim=-1)
+
+    h = w["model.embed_tokens.weight"][tokens]
+    eps = cfg["rms_norm_eps"]
+    for layer in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{layer}."
+        x = plain_llama.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+        q = half_rotary((x @ w[p + "self_attn.q_proj.weight"].T).view(S, nq, d))
+        k = half_rotary((x @ w[p + "self_attn.k_proj.weight"].T).view(S, nkv, d))
+        v = (x @ w[p + "self_attn.v_proj.weight"].T).view(S, nkv, d)
+        h = h + plain_llama.causal_gqa_attention(q, k, v).reshape(S, nq * d) @ w[p + "self_attn.o_proj.weight"].T
+        x = plain_llama.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
+        if layer == 1:
+            logits = x @ w[p + "moe.router"].T
+            probs = torch.softmax(logits, -1)
+            choice = logits.argmax(-1)
+            w1 = w[p + "moe.w1"].view(experts, inter, -1)
+            w2 = w[p + "moe.w2"].view(experts, -1, inter)
+            y = torch.stack([probs[t, choice[t]] * (w2[choice[t]] @ torch.relu(w1[choice[t]] @ x[t])) for t in range(S)])
+        else:
+            y = plain_llama.swiglu_ffn(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+        h = h + y
+    h = plain_llama.rms_norm(h, w["model.norm.weight"], eps)
+    return h @ w.get("lm_head.weight", w["model.embed_tokens.weight"]).T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_routed_feed_forward_and_toy_position_encoding(tmp_path, dtype):
+    """Different feed-forwards in different layers, one of them with routing, and a position
+    encoding the package does not have: registered here, built by the model's spec, stepped
+    through the engine in mixed batches, compared with a plain float64 statement."""
+    import traces
+    from pytriton_llama_b200.config import EngineConfig, LlamaConfig, register_architecture
+    from pytriton_llama_b200.engine.engine import Engine
+    from pytriton_llama_b200.models.llama import llama_spec
+    from pytriton_llama_b200.parts import PartSpec
+    from pytriton_llama_b200.weights import read_folder, write_random_model
+    _register_toy_routed_ffn_and_position()
+    cfg = dict(TINY["B"], architectures=["ToyRoutedForCausalLM"], num_hidden_layers=2)
+    experts, inter = 3, 48
+
+    def spec(c, norm_init="ones"):
+        sp = llama_spec(LlamaConfig.from_dict(cfg), norm_init="ones_jitter")
+        for i, layer in enumerate(sp.layers):
+            layer.parts["mixer"].parts["position"] = PartSpec("toy_half_rotary", {"head_dim": LlamaConfig.from_dict(cfg).head_dim})
+            if i == 1:
+                p = f"model.layers.{i}.moe."
+                layer.parts["ffn"] = PartSpec("toy_top1_experts", {"hidden": cfg["hidden_size"], "inter": inter, "experts": experts},
+                                              {"router": p + "router", "w1": p + "w1", "w2": p + "w2"})
+        return sp
+
+    register_architecture("ToyRoutedForCausalLM", LlamaConfig.from_dict, spec)
+    stored = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = write_random_model(tmp_path / "routed", cfg, seed=9, dtype=stored, std=0.08)
+    tensors = read_folder(folder)
+    assert "model.layers.1.moe.router" in tensors and "model.layers.1.mlp.gate_proj.weight" not in tensors
+    vocab = cfg["vocab_size"]
+    eng = Engine(folder, EngineConfig(dtype=dtype, page_size=8, max_gpu_num_blocks=40, max_seq_len=160, max_num_seqs=3))
+    seqs = {f"m{i}": random_tokens(n, vocab, 70 + i) for i, n in enumerate([37, 9, 70, 18])}
+    w = {k: v.double() for k, v in tensors.items()}
+    ref = {r: _plain_routed_forward(cfg, w, s, experts, inter) for r, s in seqs.items()}
+    got = traces.replay(eng, traces.mixed(seqs, live=3))
+    for r in seqs:
+        assert_close(got[r], ref[r], dtype, r)
