@@ -485,6 +485,8 @@ class CudaOps:
             # small batches: 128-key tiles at two blocks per SM (296 in flight); large ones: 64-key tiles, four per SM
             target = 296 if pairs <= 148 else self.DECODE_BLOCKS
             splits = max(1, min(target // pairs, -(-longest // 128)))
+            if target == 296 and splits > 8:
+                splits = 8      # what a cluster merges through shared memory; more splits would go through global memory (slower)
             part_acc = part_ml = counters = None
             if splits > 1:
                 splits = min(splits, 512)
