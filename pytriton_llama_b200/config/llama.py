@@ -72,6 +72,7 @@ class LlamaConfig:
     rms_norm_eps: float = 1e-5
     rope_theta: float = 10000.0
     rope_scaling: Optional[RopeScaling] = None
+    partial_rotary_factor: float = 1.0   # share of every head that is rotated (lite_llama/models/RotaryEmbedding.py:43)
     tie_word_embeddings: bool = True
     max_position_embeddings: Optional[int] = None
     initializer_range: float = 0.02
@@ -111,6 +112,7 @@ class LlamaConfig:
             rms_norm_eps=float(data.get("rms_norm_eps", 1e-5)),
             rope_theta=float(data.get("rope_theta", 10000.0)),
             rope_scaling=RopeScaling.from_dict(data.get("rope_scaling")),
+            partial_rotary_factor=float(data.get("partial_rotary_factor", 1.0)),
             tie_word_embeddings=bool(data.get("tie_word_embeddings", True)),
             max_position_embeddings=data.get("max_position_embeddings"),
             initializer_range=float(data.get("initializer_range", 0.02)),
@@ -141,6 +143,9 @@ class LlamaConfig:
             raise ConfigError(f"rms_norm_eps must be positive, got {self.rms_norm_eps}")
         if not (self.rope_theta > 0):
             raise ConfigError(f"rope_theta must be positive, got {self.rope_theta}")
+        if not (0 < self.partial_rotary_factor <= 1) or self.rotary_dim % 2 or self.rotary_dim <= 0:
+            raise ConfigError(f"partial_rotary_factor={self.partial_rotary_factor} must lie in (0, 1] and leave an even "
+                              f"rotary width (head_dim {self.head_dim} gives {self.rotary_dim})")
 
     # ------------------------------------------------------------------ writing
     def to_dict(self) -> Dict[str, Any]:
@@ -154,6 +159,7 @@ class LlamaConfig:
             "hidden_act": "silu", "attention_bias": False, "mlp_bias": False,
             "rms_norm_eps": self.rms_norm_eps, "rope_theta": self.rope_theta,
             "rope_scaling": None if self.rope_scaling is None else self.rope_scaling.to_dict(),
+            "partial_rotary_factor": self.partial_rotary_factor,
             "tie_word_embeddings": self.tie_word_embeddings,
             "max_position_embeddings": self.max_position_embeddings,
             "initializer_range": self.initializer_range,
@@ -161,6 +167,11 @@ class LlamaConfig:
             "torch_dtype": self.torch_dtype,
         }
         return d
+
+    @property
+    def rotary_dim(self) -> int:
+        """Leading elements of every head that the position encoding rotates: int(head_dim * factor)."""
+        return int(self.head_dim * self.partial_rotary_factor)
 
     @property
     def eos_token_ids(self) -> List[int]:

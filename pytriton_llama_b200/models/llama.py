@@ -18,7 +18,8 @@ def llama_spec(cfg: LlamaConfig, norm_init: str = "ones") -> ModelSpec:
     layers = []
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."
-        position = PartSpec("rope", {"head_dim": cfg.head_dim, "theta": cfg.rope_theta, "scaling": scaling})
+        position = PartSpec("rope", {"head_dim": cfg.head_dim, "theta": cfg.rope_theta, "scaling": scaling,
+                                     "rotary_dim": cfg.rotary_dim})
         mixer = PartSpec(
             "gqa_attention",
             {"hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,

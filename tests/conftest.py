@@ -51,6 +51,7 @@ TINY_C = {
     "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 2.0, "high_freq_factor": 8.0,
                      "original_max_position_embeddings": 32},
     "rms_norm_eps": 3e-4, "tie_word_embeddings": True, "max_position_embeddings": 1024,
+    "partial_rotary_factor": 0.5,      # only the first 24 elements of a head are rotated
 }
 # Tolerances, fixed before the kernels were written.  float32 engine against the float64 plain
 # implementation: 1e-4 absolute on logits of size up to ~6.  bfloat16 engine (same bfloat16

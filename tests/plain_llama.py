@@ -55,11 +55,16 @@ def head_dim_of(cfg):
     return hd if hd is not None else cfg["hidden_size"] // cfg["num_attention_heads"]
 
 
+def rotary_dim_of(cfg):
+    # lite_llama/models/RotaryEmbedding.py:43-44: dim = int(head_dim * partial_rotary_factor), factor 1.0 when absent
+    return int(head_dim_of(cfg) * cfg.get("partial_rotary_factor", 1.0))
+
+
 def rope_inv_freq(cfg):
     """Inverse frequencies, float32.  lite_llama/models/RotaryEmbedding.py:51 (default) and
     :80-98 (llama3 scaling: long wavelengths divided by ``factor``, a smooth blend in the
     medium band, short wavelengths untouched)."""
-    d = head_dim_of(cfg)
+    d = rotary_dim_of(cfg)
     base = cfg.get("rope_theta", 10000.0)
     inv_freq = 1.0 / (base ** (torch.arange(0, d, 2, dtype=torch.int64).float() / d))
     sc = cfg.get("rope_scaling")
@@ -151,8 +156,9 @@ def attention_block(x, positions, cfg, w, prefix, window=None):
     k = (x @ w[prefix + "self_attn.k_proj.weight"].T).view(S, nkv, d)
     v = (x @ w[prefix + "self_attn.v_proj.weight"].T).view(S, nkv, d)
     cos, sin = rope_cos_sin(rope_inv_freq(cfg), positions, x.dtype)
-    q = apply_rope(q, cos, sin)
-    k = apply_rope(k, cos, sin)
+    rot = rotary_dim_of(cfg)      # the leading `rot` elements of a head are rotated, the rest pass through
+    q = torch.cat((apply_rope(q[..., :rot], cos, sin), q[..., rot:]), dim=-1)
+    k = torch.cat((apply_rope(k[..., :rot], cos, sin), k[..., rot:]), dim=-1)
     o = causal_gqa_attention(q, k, v, window)
     return o.reshape(S, nq * d) @ w[prefix + "self_attn.o_proj.weight"].T
 

@@ -45,6 +45,8 @@ def test_round_trip_through_json():
     ({"rope_scaling": {"rope_type": "llama3", "factor": 2.0}}, "lacks"),
     ({"vocab_size": None}, "vocab_size"),
     ({"rms_norm_eps": 0.0}, "rms_norm_eps"),
+    ({"partial_rotary_factor": 1.5}, "partial_rotary_factor"),
+    ({"partial_rotary_factor": 0.3}, "partial_rotary_factor"),       # 32 * 0.3 = 9: an odd rotary width
 ])
 def test_refuses_what_it_cannot_run(change, word):
     d = dict(TINY_B)
@@ -76,6 +78,9 @@ def test_spec_carries_the_configs_constants():
     assert blk.parts["mixer"].parts["position"].params["theta"] == 500000.0
     assert blk.parts["mixer"].parts["position"].params["scaling"]["factor"] == 8.0
     assert blk.parts["ffn"].params == {"hidden": 192, "inter": 320}
+    assert blk.parts["mixer"].parts["position"].params["rotary_dim"] == 32
+    half = llama_spec(LlamaConfig.from_dict(dict(TINY_B, partial_rotary_factor=0.5)))
+    assert half.layers[0].parts["mixer"].parts["position"].params["rotary_dim"] == 16
     assert [(e.layer, e.cache, e.write) for e in spec.run_order] == [(0, 0, True), (1, 1, True), (2, 2, True)]
 
 

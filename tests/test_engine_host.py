@@ -101,3 +101,23 @@ def test_overlapped_steps_generate_the_same_tokens(model_folders, name):
             preempted += runs[1][3] if pages < 64 else 0
     assert preempted > 0, "the tight cache pre-empted nothing"
     assert any(len(o) < 12 for o in _llm(folder, name, 64, True).generate(prompts, settings[0])), "no stop token ended a request"
+
+
+def test_partial_rotary_factor_rotates_the_leading_part_of_every_head(tmp_path):
+    """config.json's partial_rotary_factor (read by lite_llama/models/RotaryEmbedding.py:43): the
+    engine and the plain implementation rotate the first head_dim * factor elements of a head."""
+    from conftest import make_model_folder
+    from pytriton_llama_b200.weights import write_random_model
+    cfg = dict(TINY["B"], partial_rotary_factor=0.5)
+    folder = write_random_model(tmp_path / "half", cfg, seed=21, dtype=torch.float32, std=0.08)
+    pcfg, w = plain_llama.load_model_folder(folder, dtype=torch.float64)
+    assert pcfg["partial_rotary_factor"] == 0.5
+    seqs = {f"r{i}": random_tokens(n, 384, 900 + i) for i, n in enumerate([9, 40, 70])}
+    ref = {r: plain_llama.forward(pcfg, w, s) for r, s in seqs.items()}
+    full = plain_llama.forward(dict(pcfg, partial_rotary_factor=1.0), w, seqs["r2"])
+    assert (full - ref["r2"]).abs().max() > 1e-2, "the factor changes nothing in the plain implementation"
+    eng = Engine(folder, EngineConfig(dtype="float32", page_size=8, max_gpu_num_blocks=40, max_seq_len=128, max_num_seqs=3),
+                 device="cpu", ops=TorchOps())
+    got = traces.replay(eng, traces.portions(seqs))
+    for r in seqs:
+        assert (got[r].double() - ref[r]).abs().max() < FP32_TOL, r

@@ -61,10 +61,11 @@ def test_rope_part_builds_the_reference_frequencies(rt):
     from pytriton_llama_b200.parts import PartSpec, build_part
     for cfg in TINY.values():
         hd = cfg["head_dim"]
-        part = build_part("position", PartSpec("rope", {"head_dim": hd, "theta": cfg["rope_theta"], "scaling": cfg["rope_scaling"]}),
-                          rt[torch.float32])
+        want_rot = plain_llama.rotary_dim_of(cfg)
+        part = build_part("position", PartSpec("rope", {"head_dim": hd, "theta": cfg["rope_theta"], "scaling": cfg["rope_scaling"],
+                                                        "rotary_dim": want_rot}), rt[torch.float32])
         inv, rot = part.rotary_table()
-        assert rot == hd and inv.dtype == torch.float32
+        assert rot == want_rot and inv.dtype == torch.float32
         assert torch.equal(inv.cpu(), plain_llama.rope_inv_freq(cfg))      # bit for bit, llama3 scaling included
 
 
