@@ -525,14 +525,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     const int rows_per = kTileRows / S;                    // rows of the tile that each block owns (S is 2, 4 or 8)
     float* recv = reinterpret_cast<float*>(smem + Cfg::kPipeSmem - 1024);      // [S sources][BN columns][rows_per]
     cluster_wait();                                        // every block of the cluster runs
-    if (warp >= 2 && warp < 6 && !*abort_flag) {
+    // Both sets of four warps send (a warp reaches the TMEM lanes 32 * (warp % 4)..): they take turns
+    // at the groups of 16 columns.  The warps that issued MMAs have not waited for the accumulators yet.
+    bool acc_ok = true;
+    if (warp >= 6 && BN > 16) {
+      acc_ok = mbar_wait(acc_full(0), 0, abort_flag, p.status, 3);
+      tcgen05_fence_after();
+    }
+    if (warp >= 2 && (warp < 6 || BN > 16) && acc_ok && !*abort_flag) {
       // this thread's row of the tile goes to the block that owns it (neighbouring lanes write
       // neighbouring words: wider stores of a row's columns would collide in the banks)
       const int rl = (warp & 3) * 32 + lane;
       const uint32_t acc = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
       const uint32_t dst = map_to_peer(smem_addr(recv) + 4u * ((split * BN) * rows_per + rl % rows_per), rl / rows_per);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
+      for (int c0 = (BN > 16 ? ((warp - 2) >> 2) * 16 : 0); c0 < BN; c0 += (BN > 16 ? 32 : 16)) {
         float v[16];
         load_ways<BN, Cfg::kAccWays>(acc + c0, my_kb, v);
 #pragma unroll
