@@ -25,7 +25,7 @@ __device__ __forceinline__ float dec_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));   // 0 for -inf; P is rounded to bfloat16 anyway
   return y;
 }
-constexpr int kDecStagedPages = 1024;   // block-table entries of a block's key range kept in shared memory
+constexpr int kDecStagedPages = 512;    // block-table entries of a block's key range kept in shared memory (8,192 keys with pages of 16)
 
 // KP = groups of 16 keys per warp and tile: 1 (64-key tiles, four blocks per SM) for large batches,
 // 2 (128-key tiles, two blocks per SM, fewer barriers per key) when few blocks are in flight.

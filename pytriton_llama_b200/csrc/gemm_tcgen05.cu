@@ -78,7 +78,7 @@ template <int BN> struct TcCfg {
   static_assert(kStages % kAccWays == 0, "every stage belongs to one issuer");
   static constexpr int kTmemCols = BN == 192 ? 512 : (BN >= 128 ? BN * kAccBufs : (BN == 64 ? 256 : (BN * kAccWays < 32 ? 32 : BN * kAccWays)));   // power of two >= 32
   static constexpr int kBarBytes = 512;                        // barriers and TMEM slot, then 64 per-token scales
-  static constexpr int kPipeSmem = kStages * kStageBytes + 1024 /* alignment slack */ + kBarBytes;
+  static constexpr int kPipeSmem = kStages * kStageBytes + kBarBytes;   // (the dynamic shared memory is declared 1024-byte aligned)
   // few tokens, K split over a cluster: where the peers' partial sums of this block's rows arrive
   static constexpr int kRecvBytes = BN < 128 ? BN * kTileRows * 4 : 0;
   // many tokens, add epilogue: two tiles of 128 rows x 32 float32 from which TMA adds into the residual
@@ -234,9 +234,13 @@ __global__ void __launch_bounds__(kGemmThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col,
                const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
   using Cfg = TcCfg<BN>;
-  extern __shared__ unsigned char smem_raw[];
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   // tiles need 1024-byte alignment for the 128-byte swizzle pattern to start at row 0
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* smem = smem_raw;
+  if (smem_addr(smem) & 1023u) {                               // never expected (the same in every block): refuse rather than compute garbage
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, 99);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
   // bars: [0,S) stage full, [S,2S) stage empty, then accumulator full[2], accumulator empty[2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::kStages + 4);
@@ -523,7 +527,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     const int row_tile = blockIdx.x;
     const int S = p.splits;
     const int rows_per = kTileRows / S;                    // rows of the tile that each block owns (S is 2, 4 or 8)
-    float* recv = reinterpret_cast<float*>(smem + Cfg::kPipeSmem - 1024);      // [S sources][BN columns][rows_per]
+    float* recv = reinterpret_cast<float*>(smem + Cfg::kPipeSmem);             // [S sources][BN columns][rows_per]
     cluster_wait();                                        // every block of the cluster runs
     // Both sets of four warps send (a warp reaches the TMEM lanes 32 * (warp % 4)..): they take turns
     // at the groups of 16 columns.  The warps that issued MMAs have not waited for the accumulators yet.
