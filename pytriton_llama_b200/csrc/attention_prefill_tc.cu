@@ -1,25 +1,28 @@
 // Attention of prompt portions over the paged cache on the fifth-generation tensor cores
-// (head size 64, bfloat16).  One block per (pair of tiles of up to 128 query tokens each, query
+// (head size 64 or 128, bfloat16).  One block per (pair of tiles of up to 128 query tokens each, query
 // head); the pair are consecutive rows of one request (tile B continues tile A; B may be absent),
 // so both walk the same keys and every key/value tile is fetched once for 256 query rows:
-//   S = Q K^T       tcgen05.mma 128 x 128 x 64 into TMEM (float32), per tile of the pair; the K
-//                   tile is fetched page by page with TMA into 128-byte-swizzled shared memory;
+//   S = Q K^T       tcgen05.mma 128 x keys x D into TMEM (float32), per tile of the pair; the K
+//                   tile (128 keys with head size 64, 64 keys with 128: 16 KB either way) is
+//                   fetched page by page with TMA into 128-byte-swizzled shared memory, 64
+//                   values of a row at a time;
 //   softmax         a group of four warps per tile of the pair, one thread per query row:
-//                   tcgen05.ld of the row's 128 scores, running max and sum in float32 (base-2
+//                   tcgen05.ld of the row's scores, running max and sum in float32 (base-2
 //                   exponentials), P rounded to bfloat16 and written to shared memory in the
 //                   layout of a K-major MMA operand, the output accumulator in TMEM rescaled by
 //                   the change of the maximum;
-//   O += P V        tcgen05.mma 128 x 64 x 128; V stays as the cache has it ([key][dim], the
+//   O += P V        tcgen05.mma 128 x D x keys; V stays as the cache has it ([key][dim], the
 //                   "MN-major" operand form), so nothing is transposed;
 //   epilogue        O / sum -> bfloat16.
 // The two tiles of the pair take turns: while group A works on the scores of a key tile, the
 // tensor core computes those of group B, then A's P V while B is in its softmax, and so on -- the
 // exponentials of one tile run under the matrix products of the other inside one block (one
-// block per SM: 193 KB of shared memory, 384 TMEM columns).  Queries attend over the pages up to
+// block per SM: 193 or 225 KB of shared memory, 384 or 512 TMEM columns).  Queries attend over the pages up to
 // their own position (the step's own keys were written before), optionally within a window.
 //
-// Warp roles (320 threads): warp 0 TMA producer, warp 1 TMEM allocation + MMA issue, warps 2..5
-// softmax and epilogue of tile A, warps 6..9 of tile B (warp w owns TMEM lanes 32*(w%4)..+31).
+// Warp roles (352 threads): warp 0 TMA producer, warp 1 TMEM allocation + MMA issue for tile A, warps
+// 2..5 softmax and epilogue of tile A, warps 6..9 of tile B (warp w owns TMEM lanes 32*(w%4)..+31),
+// warp 10 MMA issue for tile B.
 // Waits are bounded as in the matrix product: a wait that gives up records a code in *status and
 // the block drains.
 //
@@ -31,17 +34,27 @@
 namespace ptl {
 
 constexpr int kTcRows = 128;       // query rows per tile of the pair
-constexpr int kTcKeys = 128;       // keys per tile
-constexpr int kTcD = 64;           // head size
-constexpr int kTcThreads = 320;
-constexpr int kTcStages = 3;
-constexpr int kTcTileBytes = kTcKeys * kTcD * 2;           // one of K / V: 16 KB
-constexpr int kTcQBytes = kTcRows * kTcD * 2;              // 16 KB per tile of the pair
-constexpr int kTcPBytes = kTcRows * kTcKeys * 2;           // 32 KB per tile of the pair: two 64-key blocks of [128 rows][128 B]
+constexpr int kTcIssuerB = 10;      // the warp that issues the MMAs of tile B (warp 1: of tile A)
 constexpr int kTcStagedPages = 264;    // block-table entries kept in shared memory (4,096 + 128 keys with pages of 16)
 constexpr int kTcBarBytes = 256;
-constexpr int kTcSmem = 2 * kTcQBytes + kTcStages * 2 * kTcTileBytes + 2 * kTcPBytes + kTcBarBytes + kTcStagedPages * 4;
-constexpr int kTcTmemCols = 512;   // S of A and B: columns 0..127, 128..255; O of A and B: 256..319, 320..383
+constexpr int kTcTmemCols = 512;   // S of A and B: columns 0..127, 128..255; O of A and B: 256.., 256 + D..
+constexpr int kTcChunk = kTcRows * 128;                      // 128 rows of 64 bfloat16: one swizzled block of an operand
+
+template <int D> struct PfCfg {
+  static_assert(D == 64 || D == 128, "head size 64 or 128");
+  static constexpr int kKeys = D == 64 ? 128 : 64;           // keys per tile
+  static constexpr int kTileBytes = kKeys * D * 2;           // one of K / V: 16 KB
+  static constexpr int kQBytes = kTcRows * D * 2;            // per tile of the pair: D / 64 blocks of [128 rows][128 B]
+  static constexpr int kPBytes = kTcRows * kKeys * 2;        // per tile of the pair: kKeys / 64 blocks of [128 rows][128 B]
+  // P of a tile of the pair lives in one buffer or in two that alternate: with two, the softmax of a
+  // key tile does not have to wait for the P V product of the tile before it (which may still
+  // stand in the tensor core's queue behind the other group's products), only for the one before that
+  // (two where they fit: with head size 64 a P buffer is 32 KB, and two per tile would cost a K/V stage)
+  static constexpr int kPBufs = D == 64 ? 1 : 2;
+  static constexpr int kThreads = 352;
+  static constexpr int kStages = 3;                          // K/V tiles in flight
+  static constexpr int kSmem = 2 * kQBytes + kStages * 2 * kTileBytes + 2 * kPBufs * kPBytes + kTcBarBytes + kTcStagedPages * 4;
+};
 
 struct PrefillTcParams {
   __nv_bfloat16* out;
@@ -52,8 +65,12 @@ struct PrefillTcParams {
   float scale_log2;
 };
 
-// Barriers (8 bytes each): q_full, kv_full[3], kv_empty[3], then per tile of the pair s_full, p_full, o_done, s_free.
-enum : int { kBarQ = 0, kBarKvFull = 1, kBarKvEmpty = 4, kBarSFull = 7, kBarPFull = 9, kBarODone = 11, kBarSFree = 13, kBarCount = 15 };
+// Barriers (8 bytes each): q_full, per tile of the pair s_full, s_free, p_full and o_done (one of each per P
+// buffer), then kv_full[stages], kv_empty[stages].  P buffers have barriers of their own because a wait
+// only tells the phases of a barrier apart by their parity: with one p_full for both buffers the softmax
+// could hand over two tiles before the issuing thread, held up at a full tensor-core queue, looked
+// again, and it would then wait for ever.
+enum : int { kBarQ = 0, kBarSFull = 1, kBarSFree = 3, kBarPFull = 5, kBarODone = 9, kBarKvFull = 13 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -61,14 +78,20 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(kTcThreads)
+template <int D>
+__global__ void __launch_bounds__(PfCfg<D>::kThreads)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             const PrefillTcParams p) {
+  using Cfg = PfCfg<D>;
+  constexpr int kTcStages = Cfg::kStages, kBarKvEmpty = kBarKvFull + kTcStages, kBarCount = kBarKvEmpty + kTcStages;
+  static_assert(kBarCount * 8 + 8 <= kTcBarBytes, "barriers, TMEM slot and abort flag fit their region");
+  constexpr int kPB = Cfg::kPBufs;
+  constexpr int kTcKeys = Cfg::kKeys, kTcD = D, kTcTileBytes = Cfg::kTileBytes, kTcQBytes = Cfg::kQBytes, kTcPBytes = Cfg::kPBytes;
   extern __shared__ __align__(1024) unsigned char smem[];     // swizzled tiles need 1024-byte alignment
   const uint32_t q_smem = smem_addr(smem);
   const uint32_t kv_smem = q_smem + 2 * kTcQBytes;
   const uint32_t p_smem = kv_smem + kTcStages * 2 * kTcTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * kTcQBytes + kTcStages * 2 * kTcTileBytes + 2 * kTcPBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * kTcQBytes + kTcStages * 2 * kTcTileBytes + 2 * kPB * kTcPBytes);
   const uint32_t bar_base = smem_addr(bars);
   auto bar = [&](int i) { return bar_base + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kBarCount);
@@ -110,9 +133,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   if (threadIdx.x == 0) {
     mbar_init(bar(kBarQ), 1);
-    for (int s = 0; s < kTcStages; ++s) { mbar_init(bar(kBarKvFull + s), 1); mbar_init(bar(kBarKvEmpty + s), 1); }
+    for (int s = 0; s < kTcStages; ++s) { mbar_init(bar(kBarKvFull + s), 1); mbar_init(bar(kBarKvEmpty + s), rows_g[1] > 0 ? 2 : 1); }
     for (int g = 0; g < 2; ++g) {
-      mbar_init(bar(kBarSFull + g), 1); mbar_init(bar(kBarPFull + g), 4); mbar_init(bar(kBarODone + g), 1); mbar_init(bar(kBarSFree + g), 4);
+      mbar_init(bar(kBarSFull + g), 1); mbar_init(bar(kBarSFree + g), 4);
+      for (int b = 0; b < 2; ++b) { mbar_init(bar(kBarPFull + 2 * g + b), 4); mbar_init(bar(kBarODone + 2 * g + b), 1); }
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -131,17 +155,45 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int have_blocks = (max(k_end[0], k_end[1]) - 1) / p.page_size - first_block + 1;   // entries that exist for this request
   const bool staged = n_blocks <= kTcStagedPages;
   if (staged)
-    for (int i = threadIdx.x; i < n_blocks; i += kTcThreads) s_pages[i] = i < have_blocks ? bt_global[first_block + i] : -1;
+    for (int i = threadIdx.x; i < n_blocks; i += Cfg::kThreads) s_pages[i] = i < have_blocks ? bt_global[first_block + i] : -1;
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // The two kinds of product, as the issuing threads call them.
+  constexpr uint32_t idesc_s = instr_desc_bf16(kTcRows, kTcKeys);                    // Q, K both K-major
+  constexpr uint32_t idesc_o = instr_desc_bf16(kTcRows, kTcD) | (1u << 16);          // V is MN-major
+  auto stage_of = [&](int t) { return t % kTcStages; };
+  auto issue_s = [&](int g, int t) {
+    const uint32_t kb = kv_smem + stage_of(t) * 2 * kTcTileBytes;
+#pragma unroll
+    for (int k = 0; k < kTcD / 16; ++k)       // 16 values of the head per step: block k / 4 of the operands, 32 bytes along its rows
+      tcgen05_mma_bf16(tmem_base + g * kTcRows, smem_desc_sw128(q_smem + g * kTcQBytes + (k >> 2) * kTcChunk + (k & 3) * 32),
+                       smem_desc_sw128(kb + (k >> 2) * (kTcKeys * 128) + (k & 3) * 32), idesc_s, k > 0 ? 1u : 0u);
+    tcgen05_commit(bar(kBarSFull + g));                           // S of this tile complete
+  };
+  auto issue_pv = [&](int g, int t, int n_pv) {                    // n_pv: how many of the group's products came before
+    const uint32_t vb = kv_smem + stage_of(t) * 2 * kTcTileBytes + kTcTileBytes;
+#pragma unroll
+    for (int k = 0; k < kTcKeys / 16; ++k) {
+      // A: P, K-major, 64-key blocks of 16 KB; B: V rows = keys, 16 keys = 2 KB per step, and with
+      // head size 128 a second block of 64 values per row, one K/V block further on
+      const uint64_t adesc = smem_desc_sw128(p_smem + (g * kPB + n_pv % kPB) * kTcPBytes + (k >> 2) * kTcChunk + (k & 3) * 32);
+      const uint64_t bdesc = kTcD == 64 ? smem_desc_sw128(vb + k * 2048) : smem_desc_sw128_mn(vb + k * 2048, kTcKeys * 128);
+      tcgen05_mma_bf16(tmem_base + 2 * kTcRows + g * kTcD, adesc, bdesc, idesc_o, (n_pv > 0 || k > 0) ? 1u : 0u);
+    }
+    tcgen05_commit(bar(kBarODone + 2 * g + n_pv % kPB));          // O of this tile updated, its P buffer free
+  };
+
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ TMA producer
     mbar_expect_tx(bar(kBarQ), (rows_g[1] > 0 ? 2 : 1) * kTcQBytes);
-    tma_load_2d(q_smem, &map_q, bar(kBarQ), h * kTcD, tok0);       // rows past the step's tokens arrive as zeros
-    if (rows_g[1] > 0) tma_load_2d(q_smem + kTcQBytes, &map_q, bar(kBarQ), h * kTcD, tok0 + kTcRows);
+#pragma unroll
+    for (int c = 0; c < kTcD / 64; ++c) {                          // 64 values of every row at a time
+      tma_load_2d(q_smem + c * kTcChunk, &map_q, bar(kBarQ), h * kTcD + c * 64, tok0);     // rows past the step's tokens arrive as zeros
+      if (rows_g[1] > 0) tma_load_2d(q_smem + kTcQBytes + c * kTcChunk, &map_q, bar(kBarQ), h * kTcD + c * 64, tok0 + kTcRows);
+    }
     const int rows_per_page_group = p.nkv * p.page_size;           // cache rows between the k and v planes of a page
     for (int t = 0; t < ntiles; ++t) {
       const int s = t % kTcStages;
@@ -155,43 +207,29 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (page < 0 || page >= p.num_pages) page = 0;             // beyond the request: any page, its keys get masked
         const int krow = (page * 2 * p.nkv + kvh) * p.page_size;
         const uint32_t off = (uint32_t)i * p.page_size * 128u;
-        tma_load_2d(kdst + off, &map_kv, bar(kBarKvFull + s), 0, krow);
-        tma_load_2d(vdst + off, &map_kv, bar(kBarKvFull + s), 0, krow + rows_per_page_group);
+#pragma unroll
+        for (int c = 0; c < kTcD / 64; ++c) {
+          tma_load_2d(kdst + c * (kTcKeys * 128) + off, &map_kv, bar(kBarKvFull + s), c * 64, krow);
+          tma_load_2d(vdst + c * (kTcKeys * 128) + off, &map_kv, bar(kBarKvFull + s), c * 64, krow + rows_per_page_group);
+        }
       }
     }
-  } else if (warp == 1 && lane == 0) {
-    // ------------------------------------------------------------ MMA issuer
-    constexpr uint32_t idesc_s = instr_desc_bf16(kTcRows, kTcKeys);                    // Q, K both K-major
-    constexpr uint32_t idesc_o = instr_desc_bf16(kTcRows, kTcD) | (1u << 16);          // V is MN-major
-    bool ok = mbar_wait(bar(kBarQ), 0, abort_flag, p.status, 12);
-    int n_g[2] = {0, 0};                                          // P V products issued so far for each tile of the pair
-    auto stage_of = [&](int t) { return t % kTcStages; };
-    auto issue_s = [&](int g, int t) {
-      const uint32_t kb = kv_smem + stage_of(t) * 2 * kTcTileBytes;
-#pragma unroll
-      for (int k = 0; k < kTcD / 16; ++k)
-        tcgen05_mma_bf16(tmem_base + g * kTcKeys, smem_desc_sw128(q_smem + g * kTcQBytes + k * 32), smem_desc_sw128(kb + k * 32),
-                         idesc_s, k > 0 ? 1u : 0u);
-      tcgen05_commit(bar(kBarSFull + g));                           // S of this tile complete
-    };
-    auto issue_pv = [&](int g, int t) {
-      const uint32_t vb = kv_smem + stage_of(t) * 2 * kTcTileBytes + kTcTileBytes;
-#pragma unroll
-      for (int k = 0; k < kTcKeys / 16; ++k) {
-        // A: P, K-major, 64-key blocks of 16 KB; B: V rows = keys, 16 keys = 2 KB per step
-        const uint64_t adesc = smem_desc_sw128(p_smem + g * kTcPBytes + (k >> 2) * (kTcRows * 128) + (k & 3) * 32);
-        const uint64_t bdesc = smem_desc_sw128(vb + k * 2048);
-        tcgen05_mma_bf16(tmem_base + 2 * kTcKeys + g * kTcD, adesc, bdesc, idesc_o, (n_g[g] > 0 || k > 0) ? 1u : 0u);
-      }
-      tcgen05_commit(bar(kBarODone + g));                           // O of this tile updated, its P free
-      ++n_g[g];
-    };
-    // This thread serves whichever of the two groups is ready: the scores of a group's next key
-    // tile are issued as soon as the group has taken the previous ones out of TMEM (s_free), long
-    // before its softmax is done, so a group does not wait for its scores; its P V product follows
-    // when it hands over P.  Barriers are tested without suspending; a key tile's stage is given
-    // back once every product that reads it has been issued.
-    int next_s[2] = {t_first[0], t_first[1]}, next_pv[2] = {t_first[0], t_first[1]};
+  } else if ((warp == 1 || warp == kTcIssuerB) && lane == 0) {
+    // ------------------------------------------------------------ MMA issuers, one per tile of the pair
+    // (A thread that issues MMAs is held up by every MMA, about as long as it runs, and by every look
+    // at a barrier after one, a couple of hundred cycles: one thread for both tiles was what the
+    // softmax groups ended up waiting for.  Four threads, the scores and the P V products of each
+    // tile apart, were no faster than two.)
+    const int g = warp == 1 ? 0 : 1;
+    bool ok = rows_g[g] > 0 && mbar_wait(bar(kBarQ), 0, abort_flag, p.status, 12);
+    int n_pv = 0;                                                 // P V products issued so far
+    // The scores of the group's next key tile are issued as soon as the group has taken the previous
+    // ones out of TMEM (s_free), long before its softmax is done, so that it does not wait for its
+    // scores; its P V product follows when it hands over P.  Barriers are tested without suspending.
+    // A key tile's stage is given back by both issuers (where both tiles of the pair exist): each
+    // arrives once it has seen the tile arrive and has issued its product on it, if it has one --
+    // having seen it, it cannot arrive for the stage's next filling too early.
+    int next_s = t_first[g], next_pv = t_first[g];
     int kv_ready = 0, released = 0;
     uint32_t idle = 0;
     while (ok && released < ntiles) {
@@ -200,26 +238,21 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         ++kv_ready;
         progress = true;
       }
-#pragma unroll
-      for (int g = 0; g < 2; ++g) {
-        if (rows_g[g] <= 0) continue;
-        const int issued = next_s[g] - t_first[g];
-        if (next_s[g] < t_last[g] && next_s[g] < kv_ready &&
-            (issued == 0 || mbar_test_wait(bar(kBarSFree + g), (issued - 1) & 1))) {
-          tcgen05_fence_after();
-          issue_s(g, next_s[g]);
-          ++next_s[g];
-          progress = true;
-        }
-        if (next_pv[g] < next_s[g] && mbar_test_wait(bar(kBarPFull + g), n_g[g] & 1)) {     // P written, O rescaled
-          tcgen05_fence_after();
-          issue_pv(g, next_pv[g]);
-          ++next_pv[g];
-          progress = true;
-        }
+      const int issued = next_s - t_first[g];
+      if (next_s < t_last[g] && next_s < kv_ready && (issued == 0 || mbar_test_wait(bar(kBarSFree + g), (issued - 1) & 1))) {
+        tcgen05_fence_after();
+        issue_s(g, next_s);
+        ++next_s;
+        progress = true;
       }
-      while (released < ntiles && (!takes_part(0, released) || next_pv[0] > released) &&
-             (!takes_part(1, released) || next_pv[1] > released)) {
+      if (next_pv < next_s && mbar_test_wait(bar(kBarPFull + 2 * g + n_pv % kPB), (n_pv / kPB) & 1)) {     // P written, O rescaled
+        tcgen05_fence_after();
+        issue_pv(g, next_pv, n_pv);
+        ++n_pv;
+        ++next_pv;
+        progress = true;
+      }
+      while (released < kv_ready && (!takes_part(g, released) || next_pv > released)) {
         tcgen05_commit(bar(kBarKvEmpty + stage_of(released)));
         ++released;
         progress = true;
@@ -233,7 +266,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         __nanosleep(32);
       }
     }
-  } else if (warp >= 2) {
+  } else if (warp >= 2 && warp < 10) {
     // ------------------------------------------------------------ softmax, correction, epilogue
     const int g = (warp - 2) >> 2;                                // which tile of the pair
     const int quad = warp & 3;
@@ -242,8 +275,12 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int tile_pos0 = pos_g[g];
     const int qpos = tile_pos0 + r;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-    const uint32_t tmem_s = tmem_base + g * kTcKeys, tmem_o = tmem_base + 2 * kTcKeys + g * kTcD;
-    const uint32_t my_p = p_smem + g * kTcPBytes;
+    const uint32_t tmem_s = tmem_base + g * kTcRows, tmem_o = tmem_base + 2 * kTcRows + g * kTcD;
+    const uint32_t my_p0 = p_smem + g * kPB * kTcPBytes;
+    // the P V product of this group's i-th key tile is complete (barrier of the P buffer it read, that buffer's (i / kPB)-th use)
+    auto wait_pv = [&](int i, int code) {
+      return mbar_wait(bar(kBarODone + 2 * g + i % kPB), (i / kPB) & 1, abort_flag, p.status, code);
+    };
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     int n = 0;                                                    // key tiles taken so far
@@ -254,7 +291,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int key0 = k_base + t * kTcKeys;
       const bool need_mask = key0 + kTcKeys - 1 > tile_pos0 || key0 < lo_raw[g] ||
                              (p.window > 0 && key0 < tile_pos0 + kTcRows - 1 - p.window + 1);
-      // the row's 128 scores come out of TMEM once and stay in registers
+      // the row's scores come out of TMEM once and stay in registers
       uint32_t v[kTcKeys];
 #pragma unroll
       for (int c0 = 0; c0 < kTcKeys; c0 += 32) tmem_load_32_nowait(tmem_s + lane_addr + c0, v + c0);
@@ -285,12 +322,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const float m_new = moved ? m_top : m_run;
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       const float alpha = moved ? ex2_approx(m_run - m_use) : 1.0f;
-      // the previous P V product must be complete before P is overwritten and O rescaled
-      if (n > 0) {
-        ok = mbar_wait(bar(kBarODone + g), (n - 1) & 1, abort_flag, p.status, 16);
+      // the P V product that read this P buffer last must be complete before it is overwritten
+      if (n >= kPB) {
+        ok = wait_pv(n - kPB, 16);
         if (!ok) break;
         tcgen05_fence_after();
       }
+      const uint32_t my_p = my_p0 + (n % kPB) * kTcPBytes;
       // P = 2^(s * scale - m) as bfloat16 into shared memory (K-major operand layout), row sum
       float sum = 0.f;
 #pragma unroll
@@ -305,7 +343,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           packed[j >> 1] = *reinterpret_cast<uint32_t*>(&pk);
         }
         // keys c0..c0+7 are 16-byte chunk (c0 % 64) / 8 of this row inside 64-key block c0 / 64
-        const uint32_t dst = my_p + (c0 >> 6) * (kTcRows * 128) + r * 128 + (((((c0 & 63) >> 3)) ^ (r & 7)) << 4);
+        const uint32_t dst = my_p + (c0 >> 6) * kTcChunk + r * 128 + (((((c0 & 63) >> 3)) ^ (r & 7)) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(packed[0]), "r"(packed[1]), "r"(packed[2]),
                      "r"(packed[3]) : "memory");
       }
@@ -313,6 +351,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       m_run = m_new;
       // rescale the output accumulator where the maximum moved (never on the first tile: O is overwritten there)
       if (n > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+        if (kPB > 1) {                                              // (every P V product so far must have landed in O)
+          ok = wait_pv(n - 1, 18);
+          if (!ok) break;
+          tcgen05_fence_after();
+        }
 #pragma unroll 1
         for (int c0 = 0; c0 < kTcD; c0 += 32) {
           uint32_t o[32];
@@ -326,10 +369,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kBarPFull + g));
+      if (lane == 0) mbar_arrive(bar(kBarPFull + 2 * g + n % kPB));
     }
     // epilogue: wait for the last P V product, then O / sum
-    if (ok && n > 0) ok = mbar_wait(bar(kBarODone + g), (n - 1) & 1, abort_flag, p.status, 17);
+    if (ok && n > 0) ok = wait_pv(n - 1, 17);
     if (ok && n > 0) {
       tcgen05_fence_after();
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
@@ -363,9 +406,33 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
 }  // namespace ptl
 
+namespace ptl {
+
+template <int D>
+static int launch_prefill_tc(const void* q, const void* cache, int n_tiles, int n_tokens, int q_stride, int nq, int nkv,
+                             int page_size, int num_pages, const PrefillTcParams& p, cudaStream_t stream) {
+  using Cfg = PfCfg<D>;
+  static bool raised = false;
+  if (!raised) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
+    PTL_REQUIRE(e == cudaSuccess, "prefill_attention_tc: cannot raise shared memory: %s", cudaGetErrorString(e));
+    raised = true;
+  }
+  CUtensorMap mq, mkv;
+  int rc = make_map(&mq, q, n_tokens, q_stride, kTcRows);                 // whole step: [tokens, q_stride], boxes of 64 x 128
+  if (rc) return rc;
+  rc = make_map(&mkv, cache, num_pages * 2 * nkv * page_size, D, page_size);     // cache as rows of one head's D values, boxes of 64 x page
+  if (rc) return rc;
+  return launch_kernel("prefill_attention_tc", prefill_attention_tc_kernel<D>, dim3(nq, n_tiles / 2), dim3(Cfg::kThreads), Cfg::kSmem,
+                       stream, mq, mkv, p);
+}
+
+}  // namespace ptl
+
 // Returns 0 on success; -2 if this kernel does not take the sizes (the caller then uses the
-// warp-level kernel): head size 64 only, pages of 8..128 keys that divide 128, 16-byte aligned
-// rows; -1 on an error.  `tiles` holds n_tiles entries in pairs (n_tiles is even): see the top of the file.
+// warp-level kernel): head size 64 or 128 only, pages of 8 keys or more that divide the key tile
+// (128 keys with head size 64, 64 with 128), 16-byte aligned rows; -1 on an error.  `tiles` holds
+// n_tiles entries in pairs (n_tiles is even): see the top of the file.
 PTL_EXPORT int ptl_prefill_attention_tc_bf16(void* out, const void* q, const void* cache, const int* block_table,
                                              const int* tiles, int n_tiles, int n_tokens, int q_stride, int out_stride,
                                              int bt_stride, int nq, int nkv, int d, int page_size, float scale,
@@ -374,26 +441,16 @@ PTL_EXPORT int ptl_prefill_attention_tc_bf16(void* out, const void* q, const voi
   PTL_REQUIRE(n_tiles >= 0 && nq > 0 && nkv > 0 && page_size > 0 && num_pages > 0, "prefill_attention_tc: bad sizes");
   PTL_REQUIRE(n_tiles % 2 == 0, "prefill_attention_tc: tiles come in pairs, %d is odd", n_tiles);
   PTL_REQUIRE(nq % nkv == 0, "prefill_attention_tc: %d query heads are no multiple of %d kv heads", nq, nkv);
-  if (d != kTcD || page_size < 8 || page_size > kTcKeys || kTcKeys % page_size != 0 || q_stride % 8 != 0 ||
-      out_stride % 8 != 0 || n_tiles / 2 > 65535)
+  if (d != 64 && d != 128) return -2;
+  const int keys = d == 64 ? PfCfg<64>::kKeys : PfCfg<128>::kKeys;
+  if (page_size < 8 || page_size > keys || keys % page_size != 0 || q_stride % 8 != 0 || out_stride % 8 != 0 || n_tiles / 2 > 65535)
     return -2;
   PTL_REQUIRE(aligned16(q) && aligned16(cache) && aligned16(out), "prefill_attention_tc: q, cache and out must be 16-byte aligned");
   if (n_tiles == 0) return 0;
-  static bool raised = false;
-  if (!raised) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem);
-    PTL_REQUIRE(e == cudaSuccess, "prefill_attention_tc: cannot raise shared memory: %s", cudaGetErrorString(e));
-    raised = true;
-  }
-  CUtensorMap mq, mkv;
-  int rc = make_map(&mq, q, n_tokens, q_stride, kTcRows);                 // whole step: [tokens, q_stride], boxes of 64 x 128
-  if (rc) return rc;
-  rc = make_map(&mkv, cache, num_pages * 2 * nkv * page_size, kTcD, page_size);   // cache as rows of one head's 64 values
-  if (rc) return rc;
   PrefillTcParams p{};
   p.out = (__nv_bfloat16*)out; p.block_table = block_table; p.tiles = tiles; p.status = status;
   p.out_stride = out_stride; p.bt_stride = bt_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size;
   p.window = window; p.num_pages = num_pages; p.scale_log2 = scale * 1.4426950408889634f;
-  return launch_kernel("prefill_attention_tc", prefill_attention_tc_kernel, dim3(nq, n_tiles / 2), dim3(kTcThreads), kTcSmem,
-                       as_stream(stream), mq, mkv, p);
+  if (d == 64) return launch_prefill_tc<64>(q, cache, n_tiles, n_tokens, q_stride, nq, nkv, page_size, num_pages, p, as_stream(stream));
+  return launch_prefill_tc<128>(q, cache, n_tiles, n_tokens, q_stride, nq, nkv, page_size, num_pages, p, as_stream(stream));
 }

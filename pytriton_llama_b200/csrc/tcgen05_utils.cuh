@@ -99,6 +99,18 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
   d |= (uint64_t)2 << 61;                     // 128-byte swizzle
   return d;
 }
+// The same for an MN-major tile (rows = K index, 64 bfloat16 of the M/N extent per 128-byte row,
+// as a [key][dim] value tile is): groups of 8 rows are 1024 bytes apart, and each further 64
+// elements of the M/N extent start `mn_block_bytes` after the previous ones.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t addr, uint32_t mn_block_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((mn_block_bytes >> 4) & 0x3FFFu) << 16;   // leading byte offset: between blocks of 64 along M/N
+  d |= (uint64_t)(1024 >> 4) << 32;                          // stride byte offset: 8 rows (K) x 128 bytes
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
 // Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major, M x N tile.
 __host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);

@@ -6,7 +6,7 @@ Cases: ``decode_attention`` (32 requests x 4,096 cached tokens, 268 MB of keys a
 ``decode_step_attention`` (8 requests x 4,096 tokens with rotary encoding and cache write folded in),
 ``gemm_decode`` (8 tokens x a [65536, 2048] weight, 268 MB), ``gemm_prefill`` (2,048 tokens x the
 gate/up weight [16384, 2048] with the SiLU*up epilogue), ``prefill_attention`` (one 2,048-token
-prompt, 32 query heads).  Inputs are larger than the 126 MB L2 where the kernel is a stream, so
+prompt, 32 query heads of size 64; ``prefill_attention_d128``: of size 128).  Inputs are larger than the 126 MB L2 where the kernel is a stream, so
 DRAM figures mean something, yet small enough for a profiler to replay.  Each case prints its
 time from CUDA events after warm-up and the bytes or FLOPs per second that follow from it.
 lite_llama benchmarks its Triton kernels the same way from their ``__main__`` blocks
@@ -23,7 +23,7 @@ import torch
 from .cuda import CudaOps
 
 
-def _time(fn, reps: int) -> float:
+def _time(fn, reps: int, ops: CudaOps) -> float:
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
@@ -33,6 +33,7 @@ def _time(fn, reps: int) -> float:
         fn()
     end.record()
     torch.cuda.synchronize()
+    ops.check_status()          # a kernel whose waits ran out would have been timed for nothing
     return start.elapsed_time(end) / reps * 1e-3
 
 
@@ -50,7 +51,7 @@ def run(case: str, reps: int) -> dict:
         qkv = torch.randn(batch, (nq + 2 * nkv) * d, device=dev).bfloat16()
         hints = SimpleNamespace(n_decode=batch, decode_items=rows, n_prefill_tiles=0, prefill_tiles=rows,
                                 max_ctx_len=ctx, decode_in_order=True)
-        sec = _time(lambda: ops.paged_attention(qkv, cache, table, rows, pos, nq, nkv, d, page, d ** -0.5, hints=hints), reps)
+        sec = _time(lambda: ops.paged_attention(qkv, cache, table, rows, pos, nq, nkv, d, page, d ** -0.5, hints=hints), reps, ops)
         return {"case": case, "us": sec * 1e6, "bytes": cache.numel() * 2, "GB/s": cache.numel() * 2 / sec / 1e9}
     if case == "decode_step_attention":
         # the attention of one layer of a decode step at batch 8: q|k|v unrotated, rotary encoding and
@@ -67,22 +68,24 @@ def run(case: str, reps: int) -> dict:
         hints = SimpleNamespace(n_decode=batch, decode_items=rows, n_prefill_tiles=0, prefill_tiles=rows,
                                 max_ctx_len=ctx, decode_in_order=True)
         sec = _time(lambda: ops.rope_attention(qkv, pos, inv, d, slots, cache, table, rows, nq, nkv, d, page, d ** -0.5,
-                                               hints=hints), reps)
+                                               hints=hints), reps, ops)
         nbytes = cache.numel() * 2
         return {"case": case, "us": sec * 1e6, "bytes": nbytes, "GB/s": nbytes / sec / 1e9}
     if case == "gemm_decode":
         m, n, k = 8, 65536, 2048
         x = torch.randn(m, k, device=dev).bfloat16()
         w = torch.randn(n, k, device=dev).bfloat16()
-        sec = _time(lambda: ops.gemm_tc(x, w, ops.EPI_BF16), reps)
+        sec = _time(lambda: ops.gemm_tc(x, w, ops.EPI_BF16), reps, ops)
         return {"case": case, "us": sec * 1e6, "bytes": n * k * 2, "GB/s": n * k * 2 / sec / 1e9}
     if case == "gemm_prefill":
         m, n, k = 2048, 16384, 2048
         x = torch.randn(m, k, device=dev).bfloat16()
         w = torch.randn(n, k, device=dev).bfloat16()
-        sec = _time(lambda: ops.gemm_tc(x, w, ops.EPI_SILU_MUL), reps)
+        sec = _time(lambda: ops.gemm_tc(x, w, ops.EPI_SILU_MUL), reps, ops)
         return {"case": case, "us": sec * 1e6, "flops": 2 * m * n * k, "TFLOP/s": 2 * m * n * k / sec / 1e12}
-    if case == "prefill_attention":
+    if case in ("prefill_attention", "prefill_attention_d128"):
+        if case.endswith("d128"):
+            d = 128
         tokens = 2048
         pages = tokens // page
         cache = torch.randn(pages, 2, nkv, page, d, device=dev).bfloat16()
@@ -93,7 +96,7 @@ def run(case: str, reps: int) -> dict:
         tiles = torch.tensor([[0, a, 128, a] for a in range(0, tokens, 128)], dtype=torch.int32, device=dev).reshape(-1)   # pairs of consecutive tiles
         hints = SimpleNamespace(n_decode=0, decode_items=rows[:0], n_prefill_tiles=tokens // 128, prefill_tiles=tiles,
                                 max_ctx_len=tokens, decode_in_order=False)
-        sec = _time(lambda: ops.paged_attention(qkv, cache, table, rows, pos, nq, nkv, d, page, d ** -0.5, hints=hints), reps)
+        sec = _time(lambda: ops.paged_attention(qkv, cache, table, rows, pos, nq, nkv, d, page, d ** -0.5, hints=hints), reps, ops)
         flops = 4 * nq * d * tokens * (tokens + 1) // 2
         return {"case": case, "us": sec * 1e6, "flops": flops, "TFLOP/s": flops / sec / 1e12}
     raise SystemExit(f"unknown case {case!r}")
@@ -101,7 +104,8 @@ def run(case: str, reps: int) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("case", choices=["decode_attention", "decode_step_attention", "gemm_decode", "gemm_prefill", "prefill_attention"])
+    ap.add_argument("case", choices=["decode_attention", "decode_step_attention", "gemm_decode", "gemm_prefill", "prefill_attention",
+                                     "prefill_attention_d128"])
     ap.add_argument("--reps", type=int, default=10)
     args = ap.parse_args()
     print(json.dumps(run(args.case, args.reps)))

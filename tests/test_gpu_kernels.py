@@ -15,9 +15,17 @@ DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
 @pytest.fixture(scope="module")
-def ops():
+def _ops():
     from pytriton_llama_b200.ops.cuda import CudaOps
     return CudaOps(torch.device("cuda:0"))
+
+
+@pytest.fixture
+def ops(_ops):
+    """The kernels; after every test, no wait inside a kernel may have given up (a kernel whose
+    waits run out still ends and may even leave a right result behind)."""
+    yield _ops
+    _ops.check_status()
 
 
 REF = TorchOps("cpu")
@@ -254,6 +262,27 @@ def test_tensor_core_attention_mixed_batch(ops, nq, nkv, d, page, window):
     close(out, ref, "bfloat16", "tensor cores", scale=4.0)
     simt = ops.paged_attention(*args, window=window, splits=2)
     close(out, simt, "bfloat16", "against the CUDA-core kernel", scale=4.0)
+
+
+@pytest.mark.parametrize("d, page, window", [(64, 16, 0), (128, 16, 0), (128, 32, 600), (64, 64, 600), (128, 8, 0)])
+def test_tensor_core_attention_over_a_long_prompt(ops, d, page, window):
+    """A 1,300-token portion after 700 cached tokens: dozens of key tiles per query tile, so that the
+    roles inside the kernel run ahead of one another as far as their barriers let them."""
+    nq, nkv = 4, 2
+    q_lens, ctx = [1300], [2000]
+    pages = -(-ctx[0] // page) + 5
+    bt = _random_paging(1, ctx, page, pages, seed=d + page)
+    cache = rnd((pages, 2, nkv, page, d), torch.bfloat16, 21)
+    q = rnd((q_lens[0], (nq + 2 * nkv) * d), torch.bfloat16, 22, 2.0)
+    tok_req = torch.zeros(q_lens[0], dtype=torch.int32)
+    positions = torch.arange(ctx[0] - q_lens[0], ctx[0]).int()
+    scale = 1 / math.sqrt(d)
+    ref = REF.paged_attention(q, cache, bt, tok_req, positions, nq, nkv, d, page, scale, window=window)
+    launches = ops.launches
+    out = ops.paged_attention(q.cuda(), cache.cuda(), bt.cuda(), tok_req.cuda(), positions.cuda(), nq, nkv, d, page, scale,
+                              window=window, hints=_hints(q_lens, ctx))
+    assert ops.launches - launches == 1                          # the prompt kernel alone
+    close(out, ref, "bfloat16", "long prompt", scale=4.0)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
