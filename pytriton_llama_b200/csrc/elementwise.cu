@@ -210,6 +210,26 @@ __global__ void take_tokens_kernel(int* __restrict__ tokens, const int* __restri
   if (s >= 0 && s < n_sampled) tokens[i] = sampled[s];
 }
 
+// acc[i] = (((acc[i] + parts[0][i]) + parts[1][i]) + ...): the partial sums of a product whose K
+// range was cut into parts, added into the residual in a fixed order (n4 groups of four values;
+// part s starts s * stride4 groups after the first).
+__global__ void add_partials_kernel(float4* __restrict__ acc, const float4* __restrict__ parts, int n_parts, size_t n4, size_t stride4) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  float4 a = acc[i];
+  float4 q[8];
+  for (int s0 = 0; s0 < n_parts; s0 += 8) {
+#pragma unroll
+    for (int s = 0; s < 8; ++s) q[s] = s0 + s < n_parts ? __ldcg(parts + (size_t)(s0 + s) * stride4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+      if (s0 + s < n_parts) { a.x += q[s].x; a.y += q[s].y; a.z += q[s].z; a.w += q[s].w; }
+  }
+  acc[i] = a;
+}
+
 template <typename T>
 int embed_gather(void* out, const void* table, const int* ids, int tokens, int hidden, int vocab,
                  int* status, void* stream) {
@@ -277,6 +297,15 @@ PTL_EXPORT int ptl_take_tokens(int* tokens, const int* src, const int* sampled, 
   if (n == 0) return 0;
   return ptl::launch_kernel("take_tokens", ptl::take_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0,
                             ptl::as_stream(stream), tokens, src, sampled, n, n_sampled);
+}
+
+PTL_EXPORT int ptl_add_partials(float* acc, const float* parts, int n_parts, long long n, long long stride, void* stream) {
+  PTL_REQUIRE(n_parts > 0 && n >= 0 && stride >= n, "add_partials: bad sizes parts=%d n=%lld stride=%lld", n_parts, n, stride);
+  PTL_REQUIRE(n % 4 == 0 && stride % 4 == 0 && ptl::aligned16(acc) && ptl::aligned16(parts), "add_partials: sizes must be multiples of 4 values and pointers 16-byte aligned");
+  if (n == 0) return 0;
+  const size_t n4 = (size_t)n / 4;
+  return ptl::launch_kernel("add_partials", ptl::add_partials_kernel, dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0,
+                            ptl::as_stream(stream), (float4*)acc, (const float4*)parts, n_parts, n4, (size_t)stride / 4);
 }
 
 PTL_EXPORT int ptl_embed_gather_f32(void* out, const void* table, const int* ids, int tokens, int hidden, int vocab, int* status, void* stream) {

@@ -59,6 +59,8 @@ struct GemmParams {
   float scale_eps;
   float scale_inv_n;
   int tma_add;           // many tokens, add epilogue: the accumulator tiles are added into `out` by TMA (map_out)
+  int ksplits;           // many tokens, float32 store: the K range is cut into this many parts (work units = tiles x parts),
+                         // part s stores its partial sums as rows s * rows.. of `out` ([ksplits, rows, cols])
 };
 
 template <int BN> struct TcCfg {
@@ -93,11 +95,11 @@ __device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + _
 // ---------------------------------------------------------------- epilogue of one row's 16 accumulators
 // Normal mode: `row` is a token, columns c0..c0+15 are features.
 template <int EPI>
-__device__ __forceinline__ void store_normal(const GemmParams& p, int row, int c0, const float (&v)[16]) {
+__device__ __forceinline__ void store_normal(const GemmParams& p, int row, int c0, const float (&v)[16], size_t out_row) {
   if (row >= p.rows) return;
   const int n_total = p.cols;
   if (EPI == 3) {
-    __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)row * p.ld_out + c0 / 2;
+    __nv_bfloat16* o = (__nv_bfloat16*)p.out + out_row * p.ld_out + c0 / 2;
     if (c0 + 16 <= n_total && (p.ld_out % 8 == 0)) {
       uint4 pk;
       uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
@@ -116,7 +118,7 @@ __device__ __forceinline__ void store_normal(const GemmParams& p, int row, int c
   }
   const bool full = c0 + 16 <= n_total;
   if (EPI == 0) {
-    __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)row * p.ld_out + c0;
+    __nv_bfloat16* o = (__nv_bfloat16*)p.out + out_row * p.ld_out + c0;
     if (full && p.ld_out % 8 == 0) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -135,7 +137,7 @@ __device__ __forceinline__ void store_normal(const GemmParams& p, int row, int c
         if (c0 + j < n_total) o[j] = __float2bfloat16_rn(v[j]);
     }
   } else {   // EPI 1 (store float32) or 2 (add into float32)
-    float* o = (float*)p.out + (size_t)row * p.ld_out + c0;
+    float* o = (float*)p.out + out_row * p.ld_out + c0;
     if (full && p.ld_out % 4 == 0) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -251,7 +253,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
   const int num_kb = (p.K + kTileK - 1) / kTileK;
   // swapped mode: one tile per block (blockIdx.x = row tile, blockIdx.y = K split);
   // normal mode: the block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (token tiles fastest)
-  const int total_tiles = p.swapped ? 1 : p.tiles_m * p.tiles_n;
+  const int tiles_mn = p.tiles_m * p.tiles_n;
+  const int total_tiles = p.swapped ? 1 : tiles_mn * p.ksplits;      // work units: (tile, part of the K range)
   const int first_tile = p.swapped ? 0 : blockIdx.x;
   const int tile_step = p.swapped ? 1 : gridDim.x;
   const int split = p.swapped ? blockIdx.y : 0;
@@ -266,7 +269,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
   auto acc_empty = [&](int b) { return bar_base + 8u * (2 * Cfg::kStages + 2 + b); };
   auto tile_rows_cols = [&](int tile, int& row_tile, int& col_tile) {
     if (p.swapped) { row_tile = blockIdx.x; col_tile = 0; }
-    else { row_tile = tile % p.tiles_m; col_tile = tile / p.tiles_m; }
+    else { const int t = tile % tiles_mn; row_tile = t % p.tiles_m; col_tile = t / p.tiles_m; }
+  };
+  // the K blocks of a work unit: first one and how many
+  auto unit_k = [&](int tile, int& first_kb, int& n_kb) {
+    if (p.swapped || p.ksplits == 1) { first_kb = kb0; n_kb = my_kb; return; }
+    first_kb = (tile / tiles_mn) * p.kb_per_split;
+    n_kb = max(0, min(num_kb, first_kb + p.kb_per_split) - first_kb);
   };
 
   if (threadIdx.x == 0) {
@@ -308,16 +317,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     it = pre;
     bool ok = true;
     for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
-      int row_tile, col_tile;
+      int row_tile, col_tile, ukb0, unkb;
       tile_rows_cols(tile, row_tile, col_tile);
-      for (int i = (tile == first_tile ? pre : 0); i < my_kb; ++i, ++it) {
+      unit_k(tile, ukb0, unkb);
+      for (int i = (tile == first_tile ? pre : 0); i < unkb; ++i, ++it) {
         const int s = it % Cfg::kStages;
         const uint32_t ph = (it / Cfg::kStages) & 1;
         if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
         mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
         const uint32_t dst = smem_base + s * Cfg::kStageBytes;
-        tma_load_2d(dst, &map_row, full_bar(s), (kb0 + i) * kTileK, row_tile * kTileRows);
-        tma_load_2d(dst + Cfg::kRowBytes, &map_col, full_bar(s), (kb0 + i) * kTileK, col_tile * BN);
+        tma_load_2d(dst, &map_row, full_bar(s), (ukb0 + i) * kTileK, row_tile * kTileRows);
+        tma_load_2d(dst + Cfg::kRowBytes, &map_col, full_bar(s), (ukb0 + i) * kTileK, col_tile * BN);
       }
     }
     if (*abort_flag) {
@@ -366,7 +376,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       if (!ok) break;
       tcgen05_fence_after();
       const uint32_t acc = tmem_base + buf * BN;
-      for (int i = 0; i < my_kb; ++i, ++it) {
+      int ukb0, unkb;
+      unit_k(tile, ukb0, unkb);
+      for (int i = 0; i < unkb; ++i, ++it) {
         const int s = it % Cfg::kStages;
         const uint32_t ph = (it / Cfg::kStages) & 1;
         ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 2);
@@ -419,6 +431,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       const int buf = Cfg::kAccBufs == 2 ? (lt & 1) : 0;
       const int use = Cfg::kAccBufs == 2 ? (lt >> 1) : lt;
       const int row = row_tile * kTileRows + row_in_tile;
+      int ukb0, unkb;
+      unit_k(tile, ukb0, unkb);
+      const size_t out_row = (size_t)row + (p.swapped ? 0 : (size_t)(tile / tiles_mn) * p.rows);     // partial sums of part s: rows s * rows..
       // the add epilogue fetches what it adds to ahead of time: 32 columns before the accumulator
       // is even complete, then the next 32 while the current ones are being written
       constexpr int kHalfCols = BN / 2 >= 32 ? BN / 2 : 32;
@@ -494,8 +509,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = my_kb > 0 ? __uint_as_float(r[16 * h + j]) * row_scale : 0.f;
-            store_normal<EPI>(p, row, col_tile * BN + c0 + 16 * h, v);
+            for (int j = 0; j < 16; ++j) v[j] = unkb > 0 ? __uint_as_float(r[16 * h + j]) * row_scale : 0.f;
+            store_normal<EPI>(p, row, col_tile * BN + c0 + 16 * h, v, out_row);
           }
         }
         if (can_prefetch && p.xs) p.sumsq[(size_t)row * p.sumsq_ld + col_tile * 2 + half] = ss;
@@ -649,11 +664,71 @@ static int launch_epi(int epi, const CUtensorMap& mr, const CUtensorMap& mc, con
   return fail("gemm_tc: unknown epilogue %d", epi);
 }
 
+static int sm_count_of_device() {
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  return sm_count;
+}
+
+// The plan for a product with many tokens: features per tile (256, 192 where N is a multiple of
+// it, or 128) and, where the caller can add partial sums up, into how many parts the K range is cut.
+// The cost of a candidate is the number of rounds its work units (tiles x parts) take on the SMs times
+// the length of a unit: K blocks per part x 4 MMAs x the cycles of an MMA of that width as one
+// thread gets them through (129, 115, 92 per 128 x width x 16: measured; narrow MMAs are bound by
+// the rate at which one thread can issue them).  16 x 12 tiles of 256 take two rounds of 148 SMs,
+// 16 x 16 of 192 take two cheaper ones; a few hundred tokens make too few wide tiles to fill the
+// SMs once.  A narrower tile has to win by a tenth.
+struct TilePlan { int bn, parts; };
+static TilePlan plan_tiles(int M, int N, int K, bool with_parts) {
+  const int sm_count = sm_count_of_device();
+  const long long tm = (M + kTileRows - 1) / kTileRows;
+  const int num_kb = (K + kTileK - 1) / kTileK;
+  const int widths[3] = {256, 192, 128}, cycles[3] = {129, 115, 92};
+  static const int forced = [] { const char* e = getenv("PTL_GEMM_TILE_FEATURES"); return e ? atoi(e) : 0; }();   // (for measurements)
+  TilePlan best{128, 1};
+  long long best_cost = -1;
+  for (int i = 0; i < 3; ++i) {
+    const int bn = widths[i];
+    if (bn == 192 && N % 192 != 0) continue;
+    if (bn == 256 && N % 256 != 0 && N < 2048) continue;        // a narrow product with a ragged edge: 128
+    if (forced && forced != bn) continue;
+    const long long tiles = tm * ((N + bn - 1) / bn);
+    long long parts = 1;
+    if (with_parts && tiles * 2 <= sm_count) {
+      parts = sm_count / tiles;
+      if (parts > 8) parts = 8;
+      if (parts > num_kb / 8) parts = num_kb / 8;                // at least 8 K blocks (512 values) per part
+      if (parts < 1) parts = 1;
+    }
+    const long long kb_per = (num_kb + parts - 1) / parts;
+    const long long cost = (tiles * parts + sm_count - 1) / sm_count * kb_per * cycles[i];
+    if (best_cost < 0 || cost * 100 < best_cost * 90) { best = TilePlan{bn, (int)parts}; best_cost = cost; }
+  }
+  return best;
+}
+
 }  // namespace ptl
+
+// With more than 64 tokens but few of them (or a narrow product) the tiles fill only some of the SMs,
+// and each walks the whole K range.  Returns into how many parts the K range is best cut so that the
+// work units fill the SMs (1: leave it whole): the caller then asks for float32 partial sums
+// (epi 1, `splits_hint` = parts, out [parts, M, N]) and adds them up in order.
+PTL_EXPORT int ptl_gemm_tc_k_parts(int M, int N, int K) {
+  using namespace ptl;
+  if (M <= 64 || K % 8 != 0 || K < kTileK) return 1;
+  return plan_tiles(M, N, K, true).parts;
+}
 
 // out: epi 0 bf16 [M,N]; 1 float32 [M,N]; 2 float32 [M,N] added to in place; 3 bf16 [M,N/2].
 // Returns -2 when the sizes are not ones this kernel takes (K % 8 != 0 or K < 64), so that the caller
-// can use another product.  `splits_hint` > 0 forces the number of K splits when M <= 64 (1, 2, 4 or 8).
+// can use another product.  `splits_hint` > 0 forces the number of K splits when M <= 64 (1, 2, 4 or 8);
+// when M > 64 it asks for that many parts of the K range, whose partial sums are stored one after
+// another (epi 1 only: out is [splits_hint, M, N] float32).
 //
 // Around an RMS norm: with `xs` (bf16 [M,N]), `norm_w` (float32 [N]) and `sumsq` (float32 [M, sumsq_ld],
 // sumsq_ld >= ceil(N/16)) the add epilogue also writes the next norm's input, xs = bfloat16(new
@@ -692,23 +767,16 @@ PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, in
   cudaStream_t s = as_stream(stream);
   if (M > 64) {
     p.swapped = 0; p.rows = M; p.cols = N; p.splits = 1; p.kb_per_split = num_kb;
-    static int sm_count = 0;
-    if (!sm_count) {
-      int dev = 0;
-      cudaGetDevice(&dev);
-      cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-      if (sm_count <= 0) sm_count = 148;
+    const int sm_count = sm_count_of_device();
+    int parts = 1;
+    const int bn = plan_tiles(M, N, K, splits_hint > 1).bn;
+    if (splits_hint > 1) {
+      PTL_REQUIRE(epi == 1 && !scale_sumsq && splits_hint <= 64 && splits_hint <= num_kb,
+                  "gemm_tc: with more than 64 tokens the K range is cut only for plain float32 partial sums, into at most 64 parts");
+      parts = splits_hint;
     }
-    // 256 features per tile; 192 where N is a multiple of it and the tiles then fill the rounds of
-    // the SMs better (16 x 12 tiles of 256 take two rounds of 148, 16 x 16 of 192 take two cheaper
-    // ones); 128 for narrow products
-    const long long tm = (M + kTileRows - 1) / kTileRows;
-    int bn = (N % 256 == 0 || N >= 2048) ? 256 : 128;
-    if (bn == 256 && N % 192 == 0) {
-      const long long cost256 = (tm * ((N + 255) / 256) + sm_count - 1) / sm_count * 256;
-      const long long cost192 = (tm * (N / 192) + sm_count - 1) / sm_count * 192;
-      if (cost192 < cost256) bn = 192;
-    }
+    p.ksplits = parts;
+    p.kb_per_split = (num_kb + parts - 1) / parts;
     int rc = make_map(&mr, X, M, K, kTileRows);
     if (rc) return rc;
     rc = make_map(&mc, W, N, K, bn);
@@ -716,7 +784,7 @@ PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, in
     p.tiles_m = (M + kTileRows - 1) / kTileRows;
     p.tiles_n = (N + bn - 1) / bn;
     if (slots_out) *slots_out = p.tiles_n * 2;
-    const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    const long long tiles = (long long)p.tiles_m * p.tiles_n * parts;
     dim3 grid((unsigned)(tiles < sm_count ? tiles : sm_count));
     // the add epilogue hands its tiles to TMA, which adds them into the residual (unless the next norm's input is wanted too)
     CUtensorMap mo = mr;
@@ -741,7 +809,7 @@ PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, in
   }
   PTL_REQUIRE(splits == 1 || splits == 2 || splits == 4 || splits == 8, "gemm_tc: the K range splits 1, 2, 4 or 8 ways, not %d", splits);
   const int kb_per = (num_kb + splits - 1) / splits;
-  p.swapped = 1; p.rows = N; p.cols = M; p.splits = splits; p.kb_per_split = kb_per;
+  p.swapped = 1; p.rows = N; p.cols = M; p.splits = splits; p.kb_per_split = kb_per; p.ksplits = 1;
   int rc = make_map(&mr, W, N, K, kTileRows);
   if (rc) return rc;
   rc = make_map(&mc, X, M, K, bn);

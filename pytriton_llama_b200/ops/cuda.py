@@ -94,6 +94,10 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_gemm_tc_bf16_norm.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int,
                                           _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _c_int, _c_int, _c_f, _ptr]
     lib.ptl_gemm_tc_bf16_norm.restype = _c_int
+    lib.ptl_gemm_tc_k_parts.argtypes = [_c_int, _c_int, _c_int]
+    lib.ptl_gemm_tc_k_parts.restype = _c_int
+    lib.ptl_add_partials.argtypes = [_ptr, _ptr, _c_int, _c_ll, _c_ll, _ptr]
+    lib.ptl_add_partials.restype = _c_int
     lib.ptl_prefill_attention_tc_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                   _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _ptr, _ptr]
     lib.ptl_prefill_attention_tc_bf16.restype = _c_int
@@ -315,9 +319,22 @@ class CudaOps:
         elif epi == self.EPI_SILU_MUL:
             out = self.empty((M, N // 2), torch.bfloat16)
             ld = N // 2
+        elif epi == self.EPI_F32 and M > 64 and splits > 1:
+            out = self.empty((splits, M, N), torch.float32)      # partial sums of the parts of the K range
+            ld = N
         else:
             out = self.empty((M, N), torch.float32 if epi == self.EPI_F32 else torch.bfloat16)
             ld = N
+        if epi == self.EPI_ADD_F32 and scale is None and emit_norm is None and M > 64 and N % 4 == 0 and splits == 0:
+            # a few hundred tokens, or a narrow product: too few tiles for the SMs, so the K range is
+            # cut into parts as well; their float32 partial sums are added into ``out`` in a fixed order
+            parts = self.lib.ptl_gemm_tc_k_parts(M, N, K)
+            if parts > 1:
+                partial = self.empty((parts, M, N), torch.float32)
+                self._check(self.lib.ptl_gemm_tc_bf16(_p(partial), _p(x), _p(w), M, N, K, N, self.EPI_F32,
+                                                      _p(self._tc_status_word()), parts, self._stream()))
+                self._check(self.lib.ptl_add_partials(_p(out), _p(partial), parts, M * N, M * N, self._stream()))
+                return out
         if scale is None and emit_norm is None:
             rc = self.lib.ptl_gemm_tc_bf16(_p(out), _p(x), _p(w), M, N, K, ld, epi, _p(self._tc_status_word()), splits,
                                            self._stream())

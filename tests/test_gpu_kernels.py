@@ -108,6 +108,7 @@ def test_linear_bfloat16(ops, M, N, K):
 @pytest.mark.parametrize("M, N, K", [
     (128, 128, 64), (130, 264, 96), (200, 1000, 512), (300, 128, 4096), (1100, 768, 200),      # many tokens: 128-token tiles
     (300, 3072, 128), (260, 2304, 64),                                                          # ... of 192 features
+    (130, 2048, 8192), (520, 2048, 2048), (1000, 1024, 1024),                                   # ... too few tiles: the add cuts the K range
     (1, 304, 80), (8, 3072, 2048), (16, 2048, 2048), (17, 1000, 72), (33, 2048, 8192), (64, 1000, 512),
     (64, 9600, 512), (40, 16384, 2048), (8, 16384, 2048), (24, 12000, 1024)])   # few: swapped, K split 2, 4 or 8 ways
 def test_tensor_core_product_and_its_epilogues(ops, M, N, K):
@@ -134,6 +135,22 @@ def test_tensor_core_product_and_its_epilogues(ops, M, N, K):
     assert ops.gemm_tc_status() == 0
     # the same product twice gives the same bits (split partial sums are added in a fixed order)
     assert torch.equal(ops.gemm_tc(x.cuda(), w.cuda(), ops.EPI_F32), out32)
+
+
+@pytest.mark.parametrize("M, N, K, parts", [(130, 264, 200, 3), (300, 512, 1024, 4), (65, 128, 4096, 16)])
+def test_tensor_core_product_in_parts_of_the_K_range(ops, M, N, K, parts):
+    """With more than 64 tokens the product can be asked for as float32 partial sums over parts of the
+    K range (K = 200 in three parts of two 64-blocks leaves the last part empty: it must hold zeros)."""
+    x, w = rnd((M, K), torch.bfloat16, 15), rnd((N, K), torch.bfloat16, 16, 0.5)
+    ref = x.double() @ w.double().T
+    out = ops.gemm_tc(x.cuda(), w.cuda(), ops.EPI_F32, splits=parts)
+    assert out.shape == (parts, M, N)
+    per = -(-(-(-K // 64)) // parts) * 64                         # K values per part: whole 64-blocks
+    for i in range(parts):
+        lo, hi = min(K, i * per), min(K, (i + 1) * per)
+        want = x[:, lo:hi].double() @ w[:, lo:hi].double().T
+        assert (out[i].double().cpu() - want).abs().max() <= 2e-6 * math.sqrt(K) * float(ref.abs().max()) / 10 + 1e-5, i
+    assert 1 <= ops.lib.ptl_gemm_tc_k_parts(300, 2048, 8192) <= 8 and ops.lib.ptl_gemm_tc_k_parts(4096, 8192, 2048) == 1
 
 
 def test_tensor_core_product_leaves_other_sizes_to_the_library(ops):
