@@ -789,7 +789,7 @@ PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, in
     // the add epilogue hands its tiles to TMA, which adds them into the residual (unless the next norm's input is wanted too)
     CUtensorMap mo = mr;
     if (epi == 2 && !xs && N % 32 == 0 && ld_out % 4 == 0) {
-      rc = encode_map_f32(&mo, out, M, N, ld_out, kTileRows);
+      rc = make_map(&mo, out, M, N, kTileRows, ld_out);
       if (rc) return rc;
       p.tma_add = 1;
     }

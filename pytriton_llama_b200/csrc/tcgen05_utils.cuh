@@ -163,28 +163,34 @@ inline EncodeTiledFn encode_fn() {
 
 // Tensor maps already encoded by this process: weights are asked for again every step.
 struct MapKey {
-  const void* base; int rows, K, box;
-  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && K == o.K && box == o.box; }
+  const void* base; int rows, K, box, ld;      // ld: 0 for bfloat16 matrices (rows are K apart), else the float32 row distance
+  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && K == o.K && box == o.box && ld == o.ld; }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
     size_t h = reinterpret_cast<size_t>(k.base);
-    h ^= (size_t)k.rows * 0x9E3779B97F4A7C15ull + (size_t)k.K * 0xC2B2AE3D27D4EB4Full + (size_t)k.box * 0x165667B19E3779F9ull;
+    h ^= (size_t)k.rows * 0x9E3779B97F4A7C15ull + (size_t)k.K * 0xC2B2AE3D27D4EB4Full + (size_t)k.box * 0x165667B19E3779F9ull +
+         (size_t)k.ld * 0x27D4EB2F165667C5ull;
     return h;
   }
 };
 
-// A [rows, K] bfloat16 matrix, K contiguous, fetched in boxes of 64 (K) x box_rows with the 128-byte swizzle.
-inline int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+inline int encode_map_f32(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows);
+
+// A [rows, K] bfloat16 matrix, K contiguous, fetched in boxes of 64 (K) x box_rows with the 128-byte
+// swizzle; with ld > 0 a [rows, K] float32 matrix whose rows are ld apart, in boxes of 32 x box_rows.
+// (A map says where a matrix lies and how it is cut, nothing about its contents: one that was
+// encoded for an address and shape serves every later matrix there.)
+inline int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows, int ld = 0) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex lock;
-  const MapKey key{base, rows, K, box_rows};
+  const MapKey key{base, rows, K, box_rows, ld};
   {
     std::lock_guard<std::mutex> g(lock);
     auto it = cache.find(key);
     if (it != cache.end()) { *map = it->second; return 0; }
   }
-  int rc = encode_map(map, base, rows, K, box_rows);
+  int rc = ld > 0 ? encode_map_f32(map, base, rows, K, ld, box_rows) : encode_map(map, base, rows, K, box_rows);
   if (rc) return rc;
   std::lock_guard<std::mutex> g(lock);
   if (cache.size() > 8192) cache.clear();
@@ -193,7 +199,7 @@ inline int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
 }
 
 // A [rows, cols] float32 matrix with `ld` elements between rows, written in boxes of 32 (cols) x
-// box_rows with the 128-byte swizzle (for tma_reduce_add_2d).  Not cached: the residual moves.
+// box_rows with the 128-byte swizzle (for tma_reduce_add_2d).
 inline int encode_map_f32(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   PTL_REQUIRE(fn != nullptr, "gemm_tc: the driver has no cuTensorMapEncodeTiled");

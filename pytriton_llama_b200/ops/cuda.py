@@ -146,11 +146,18 @@ class CudaOps:
         major, minor = torch.cuda.get_device_capability(device)
         if major != 10:
             raise KernelError(f"the kernels are compiled for sm_100a only; device reports sm_{major}{minor}")
+        self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+        self._device_index = device.index if device.index is not None else torch.cuda.current_device()
         self._status = torch.zeros(1, dtype=torch.int32, device=device)
         self.launches = 0      # kernels of this library launched so far (library matrix products not counted)
 
     # ------------------------------------------------------------------ helpers
     def _stream(self) -> int:
+        """The current stream's handle.  Asked for before every launch (a graph capture changes it), so
+        through torch's raw accessor where it has one: building a Stream object each time took 7 us."""
+        raw = self._raw_stream
+        if raw is not None:
+            return raw(self._device_index)
         return torch.cuda.current_stream(self.device).cuda_stream
 
     def _check(self, rc: int, kernels: int = 1) -> None:
