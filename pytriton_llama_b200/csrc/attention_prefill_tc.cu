@@ -109,6 +109,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int* tl = p.tiles + 8 * pair;
   const int req = tl[0], tok0 = tl[1], pos0 = tl[3];
   const int rows_g[2] = {tl[2], tl[6]};                        // rows of tile A and of tile B (0: absent)
+  if (rows_g[0] <= 0 && rows_g[1] <= 0) return;                // an empty pair (padding of a captured step): nothing to do, nothing allocated yet
   const int h = blockIdx.x;
   const int kvh = h / (p.nq / p.nkv);
   // Per tile of the pair: first key it may see (window), one past the last, and the range of key

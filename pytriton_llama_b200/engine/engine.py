@@ -108,6 +108,7 @@ class _DecodeGraph:
     logits: torch.Tensor
     launches: int
     turn: int = 0
+    last_used: int = 0
 
 
 class Engine:
@@ -151,7 +152,9 @@ class Engine:
         # token from here.
         self.sampled = torch.zeros(max(1, self.config.max_num_seqs), dtype=torch.int32, device=self.device)
         self.steps_run = 0
-        self._graphs = {}
+        self._graphs = {}          # captured steps: padded batch size (single tokens only) or a _StepShape
+        self._shape_seen: Dict[tuple, int] = {}
+        self._graph_pool = None    # one memory pool for the captured steps of mixed shapes
 
     # ------------------------------------------------------------------ sizing
     def _pages_from_free_memory(self, entries) -> int:
@@ -229,7 +232,9 @@ class Engine:
         bucket = self._graph_bucket(batch)
         if bucket:
             logits = self._run_graph(bucket, batch)
-            if logit_rows != list(range(len(entries))):
+            if isinstance(bucket, tuple):
+                logits = logits[:len(logit_rows)] if logit_rows else None      # the wanted rows, in order
+            elif logit_rows != list(range(len(entries))):
                 idx = torch.tensor(logit_rows, dtype=torch.long, device=self.device)
                 logits = logits.index_select(0, idx) if logit_rows else None
             return StepOutput(logits, rows, batch.T)
@@ -285,14 +290,15 @@ class Engine:
         if layout.static_rows:
             h[lo:lo + n] = np.arange(n, dtype=np.int32)
         elif n:
-            h[lo:lo + n] = b.logit_rows
+            put("logit_rows", b.logit_rows)          # (a padded shape asks for row 0 again in the rows it has too many)
         if layout.static_rows:
             lo, n = layout.seg["dec_items"]
             h[lo:lo + n] = np.arange(n, dtype=np.int32)
         else:
-            put("dec_items", b.dec_items)
-            if b.pf_tiles:
-                put("pf_tiles", b.pf_tiles)
+            # a padded shape has more single-token items than the step: the rest name a token row
+            # beyond the step's, whose request is -1 (the shape is chosen so that there is one)
+            put("dec_items", b.dec_items, fill=min(T, layout.T - 1))
+            put("pf_tiles", b.pf_tiles)              # (empty pairs beyond the step's: rows 0)
         for g in layout.groups:
             put(f"slots{g}", b.slots_by_group[g], fill=-1)
             lo, n = layout.seg[f"bt{g}"]
@@ -336,19 +342,57 @@ class Engine:
         single tokens qualify, and only models whose mixers keep nothing but paged keys and values
         (lite_llama captures its decode step for batch sizes 1, 2, 4, 8, 16, ...:
         lite_llama/executor/cuda_graph.py:6-7,113-132)."""
-        if not self.config.compiled_model or self.device.type != "cuda" or batch.max_q_len != 1:
+        if not self.config.compiled_model or self.device.type != "cuda":
             return 0
         if any(not grp.paged or grp.state for grp in self.cache.groups):
             return 0
+        if batch.max_q_len != 1:
+            return self._shape_bucket(batch)
         b = 1
         while b < batch.R:
             b *= 2
         return b if b <= max(64, self.config.max_num_seqs) else 0
 
-    def _run_graph(self, bucket: int, batch: "_HostBatch") -> torch.Tensor:
+    GRAPH_MAX_TOKENS = 1024      # larger steps keep the GPU busy for longer than the host needs to launch them
+    GRAPH_MAX_SHAPES = 24
+
+    def _shape_bucket(self, batch: "_HostBatch"):
+        """Steps with prompt portions of up to 1,024 tokens are bound by the host's launches (about
+        11 us each, twice the GPU's time at 300 tokens), so they run from captured graphs too: the
+        step's shape is padded to (tokens, requests, single-token items, pairs of prompt tiles, wants
+        logits) with few values each, and a shape that comes a second time is captured.  Padded token
+        rows have request -1 and slot -1, padded tile pairs have no rows: every kernel skips them."""
+        T, R = batch.T, batch.R
+        n_dec, n_pairs, M = len(batch.dec_items), len(batch.pf_tiles) // 8, len(batch.logit_rows)
+        if T > self.GRAPH_MAX_TOKENS:
+            return 0
+        pow2 = lambda n: 0 if n == 0 else 1 << (n - 1).bit_length()
+        step = 64 if T <= 256 else 128
+        t_pad = -(-T // step) * step
+        d_pad = pow2(n_dec)
+        if d_pad > n_dec and t_pad == T:
+            t_pad += step                                   # the padded items need a token row that belongs to no request
+        r_pad = pow2(R)
+        if M > r_pad:
+            return 0                                        # (a replay that wants many rows of a prompt)
+        shape = (t_pad, r_pad, d_pad, pow2(n_pairs), 1 if M else 0)
+        if shape in self._graphs:
+            return shape
+        seen = self._shape_seen.get(shape, 0) + 1
+        self._shape_seen[shape] = seen
+        if len(self._shape_seen) > 4096:
+            self._shape_seen.clear()
+        return shape if seen >= 2 else 0
+
+    def _run_graph(self, bucket, batch: "_HostBatch") -> torch.Tensor:
         g = self._graphs.get(bucket)
         if g is None:
+            if isinstance(bucket, tuple):
+                shapes = [k for k in self._graphs if isinstance(k, tuple)]
+                if len(shapes) >= self.GRAPH_MAX_SHAPES:    # drop the shape that was used longest ago
+                    del self._graphs[min(shapes, key=lambda k: self._graphs[k].last_used)]
             g = self._graphs[bucket] = self._capture(bucket)
+        g.last_used = self.steps_run
         # The copy below is asynchronous: a staging buffer may be rewritten only after the copy that
         # last read it has finished, so each buffer of the ring carries an event.
         host, event = g.staging[g.turn % len(g.staging)]
@@ -360,27 +404,41 @@ class Engine:
         g.graph.replay()
         if hasattr(self.ops, "launches"):
             self.ops.launches += g.launches
+        if g.logits is None or isinstance(bucket, tuple):
+            return g.logits
         return g.logits[:batch.R]
 
-    def _capture(self, bucket: int) -> "_DecodeGraph":
-        layout = _Layout(bucket, bucket, bucket, _pad4(self.cache.max_blocks), self._paged_groups(), static_rows=True)
+    def _capture(self, bucket) -> "_DecodeGraph":
+        """Captures the step of a padded batch of single tokens (``bucket`` an int) or of a padded
+        shape (a tuple, see ``_shape_bucket``).  While it is captured every token row belongs to no
+        request, so the runs that record it touch no page of the cache."""
+        width = _pad4(self.cache.max_blocks)
+        if isinstance(bucket, tuple):
+            t_pad, r_pad, d_pad, pairs, wants = bucket
+            layout = _Layout(t_pad, r_pad, r_pad if wants else 0, width, self._paged_groups(), max_tiles=2 * pairs)
+            n_decode, n_tiles, q_lens = d_pad, 2 * pairs, [t_pad] + [1] * (r_pad - 1)
+        else:
+            layout = _Layout(bucket, bucket, bucket, width, self._paged_groups(), static_rows=True)
+            n_decode, n_tiles, q_lens, wants = bucket, 0, [1] * bucket, 1
         host = torch.empty(layout.size, dtype=torch.int32, pin_memory=True)
         h = host.numpy()
         h.fill(0)
         for name, fill in [("tok_req", -1), ("token_src", -1)] + [(f"slots{g}", -1) for g in layout.groups] + [(f"bt{g}", -1) for g in layout.groups]:
             lo, n = layout.seg[name]
             h[lo:lo + n] = fill
-        for name in ("logit_rows", "dec_items"):
-            lo, n = layout.seg[name]
-            h[lo:lo + n] = np.arange(n, dtype=np.int32)
+        if layout.static_rows:
+            for name in ("logit_rows", "dec_items"):
+                lo, n = layout.seg[name]
+                h[lo:lo + n] = np.arange(n, dtype=np.int32)
         dev = host.to(self.device)
-        splits = self._choose_splits(bucket, self.config.max_seq_len)
-        ctx, cache_view = self._context(dev, layout, [1] * bucket, [self.config.max_seq_len] * bucket, splits,
-                                        n_decode=bucket, n_tiles=0)
+        splits = self._choose_splits(layout.T, self.config.max_seq_len)
+        ctx, cache_view = self._context(dev, layout, q_lens, [self.config.max_seq_len] * layout.R, splits,
+                                        n_decode=n_decode, n_tiles=n_tiles)
 
         def run():
             self.ops.take_tokens(layout.view(dev, "tokens"), layout.view(dev, "token_src"), self.sampled)
-            return self.model.forward(layout.view(dev, "tokens"), ctx, cache_view, layout.view(dev, "logit_rows"))
+            return self.model.forward(layout.view(dev, "tokens"), ctx, cache_view,
+                                      layout.view(dev, "logit_rows") if wants else None)
         side = torch.cuda.Stream(self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
@@ -390,7 +448,12 @@ class Engine:
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         before = getattr(self.ops, "launches", 0)
-        with torch.cuda.graph(graph):
+        pool = None
+        if isinstance(bucket, tuple):                        # mixed shapes share one pool: only one of them runs at a time
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            pool = self._graph_pool
+        with torch.cuda.graph(graph, pool=pool):
             logits = run()
         launches = getattr(self.ops, "launches", 0) - before
         staging = [(torch.empty(layout.size, dtype=torch.int32, pin_memory=True), torch.cuda.Event()) for _ in range(4)]

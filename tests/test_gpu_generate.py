@@ -191,3 +191,45 @@ def test_command_line(model_folders, tmp_path):
     loop = subprocess.run(base, input=" ".join(str(t) for t in prompt) + "\nexit\n", capture_output=True, text=True, timeout=600)
     assert loop.returncode == 0, loop.stderr[-2000:]
     assert " ".join(str(t) for t in want) in loop.stdout
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_steps_of_mixed_shapes_give_the_same_logits(model_folders, dtype):
+    """Steps that hold prompt portions run from captured graphs of padded shapes once a shape has
+    come twice.  The same steps (portions beside single tokens, three live requests, shapes that
+    repeat and a step that wants two rows of one request) with and without captured graphs must
+    agree, and the second engine must really have captured mixed shapes."""
+    from pytriton_llama_b200.config import EngineConfig
+    from pytriton_llama_b200.engine.engine import Engine, StepEntry
+    folder = model_folders("B", stored_dtype(dtype))
+    vocab = TINY["B"]["vocab_size"]
+    prompts = {"a": random_tokens(150, vocab, 1), "b": random_tokens(90, vocab, 2), "c": random_tokens(40, vocab, 3)}
+    steps = []
+    for i in range(5):
+        entries = [("a", prompts["a"][30 * i:30 * (i + 1)], [29])]
+        if i >= 2:
+            entries.append(("b", prompts["b"][30 * (i - 2):30 * (i - 1)], [0, 29] if i == 3 else [29]))
+        if i >= 1:
+            lo = 11 * (i - 1)
+            entries.append(("c", prompts["c"][lo:lo + (1 if i % 2 else 10)], [0]))
+        steps.append(entries)
+    outs = {}
+    for compiled in (False, True):
+        cfg = EngineConfig(dtype=dtype, page_size=PAGE_SIZE["B"], max_gpu_num_blocks=64, max_seq_len=256, max_num_seqs=4,
+                           max_batched_tokens=256, compiled_model=compiled, seed=0)
+        eng = Engine(folder, cfg)
+        res = []
+        for _ in range(3):                         # the whole sequence three times: every shape has come before
+            for entries in steps:
+                out = eng.step([StepEntry(r, t, w) for r, t, w in entries])
+                res.append(out.logits.float().cpu())
+            eng.finish_all()
+        eng.check_device_status()
+        outs[compiled] = res
+        if compiled:
+            shapes = [k for k in eng._graphs if isinstance(k, tuple)]
+            assert len(shapes) >= 3, shapes
+    for a, b in zip(outs[False], outs[True]):
+        assert a.shape == b.shape
+        top = float(a.abs().max())
+        assert float((a - b).abs().max()) <= (1e-5 if dtype == "float32" else 0.03) * top
