@@ -260,14 +260,18 @@ int add_rmsnorm(void* y, float* residual_out, const float* residual_in, const vo
   const int vec_ok = hidden % 4 == 0 && aligned16(y) && aligned16(w) && (!x || aligned16(x)) &&
                      (!residual_in || aligned16(residual_in)) && (!residual_out || aligned16(residual_out));
   // many rows of a common width: a warp per row
-  if (vec_ok && out_rows >= 256 && (hidden == 512 || hidden == 1024 || hidden == 2048 || hidden == 4096)) {
+  if (vec_ok && out_rows >= 256 && hidden % 512 == 0 && hidden <= 4096) {
     const dim3 grid((out_rows + 7) / 8), block(256);
 #define PTL_NORM_ROWS(N4) launch_kernel("add_rmsnorm", add_rmsnorm_warp_kernel<T, N4>, grid, block, 0, as_stream(stream), \
                                         (T*)y, residual_out, residual_in, (const T*)x, w, rows, out_rows, eps)
     switch (hidden) {
       case 512: return PTL_NORM_ROWS(4);
       case 1024: return PTL_NORM_ROWS(8);
+      case 1536: return PTL_NORM_ROWS(12);
       case 2048: return PTL_NORM_ROWS(16);
+      case 2560: return PTL_NORM_ROWS(20);
+      case 3072: return PTL_NORM_ROWS(24);
+      case 3584: return PTL_NORM_ROWS(28);
       default: return PTL_NORM_ROWS(32);
     }
 #undef PTL_NORM_ROWS

@@ -59,7 +59,8 @@ def test_embed(ops, dtype, vocab, hidden):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("rows, hidden, eps", [(5, 200, 1e-5), (3, 2048, 1e-6), (2, 5000, 3e-4), (4, 100, 1e-2), (1, 30000, 1e-5),
-                                               (300, 2048, 1e-5), (257, 512, 1e-6), (1000, 4096, 1e-5)])   # many rows: a warp per row
+                                               (300, 2048, 1e-5), (257, 512, 1e-6), (1000, 4096, 1e-5), (260, 3072, 1e-5),
+                                               (300, 1536, 1e-6), (256, 3584, 1e-5), (270, 2560, 1e-5)])   # many rows: a warp per row
 def test_add_rmsnorm(ops, dtype, rows, hidden, eps):
     x = rnd((rows, hidden), DT[dtype], 2, 3.0)
     res = rnd((rows, hidden), torch.float32, 3, 5.0)
