@@ -63,10 +63,15 @@ struct GemmParams {
                          // part s stores its partial sums as rows s * rows.. of `out` ([ksplits, rows, cols])
 };
 
-template <int BN> struct TcCfg {
-  static constexpr int kStages = BN >= 192 ? 4 : (BN >= 128 ? 6 : (BN == 64 ? 3 : 4));   // few tokens: small blocks, two or three per SM
+// PAIR: two blocks on the SMs of one TPC work as one (cta_group::2): an MMA of 256 token rows x BN
+// features, of which each block holds its 128 rows of X, BN/2 rows of W and its 128 rows of the
+// accumulator.  A pair fetches W once instead of twice: a third less traffic from L2 into shared
+// memory, which is what bounds the many-token product (14-15 TB/s over all SMs).
+template <int BN, bool PAIR = false> struct TcCfg {
+  static_assert(!PAIR || BN >= 128, "pairs of blocks only with many tokens");
+  static constexpr int kStages = PAIR ? 6 : (BN >= 192 ? 4 : (BN >= 128 ? 6 : (BN == 64 ? 3 : 4)));   // few tokens: small blocks, two or three per SM
   static constexpr int kRowBytes = kTileRows * kTileK * 2;     // 16 KB
-  static constexpr int kColBytes = BN * kTileK * 2;
+  static constexpr int kColBytes = (PAIR ? BN / 2 : BN) * kTileK * 2;
   static constexpr int kStageBytes = kRowBytes + kColBytes;
   static constexpr int kAccBufs = BN >= 128 ? 2 : 1;           // many tokens: the epilogue of a tile overlaps the next tile's MMAs
   // few tokens: an MMA of 128 x BN x 16 is short, and one thread that waits for a stage, issues its
@@ -233,11 +238,12 @@ __device__ __forceinline__ void load_ways(uint32_t taddr, int stages, float (&v)
 
 // (Few tokens: two blocks per SM must fit the register file, 102 registers a thread.  The compiler
 // kept to that by itself until the many-token paths grew; now it is told.)
-template <int BN, int EPI>
+template <int BN, int EPI, bool PAIR = false>
 __global__ void __launch_bounds__(kGemmThreads, BN < 128 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col,
                const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
-  using Cfg = TcCfg<BN>;
+  using Cfg = TcCfg<BN, PAIR>;
+  const uint32_t pair_rank = PAIR ? cluster_ctarank() : 0;     // 0: the block of a pair that issues the MMAs
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // tiles need 1024-byte alignment for the 128-byte swizzle pattern to start at row 0
   unsigned char* smem = smem_raw;
@@ -255,10 +261,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
   const int num_kb = (p.K + kTileK - 1) / kTileK;
   // swapped mode: one tile per block (blockIdx.x = row tile, blockIdx.y = K split);
   // normal mode: the block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (token tiles fastest)
-  const int tiles_mn = p.tiles_m * p.tiles_n;
+  // a pair walks the tiles two token tiles at a time (the second one may lie beyond the tokens: it reads zeros and stores nothing)
+  const int tiles_mp = PAIR ? (p.tiles_m + 1) / 2 : p.tiles_m;
+  const int tiles_mn = tiles_mp * p.tiles_n;
   const int total_tiles = p.swapped ? 1 : tiles_mn * p.ksplits;      // work units: (tile, part of the K range)
-  const int first_tile = p.swapped ? 0 : blockIdx.x;
-  const int tile_step = p.swapped ? 1 : gridDim.x;
+  const int first_tile = p.swapped ? 0 : (PAIR ? blockIdx.x / 2 : blockIdx.x);
+  const int tile_step = p.swapped ? 1 : (PAIR ? gridDim.x / 2 : gridDim.x);
   const int split = p.swapped ? blockIdx.y : 0;
   const int kb0 = split * p.kb_per_split;
   const int kb1 = min(num_kb, kb0 + p.kb_per_split);
@@ -271,7 +279,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
   auto acc_empty = [&](int b) { return bar_base + 8u * (2 * Cfg::kStages + 2 + b); };
   auto tile_rows_cols = [&](int tile, int& row_tile, int& col_tile) {
     if (p.swapped) { row_tile = blockIdx.x; col_tile = 0; }
-    else { const int t = tile % tiles_mn; row_tile = t % p.tiles_m; col_tile = t / p.tiles_m; }
+    else { const int t = tile % tiles_mn; row_tile = (t % tiles_mp) * (PAIR ? 2 : 1) + pair_rank; col_tile = t / tiles_mp; }
   };
   // the K blocks of a work unit: first one and how many
   auto unit_k = [&](int tile, int& first_kb, int& n_kb) {
@@ -282,7 +290,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), p.swapped ? Cfg::kAccWays : 1); mbar_init(acc_empty(b), 8); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), p.swapped ? Cfg::kAccWays : 1); mbar_init(acc_empty(b), PAIR ? 16 : 8); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_row) : "memory");
@@ -290,13 +298,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     if (EPI == 2 && p.tma_add) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_out) : "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(Cfg::kTmemCols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {               // (the same warp in both blocks of the pair, the same place for the address)
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(Cfg::kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(Cfg::kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // a pair: neither block may count bytes on the other's barriers, arrive on them or write its
+  // TMEM before both have set theirs up
+  if (PAIR) { cluster_arrive(); cluster_wait(); }
   // blocks of a cluster write into each other's shared memory later on; none may do so before all
   // of them run, which the wait that matches this arrival establishes
   if (p.swapped && p.splits > 1) cluster_arrive();
@@ -326,8 +342,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
         const int s = it % Cfg::kStages;
         const uint32_t ph = (it / Cfg::kStages) & 1;
         if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
-        mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
         const uint32_t dst = smem_base + s * Cfg::kStageBytes;
+        if (PAIR) {
+          // both blocks' tiles are counted on the issuing block's barrier, which expects both (a
+          // count that arrives before the expectation is made just runs negative for a while)
+          if (pair_rank == 0) mbar_expect_tx(full_bar(s), 2 * Cfg::kStageBytes);
+          const uint32_t bar = map_to_peer(full_bar(s), 0);
+          tma_load_2d_pair(dst, &map_row, bar, (ukb0 + i) * kTileK, row_tile * kTileRows);
+          tma_load_2d_pair(dst + Cfg::kRowBytes, &map_col, bar, (ukb0 + i) * kTileK, col_tile * BN + (int)pair_rank * (BN / 2));
+          continue;
+        }
+        mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
         tma_load_2d(dst, &map_row, full_bar(s), (ukb0 + i) * kTileK, row_tile * kTileRows);
         tma_load_2d(dst + Cfg::kRowBytes, &map_col, full_bar(s), (ukb0 + i) * kTileK, col_tile * BN);
       }
@@ -363,11 +388,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       }
       tcgen05_commit(acc_full(0));         // this issuer's accumulator is complete (also when it had nothing to do)
     }
-  } else if (warp == 1 && lane == 0) {
-    // ------------------------------------------------------------ MMA issuer, many tokens
+  } else if (warp == 1 && lane == 0 && pair_rank == 0) {
+    // ------------------------------------------------------------ MMA issuer, many tokens (of a pair: the even block's)
     pdl_wait();
     pdl_launch_dependents();
-    constexpr uint32_t idesc = instr_desc_bf16(kTileRows, BN);
+    constexpr uint32_t idesc = instr_desc_bf16(PAIR ? 2 * kTileRows : kTileRows, BN);
     int it = 0;
     bool ok = true;
     int lt = 0;          // tiles of this block so far
@@ -390,11 +415,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
         const uint32_t b = a + Cfg::kRowBytes;
 #pragma unroll
         for (int k = 0; k < kTileK / 16; ++k) {
-          tcgen05_mma_bf16(acc, smem_desc_sw128(a + k * 32), smem_desc_sw128(b + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
+          if (PAIR) tcgen05_mma_bf16_pair(acc, smem_desc_sw128(a + k * 32), smem_desc_sw128(b + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
+          else tcgen05_mma_bf16(acc, smem_desc_sw128(a + k * 32), smem_desc_sw128(b + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
         }
-        tcgen05_commit(empty_bar(s));      // the stage is free once these MMAs have read it
+        if (PAIR) tcgen05_commit_pair(empty_bar(s));     // the stage is free, in both blocks, once these MMAs have read it
+        else tcgen05_commit(empty_bar(s));
       }
-      tcgen05_commit(acc_full(buf));       // the accumulator is complete (also when there was nothing to do)
+      if (PAIR) tcgen05_commit_pair(acc_full(buf));      // the accumulator is complete (also when there was nothing to do)
+      else tcgen05_commit(acc_full(buf));
     }
   } else if (warp >= 2) {
     // ------------------------------------------------------------ epilogue
@@ -457,7 +485,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       if (!mbar_wait(acc_full(buf), use & 1, abort_flag, p.status, 3)) break;
       tcgen05_fence_after();
       const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
-      if (EPI == 2 && !p.swapped && p.tma_add) {
+      if (!p.swapped && row_tile * kTileRows >= p.rows) {
+        // the second token tile of a pair, beyond the tokens: nothing to store
+      } else if (EPI == 2 && !p.swapped && p.tma_add) {
         // The accumulator goes out through shared memory, 32 columns at a time, and TMA adds it into
         // the residual: nothing of the residual is read here, and global memory sees whole rows of 128 bytes.
         const uint32_t buf = smem_base + Cfg::kStages * Cfg::kStageBytes + 1024 + half * (kTileRows * 128);
@@ -536,7 +566,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       // this warp has read its share of the buffer: one of the eight arrivals that free it
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty(buf));
+      if (lane == 0) {
+        if (PAIR && pair_rank != 0) mbar_arrive_cluster(map_to_peer(acc_empty(buf), 0));      // the issuing block waits for both blocks' warps
+        else mbar_arrive(acc_empty(buf));
+      }
     }
     if (EPI == 2 && !p.swapped && p.tma_add && quad == 0 && lane == 0) bulk_wait_all();   // the adds have landed
   }
@@ -612,19 +645,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     tcgen05_fence_before();
     __syncthreads();
   }
+  if (PAIR) { cluster_arrive(); cluster_wait(); }        // neither block frees TMEM or leaves while the other may still reach into it
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols) : "memory");
+    if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols) : "memory");
   }
 }
 
 // ---------------------------------------------------------------- host side
-template <int BN, int EPI>
+template <int BN, int EPI, bool PAIR = false>
 static int launch_tc(const CUtensorMap& mr, const CUtensorMap& mc, const CUtensorMap& mo, const GemmParams& p, dim3 grid,
                      cudaStream_t stream) {
-  using Cfg = TcCfg<BN>;
+  using Cfg = TcCfg<BN, PAIR>;
   static bool raised = false;
   if (!raised) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
     PTL_REQUIRE(e == cudaSuccess, "gemm_tc: cannot raise shared memory to %d: %s", Cfg::kSmem, cudaGetErrorString(e));
     raised = true;
   }
@@ -640,28 +675,28 @@ static int launch_tc(const CUtensorMap& mr, const CUtensorMap& mc, const CUtenso
     attr[nattr].val.programmaticStreamSerializationAllowed = 1;
     ++nattr;
   }
-  if (p.swapped && p.splits > 1) {
+  if (PAIR || (p.swapped && p.splits > 1)) {
     attr[nattr].id = cudaLaunchAttributeClusterDimension;
-    attr[nattr].val.clusterDim.x = 1;
-    attr[nattr].val.clusterDim.y = p.splits;
+    attr[nattr].val.clusterDim.x = PAIR ? 2 : 1;
+    attr[nattr].val.clusterDim.y = PAIR ? 1 : p.splits;
     attr[nattr].val.clusterDim.z = 1;
     ++nattr;
   }
   cfg.attrs = attr;
   cfg.numAttrs = nattr;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI>, mr, mc, mo, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, PAIR>, mr, mc, mo, p);
   if (e != cudaSuccess) return fail("gemm_tc: launch failed: %s", cudaGetErrorString(e));
   return check_launch("gemm_tc");
 }
 
-template <int BN>
+template <int BN, bool PAIR = false>
 static int launch_epi(int epi, const CUtensorMap& mr, const CUtensorMap& mc, const CUtensorMap& mo, const GemmParams& p, dim3 grid,
                       cudaStream_t s) {
   switch (epi) {
-    case 0: return launch_tc<BN, 0>(mr, mc, mo, p, grid, s);
-    case 1: return launch_tc<BN, 1>(mr, mc, mo, p, grid, s);
-    case 2: return launch_tc<BN, 2>(mr, mc, mo, p, grid, s);
-    case 3: return launch_tc<BN, 3>(mr, mc, mo, p, grid, s);
+    case 0: return launch_tc<BN, 0, PAIR>(mr, mc, mo, p, grid, s);
+    case 1: return launch_tc<BN, 1, PAIR>(mr, mc, mo, p, grid, s);
+    case 2: return launch_tc<BN, 2, PAIR>(mr, mc, mo, p, grid, s);
+    case 3: return launch_tc<BN, 3, PAIR>(mr, mc, mo, p, grid, s);
   }
   return fail("gemm_tc: unknown epilogue %d", epi);
 }
@@ -779,15 +814,19 @@ PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, in
     }
     p.ksplits = parts;
     p.kb_per_split = (num_kb + parts - 1) / parts;
+    // wide tiles over at least two token tiles go to pairs of blocks (one MMA of 256 rows, W fetched once per pair)
+    static const bool pairs_allowed = [] { const char* e = getenv("PTL_GEMM_PAIRS"); return !(e && e[0] == '0'); }();
+    const bool pair = pairs_allowed && bn >= 192 && parts == 1 && M > kTileRows && sm_count >= 2;
     int rc = make_map(&mr, X, M, K, kTileRows);
     if (rc) return rc;
-    rc = make_map(&mc, W, N, K, bn);
+    rc = make_map(&mc, W, N, K, pair ? bn / 2 : bn);
     if (rc) return rc;
     p.tiles_m = (M + kTileRows - 1) / kTileRows;
     p.tiles_n = (N + bn - 1) / bn;
     if (slots_out) *slots_out = p.tiles_n * 2;
-    const long long tiles = (long long)p.tiles_m * p.tiles_n * parts;
-    dim3 grid((unsigned)(tiles < sm_count ? tiles : sm_count));
+    const long long tiles = pair ? (long long)((p.tiles_m + 1) / 2) * p.tiles_n * 2 : (long long)p.tiles_m * p.tiles_n * parts;
+    const long long most = pair ? sm_count / 2 * 2 : sm_count;
+    dim3 grid((unsigned)(tiles < most ? tiles : most));
     // the add epilogue hands its tiles to TMA, which adds them into the residual (unless the next norm's input is wanted too)
     CUtensorMap mo = mr;
     if (epi == 2 && !xs && N % 32 == 0 && ld_out % 4 == 0) {
@@ -795,6 +834,7 @@ PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, in
       if (rc) return rc;
       p.tma_add = 1;
     }
+    if (pair) return bn == 256 ? launch_epi<256, true>(epi, mr, mc, mo, p, grid, s) : launch_epi<192, true>(epi, mr, mc, mo, p, grid, s);
     if (bn == 256) return launch_epi<256>(epi, mr, mc, mo, p, grid, s);
     if (bn == 192) return launch_epi<192>(epi, mr, mc, mo, p, grid, s);
     return launch_epi<128>(epi, mr, mc, mo, p, grid, s);

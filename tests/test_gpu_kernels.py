@@ -110,6 +110,7 @@ def test_linear_bfloat16(ops, M, N, K):
     (128, 128, 64), (130, 264, 96), (200, 1000, 512), (300, 128, 4096), (1100, 768, 200),      # many tokens: 128-token tiles
     (300, 3072, 128), (260, 2304, 64),                                                          # ... of 192 features
     (130, 2048, 8192), (520, 2048, 2048), (1000, 1024, 1024),                                   # ... too few tiles: the add cuts the K range
+    (1024, 8192, 128), (600, 4096, 192), (2048, 3072, 256),                                     # ... wide tiles: pairs of blocks (MMAs of 256 rows)
     (1, 304, 80), (8, 3072, 2048), (16, 2048, 2048), (17, 1000, 72), (33, 2048, 8192), (64, 1000, 512),
     (64, 9600, 512), (40, 16384, 2048), (8, 16384, 2048), (24, 12000, 1024)])   # few: swapped, K split 2, 4 or 8 ways
 def test_tensor_core_product_and_its_epilogues(ops, M, N, K):
