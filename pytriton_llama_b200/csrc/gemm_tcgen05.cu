@@ -816,6 +816,8 @@ PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, in
     p.kb_per_split = (num_kb + parts - 1) / parts;
     // wide tiles over at least two token tiles go to pairs of blocks (one MMA of 256 rows, W fetched once per pair)
     static const bool pairs_allowed = [] { const char* e = getenv("PTL_GEMM_PAIRS"); return !(e && e[0] == '0'); }();
+    // (not the 128-wide tiles of a few hundred tokens: measured, pairs made them 5 % slower: there the
+    // issuing thread's wait for each stage bounds the loop, 160 cycles per MMA of 256 x 128 x 16)
     const bool pair = pairs_allowed && bn >= 192 && parts == 1 && M > kTileRows && sm_count >= 2;
     int rc = make_map(&mr, X, M, K, kTileRows);
     if (rc) return rc;
