@@ -319,19 +319,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
 
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ TMA producer
-    // Weights do not depend on earlier kernels of the step: with swapped operands their tiles for
-    // the first ring of stages are requested before the wait on the predecessor, the tokens after.
+    // Weights do not depend on earlier kernels of the step: their tiles for the first ring of
+    // stages are requested before the wait on the predecessor, the tokens after.
     int it = 0;          // stage uses so far, over all tiles of this block
     int pre = 0;
+    int row0 = 0, col0 = 0, kb00 = 0, nkb0 = 0;     // many tokens: this block's first work unit
     if (p.swapped) {
       pre = min(my_kb, Cfg::kStages);
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(full_bar(i), Cfg::kStageBytes);
         tma_load_2d(smem_base + i * Cfg::kStageBytes, &map_row, full_bar(i), (kb0 + i) * kTileK, blockIdx.x * kTileRows);
       }
+    } else if (first_tile < total_tiles) {
+      tile_rows_cols(first_tile, row0, col0);
+      unit_k(first_tile, kb00, nkb0);
+      pre = min(nkb0, Cfg::kStages);
+      for (int i = 0; i < pre; ++i) {
+        const uint32_t dst = smem_base + i * Cfg::kStageBytes + Cfg::kRowBytes;
+        if (PAIR) {
+          if (pair_rank == 0) mbar_expect_tx(full_bar(i), 2 * Cfg::kStageBytes);
+          tma_load_2d_pair(dst, &map_col, map_to_peer(full_bar(i), 0), (kb00 + i) * kTileK, col0 * BN + (int)pair_rank * (BN / 2));
+        } else {
+          mbar_expect_tx(full_bar(i), Cfg::kStageBytes);
+          tma_load_2d(dst, &map_col, full_bar(i), (kb00 + i) * kTileK, col0 * BN);
+        }
+      }
     }
-    pdl_wait();                // (the tokens of those stages are requested by the MMA issuers, each for its own stages)
+    pdl_wait();                // (few tokens: the tokens of those stages are requested by the MMA issuers, each for its own stages)
     pdl_launch_dependents();
+    if (!p.swapped) {
+      for (int i = 0; i < pre; ++i) {
+        const uint32_t dst = smem_base + i * Cfg::kStageBytes;
+        if (PAIR) tma_load_2d_pair(dst, &map_row, map_to_peer(full_bar(i), 0), (kb00 + i) * kTileK, row0 * kTileRows);
+        else tma_load_2d(dst, &map_row, full_bar(i), (kb00 + i) * kTileK, row0 * kTileRows);
+      }
+    }
     it = pre;
     bool ok = true;
     for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
