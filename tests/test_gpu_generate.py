@@ -233,3 +233,43 @@ def test_captured_steps_of_mixed_shapes_give_the_same_logits(model_folders, dtyp
         assert a.shape == b.shape
         top = float(a.abs().max())
         assert float((a - b).abs().max()) <= (1e-5 if dtype == "float32" else 0.03) * top
+
+
+@pytest.mark.parametrize("hidden, heads, kv_heads, head_dim, inter", [(2048, 32, 8, 64, 8192), (3072, 24, 8, 128, 8192)])
+def test_one_layer_of_real_widths_in_bfloat16(tmp_path, hidden, heads, kv_heads, head_dim, inter):
+    """The tiny configurations never reach the kernels' paths for real widths: products of 2,048-wide
+    rows with a few hundred and with more than a thousand tokens (parts of the K range, wide tiles on
+    pairs of blocks), 32 query heads over 8 kv heads or 24 over 8 with head size 128, prompts of many
+    key tiles.  One layer of the Llama-3.2-1B and -3B widths with a smaller vocabulary: a 1,400-token prompt in portions of 300 and 1,100
+    (the first as a captured shape the second time round), then single tokens, against the plain
+    implementation."""
+    from pytriton_llama_b200.config import EngineConfig
+    from pytriton_llama_b200.engine.engine import Engine, StepEntry
+    from pytriton_llama_b200.weights.random_init import write_random_model
+    config = {
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 1, "hidden_size": hidden,
+        "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": head_dim, "intermediate_size": inter, "vocab_size": 32064,
+        "rope_theta": 500000.0, "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                                                  "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+        "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 131072,
+    }
+    folder = write_random_model(tmp_path / "wide", config, seed=5, dtype=torch.bfloat16)
+    prompt = random_tokens(1400, config["vocab_size"], 6)
+    tail = random_tokens(6, config["vocab_size"], 7)
+    cfg, w = plain_llama.load_model_folder(folder, dtype=torch.float64)
+    ref = plain_llama.forward(cfg, w, prompt + tail)
+    ecfg = EngineConfig(dtype="bfloat16", page_size=16, max_gpu_num_blocks=200, max_seq_len=1536, max_num_seqs=2,
+                        max_batched_tokens=2048, compiled_model=True, seed=0)
+    eng = Engine(folder, ecfg)
+    from gpu_common import assert_close
+    for attempt in range(2):                     # the second time the 300-token step runs from its captured graph
+        out = eng.step([StepEntry("r", prompt[:300], [299])])
+        assert_close(out.logits, ref[[299]], "bfloat16", f"portion of 300, attempt {attempt}")
+        out = eng.step([StepEntry("r", prompt[300:], [0, 747, 1099])])
+        assert_close(out.logits, ref[[300, 1047, 1399]], "bfloat16", f"portion of 1,100, attempt {attempt}")
+        for i, t in enumerate(tail):
+            out = eng.step([StepEntry("r", [t], [0])])
+            assert_close(out.logits, ref[[1400 + i]], "bfloat16", f"single token {i}, attempt {attempt}")
+        eng.finish("r")
+    eng.check_device_status()
+    assert any(isinstance(k, tuple) for k in eng._graphs)
