@@ -304,6 +304,27 @@ def test_tensor_core_attention_over_a_long_prompt(ops, d, page, window):
     close(out, ref, "bfloat16", "long prompt", scale=4.0)
 
 
+@pytest.mark.parametrize("d, window", [(64, 0), (128, 0), (64, 5000)])
+def test_tensor_core_attention_over_more_pages_than_the_kernels_stage(ops, d, window):
+    """The attention kernels keep a request's block-table entries in shared memory up to a limit
+    (264 entries for a prompt tile pair, 512 for a decode split) and read the table from global
+    memory beyond it: 9,000 cached tokens in pages of 16 are 563 entries.  A 130-token portion at the
+    end of such a context, a single token after 9,000 and one after 600, scattered pages."""
+    nq, nkv, page = 4, 2, 16
+    q_lens, ctx = [130, 1, 1], [9000, 9000, 600]
+    pages = sum(-(-c // page) for c in ctx) + 7
+    bt = _random_paging(3, ctx, page, pages, seed=d)
+    cache = rnd((pages, 2, nkv, page, d), torch.bfloat16, 31)
+    q = rnd((sum(q_lens), (nq + 2 * nkv) * d), torch.bfloat16, 32, 2.0)
+    tok_req = torch.repeat_interleave(torch.arange(3), torch.tensor(q_lens)).int()
+    positions = torch.cat([torch.arange(c - n, c) for n, c in zip(q_lens, ctx)]).int()
+    scale = 1 / math.sqrt(d)
+    ref = REF.paged_attention(q, cache, bt, tok_req, positions, nq, nkv, d, page, scale, window=window)
+    out = ops.paged_attention(q.cuda(), cache.cuda(), bt.cuda(), tok_req.cuda(), positions.cuda(), nq, nkv, d, page, scale,
+                              window=window, hints=_hints(q_lens, ctx))
+    close(out, ref, "bfloat16", "long context", scale=4.0)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("window", [0, 100])
 def test_attention_finds_one_far_key(ops, dtype, window):
