@@ -35,6 +35,7 @@ class EngineConfig:
     max_num_seqs: int = 64                     # live requests (lite_llama's max_batch_size)
     max_batched_tokens: int = 2048             # token budget of one step
     compiled_model: bool = False               # capture decode steps in CUDA graphs
+    capture_mixed_steps: bool = True           # with compiled_model: also steps that hold prompt portions (padded shapes, up to 1,024 tokens)
     overlap_steps: bool = True                 # plan and launch the next step while the last one's tokens are read
     seed: int = 0
 

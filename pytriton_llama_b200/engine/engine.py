@@ -347,7 +347,7 @@ class Engine:
         if any(not grp.paged or grp.state for grp in self.cache.groups):
             return 0
         if batch.max_q_len != 1:
-            return self._shape_bucket(batch)
+            return self._shape_bucket(batch) if self.config.capture_mixed_steps else 0
         b = 1
         while b < batch.R:
             b *= 2
