@@ -24,7 +24,7 @@ static int sm_count_of_device() {
 // 16 x 16 of 192 take two cheaper ones; a few hundred tokens make too few wide tiles to fill the
 // SMs once.  A narrower tile has to win by a tenth.
 struct TilePlan { int bn, parts; };
-static TilePlan plan_tiles(int M, int N, int K, bool with_parts) {
+static TilePlan plan_tiles(int M, int N, int K, bool with_parts, int whole_heads = 0) {
   const int sm_count = sm_count_of_device();
   const long long tm = (M + kTileRows - 1) / kTileRows;
   const int num_kb = (K + kTileK - 1) / kTileK;
@@ -37,6 +37,7 @@ static TilePlan plan_tiles(int M, int N, int K, bool with_parts) {
     if (bn == 192 && N % 192 != 0) continue;
     if (bn == 256 && N % 256 != 0 && N < 2048) continue;        // a narrow product with a ragged edge: 128
     if (forced && forced != bn) continue;
+    if (whole_heads && bn % whole_heads != 0) continue;         // the rotary epilogue: a tile's columns hold whole heads
     const long long tiles = tm * ((N + bn - 1) / bn);
     long long parts = 1;
     if (with_parts && tiles * 2 <= sm_count) {
@@ -77,10 +78,10 @@ PTL_EXPORT int ptl_gemm_tc_k_parts(int M, int N, int K) {
 // (that array), `scale_slots`, `scale_ld` and `scale_eps` multiplies every output row by
 // rsqrt(sum of the row's slots / K + eps), which completes the norm (epi 0, 1 and 3).  -2 is also
 // returned when what was asked for around the norm cannot be done for these sizes.
-PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, int M, int N, int K, int ld_out, int epi,
-                                     int* status, int splits_hint, void* xs, const float* norm_w, float* sumsq,
-                                     int sumsq_ld, int* slots_out, const float* scale_sumsq, int scale_slots,
-                                     int scale_ld, float scale_eps, void* stream) {
+static int gemm_tc_impl(void* out, const void* X, const void* W, int M, int N, int K, int ld_out, int epi,
+                        int* status, int splits_hint, void* xs, const float* norm_w, float* sumsq,
+                        int sumsq_ld, int* slots_out, const float* scale_sumsq, int scale_slots,
+                        int scale_ld, float scale_eps, const ptl::GemmParams* rope, void* stream) {
   using namespace ptl;
   PTL_REQUIRE(M >= 0 && N > 0 && K > 0 && ld_out > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
   if (K % 8 != 0 || K < kTileK) return -2;
@@ -109,7 +110,13 @@ PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, in
     p.swapped = 0; p.rows = M; p.cols = N; p.splits = 1; p.kb_per_split = num_kb;
     const int sm_count = sm_count_of_device();
     int parts = 1;
-    const int bn = plan_tiles(M, N, K, splits_hint > 1).bn;
+    const int bn = plan_tiles(M, N, K, splits_hint > 1, rope ? rope->rope_d : 0).bn;
+    if (rope) {
+      if (epi != 4 || bn % rope->rope_d != 0) return -2;
+      p.rope_table = rope->rope_table; p.rope_slots = rope->rope_slots; p.rope_cache = rope->rope_cache;
+      p.rope_nq = rope->rope_nq; p.rope_nkv = rope->rope_nkv; p.rope_d = rope->rope_d; p.rope_page = rope->rope_page;
+      p.rope_num_slots = rope->rope_num_slots;
+    }
     if (splits_hint > 1) {
       PTL_REQUIRE(epi == 1 && !scale_sumsq && splits_hint <= 64 && splits_hint <= num_kb,
                   "gemm_tc: with more than 64 tokens the K range is cut only for plain float32 partial sums, into at most 64 parts");
@@ -162,6 +169,33 @@ PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, in
   dim3 grid(row_tiles, splits);
   if (slots_out) *slots_out = (N + 15) / 16;
   return launch_few_tokens(bn, epi, mr, mc, mr, p, grid, s);
+}
+
+PTL_EXPORT int ptl_gemm_tc_bf16_norm(void* out, const void* X, const void* W, int M, int N, int K, int ld_out, int epi,
+                                     int* status, int splits_hint, void* xs, const float* norm_w, float* sumsq,
+                                     int sumsq_ld, int* slots_out, const float* scale_sumsq, int scale_slots,
+                                     int scale_ld, float scale_eps, void* stream) {
+  PTL_REQUIRE(epi >= 0 && epi <= 3, "gemm_tc: unknown epilogue %d", epi);
+  return gemm_tc_impl(out, X, W, M, N, K, ld_out, epi, status, splits_hint, xs, norm_w, sumsq, sumsq_ld, slots_out, scale_sumsq,
+                      scale_slots, scale_ld, scale_eps, nullptr, stream);
+}
+
+// The q|k|v projection of a step with more than 64 tokens, with rotary position encoding and the
+// cache write in its epilogue: out [M, N] bfloat16 gets the rotated q columns (its k and v columns
+// are not written), cache slot slots[t] gets token t's rotated k and plain v.  table [M, d/2] holds
+// (cos, sin) of every token's angles (ptl_rope_table).  N = (nq + 2 nkv) d, d 64 or 128, the whole
+// head rotated.  Returns -2 where this is not possible (the caller then runs the steps apart).
+PTL_EXPORT int ptl_gemm_tc_bf16_qkv_rope(void* out, const void* X, const void* W, int M, int N, int K, int* status,
+                                         const void* table, const int* slots, void* cache, int nq, int nkv, int d,
+                                         int page_size, long long num_slots, void* stream) {
+  using namespace ptl;
+  PTL_REQUIRE(nq > 0 && nkv > 0 && d > 0 && page_size > 0 && num_slots > 0, "qkv_rope: bad sizes");
+  if (M <= 64 || (d != 64 && d != 128) || N != (nq + 2 * nkv) * d) return -2;
+  PTL_REQUIRE(table && slots && cache && aligned16(table) && aligned16(cache), "qkv_rope: needs the angle table, slots and an aligned cache");
+  GemmParams rope{};
+  rope.rope_table = (const float2*)table; rope.rope_slots = slots; rope.rope_cache = (__nv_bfloat16*)cache;
+  rope.rope_nq = nq; rope.rope_nkv = nkv; rope.rope_d = d; rope.rope_page = page_size; rope.rope_num_slots = num_slots;
+  return gemm_tc_impl(out, X, W, M, N, K, N, 4, status, 0, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0.f, &rope, stream);
 }
 
 PTL_EXPORT int ptl_gemm_tc_bf16(void* out, const void* X, const void* W, int M, int N, int K, int ld_out, int epi,

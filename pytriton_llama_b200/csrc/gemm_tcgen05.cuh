@@ -65,6 +65,15 @@ struct GemmParams {
   int tma_add;           // many tokens, add epilogue: the accumulator tiles are added into `out` by TMA (map_out)
   int ksplits;           // many tokens, float32 store: the K range is cut into this many parts (work units = tiles x parts),
                          // part s stores its partial sums as rows s * rows.. of `out` ([ksplits, rows, cols])
+  // Epilogue 4, the q|k|v projection of a step with many tokens: rotary position encoding of q and k
+  // and the write of k and v into the paged cache happen here.  rope_table [tokens, rope_d / 2] holds
+  // (cos, sin) of every token's angles; rotated q goes to `out` (bfloat16, the q columns only),
+  // rotated k and plain v to cache slot rope_slots[token] (negative: nowhere).
+  const float2* rope_table;
+  const int* rope_slots;
+  __nv_bfloat16* rope_cache;     // [pages][2 (k, v)][rope_nkv][rope_page][rope_d]
+  int rope_nq, rope_nkv, rope_d, rope_page;
+  long long rope_num_slots;
 };
 
 // PAIR: two blocks on the SMs of one TPC work as one (cta_group::2): an MMA of 256 token rows x BN
@@ -532,6 +541,61 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
           asm volatile("bar.sync %0, 128;" ::"r"(2 + half) : "memory");
           if (issuer) tma_reduce_add_2d(&map_out, buf, col_tile * BN + c0, row_tile * kTileRows);
         }
+      } else if (EPI == 4 && !p.swapped) {
+        // q|k|v with rotary encoding and cache write: this thread's token, every second head of the
+        // tile's columns (the two warps of a lane quarter take turns; tiles start on head
+        // boundaries), 32 pairs (x[j], x[j + d/2]) at a time.  The accumulator is rounded to bfloat16 first and rotated
+        // from there, as the separate kernel does with the stored projection: the same bits.
+        const int hd = p.rope_d, hh2 = hd / 2;
+        int slot = row < p.rows ? __ldcg(p.rope_slots + row) : -1;
+        if (slot >= p.rope_num_slots) slot = -1;                                   // never write outside the pool
+        const int page = slot >= 0 ? slot / p.rope_page : 0, off = slot >= 0 ? slot % p.rope_page : 0;
+        const size_t plane = (size_t)p.rope_nkv * p.rope_page * hd;              // one of k / v inside a page
+        __nv_bfloat16* kdst = p.rope_cache + ((size_t)page * 2) * plane + (size_t)off * hd;
+        const float2* cs_row = p.rope_table + (size_t)(row < p.rows ? row : 0) * hh2;
+#pragma unroll 1
+        for (int h0 = half * hd; h0 + hd <= BN; h0 += 2 * hd) {
+          const int col = col_tile * BN + h0;                                      // first column of the head
+          const int gh = col / hd;                                                 // head number among q, k, v heads
+          const bool live = col < p.cols;
+          const int kind = gh < p.rope_nq ? 0 : (gh < p.rope_nq + p.rope_nkv ? 1 : 2);
+#pragma unroll 1
+          for (int c = 0; c < hh2; c += 32) {
+            uint32_t a[32], b[32];
+            tmem_load_32_nowait(acc + h0 + c, a);
+            tmem_load_32_nowait(acc + h0 + c + hh2, b);
+            tmem_wait_ld();
+            uint32_t pa[16], pb[16];
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              float x1a = __bfloat162float(__float2bfloat16_rn(__uint_as_float(a[j]) * row_scale));
+              float x1b = __bfloat162float(__float2bfloat16_rn(__uint_as_float(a[j + 1]) * row_scale));
+              float x2a = __bfloat162float(__float2bfloat16_rn(__uint_as_float(b[j]) * row_scale));
+              float x2b = __bfloat162float(__float2bfloat16_rn(__uint_as_float(b[j + 1]) * row_scale));
+              float o1a = x1a, o1b = x1b, o2a = x2a, o2b = x2b;
+              if (kind != 2 && live) {
+                const float4 cs = __ldg(reinterpret_cast<const float4*>(cs_row + c + j));   // (cos, sin) of two neighbouring frequencies
+                rope_rotate(x1a, x2a, cs.x, cs.y, o1a, o2a);
+                rope_rotate(x1b, x2b, cs.z, cs.w, o1b, o2b);
+              }
+              __nv_bfloat162 t1 = __floats2bfloat162_rn(o1a, o1b), t2 = __floats2bfloat162_rn(o2a, o2b);
+              pa[j >> 1] = *reinterpret_cast<uint32_t*>(&t1);
+              pb[j >> 1] = *reinterpret_cast<uint32_t*>(&t2);
+            }
+            __nv_bfloat16* dst = nullptr;
+            if (live && row < p.rows) {
+              if (kind == 0) dst = (__nv_bfloat16*)p.out + (size_t)row * p.ld_out + col + c;
+              else if (slot >= 0) dst = kdst + (kind == 2 ? plane : 0) + (size_t)(gh - p.rope_nq - (kind == 2 ? p.rope_nkv : 0)) * p.rope_page * hd + c;
+            }
+            if (dst) {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                *reinterpret_cast<uint4*>(dst + 8 * q4) = make_uint4(pa[4 * q4], pa[4 * q4 + 1], pa[4 * q4 + 2], pa[4 * q4 + 3]);
+                *reinterpret_cast<uint4*>(dst + hh2 + 8 * q4) = make_uint4(pb[4 * q4], pb[4 * q4 + 1], pb[4 * q4 + 2], pb[4 * q4 + 3]);
+              }
+            }
+          }
+        }
       } else if (!p.swapped) {
 #pragma unroll 1
         for (int c0 = half * kHalfCols; c0 < (half + 1) * kHalfCols && c0 < BN; c0 += 32) {
@@ -723,6 +787,9 @@ static int launch_epi(int epi, const CUtensorMap& mr, const CUtensorMap& mc, con
     case 1: return launch_tc<BN, 1, PAIR>(mr, mc, mo, p, grid, s);
     case 2: return launch_tc<BN, 2, PAIR>(mr, mc, mo, p, grid, s);
     case 3: return launch_tc<BN, 3, PAIR>(mr, mc, mo, p, grid, s);
+    case 4:
+      if constexpr (BN >= 128) return launch_tc<BN, 4, PAIR>(mr, mc, mo, p, grid, s);
+      else break;
   }
   return fail("gemm_tc: unknown epilogue %d", epi);
 }

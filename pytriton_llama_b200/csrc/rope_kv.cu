@@ -117,6 +117,20 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   }
 }
 
+// (cos, sin) of angle float(position) * inv_freq[j] for every token and frequency, for kernels that
+// rotate without working the angles out themselves: table [tokens, half].
+__global__ void rope_table_kernel(float2* __restrict__ table, const int* __restrict__ positions,
+                                  const float* __restrict__ inv_freq, int tokens, int half) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= tokens * half) return;
+  const float pos = (float)positions[i / half];
+  float s, c;
+  sincosf(pos * inv_freq[i % half], &s, &c);
+  table[i] = make_float2(c, s);
+}
+
 template <typename T>
 int rope_kv_write(void* qkv, const int* positions, const float* inv_freq, const int* slots, void* cache,
                   int tokens, int nq, int nkv, int d, int rot, int page_size, long long num_slots,
@@ -136,6 +150,14 @@ int rope_kv_write(void* qkv, const int* positions, const float* inv_freq, const 
 }
 
 }  // namespace ptl
+
+PTL_EXPORT int ptl_rope_table(void* table, const int* positions, const float* inv_freq, int tokens, int half, void* stream) {
+  PTL_REQUIRE(tokens >= 0 && half > 0 && table && positions && inv_freq, "rope_table: bad arguments");
+  if (tokens == 0) return 0;
+  const int n = tokens * half;
+  return ptl::launch_kernel("rope_table", ptl::rope_table_kernel, dim3((n + 255) / 256), dim3(256), 0, ptl::as_stream(stream),
+                            (float2*)table, positions, inv_freq, tokens, half);
+}
 
 PTL_EXPORT int ptl_rope_kv_write_f32(void* qkv, const int* positions, const float* inv_freq, const int* slots, void* cache, int tokens, int nq, int nkv, int d, int rot, int page_size, long long num_slots, void* stream) {
   return ptl::rope_kv_write<float>(qkv, positions, inv_freq, slots, cache, tokens, nq, nkv, d, rot, page_size, num_slots, stream);

@@ -77,6 +77,9 @@ class DecoderModel:
         """token_ids int32 [T]; ``cache_views(entry, write)`` gives the LayerCacheView of a run;
         returns float32 logits [len(logit_rows), vocab] (None when no row is wanted)."""
         ops = self.rt.ops
+        begin = getattr(ops, "begin_forward", None)
+        if begin is not None:
+            begin()             # (what an operator set keeps per step, such as rotary angles, starts afresh)
         x = ops.embed(token_ids, self.embedding)
         residual = None
         run = self.spec.run_order

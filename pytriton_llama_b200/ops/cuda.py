@@ -94,6 +94,11 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_gemm_tc_bf16_norm.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int,
                                           _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _c_int, _c_int, _c_f, _ptr]
     lib.ptl_gemm_tc_bf16_norm.restype = _c_int
+    lib.ptl_gemm_tc_bf16_qkv_rope.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int,
+                                              _c_int, _c_int, _c_ll, _ptr]
+    lib.ptl_gemm_tc_bf16_qkv_rope.restype = _c_int
+    lib.ptl_rope_table.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _ptr]
+    lib.ptl_rope_table.restype = _c_int
     lib.ptl_gemm_tc_k_parts.argtypes = [_c_int, _c_int, _c_int]
     lib.ptl_gemm_tc_k_parts.restype = _c_int
     lib.ptl_add_partials.argtypes = [_ptr, _ptr, _c_int, _c_ll, _c_ll, _ptr]
@@ -492,6 +497,56 @@ class CudaOps:
         self._attention_tensor_cores(out, qkv, cache, block_table, tok_req, positions, nq, nkv, d, page_size, scale,
                                      window, hints, rope=(inv_freq, slots if write else None))
         return out
+
+    def begin_forward(self) -> None:
+        """Called by the model at the start of every forward pass: what was worked out for the last
+        step's positions (the table of rotary angles) is forgotten."""
+        self._rope_memo = None
+
+    def _rope_table(self, positions: torch.Tensor, inv_freq: torch.Tensor, half: int) -> torch.Tensor:
+        """(cos, sin) [tokens, half] of this step's angles, worked out once per forward pass and used by every layer."""
+        key = (positions.data_ptr(), inv_freq.data_ptr(), positions.shape[0], half)
+        memo = getattr(self, "_rope_memo", None)
+        if memo is not None and memo[0] == key:
+            return memo[1]
+        table = self.empty((positions.shape[0], half, 2), torch.float32)
+        self._check(self.lib.ptl_rope_table(_p(table), _p(positions), _p(inv_freq), positions.shape[0], half, self._stream()))
+        self._rope_memo = (key, table)
+        return table
+
+    def projected_rope_attention(self, x, w_qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                                 rot: int, slots: Optional[torch.Tensor], cache: torch.Tensor, block_table: torch.Tensor,
+                                 tok_req: torch.Tensor, nq: int, nkv: int, d: int, page_size: int, scale: float,
+                                 window: int = 0, splits: int = 1, hints=None, write: bool = True) -> torch.Tensor:
+        """The q|k|v projection, ``rope_kv_write`` and ``paged_attention`` of a mixer.  A bfloat16
+        step of more than 64 tokens rotates q and k and writes k and v to the cache in the
+        projection's epilogue (head sizes 64 and 128, the whole head rotated); everything else
+        projects first and goes on with ``rope_attention``."""
+        fused = (os.environ.get("PTL_FUSED_QKV_ROPE", "1") != "0" and isinstance(x, torch.Tensor) and x.dtype == torch.bfloat16
+                 and x.shape[0] > 64 and write and slots is not None and inv_freq is not None and rot == d and d in (64, 128)
+                 and w_qkv.shape[0] == (nq + 2 * nkv) * d and cache.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+                 and x.shape[1] >= 64)
+        if fused:
+            self._want(x, "x", torch.bfloat16)
+            self._want(w_qkv, "w_qkv", torch.bfloat16)
+            self._want(cache, "cache", torch.bfloat16)
+            self._want(slots, "slots", torch.int32)
+            self._want(positions, "positions", torch.int32)
+            self._want(inv_freq, "inv_freq", torch.float32)
+            M, K = x.shape
+            N = w_qkv.shape[0]
+            table = self._rope_table(positions, inv_freq, d // 2)
+            qkv = self.empty((M, N), torch.bfloat16)          # only the q columns are written (and read)
+            rc = self.lib.ptl_gemm_tc_bf16_qkv_rope(_p(qkv), _p(x), _p(w_qkv), M, N, K, _p(self._tc_status_word()), _p(table),
+                                                    _p(slots), _p(cache), nq, nkv, d, page_size,
+                                                    cache.shape[0] * page_size, self._stream())
+            if rc != -2:
+                self._check(rc)
+                return self.paged_attention(qkv, cache, block_table, tok_req, positions, nq, nkv, d, page_size, scale,
+                                            window=window, splits=splits, hints=hints)
+        qkv = self.linear(x, w_qkv)
+        return self.rope_attention(qkv, positions, inv_freq, rot, slots, cache, block_table, tok_req, nq, nkv, d, page_size,
+                                   scale, window=window, splits=splits, hints=hints, write=write)
 
     DECODE_BLOCKS = int(os.environ.get("PTL_DECODE_BLOCKS", "592"))    # blocks the decode attention aims for: the four per SM that fit at once
 

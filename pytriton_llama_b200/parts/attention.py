@@ -68,17 +68,23 @@ class GQAttention(Part):
 
     def forward(self, x, ctx, cache, residual=None, next_norm=None):
         ops = self.rt.ops
-        qkv = ops.linear(x, self.w_qkv)
         inv_freq, rot = self.position.rotary_table()
         if inv_freq is None and rot != 0:
             raise NotImplementedError("a position encoding without a rotary table must rotate q and k itself")
         g = cache.group
-        both = getattr(ops, "rope_attention", None)      # an operator set may run the two steps as one
-        if both is not None:
+        whole = getattr(ops, "projected_rope_attention", None)      # an operator set may run projection, rotation and attention as one
+        both = getattr(ops, "rope_attention", None)                 # ... or rotation and attention
+        if whole is not None:
+            o = whole(x, self.w_qkv, ctx.positions, inv_freq, rot, g.slots, cache.kv, g.block_table, ctx.tok_req, self.heads,
+                      self.kv_heads, self.head_dim, g.page_size, self.scale, window=self.window,
+                      splits=ctx.attn_splits, hints=ctx, write=cache.write)
+        elif both is not None:
+            qkv = ops.linear(x, self.w_qkv)
             o = both(qkv, ctx.positions, inv_freq, rot, g.slots, cache.kv, g.block_table, ctx.tok_req, self.heads,
                      self.kv_heads, self.head_dim, g.page_size, self.scale, window=self.window,
                      splits=ctx.attn_splits, hints=ctx, write=cache.write)
         else:
+            qkv = ops.linear(x, self.w_qkv)
             ops.rope_kv_write(qkv, ctx.positions, inv_freq, rot, g.slots if cache.write else None,
                               cache.kv if cache.write else None, self.heads, self.kv_heads, self.head_dim,
                               g.page_size)

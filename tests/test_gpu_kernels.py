@@ -155,6 +155,41 @@ def test_tensor_core_product_in_parts_of_the_K_range(ops, M, N, K, parts):
     assert 1 <= ops.lib.ptl_gemm_tc_k_parts(300, 2048, 8192) <= 8 and ops.lib.ptl_gemm_tc_k_parts(4096, 8192, 2048) == 1
 
 
+@pytest.mark.parametrize("M, K, nq, nkv, d, page", [(300, 512, 8, 2, 64, 16), (1100, 256, 6, 2, 128, 16), (130, 192, 5, 1, 64, 8),
+                                                    (2048, 128, 32, 8, 64, 16), (700, 320, 24, 8, 128, 32)])
+def test_projection_with_rotary_encoding_and_cache_write_in_its_epilogue(ops, M, K, nq, nkv, d, page):
+    """The q|k|v projection of many tokens that rotates q and k and writes k and v to the cache
+    itself, against the projection followed by ``rope_kv_write``: the same bits in the q columns
+    and in every page of the cache (some tokens have no slot and must leave no trace)."""
+    N = (nq + 2 * nkv) * d
+    x, w = rnd((M, K), torch.bfloat16, 41), rnd((N, K), torch.bfloat16, 42, 0.3)
+    g = torch.Generator().manual_seed(43)
+    pages = -(-M // page) + 3
+    slots = torch.randperm(pages * page, generator=g)[:M].int()
+    slots[::7] = -1
+    positions = torch.randint(0, 100000, (M,), generator=g).int()
+    inv_freq = (10000.0 ** (-torch.arange(0, d, 2).float() / d))
+    blank = rnd((pages, 2, nkv, page, d), torch.bfloat16, 44)
+    # apart
+    qkv = ops.gemm_tc(x.cuda(), w.cuda(), ops.EPI_BF16)
+    cache_a = blank.clone().cuda()
+    ops.rope_kv_write(qkv, positions.cuda(), inv_freq.cuda(), d, slots.cuda(), cache_a, nq, nkv, d, page)
+    # as one
+    cache_b = blank.clone().cuda()
+    ops.begin_forward()
+    table = ops._rope_table(positions.cuda(), inv_freq.cuda(), d // 2)
+    out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    xc, wc, sc = x.cuda(), w.cuda(), slots.cuda()
+    rc = ops.lib.ptl_gemm_tc_bf16_qkv_rope(out.data_ptr(), xc.data_ptr(), wc.data_ptr(), M, N, K,
+                                           ops._tc_status_word().data_ptr(), table.data_ptr(), sc.data_ptr(),
+                                           cache_b.data_ptr(), nq, nkv, d, page, pages * page, ops._stream())
+    assert rc == 0, ops.lib.ptl_last_error()
+    torch.cuda.synchronize()
+    assert torch.equal(out[:, :nq * d], qkv[:, :nq * d])
+    assert torch.equal(cache_b, cache_a)
+    assert bool((out[:, nq * d:] == 7.0).all())          # the k and v columns of the output are left alone
+
+
 def test_tensor_core_product_leaves_other_sizes_to_the_library(ops):
     x, w = rnd((4, 100), torch.bfloat16, 1), rnd((32, 100), torch.bfloat16, 2)    # K no multiple of 8
     assert ops.gemm_tc(x.cuda(), w.cuda()) is None
