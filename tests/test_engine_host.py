@@ -121,3 +121,36 @@ def test_partial_rotary_factor_rotates_the_leading_part_of_every_head(tmp_path):
     got = traces.replay(eng, traces.portions(seqs))
     for r in seqs:
         assert (got[r].double() - ref[r]).abs().max() < FP32_TOL, r
+
+
+def test_padded_shapes_of_captured_steps(model_folders):
+    """The shape a step with prompt portions is padded to before it is captured in a graph: few
+    values per dimension, always room for what the step holds, a spare token row whenever single-token
+    items are padded, nothing for steps that are too large or want too many rows, and a shape only
+    from its second appearance on."""
+    from pytriton_llama_b200.engine.engine import _HostBatch
+    eng = _engine(model_folders("A"), "A", 16)
+
+    def batch(q_lens, wants):
+        entries = [StepEntry(f"r{i}", [0] * n, []) for i, n in enumerate(q_lens)]
+        return _HostBatch(entries, q_lens, [0] * len(q_lens), [1] * len(q_lens), list(range(len(q_lens))), {}, list(range(wants)))
+
+    def shape_of(q_lens, wants=1):
+        eng._shape_seen.clear()
+        assert eng._shape_bucket(batch(q_lens, wants)) == 0          # the first time a shape is only counted
+        return eng._shape_bucket(batch(q_lens, wants))
+
+    assert shape_of([300]) == (384, 1, 0, 2, 1)                       # 300 tokens -> 384, one pair of tiles per 256 rows
+    assert shape_of([30]) == (64, 1, 0, 1, 1)
+    assert shape_of([30], wants=0) == (64, 1, 0, 1, 0)
+    assert shape_of([1000, 1, 1, 1], wants=4) == (1024, 4, 4, 4, 1)   # 1,003 tokens: 21 spare rows for the fourth, padded item
+    t_pad, r_pad, d_pad, pairs, _ = shape_of([61, 1, 1, 1], wants=4)  # 64 tokens fill 64 rows: the padded item needs one more
+    assert (t_pad, r_pad, d_pad, pairs) == (128, 4, 4, 1)
+    assert shape_of([62, 1, 1], wants=3) == (64, 4, 2, 1, 1)          # no item is padded: no spare row needed
+    assert shape_of([1025]) == 0 and shape_of([500, 600]) == 0        # more than 1,024 tokens
+    assert shape_of([40], wants=2) == 0                               # more wanted rows than padded requests
+    for q_lens in ([5, 1, 300, 1, 1], [2, 2], [257], [256, 1]):
+        b = batch(q_lens, len(q_lens))
+        t_pad, r_pad, d_pad, pairs, _ = shape_of(q_lens, len(q_lens))
+        assert t_pad >= b.T and r_pad >= b.R and d_pad >= len(b.dec_items) and 2 * pairs >= len(b.pf_tiles) // 4
+        assert d_pad == len(b.dec_items) or t_pad > b.T
