@@ -249,10 +249,11 @@ __device__ __forceinline__ void load_ways(uint32_t taddr, int stages, float (&v)
   }
 }
 
-// (Few tokens: two blocks per SM must fit the register file, 102 registers a thread.  The compiler
-// kept to that by itself until the many-token paths grew; now it is told.)
+// (Few tokens: two blocks per SM must fit the register file, 102 registers a thread, and three of
+// the 16- and 32-token instances without the add epilogue, 68: measured, 1 % of a decode step.  The
+// compiler kept to that by itself until the many-token paths grew; now it is told.)
 template <int BN, int EPI, bool PAIR = false>
-__global__ void __launch_bounds__(kGemmThreads, BN < 128 ? 2 : 1)
+__global__ void __launch_bounds__(kGemmThreads, BN < 128 ? ((EPI == 2 || BN == 64) ? 2 : 3) : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col,
                const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
   using Cfg = TcCfg<BN, PAIR>;
