@@ -505,7 +505,7 @@ class CudaOps:
 
     def _rope_table(self, positions: torch.Tensor, inv_freq: torch.Tensor, half: int) -> torch.Tensor:
         """(cos, sin) [tokens, half] of this step's angles, worked out once per forward pass and used by every layer."""
-        key = (positions.data_ptr(), inv_freq.data_ptr(), positions.shape[0], half)
+        key = (positions.data_ptr(), positions._version, inv_freq.data_ptr(), positions.shape[0], half)
         memo = getattr(self, "_rope_memo", None)
         if memo is not None and memo[0] == key:
             return memo[1]
