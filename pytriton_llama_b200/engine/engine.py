@@ -336,12 +336,12 @@ class Engine:
             return 1
         return int(min(32, max(1, max_ctx // 256)))
 
-    # ------------------------------------------------------------------ decode steps from CUDA graphs
-    def _graph_bucket(self, batch: "_HostBatch") -> int:
-        """The padded batch size whose captured graph can run this step, or 0.  Only steps of
-        single tokens qualify, and only models whose mixers keep nothing but paged keys and values
-        (lite_llama captures its decode step for batch sizes 1, 2, 4, 8, 16, ...:
-        lite_llama/executor/cuda_graph.py:6-7,113-132)."""
+    # ------------------------------------------------------------------ steps from CUDA graphs
+    def _graph_bucket(self, batch: "_HostBatch"):
+        """What names the captured graph that can run this step, or 0: the padded batch size for a
+        step of single tokens (lite_llama captures its decode step for batch sizes 1, 2, 4, 8, 16,
+        ...: lite_llama/executor/cuda_graph.py:6-7,113-132), a padded shape (a tuple) for a step that
+        holds prompt portions.  Only for models whose mixers keep nothing but paged keys and values."""
         if not self.config.compiled_model or self.device.type != "cuda":
             return 0
         if any(not grp.paged or grp.state for grp in self.cache.groups):
