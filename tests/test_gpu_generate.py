@@ -273,3 +273,38 @@ def test_one_layer_of_real_widths_in_bfloat16(tmp_path, hidden, heads, kv_heads,
         eng.finish("r")
     eng.check_device_status()
     assert any(isinstance(k, tuple) for k in eng._graphs)
+
+
+def test_requests_that_arrive_while_others_decode(model_folders):
+    """New prompts join while earlier requests generate, so most steps hold portions beside single
+    tokens, in shapes that repeat: stepping one at a time without graphs and overlapped steps from
+    captured graphs (single-token batches and mixed shapes) give the same tokens."""
+    from pytriton_llama_b200.sampling import SamplingParams
+    name, dtype = "B", "float32"
+    folder = model_folders(name, stored_dtype(dtype))
+    vocab = TINY[name]["vocab_size"]
+    prompts = [random_tokens(n, vocab, 900 + i) for i, n in enumerate((23, 40, 9, 31, 18, 44, 12, 27, 35, 5))]
+    sp = SamplingParams(temperature=0.0, max_gen_len=20, stop_token_ids=[])
+    runs = []
+    for overlap, graphs in ((False, False), (True, True)):
+        llm = _llm(folder, name, dtype, pages=120, overlap_steps=overlap, compiled_model=graphs, max_num_seqs=8,
+                   max_batched_tokens=24)
+        reqs = [llm.add_request(p, sp) for p in prompts[:2]]
+        waiting = list(prompts[2:])
+        steps = 0
+        while True:
+            for _ in llm.run():
+                steps += 1
+                if waiting and steps % 3 == 0:
+                    reqs.append(llm.add_request(waiting.pop(0), sp))
+            if not waiting:
+                break
+            reqs.append(llm.add_request(waiting.pop(0), sp))
+        llm.engine.check_device_status()
+        llm.engine.cache.check_invariants()
+        assert llm.engine.cache.free_pages() == 120
+        if graphs:
+            assert sum(isinstance(k, tuple) for k in llm.engine._graphs) >= 2
+        runs.append({tuple(r.prompt): list(r.output) for r in reqs})
+    assert runs[0] == runs[1]
+    assert len(runs[0]) == len(prompts) and all(1 <= len(o) <= 20 for o in runs[0].values())
