@@ -48,7 +48,20 @@ class RotaryPosition(Part):
         self.rot = int(p.get("rotary_dim") or self.head_dim)
         if self.rot % 2 or self.rot > self.head_dim:
             raise ValueError(f"rotary width {self.rot} must be even and at most the head size {self.head_dim}")
-        self.inv_freq = rope_inverse_frequencies(self.head_dim, float(p["theta"]), p.get("scaling"), self.rot).to(runtime.device)
+        # layers with the same parameters share one table on the device: an operator set that works
+        # out a step's angles once for all layers tells tables apart by their address
+        scaling = p.get("scaling")
+        key = ("rope", self.head_dim, self.rot, float(p["theta"]), tuple(sorted(scaling.items())) if scaling else None)
+        shared = getattr(runtime, "_shared_tables", None)
+        if shared is None:
+            shared = {}
+            try:
+                setattr(runtime, "_shared_tables", shared)
+            except AttributeError:          # (a runtime that takes no new attributes: every part keeps its own table)
+                pass
+        if key not in shared:
+            shared[key] = rope_inverse_frequencies(self.head_dim, float(p["theta"]), scaling, self.rot).to(runtime.device)
+        self.inv_freq = shared[key]
 
     def rotary_table(self) -> Optional[Tuple[torch.Tensor, int]]:
         return self.inv_freq, self.rot
