@@ -154,3 +154,19 @@ def test_padded_shapes_of_captured_steps(model_folders):
         t_pad, r_pad, d_pad, pairs, _ = shape_of(q_lens, len(q_lens))
         assert t_pad >= b.T and r_pad >= b.R and d_pad >= len(b.dec_items) and 2 * pairs >= len(b.pf_tiles) // 4
         assert d_pad == len(b.dec_items) or t_pad > b.T
+
+
+def test_rope_parts_with_equal_parameters_share_their_table():
+    """An operator set tells frequency tables apart by address when it works a step's angles out
+    once for all layers; layers with the same parameters must therefore hold the same tensor."""
+    from pytriton_llama_b200.parts.base import PartSpec, Runtime, build_part
+    rt = Runtime(torch.device("cpu"), torch.float32, None)
+    scaling = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+               "original_max_position_embeddings": 64}
+    a = build_part("position", PartSpec("rope", {"head_dim": 64, "theta": 1e4, "scaling": dict(scaling)}), rt)
+    b = build_part("position", PartSpec("rope", {"head_dim": 64, "theta": 1e4, "scaling": dict(scaling)}), rt)
+    c = build_part("position", PartSpec("rope", {"head_dim": 64, "theta": 5e5, "scaling": dict(scaling)}), rt)
+    d = build_part("position", PartSpec("rope", {"head_dim": 64, "theta": 1e4, "scaling": None}), rt)
+    assert a.inv_freq is b.inv_freq
+    assert a.inv_freq is not c.inv_freq and a.inv_freq is not d.inv_freq
+    assert not torch.equal(a.inv_freq, d.inv_freq)
