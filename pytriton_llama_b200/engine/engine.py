@@ -154,6 +154,7 @@ class Engine:
         self.steps_run = 0
         self._graphs = {}          # captured steps: padded batch size (single tokens only) or a _StepShape
         self._shape_seen: Dict[tuple, int] = {}
+        self._shape_captures = 0
         self._graph_pool = None    # one memory pool for the captured steps of mixed shapes
 
     # ------------------------------------------------------------------ sizing
@@ -355,6 +356,7 @@ class Engine:
 
     GRAPH_MAX_TOKENS = 1024      # larger steps keep the GPU busy for longer than the host needs to launch them
     GRAPH_MAX_SHAPES = 24
+    GRAPH_MAX_CAPTURES = 96      # a workload that keeps cycling through more shapes than are kept stops capturing new ones
 
     def _shape_bucket(self, batch: "_HostBatch"):
         """Steps with prompt portions of up to 1,024 tokens are bound by the host's launches (about
@@ -378,6 +380,8 @@ class Engine:
         shape = (t_pad, r_pad, d_pad, pow2(n_pairs), 1 if M else 0)
         if shape in self._graphs:
             return shape
+        if self._shape_captures >= self.GRAPH_MAX_CAPTURES:
+            return 0                                        # capturing costs tens of milliseconds: not again and again
         seen = self._shape_seen.get(shape, 0) + 1
         self._shape_seen[shape] = seen
         if len(self._shape_seen) > 4096:
@@ -391,6 +395,7 @@ class Engine:
                 shapes = [k for k in self._graphs if isinstance(k, tuple)]
                 if len(shapes) >= self.GRAPH_MAX_SHAPES:    # drop the shape that was used longest ago
                     del self._graphs[min(shapes, key=lambda k: self._graphs[k].last_used)]
+                self._shape_captures += 1
             g = self._graphs[bucket] = self._capture(bucket)
         g.last_used = self.steps_run
         # The copy below is asynchronous: a staging buffer may be rewritten only after the copy that

@@ -149,6 +149,9 @@ def test_padded_shapes_of_captured_steps(model_folders):
     assert shape_of([62, 1, 1], wants=3) == (64, 4, 2, 1, 1)          # no item is padded: no spare row needed
     assert shape_of([1025]) == 0 and shape_of([500, 600]) == 0        # more than 1,024 tokens
     assert shape_of([40], wants=2) == 0                               # more wanted rows than padded requests
+    eng._shape_captures = eng.GRAPH_MAX_CAPTURES                       # a workload that has captured again and again: no new shapes
+    assert shape_of([300]) == 0
+    eng._shape_captures = 0
     for q_lens in ([5, 1, 300, 1, 1], [2, 2], [257], [256, 1]):
         b = batch(q_lens, len(q_lens))
         t_pad, r_pad, d_pad, pairs, _ = shape_of(q_lens, len(q_lens))
