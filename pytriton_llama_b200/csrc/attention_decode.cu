@@ -362,6 +362,16 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     return;
   }
 
+  if (r < 0 && splits > 1) {
+    // A padding row has no keys.  Its blocks take no ticket below: a captured step may name the
+    // same padding row in several items, and more than `splits` blocks on one counter would
+    // leave it non-zero for the next call.  The row reads as zeros.
+    if (split == 0)
+      for (int e = tid; e < G * D; e += kDecWarps * 32)
+        out[(size_t)t * out_stride + (size_t)kvh * G * D + e] = __float2bfloat16_rn(0.f);
+    return;
+  }
+
   // ---- merge the four warps through shared memory
   float* mo = reinterpret_cast<float*>(smem);                  // [warps][16][D]
   float* mml = mo + kDecWarps * 16 * D;                        // [warps][16][2]
@@ -515,12 +525,8 @@ int launch_decode(void* out, float* part_acc, float* part_ml, const void* q, con
                   int window, int splits, int num_pages, int* counters, void* stream, int fused,
                   const float* inv_freq, const int* slots) {
   using Cfg = DecodeCfg<D, KP>;
-  static bool raised = false;
-  if (!raised) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D, KP>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
-    PTL_REQUIRE(e == cudaSuccess, "decode_attention: cannot raise shared memory: %s", cudaGetErrorString(e));
-    raised = true;
-  }
+  static SmemRaised raised = {};                         // level 1: the ring; 2: the ring and the rows a cluster exchanges
+  if (int rc = raise_shared_memory("decode_attention", decode_attention_kernel<D, KP>, Cfg::kSmem, raised, 1)) return rc;
   int page_shift = -1;                                   // log2(page_size) when it is a power of two
   for (int b = 0; b < 20; ++b) if ((1 << b) == page_size) page_shift = b;
   const long long blocks = (long long)n_items * nkv * splits;
@@ -529,13 +535,8 @@ int launch_decode(void* out, float* part_acc, float* part_ml, const void* q, con
   const int G = nq / nkv;
   const size_t recv_bytes = (size_t)splits * kDecWarps * ((G + splits - 1) / splits) * (D + 2) * sizeof(float);
   const bool cluster = KP == 2 && splits >= 2 && splits <= 8 && recv_bytes <= 16 * 1024;
-  static bool raised_cluster = false;
-  if (cluster && !raised_cluster) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D, KP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::kSmem + 16 * 1024);
-    PTL_REQUIRE(e == cudaSuccess, "decode_attention: cannot raise shared memory: %s", cudaGetErrorString(e));
-    raised_cluster = true;
-  }
+  if (cluster)
+    if (int rc = raise_shared_memory("decode_attention", decode_attention_kernel<D, KP>, Cfg::kSmem + 16 * 1024, raised, 2)) return rc;
   int rc = launch_kernel_cluster("decode_attention", decode_attention_kernel<D, KP>, dim3((unsigned)blocks), dim3(kDecWarps * 32),
                                  Cfg::kSmem + (cluster ? recv_bytes : 0), as_stream(stream), cluster ? splits : 1,
                                  (__nv_bfloat16*)out, part_acc, part_ml, (const __nv_bfloat16*)q,

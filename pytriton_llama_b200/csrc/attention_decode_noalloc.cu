@@ -43,6 +43,15 @@ int scratch_for_current_device(float** ptr) {
 
 PTL_EXPORT unsigned long long ptl_noalloc_scratch_bytes(void) { return PTL_NOALLOC_SCRATCH_BYTES; }
 
+PTL_EXPORT int ptl_noalloc_scratch_address(void** address) {
+  PTL_REQUIRE(address != nullptr, "noalloc_scratch_address: nowhere to put the address");
+  float* base = nullptr;
+  int rc = scratch_for_current_device(&base);
+  if (rc) return rc;
+  *address = base;
+  return 0;
+}
+
 PTL_EXPORT int ptl_decode_attention_bf16_noalloc(void* out, const void* q, const void* cache, const int* block_table,
                                                  const int* items, const int* tok_req, const int* positions,
                                                  int n_items, int q_stride, int out_stride, int bt_stride, int nq,

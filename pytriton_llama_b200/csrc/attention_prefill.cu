@@ -259,12 +259,8 @@ int launch_prefill(void* out, const void* q, const void* cache, const int* block
                    int q_stride, int out_stride, int bt_stride, int nq, int nkv, int page_size, float scale,
                    int window, int num_pages, void* stream) {
   using Cfg = PrefillCfg<D, MT>;
-  static bool raised = false;
-  if (!raised) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<D, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
-    PTL_REQUIRE(e == cudaSuccess, "prefill_attention: cannot raise shared memory: %s", cudaGetErrorString(e));
-    raised = true;
-  }
+  static SmemRaised raised = {};
+  if (int rc = raise_shared_memory("prefill_attention", prefill_attention_kernel<D, MT>, Cfg::kSmem, raised)) return rc;
   PTL_REQUIRE(nq <= 65535, "prefill_attention: at most 65535 query heads");
   int page_shift = -1;
   for (int b = 0; b < 20; ++b) if ((1 << b) == page_size) page_shift = b;

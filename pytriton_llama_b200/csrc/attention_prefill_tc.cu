@@ -413,12 +413,8 @@ template <int D>
 static int launch_prefill_tc(const void* q, const void* cache, int n_tiles, int n_tokens, int q_stride, int nq, int nkv,
                              int page_size, int num_pages, const PrefillTcParams& p, cudaStream_t stream) {
   using Cfg = PfCfg<D>;
-  static bool raised = false;
-  if (!raised) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
-    PTL_REQUIRE(e == cudaSuccess, "prefill_attention_tc: cannot raise shared memory: %s", cudaGetErrorString(e));
-    raised = true;
-  }
+  static SmemRaised raised = {};
+  if (int rc = raise_shared_memory("prefill_attention_tc", prefill_attention_tc_kernel<D>, Cfg::kSmem, raised)) return rc;
   CUtensorMap mq, mkv;
   int rc = make_map(&mq, q, n_tokens, q_stride, kTcRows);                 // whole step: [tokens, q_stride], boxes of 64 x 128
   if (rc) return rc;

@@ -193,6 +193,23 @@ inline int launch_kernel(const char* what, void (*kernel)(Params...), dim3 grid,
   return launch_kernel_cluster(what, kernel, grid, block, smem, stream, 1, static_cast<Args&&>(args)...);
 }
 
+// The dynamic shared-memory limit of a kernel is a property of (kernel, device).  A launcher keeps
+// one `SmemRaised` per kernel instance (static, zero-initialised) and calls this before launching:
+// the limit is raised on the current device the first time `level` is asked for there.
+constexpr int kMaxDevices = 64;
+struct SmemRaised { unsigned char level[kMaxDevices]; };
+template <typename Kernel>
+inline int raise_shared_memory(const char* what, Kernel kernel, int bytes, SmemRaised& table, int level = 1) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return fail("%s: no current device below %d", what, kMaxDevices);
+  if (table.level[dev] >= level) return 0;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return fail("%s: cannot raise shared memory to %d bytes: %s", what, bytes, cudaGetErrorString(e));
+  table.level[dev] = (unsigned char)level;
+  return 0;
+}
+
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -250,13 +250,9 @@ int add_rmsnorm(void* y, float* residual_out, const float* residual_in, const vo
   if (out_rows == 0) return 0;
   const size_t smem = (size_t)hidden * sizeof(float);
   PTL_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: hidden=%d does not fit the row buffer (max %d)", hidden, 200 * 1024 / 4);
-  static bool raised[2] = {false, false};
-  constexpr int slot = sizeof(T) == 4 ? 0 : 1;
-  if (smem > 48 * 1024 && !raised[slot]) {
-    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    PTL_REQUIRE(e == cudaSuccess, "add_rmsnorm: cannot raise shared memory: %s", cudaGetErrorString(e));
-    raised[slot] = true;
-  }
+  static SmemRaised raised = {};                      // one per instance of this template
+  if (smem > 48 * 1024)
+    if (int rc = raise_shared_memory("add_rmsnorm", add_rmsnorm_kernel<T>, 200 * 1024, raised)) return rc;
   const int vec_ok = hidden % 4 == 0 && aligned16(y) && aligned16(w) && (!x || aligned16(x)) &&
                      (!residual_in || aligned16(residual_in)) && (!residual_out || aligned16(residual_out));
   // many rows of a common width: a warp per row

@@ -748,12 +748,8 @@ template <int BN, int EPI, bool PAIR = false>
 static int launch_tc(const CUtensorMap& mr, const CUtensorMap& mc, const CUtensorMap& mo, const GemmParams& p, dim3 grid,
                      cudaStream_t stream) {
   using Cfg = TcCfg<BN, PAIR>;
-  static bool raised = false;
-  if (!raised) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
-    PTL_REQUIRE(e == cudaSuccess, "gemm_tc: cannot raise shared memory to %d: %s", Cfg::kSmem, cudaGetErrorString(e));
-    raised = true;
-  }
+  static SmemRaised raised = {};
+  if (int rc = raise_shared_memory("gemm_tc", gemm_tc_kernel<BN, EPI, PAIR>, Cfg::kSmem, raised)) return rc;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kGemmThreads);

@@ -44,6 +44,12 @@ int ptl_decode_attention_bf16_noalloc(void* out, const void* q, const void* cach
 /* Bytes of the built-in scratch array (for callers that want to check a size beforehand). */
 unsigned long long ptl_noalloc_scratch_bytes(void);
 
+/* Device address of the built-in scratch array on the current device (the same look-up the first
+   call with splits > 1 does; allocates nothing).  For diagnostics: a host can overwrite the array
+   between calls to convince itself that no call depends on what an earlier one left there.
+   Returns 0, or -1 with a message in ptl_last_error(). */
+int ptl_noalloc_scratch_address(void** address);
+
 #ifdef __cplusplus
 }
 #endif
