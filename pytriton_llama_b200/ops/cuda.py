@@ -566,12 +566,17 @@ class CudaOps:
             splits = max(1, min(target // pairs, -(-longest // 128)))
             if target == 296 and splits > 8:
                 splits = 8      # what a cluster merges through shared memory; more splits would go through global memory (slower)
+            # The split count of this kernel is decided here, from the number of blocks the machine
+            # holds (``attn_splits`` of the step context is the CUDA-core kernel's).  A caller may fix
+            # it (``decode_splits``) and leave the counters out (``decode_counters`` False) to pin one
+            # of the three ways of merging.
+            splits = int(getattr(hints, "decode_splits", 0) or splits)
             part_acc = part_ml = counters = None
             if splits > 1:
                 splits = min(splits, 512)
                 part_acc = self.empty((q.shape[0], nq, splits, d), torch.float32)
                 part_ml = self.empty((q.shape[0], nq, splits, 2), torch.float32)
-                if q.shape[0] * nkv <= self._DECODE_COUNTERS:
+                if q.shape[0] * nkv <= self._DECODE_COUNTERS and getattr(hints, "decode_counters", True):
                     if getattr(self, "_decode_counters", None) is None:
                         self._decode_counters = torch.zeros(self._DECODE_COUNTERS, dtype=torch.int32, device=self.device)
                     counters = self._decode_counters        # the last block of a token's splits merges them in the kernel
@@ -586,7 +591,10 @@ class CudaOps:
                     _p(out), _p(part_acc), _p(part_ml), _p(q), _p(cache), _p(block_table), items, _p(tok_req),
                     _p(positions), hints.n_decode, q.shape[1], nq * d, block_table.shape[1], nq, nkv, d, page_size,
                     float(scale), int(window), splits, num_pages, _p(counters), stream)
-            self._check(rc, kernels=2 if splits > 1 and counters is None and not (2 <= splits <= 8) else 1)
+            group = nq // nkv
+            in_cluster = (hints.n_decode * nkv * splits <= 296 and 2 <= splits <= 8
+                          and splits * 4 * -(-group // splits) * (d + 2) * 4 <= 16 * 1024)     # as launch_decode decides
+            self._check(rc, kernels=2 if splits > 1 and counters is None and not in_cluster else 1)
         if hints.n_prefill_tiles:
             if os.environ.get("PTL_PREFILL_TC", "1") != "0":
                 rc = self.lib.ptl_prefill_attention_tc_bf16(

@@ -107,4 +107,5 @@ def write_file(path: Union[str, Path], tensors: Dict[str, torch.Tensor]) -> None
         f.write(blob)
         for name in order:
             t = tensors[name].detach().cpu().contiguous()
-            f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            if t.numel():
+                f.write(memoryview(t.view(torch.uint8).reshape(-1).numpy()))      # no copy of the tensor's bytes

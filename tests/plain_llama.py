@@ -91,7 +91,7 @@ def rope_inv_freq(cfg):
 def rope_cos_sin(inv_freq, positions, dtype):
     """cos/sin tables [S, d].  RotaryEmbedding.py:200-217: angle = position * inv_freq in
     float32, the half table repeated twice along the last axis."""
-    freqs = positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, :]
+    freqs = positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32).to(positions.device)[None, :]
     emb = torch.cat((freqs, freqs), dim=-1)
     if dtype == torch.float64:  # the angle stays the float32 product; only cos/sin get more digits
         emb = emb.double()
@@ -123,7 +123,7 @@ def causal_gqa_attention(q, k, v, window=None):
     nkv = k.shape[1]
     group = nq // nkv
     scale = 1.0 / math.sqrt(d)
-    pos = torch.arange(S)
+    pos = torch.arange(S, device=q.device)
     allowed = pos[None, :] <= pos[:, None]
     if window is not None:
         allowed &= pos[None, :] > pos[:, None] - window
@@ -178,8 +178,9 @@ def decoder_layer(h, positions, cfg, w, i):
 def forward(cfg, w, tokens):
     """Logits [S, vocab] of one whole sequence.  lite_llama/models/llama.py:189-223: embedding,
     positions 0..S-1, the layers in order, final norm, LM head over every position."""
-    tokens = torch.as_tensor(tokens, dtype=torch.long)
-    positions = torch.arange(tokens.shape[0])
+    device = w["model.embed_tokens.weight"].device      # the weights may have been moved to an accelerator by the caller
+    tokens = torch.as_tensor(tokens, dtype=torch.long, device=device)
+    positions = torch.arange(tokens.shape[0], device=device)
     h = w["model.embed_tokens.weight"][tokens]
     for i in range(cfg["num_hidden_layers"]):
         h = decoder_layer(h, positions, cfg, w, i)

@@ -318,6 +318,77 @@ def test_tensor_core_attention_mixed_batch(ops, nq, nkv, d, page, window):
     close(out, simt, "bfloat16", "against the CUDA-core kernel", scale=4.0)
 
 
+@pytest.mark.parametrize("d, nq, nkv", [(64, 8, 2), (128, 6, 2)])
+@pytest.mark.parametrize("merge", ["cluster", "ticket", "second_kernel", "many_blocks_ticket", "many_blocks_second_kernel"])
+def test_decode_attention_merges_its_splits_in_every_way(ops, d, nq, nkv, merge):
+    """The split-key decode kernel combines the splits of a (token, kv head) in one of three ways:
+    through the shared memory of a thread-block cluster (2-8 splits, few blocks), by the block that
+    takes the last ticket of a counter, or by a second kernel when it is given no counters.  Each
+    is pinned here by the split count, the number of blocks and the presence of counters, on
+    tokens after 1 to 3,000 cached tokens, and compared with the plain statement."""
+    page = 16
+    base_ctx = [1, 64, 65, 700, 3000, 129, 1500, 333]
+    if merge.startswith("many_blocks"):          # more than 296 blocks: 64-key tiles, no clusters
+        ctx, splits = base_ctx * 6, 4
+    else:
+        ctx, splits = base_ctx[:5], (6 if merge == "cluster" else 12)
+    n = len(ctx)
+    pages = sum(-(-c // page) for c in ctx) + 3
+    bt = _random_paging(n, ctx, page, pages, seed=d + n)
+    cache = rnd((pages, 2, nkv, page, d), torch.bfloat16, 41)
+    q = rnd((n, nq * d), torch.bfloat16, 42, 2.0)
+    tok_req = torch.arange(n).int()
+    positions = torch.tensor([c - 1 for c in ctx]).int()
+    scale = 1 / math.sqrt(d)
+    ref = REF.paged_attention(q, cache, bt, tok_req, positions, nq, nkv, d, page, scale)
+    hints = _hints([1] * n, ctx)
+    hints.decode_splits = splits
+    hints.decode_counters = "second_kernel" not in merge
+    launches = ops.launches
+    out = ops.paged_attention(q.cuda(), cache.cuda(), bt.cuda(), tok_req.cuda(), positions.cuda(), nq, nkv, d, page, scale,
+                              hints=hints)
+    assert ops.launches - launches == (2 if "second_kernel" in merge else 1)
+    close(out, ref, "bfloat16", merge, scale=4.0)
+    if "ticket" in merge:
+        assert int(ops._decode_counters.abs().sum()) == 0         # left ready for the next call
+
+
+def test_decode_attention_padding_rows_named_several_times_leave_the_counters_clean(ops):
+    """A captured step of a padded shape names one padding row (request -1) in every item it has too
+    many.  Such rows must not take tickets of the split merge: more blocks than splits on one counter
+    would leave it non-zero, and a later step with a real token in that row would merge too early or
+    never.  20 real tokens and 12 items that all name row 20, 8 kv heads, 2 splits (the counter
+    path), called twice; then a call in which row 20 is a real token."""
+    nq, nkv, d, page = 32, 8, 64, 16
+    real = 20
+    ctx = [200 + 37 * i for i in range(real + 1)]
+    n_rows = real + 1
+    pages = sum(-(-c // page) for c in ctx) + 3
+    bt = _random_paging(n_rows, ctx, page, pages, seed=5)
+    cache = rnd((pages, 2, nkv, page, d), torch.bfloat16, 51)
+    q = rnd((n_rows, nq * d), torch.bfloat16, 52, 2.0)
+    positions = torch.tensor([c - 1 for c in ctx]).int()
+    scale = 1 / math.sqrt(d)
+    full_req = torch.arange(n_rows).int()
+    ref = REF.paged_attention(q, cache, bt, full_req, positions, nq, nkv, d, page, scale)
+    padded_req = full_req.clone()
+    padded_req[real] = -1
+    hints = _hints([1] * n_rows, ctx)
+    hints.decode_items = torch.tensor(list(range(real)) + [real] * 12, dtype=torch.int32).cuda()
+    hints.n_decode = real + 12
+    hints.decode_splits = 2
+    dev = (q.cuda(), cache.cuda(), bt.cuda())
+    for _ in range(2):
+        out = ops.paged_attention(*dev, padded_req.cuda(), positions.cuda(), nq, nkv, d, page, scale, hints=hints)
+        close(out[:real], ref[:real], "bfloat16", "real rows beside padding", scale=4.0)
+        assert float(out[real].float().abs().sum()) == 0.0
+        assert int(ops._decode_counters.abs().sum()) == 0
+    hints = _hints([1] * n_rows, ctx)
+    hints.decode_splits = 14                                     # 21 x 8 x 14 blocks: tickets again, row 20 real this time
+    out = ops.paged_attention(*dev, full_req.cuda(), positions.cuda(), nq, nkv, d, page, scale, hints=hints)
+    close(out, ref, "bfloat16", "row 20 as a real token", scale=4.0)
+
+
 @pytest.mark.parametrize("d, page, window", [(64, 16, 0), (128, 16, 0), (128, 32, 600), (64, 64, 600), (128, 8, 0)])
 def test_tensor_core_attention_over_a_long_prompt(ops, d, page, window):
     """A 1,300-token portion after 700 cached tokens: dozens of key tiles per query tile, so that the
