@@ -105,6 +105,25 @@ def model_bytes_and_flops(cfg, layers):
     return matmul_params, V * H, weight_bytes, kv_bytes_per_token
 
 
+def reference_arm(args) -> int:
+    """``--impl reference``: lite_llama's own stock generate loop on the same shape (baseline/reference_arm.py;
+    nothing of this repository's engine is imported on this path).  Prints the same JSON line with
+    ``"impl": "reference"``, or an ``unavailable`` line that quotes what stopped it."""
+    sys.path.insert(0, str(ROOT / "baseline"))
+    try:
+        import reference_arm as ref
+        points = [int(p) for p in args.points.split(",") if p]
+        out = ref.run(MODEL, CONTEXT, PREFILL_TOKENS, args.batch, args.steps, args.warmup, points, clock_sampler=ClockSampler())
+    except BaseException as e:      # whatever stops the reference is the message; this arm never fails the bench
+        if isinstance(e, KeyboardInterrupt):
+            raise
+        reason = f"{type(e).__name__}: {e}".replace("\n", " ")[:600]
+        print(json.dumps({"impl": "reference", "unavailable": reason}))
+        return 0
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -120,14 +139,11 @@ def main() -> int:
     ap.add_argument("--only-prefill", action="store_true", help="measure the prefill only and print its numbers (profiling runs)")
     args = ap.parse_args()
 
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "lite_llama has no setup.py or pyproject.toml, so pip cannot install it offline; its stock path also needs "
-                          "the accelerate package, a converted checkpoint and a tokenizer, none of which exist without network"}))
-        return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.impl == "reference":
+        return reference_arm(args)
 
     import torch
     from pytriton_llama_b200.config import EngineConfig

@@ -4,6 +4,15 @@
 // maximum, sum, accumulator, merge.  It is the float32 path's attention and the reference
 // against which faster kernels are checked.
 //
+// With float32 inputs the two sums of attention are compensated, still in 32-bit arithmetic: the
+// score q.k keeps the rounding error of every product and partial sum in a second float (a dot
+// product as if summed in twice the precision), and the accumulator of P.V and the softmax sum are
+// (high, low) pairs of floats.  Scores of size 10 make softmax weights as wrong (relatively) as the
+// score is (absolutely), and a plain 64-term sum is wrong by a few 1e-7 there: over 16 layers of a
+// 2,048-wide model these sums, not the matrix products, were what kept logits 8e-5 from a float64
+// computation.  bfloat16 inputs (this kernel as the fallback for head sizes the tensor-core
+// kernels leave) take plain sums: their inputs are a thousand times coarser than that.
+//
 // Token t (request r = tok_req[t], position p = positions[t]) sees keys lo..p of its request,
 // lo = max(0, p - window + 1) when window > 0, else 0.  Key n lives in page
 // block_table[r][n / page_size] at offset n % page_size of the layer's cache
@@ -14,6 +23,23 @@ namespace ptl {
 
 constexpr int kMaxDimPerLane = 8;   // head sizes up to 256
 constexpr int kWarpsPerBlock = 4;
+
+// (hi, lo) += a * b without losing the rounding error of the product or of the sum
+__device__ __forceinline__ void two_fma(float& hi, float& lo, float a, float b) {
+  const float h = __fmul_rn(a, b);
+  const float r = fmaf(a, b, -h);                             // the product's rounding error, exactly
+  const float t = __fadd_rn(hi, h);
+  const float z = __fsub_rn(t, hi);
+  const float e = __fadd_rn(__fsub_rn(hi, __fsub_rn(t, z)), __fsub_rn(h, z));   // the sum's rounding error, exactly
+  hi = t;
+  lo = __fadd_rn(lo, __fadd_rn(e, r));
+}
+// (hi, lo) *= c
+__device__ __forceinline__ void two_scale(float& hi, float& lo, float c) {
+  const float h = __fmul_rn(hi, c);
+  lo = fmaf(lo, c, fmaf(hi, c, -h));
+  hi = h;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
@@ -33,7 +59,8 @@ paged_attention_simt_kernel(T* __restrict__ out, float* __restrict__ part_acc, f
   const int split = blockIdx.z;
   float* qs = qs_all + warp * d;
   const T* qrow = q + (size_t)t * q_stride + (size_t)h * d;
-  for (int i = lane; i < d; i += 32) qs[i] = to_f32(qrow[i]) * scale;
+  constexpr bool kCompensated = sizeof(T) == 4;
+  for (int i = lane; i < d; i += 32) qs[i] = kCompensated ? to_f32(qrow[i]) : to_f32(qrow[i]) * scale;
   __syncwarp();
 
   const int r = tok_req[t];        // r < 0: a padding row of a fixed-size batch; it sees no key and yields zeros
@@ -49,10 +76,10 @@ paged_attention_simt_kernel(T* __restrict__ out, float* __restrict__ part_acc, f
   const int* bt = block_table + (size_t)(r < 0 ? 0 : r) * bt_stride;
   constexpr int VN = Vec16<T>::N;
 
-  float m = -INFINITY, l = 0.f;
-  float acc[kMaxDimPerLane];
+  float m = -INFINITY, l = 0.f, l_lo = 0.f;
+  float acc[kMaxDimPerLane], acc_lo[kMaxDimPerLane];
 #pragma unroll
-  for (int i = 0; i < kMaxDimPerLane; ++i) acc[i] = 0.f;
+  for (int i = 0; i < kMaxDimPerLane; ++i) { acc[i] = 0.f; acc_lo[i] = 0.f; }
 
   for (int k0 = k_begin; k0 < k_end; k0 += 32) {
     const int key = k0 + lane;
@@ -64,20 +91,32 @@ paged_attention_simt_kernel(T* __restrict__ out, float* __restrict__ part_acc, f
     if (valid) {
       base = ((size_t)page * 2) * plane + ((size_t)kvh * page_size + key % page_size) * d;
       const T* kp = cache + base;
-      float dot = 0.f;
+      float dot = 0.f, dot_lo = 0.f;
       for (int i = 0; i < d; i += VN) {
         Vec16<T> kv = load16(kp + i);
 #pragma unroll
-        for (int e = 0; e < VN; ++e) dot = fmaf(qs[i + e], kv.get(e), dot);
+        for (int e = 0; e < VN; ++e) {
+          if constexpr (kCompensated) two_fma(dot, dot_lo, qs[i + e], kv.get(e));
+          else dot = fmaf(qs[i + e], kv.get(e), dot);
+        }
       }
-      s = dot;
+      s = kCompensated ? __fadd_rn(dot, dot_lo) * scale : dot;
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float pr = valid ? expf(s - m_new) : 0.f;
     const float alpha = expf(m - m_new);  // m = -inf on the first block gives 0
-    l = l * alpha + warp_sum(pr);
+    if constexpr (kCompensated) {
+      if (alpha != 1.f) {                 // (uniform over the warp) the maximum grew: everything so far shrinks
+        two_scale(l, l_lo, alpha);
 #pragma unroll
-    for (int i = 0; i < kMaxDimPerLane; ++i) acc[i] *= alpha;
+        for (int i = 0; i < kMaxDimPerLane; ++i) two_scale(acc[i], acc_lo[i], alpha);
+      }
+      two_fma(l, l_lo, warp_sum(pr), 1.f);
+    } else {
+      l = l * alpha + warp_sum(pr);
+#pragma unroll
+      for (int i = 0; i < kMaxDimPerLane; ++i) acc[i] *= alpha;
+    }
     m = m_new;
     const int nvalid = min(32, k_end - k0);
     for (int j = 0; j < nvalid; ++j) {
@@ -88,9 +127,17 @@ paged_attention_simt_kernel(T* __restrict__ out, float* __restrict__ part_acc, f
 #pragma unroll
       for (int i = 0; i < kMaxDimPerLane; ++i) {
         const int dd = lane + 32 * i;
-        if (dd < d) acc[i] = fmaf(pj, to_f32(vp[dd]), acc[i]);
+        if (dd < d) {
+          if constexpr (kCompensated) two_fma(acc[i], acc_lo[i], pj, to_f32(vp[dd]));
+          else acc[i] = fmaf(pj, to_f32(vp[dd]), acc[i]);
+        }
       }
     }
+  }
+  if constexpr (kCompensated) {
+    l = __fadd_rn(l, l_lo);
+#pragma unroll
+    for (int i = 0; i < kMaxDimPerLane; ++i) acc[i] = __fadd_rn(acc[i], acc_lo[i]);
   }
 
   if (splits == 1) {
