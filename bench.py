@@ -216,7 +216,7 @@ def main() -> int:
         feed = [[t] for t in tokens(batch)]
 
         def one():
-            out = engine.step([StepEntry(r, f, [0]) for r, f in zip(reqs, feed)])
+            out = engine.step([StepEntry(r, f, [0]) for r, f in zip(reqs, feed)], own_logits=False)   # sampled from at once
             ops.sample(out.logits, None, None, None)
         for _ in range(warmup):
             one()

@@ -34,6 +34,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     ap.add_argument("--page_size", type=int, default=16)
     ap.add_argument("--device", default="cuda")
+    ap.add_argument("--stats", action="store_true",
+                    help="time every step on the device (steps then run uncaptured, one at a time) and print, after each "
+                         "answer, steps, tokens, tokens/s, pages in use and milliseconds by class of kernels")
     ap.add_argument("--prompt", help="one text prompt (needs a tokenizer in the model folder)")
     ap.add_argument("--prompt_ids", type=int, nargs="+", help="one prompt as token ids")
     return ap
@@ -63,13 +66,21 @@ def main(argv: Optional[List[str]] = None) -> int:
         checkpoints_dir=str(folder), tokenizer_path=str(folder) if _has_tokenizer(folder) else None,
         max_gpu_num_blocks=args.max_gpu_num_blocks, max_seq_len=args.max_seq_len,
         load_model=args.load_model, triton_weight=args.triton_weight, compiled_model=args.compiled_model,
-        device=args.device, dtype=args.dtype, page_size=args.page_size, seed=args.seed)
+        device=args.device, dtype=args.dtype, page_size=args.page_size, seed=args.seed, timing=args.stats)
+    engine = generator.llm.engine
+    if args.stats and engine.memory_report:
+        print(f"[stats] cache pool: {json.dumps(engine.memory_report)}", file=sys.stderr)
+
+    def show_stats() -> None:
+        if args.stats:
+            print(f"[stats] {json.dumps(engine.stats.summary())}", file=sys.stderr)
 
     def run_ids(ids: List[int]) -> None:
         for batch in generator.generate_stream([ids], args.max_gen_len, args.temperature, args.top_p):
             if batch[0]:
                 print(" ".join(str(t) for t in batch[0]), end=" ", flush=True)
         print()
+        show_stats()
 
     def run_text(text: str) -> None:
         shown = ""
@@ -78,6 +89,7 @@ def main(argv: Optional[List[str]] = None) -> int:
             shown = completions[0]["generation"]
             print(new, end="", flush=True)
         print()
+        show_stats()
 
     if args.prompt_ids:
         run_ids(args.prompt_ids)

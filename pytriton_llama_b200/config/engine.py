@@ -37,6 +37,8 @@ class EngineConfig:
     compiled_model: bool = False               # capture decode steps in CUDA graphs
     capture_mixed_steps: bool = True           # with compiled_model: also steps that hold prompt portions (padded shapes, up to 1,024 tokens)
     overlap_steps: bool = True                 # plan and launch the next step while the last one's tokens are read
+    timing: bool = False                       # diagnostic: CUDA-event time of every step and of every class of kernels; steps run
+                                               # uncaptured and the host waits for each (lite_llama/generete_with_probs.py:124-126,176-182 times its loop so)
     seed: int = 0
 
     def __post_init__(self):

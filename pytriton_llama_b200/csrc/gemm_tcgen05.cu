@@ -81,7 +81,8 @@ PTL_EXPORT int ptl_gemm_tc_k_parts(int M, int N, int K) {
 static int gemm_tc_impl(void* out, const void* X, const void* W, int M, int N, int K, int ld_out, int epi,
                         int* status, int splits_hint, void* xs, const float* norm_w, float* sumsq,
                         int sumsq_ld, int* slots_out, const float* scale_sumsq, int scale_slots,
-                        int scale_ld, float scale_eps, const ptl::GemmParams* rope, void* stream) {
+                        int scale_ld, float scale_eps, const ptl::GemmParams* rope, void* stream,
+                        unsigned poll_limit = ptl::kPollLimit, int withhold_first_load = 0) {
   using namespace ptl;
   PTL_REQUIRE(M >= 0 && N > 0 && K > 0 && ld_out > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
   if (K % 8 != 0 || K < kTileK) return -2;
@@ -91,6 +92,7 @@ static int gemm_tc_impl(void* out, const void* X, const void* W, int M, int N, i
   GemmParams p{};
   p.out = out; p.status = status;
   p.K = K; p.ld_out = ld_out;
+  p.poll_limit = poll_limit; p.withhold_first_load = withhold_first_load;
   if (xs) {
     if (epi != 2 || N % 32 != 0 || ld_out % 4 != 0) return -2;
     PTL_REQUIRE(norm_w && sumsq && slots_out, "gemm_tc: the next norm's input needs its weight, the sums and a place for their count");
@@ -202,4 +204,20 @@ PTL_EXPORT int ptl_gemm_tc_bf16(void* out, const void* X, const void* W, int M, 
                                 int* status, int splits_hint, void* stream) {
   return ptl_gemm_tc_bf16_norm(out, X, W, M, N, K, ld_out, epi, status, splits_hint, nullptr, nullptr, nullptr, 0, nullptr,
                                nullptr, 0, 0, 0.f, stream);
+}
+
+// Self-test of the bounded waits: the product out[M,N] = X W^T (bfloat16 store) as ONE block whose
+// first stage is never filled (the load of its token tile is left out) and whose waits give up
+// after `poll_limit` polls.  The kernel must then write `*status` (code 2: a wait for a full
+// stage ran out), let every role drain, free its tensor memory and return; `out` holds nothing of
+// value.  Only sizes that make a single block without a cluster are taken (M <= 128 and N <= 128;
+// with M <= 64 also K <= 192), so that no other block or kernel can be left waiting.
+PTL_EXPORT int ptl_gemm_tc_wait_selftest(void* out, const void* X, const void* W, int M, int N, int K, int* status,
+                                         unsigned poll_limit, void* stream) {
+  PTL_REQUIRE(status != nullptr, "gemm_tc_wait_selftest: needs a status word");
+  PTL_REQUIRE(M >= 1 && M <= 128 && N >= 1 && N <= 128 && K >= 64 && K % 8 == 0 && (M > 64 || K <= 192),
+              "gemm_tc_wait_selftest: one block only (M <= 128, N <= 128, K >= 64; K <= 192 with M <= 64), got M=%d N=%d K=%d", M, N, K);
+  PTL_REQUIRE(poll_limit >= 1 && poll_limit <= (1u << 16), "gemm_tc_wait_selftest: between 1 and 65536 polls");
+  return gemm_tc_impl(out, X, W, M, N, K, N, 0, status, M <= 64 ? 1 : 0, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0.f,
+                      nullptr, stream, poll_limit, 1);
 }

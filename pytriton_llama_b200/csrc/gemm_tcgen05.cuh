@@ -74,6 +74,12 @@ struct GemmParams {
   __nv_bfloat16* rope_cache;     // [pages][2 (k, v)][rope_nkv][rope_page][rope_d]
   int rope_nq, rope_nkv, rope_d, rope_page;
   long long rope_num_slots;
+  // How often a wait on a barrier polls before it gives up (kPollLimit in every product the engine
+  // launches).  `withhold_first_load`, set by the self-test entry point alone, makes the block leave
+  // out the load of its first stage's token tile, so that the stage never fills: the waits then
+  // run out, and the test sees the status word, the drained roles and the block's clean exit.
+  uint32_t poll_limit;
+  int withhold_first_load;
 };
 
 // PAIR: two blocks on the SMs of one TPC work as one (cta_group::2): an MMA of 256 token rows x BN
@@ -364,6 +370,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     if (!p.swapped) {
       for (int i = 0; i < pre; ++i) {
         const uint32_t dst = smem_base + i * Cfg::kStageBytes;
+        if (i == 0 && p.withhold_first_load) continue;      // (self-test: this stage never fills)
         if (PAIR) tma_load_2d_pair(dst, &map_row, map_to_peer(full_bar(i), 0), (kb00 + i) * kTileK, row0 * kTileRows);
         else tma_load_2d(dst, &map_row, full_bar(i), (kb00 + i) * kTileK, row0 * kTileRows);
       }
@@ -377,7 +384,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       for (int i = (tile == first_tile ? pre : 0); i < unkb; ++i, ++it) {
         const int s = it % Cfg::kStages;
         const uint32_t ph = (it / Cfg::kStages) & 1;
-        if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+        if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, 1, p.poll_limit)) { ok = false; break; }
         const uint32_t dst = smem_base + s * Cfg::kStageBytes;
         if (PAIR) {
           // both blocks' tiles are counted on the issuing block's barrier, which expects both (a
@@ -409,11 +416,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       const int issuer = warp == 1 ? 0 : warp - 5;
       const uint32_t acc = tmem_base + issuer * BN;
       // the weights of the first ring of stages are on their way since before the wait; their tokens follow now
-      for (int i = issuer; i < min(my_kb, Cfg::kStages); i += Cfg::kAccWays)
+      for (int i = issuer; i < min(my_kb, Cfg::kStages); i += Cfg::kAccWays) {
+        if (i == 0 && p.withhold_first_load) continue;        // (self-test: this stage never fills)
         tma_load_2d(smem_base + i * Cfg::kStageBytes + Cfg::kRowBytes, &map_col, full_bar(i), (kb0 + i) * kTileK, 0);
+      }
       for (int i = issuer; i < my_kb; i += Cfg::kAccWays) {
         const int s = i % Cfg::kStages;
-        if (!mbar_wait(full_bar(s), (i / Cfg::kStages) & 1, abort_flag, p.status, 2)) break;
+        if (!mbar_wait(full_bar(s), (i / Cfg::kStages) & 1, abort_flag, p.status, 2, p.poll_limit)) break;
         tcgen05_fence_after();
         const uint32_t a = smem_base + s * Cfg::kStageBytes;
         const uint32_t b = a + Cfg::kRowBytes;
@@ -435,7 +444,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++lt) {
       const int buf = Cfg::kAccBufs == 2 ? (lt & 1) : 0;
       const int use = Cfg::kAccBufs == 2 ? (lt >> 1) : lt;            // how often this buffer was used before
-      ok = mbar_wait(acc_empty(buf), (use & 1) ^ 1, abort_flag, p.status, 4);    // the epilogue has drained it
+      ok = mbar_wait(acc_empty(buf), (use & 1) ^ 1, abort_flag, p.status, 4, p.poll_limit);    // the epilogue has drained it
       if (!ok) break;
       tcgen05_fence_after();
       const uint32_t acc = tmem_base + buf * BN;
@@ -444,7 +453,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       for (int i = 0; i < unkb; ++i, ++it) {
         const int s = it % Cfg::kStages;
         const uint32_t ph = (it / Cfg::kStages) & 1;
-        ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 2);
+        ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 2, p.poll_limit);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t a = smem_base + s * Cfg::kStageBytes;
@@ -518,7 +527,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
         row_scale = rsqrtf(sum * p.scale_inv_n + p.scale_eps);
       }
       float ss = 0.f;                          // sum of squares of this thread's share of its row (add epilogue, emitting)
-      if (!mbar_wait(acc_full(buf), use & 1, abort_flag, p.status, 3)) break;
+      if (!mbar_wait(acc_full(buf), use & 1, abort_flag, p.status, 3, p.poll_limit)) break;
       tcgen05_fence_after();
       const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
       if (!p.swapped && row_tile * kTileRows >= p.rows) {
@@ -674,7 +683,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     // at the groups of 16 columns.  The warps that issued MMAs have not waited for the accumulators yet.
     bool acc_ok = true;
     if (warp >= 6 && BN > 16) {
-      acc_ok = mbar_wait(acc_full(0), 0, abort_flag, p.status, 3);
+      acc_ok = mbar_wait(acc_full(0), 0, abort_flag, p.status, 3, p.poll_limit);
       tcgen05_fence_after();
     }
     if (warp >= 2 && (warp < 6 || BN > 16) && acc_ok && !*abort_flag) {

@@ -36,10 +36,11 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait: false (and *abort = 1, *status = code) if the phase did not complete in time or
-// another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort, int* status, int code) {
-  for (uint32_t i = 0; i < kPollLimit; ++i) {
+// Bounded wait: false (and *abort = 1, *status = code) if the phase did not complete within `limit`
+// polls or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort, int* status, int code,
+                                          uint32_t limit = kPollLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort) return false;
     if (i > 64) __nanosleep(40);

@@ -7,7 +7,7 @@ whether a request is in its prompt or decoding: a portion is ``q_len`` new token
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional
+from typing import Any, Dict, List, Optional
 
 import torch
 
@@ -46,9 +46,5 @@ class StepContext:
     max_q_len: int = 0
     max_ctx_len: int = 0
     attn_splits: int = 1
-    # work lists for attention kernels that treat single tokens and longer portions differently
-    n_decode: int = 0                                  # tokens that are the only new token of their request
-    decode_items: Optional[torch.Tensor] = None        # int32 [n_decode] their token indices
-    decode_in_order: bool = False                      # True when they are simply tokens 0..n_decode-1
-    n_prefill_tiles: int = 0                           # tiles of up to 128 rows of longer portions, in pairs (the second continues the first or has 0 rows)
-    prefill_tiles: Optional[torch.Tensor] = None       # int32 [4 * tiles]: request row, first token, rows, first position
+    # integer lists the operator set asked for (``ops.plan_step``): name -> ``StepWork``
+    work: Dict[str, Any] = field(default_factory=dict)

@@ -9,6 +9,7 @@ float32 logits at the wanted places.
 """
 from __future__ import annotations
 
+import logging
 from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Dict, Hashable, List, Optional, Sequence, Union
@@ -23,6 +24,7 @@ from ..models.decoder import DecoderModel
 from ..parts.base import Runtime
 from ..weights.loader import check_tensors
 from ..weights.safetensors_io import read_folder
+from ..ops.worklists import PAD_TOKEN_ROW, StepWork
 from .context import GroupStepView, LayerCacheView, StepContext
 
 
@@ -40,9 +42,42 @@ class StepOutput:
     logits: Optional[torch.Tensor]            # float32 [wanted, vocab], in the order of entries and of want
     rows: List[tuple] = field(default_factory=list)   # (request, index within its tokens) of each logits row
     num_tokens: int = 0
+    num_requests: int = 0
+    pages_used: int = 0                       # pages held after this step, over all groups of cache entries
+    pages_free: int = 0
+    step_ms: Optional[float] = None           # device time of the step (CUDA events); with ``EngineConfig.timing`` only
+    kernel_ms: Optional[Dict[str, float]] = None      # ... and by class of kernels, where the operator set reports it
 
 
-QUERY_TILE = 128   # query rows per block of the prompt attention kernel
+@dataclass
+class EngineStats:
+    """Running totals over the steps of an engine (``Engine.stats``)."""
+    steps: int = 0
+    tokens: int = 0
+    wanted_rows: int = 0
+    peak_pages_used: int = 0
+    step_ms: float = 0.0                      # timed steps only
+    timed_steps: int = 0
+    kernel_ms: Dict[str, float] = field(default_factory=dict)
+
+    def add(self, out: "StepOutput") -> None:
+        self.steps += 1
+        self.tokens += out.num_tokens
+        self.wanted_rows += len(out.rows)
+        self.peak_pages_used = max(self.peak_pages_used, out.pages_used)
+        if out.step_ms is not None:
+            self.step_ms += out.step_ms
+            self.timed_steps += 1
+        for k, v in (out.kernel_ms or {}).items():
+            self.kernel_ms[k] = self.kernel_ms.get(k, 0.0) + v
+
+    def summary(self) -> Dict[str, object]:
+        d = {"steps": self.steps, "tokens": self.tokens, "wanted_rows": self.wanted_rows, "peak_pages_used": self.peak_pages_used}
+        if self.timed_steps:
+            d["step_ms_mean"] = round(self.step_ms / self.timed_steps, 4)
+            d["tokens_per_s_device"] = round(self.tokens / (self.step_ms * 1e-3), 1) if self.step_ms > 0 else None
+            d["kernel_ms"] = {k: round(v, 3) for k, v in sorted(self.kernel_ms.items())}
+        return d
 
 
 def _pad4(n: int) -> int:
@@ -52,41 +87,28 @@ def _pad4(n: int) -> int:
 class _HostBatch:
     """A step's requests as host lists, before they are packed for the device."""
 
-    def __init__(self, entries, q_lens, starts, fresh, state_slots, slots_by_group, logit_rows):
+    def __init__(self, entries, q_lens, starts, fresh, state_slots, slots_by_group, logit_rows, work=None):
         self.entries, self.q_lens, self.starts, self.fresh = entries, q_lens, starts, fresh
         self.state_slots, self.slots_by_group, self.logit_rows = state_slots, slots_by_group, logit_rows
         self.takes_sampled = any(e.from_row is not None for e in entries)
         self.R = len(entries)
         self.T = sum(q_lens)
         self.max_q_len = max(q_lens)
-        # work lists of the attention kernels: single tokens, and tiles of up to 128 rows of longer portions
-        self.dec_items: List[int] = []
-        self.pf_tiles: List[int] = []
-        t0 = 0
-        for r, (n, s) in enumerate(zip(q_lens, starts)):
-            if n == 1:
-                self.dec_items.append(t0)
-            else:
-                # tiles come in pairs: the second continues the first or is empty (the prompt
-                # attention kernel fetches every key once for both)
-                for a in range(0, n, 2 * QUERY_TILE):
-                    self.pf_tiles += [r, t0 + a, min(QUERY_TILE, n - a), s + a]
-                    b = a + QUERY_TILE
-                    self.pf_tiles += [r, t0 + b, max(0, min(QUERY_TILE, n - b)), s + b]
-            t0 += n
+        self.work: Dict[str, List[int]] = work or {}      # the operator set's lists for this step (ops.plan_step)
 
 
 class _Layout:
     """Where each integer array of a step lies inside one packed int32 buffer (one copy per step)."""
 
     def __init__(self, T: int, R: int, M: int, bt_width: int, groups: List[int], static_rows: bool = False,
-                 max_tiles: int = 0):
+                 work_sizes: Optional[Dict[str, int]] = None):
         self.T, self.R, self.M, self.bt_width, self.groups, self.static_rows = T, R, M, bt_width, groups, static_rows
-        self.max_tiles = max_tiles
+        self.work_sizes = dict(work_sizes or {})           # integers each of the operator set's lists may hold
         self.seg: Dict[str, tuple] = {}
         cursor = 0
         names = [("tokens", T), ("token_src", T), ("positions", T), ("tok_req", T), ("q_start", R + 1), ("ctx_len", R),
-                 ("state_slot", R), ("fresh", R), ("logit_rows", M), ("dec_items", T), ("pf_tiles", 4 * max_tiles)]
+                 ("state_slot", R), ("fresh", R), ("logit_rows", M)]
+        names += [(f"work:{name}", n) for name, n in sorted(self.work_sizes.items())]
         for g in groups:
             names += [(f"slots{g}", T), (f"bt{g}", R * bt_width)]
         for name, n in names:
@@ -142,6 +164,7 @@ class Engine:
         del tensors
         self.vocab_size = spec.vocab_size
         self.eos_token_ids = list(spec.eos_token_ids)
+        self.memory_report: Optional[dict] = None      # filled when the pool is sized from free memory
         entries = self.model.cache_entries()
         num_pages = self.config.max_gpu_num_blocks or self._pages_from_free_memory(entries)
         self.cache = CacheManager(entries, self.config.page_size, num_pages, self.config.max_num_seqs,
@@ -152,6 +175,9 @@ class Engine:
         # token from here.
         self.sampled = torch.zeros(max(1, self.config.max_num_seqs), dtype=torch.int32, device=self.device)
         self.steps_run = 0
+        self.stats = EngineStats()
+        if self.config.timing and hasattr(self.ops, "enable_timing"):
+            self.ops.enable_timing()
         self._graphs = {}          # captured steps: padded batch size (single tokens only) or a _StepShape
         self._shape_seen: Dict[tuple, int] = {}
         self._shape_captures = 0
@@ -174,17 +200,27 @@ class Engine:
         cap = self.config.max_num_seqs * -(-self.config.max_seq_len // self.config.page_size)
         if self.device.type != "cuda":
             return cap
-        free, _ = torch.cuda.mem_get_info(self.device)
+        free, total = torch.cuda.mem_get_info(self.device)
         workspace = 2 << 30
         fit = int((free * self.config.gpu_memory_fraction - workspace) // bytes_per_page)
+        pages = min(cap, fit)
+        # what lite_llama prints when it sizes its pool (lite_llama/executor/mem_manager.py:112-123), kept for callers
+        self.memory_report = {"device_total_gb": round(total / 2 ** 30, 2), "free_after_weights_gb": round(free / 2 ** 30, 2),
+                              "fraction": self.config.gpu_memory_fraction, "bytes_per_page_all_groups": bytes_per_page,
+                              "pages_that_fit": fit, "pages_ever_needed": cap, "pages": pages,
+                              "cache_gb": round(max(pages, 0) * bytes_per_page / 2 ** 30, 3)}
+        logging.getLogger(__name__).info("cache pool sized from free memory: %s", self.memory_report)
         if fit <= 0:
             raise OutOfPages("no memory left for the cache after loading the weights")
-        return min(cap, fit)
+        return pages
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry], validate: bool = True) -> StepOutput:
+    def step(self, entries: Sequence[StepEntry], validate: bool = True, own_logits: bool = True) -> StepOutput:
         """``validate=False`` skips the checks of tokens, wanted places and free pages for callers
-        that made them already (the scheduler's plans)."""
+        that made them already (the scheduler's plans).  The logits of a step that ran from a captured
+        graph lie in memory that the next captured step writes again; they are copied out of it unless
+        ``own_logits=False`` says that the caller is done with them before its next step (the
+        generation loop, which samples at once)."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return StepOutput(None, [], 0)
@@ -228,8 +264,14 @@ class Engine:
                 rows.append((e.request, int(w)))
                 logit_rows.append(base + int(w))
             base += n
-        batch = _HostBatch(entries, q_lens, starts, fresh, state_slots, slots_by_group, logit_rows)
+        plan = getattr(self.ops, "plan_step", None)
+        batch = _HostBatch(entries, q_lens, starts, fresh, state_slots, slots_by_group, logit_rows,
+                           work=plan(q_lens, starts) if plan is not None else None)
         self.steps_run += 1
+        timing = self.config.timing and self.device.type == "cuda"
+        if timing:
+            t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t_start.record()
         bucket = self._graph_bucket(batch)
         if bucket:
             logits = self._run_graph(bucket, batch)
@@ -238,20 +280,35 @@ class Engine:
             elif logit_rows != list(range(len(entries))):
                 idx = torch.tensor(logit_rows, dtype=torch.long, device=self.device)
                 logits = logits.index_select(0, idx) if logit_rows else None
-            return StepOutput(logits, rows, batch.T)
-        layout = _Layout(batch.T, batch.R, len(logit_rows), self._table_width(batch), self._paged_groups(),
-                         max_tiles=len(batch.pf_tiles) // 4)
-        host = torch.empty(layout.size, dtype=torch.int32, pin_memory=self._pinned)
-        self._fill(host.numpy(), layout, batch)
-        dev = host.to(self.device, non_blocking=True)
-        if batch.takes_sampled:
-            self.ops.take_tokens(layout.view(dev, "tokens"), layout.view(dev, "token_src"), self.sampled)
-        ctx, cache_view = self._context(dev, layout, batch.q_lens, [s + n for s, n in zip(starts, q_lens)],
-                                        self._choose_splits(batch.T, max(s + n for s, n in zip(starts, q_lens))),
-                                        n_decode=len(batch.dec_items), n_tiles=len(batch.pf_tiles) // 4)
-        logits = self.model.forward(layout.view(dev, "tokens"), ctx, cache_view,
-                                    layout.view(dev, "logit_rows") if logit_rows else None)
-        return StepOutput(logits, rows, batch.T)
+            if logits is not None and own_logits and logits._base is not None:
+                logits = logits.clone()       # out of the captured step's memory, which the next replay writes again
+        else:
+            layout = _Layout(batch.T, batch.R, len(logit_rows), self._table_width(batch), self._paged_groups(),
+                             work_sizes={name: len(v) for name, v in batch.work.items()})
+            host = torch.empty(layout.size, dtype=torch.int32, pin_memory=self._pinned)
+            self._fill(host.numpy(), layout, batch)
+            dev = host.to(self.device, non_blocking=True)
+            if batch.takes_sampled:
+                self.ops.take_tokens(layout.view(dev, "tokens"), layout.view(dev, "token_src"), self.sampled)
+            ctx, cache_view = self._context(dev, layout, batch.q_lens, [s + n for s, n in zip(starts, q_lens)],
+                                            self._choose_splits(batch.T, max(s + n for s, n in zip(starts, q_lens))),
+                                            work_items=self._work_items(batch.work),
+                                            in_order=self._work_in_order(batch.work, batch.T))
+            logits = self.model.forward(layout.view(dev, "tokens"), ctx, cache_view,
+                                        layout.view(dev, "logit_rows") if logit_rows else None)
+        out = StepOutput(logits, rows, batch.T, batch.R)
+        for g in self._paged_groups():
+            free = cache.free_pages(g)
+            out.pages_free += free
+            out.pages_used += cache.groups[g].pool.num_pages - free
+        if timing:
+            t_end.record()
+            t_end.synchronize()
+            out.step_ms = t_start.elapsed_time(t_end)
+            take = getattr(self.ops, "take_timings", None)
+            out.kernel_ms = take() if take is not None else None
+        self.stats.add(out)
+        return out
 
     # ------------------------------------------------------------------ batch assembly
     def _paged_groups(self) -> List[int]:
@@ -292,14 +349,16 @@ class Engine:
             h[lo:lo + n] = np.arange(n, dtype=np.int32)
         elif n:
             put("logit_rows", b.logit_rows)          # (a padded shape asks for row 0 again in the rows it has too many)
-        if layout.static_rows:
-            lo, n = layout.seg["dec_items"]
-            h[lo:lo + n] = np.arange(n, dtype=np.int32)
-        else:
-            # a padded shape has more single-token items than the step: the rest name a token row
-            # beyond the step's, whose request is -1 (the shape is chosen so that there is one)
-            put("dec_items", b.dec_items, fill=min(T, layout.T - 1))
-            put("pf_tiles", b.pf_tiles)              # (empty pairs beyond the step's: rows 0)
+        # The operator set's lists.  A captured step has room for more items than the step brings:
+        # the rest is padding, either a number or a token row that belongs to no request (the
+        # shape is chosen so that there is one).
+        infos = self._work_lists()
+        for name in layout.work_sizes:
+            values = b.work.get(name, ())
+            if len(values) > layout.work_sizes[name]:
+                raise RuntimeError(f"work list {name!r} has {len(values)} integers, the captured step holds {layout.work_sizes[name]}")
+            pad = infos[name].pad if name in infos else 0
+            put(f"work:{name}", values, fill=min(T, layout.T - 1) if pad == PAD_TOKEN_ROW else pad)
         for g in layout.groups:
             put(f"slots{g}", b.slots_by_group[g], fill=-1)
             lo, n = layout.seg[f"bt{g}"]
@@ -309,8 +368,26 @@ class Engine:
                 t = self.cache.block_table_array(e.request, g)
                 bt[i, :len(t)] = t
 
-    def _context(self, dev: torch.Tensor, layout: "_Layout", q_lens, ctx_lens, splits: int, n_decode: int, n_tiles: int):
+    def _work_lists(self) -> dict:
+        """name -> ``WorkList`` of the lists the operator set wants packed with a step."""
+        return getattr(self.ops, "WORK_LISTS", {})
+
+    def _work_items(self, work: Dict[str, List[int]]) -> Dict[str, int]:
+        infos = self._work_lists()
+        return {name: len(v) // (infos[name].width if name in infos else 1) for name, v in work.items()}
+
+    def _work_in_order(self, work: Dict[str, List[int]], T: int) -> Dict[str, bool]:
+        infos = self._work_lists()
+        return {name: (name not in infos or infos[name].width == 1) and len(v) == T and list(v) == list(range(T))
+                for name, v in work.items()}
+
+    def _context(self, dev: torch.Tensor, layout: "_Layout", q_lens, ctx_lens, splits: int, work_items: Dict[str, int],
+                 in_order: Dict[str, bool]):
         cache = self.cache
+        infos = self._work_lists()
+        work = {name: StepWork(layout.view(dev, f"work:{name}")[:n * (infos[name].width if name in infos else 1)], n,
+                               bool(in_order.get(name, False)))
+                for name, n in work_items.items()}
         groups = {g: GroupStepView(page_size=cache.page_size,
                                    block_table=layout.view(dev, f"bt{g}").view(layout.R, layout.bt_width),
                                    slots=layout.view(dev, f"slots{g}"), window=cache.groups[g].need.window)
@@ -320,10 +397,7 @@ class Engine:
                           ctx_len=layout.view(dev, "ctx_len"), state_slot=layout.view(dev, "state_slot"),
                           fresh=layout.view(dev, "fresh"), groups=groups, q_lens=list(q_lens),
                           ctx_lens=list(ctx_lens), max_q_len=max(q_lens), max_ctx_len=max(ctx_lens),
-                          attn_splits=splits, n_decode=n_decode, n_prefill_tiles=n_tiles,
-                          decode_in_order=(n_decode == layout.T),
-                          decode_items=layout.view(dev, "dec_items")[:n_decode],
-                          prefill_tiles=layout.view(dev, "pf_tiles"))
+                          attn_splits=splits, work=work)
 
         def cache_view(entry: int, write: bool) -> LayerCacheView:
             g = cache.entry_group[entry]
@@ -343,8 +417,8 @@ class Engine:
         step of single tokens (lite_llama captures its decode step for batch sizes 1, 2, 4, 8, 16,
         ...: lite_llama/executor/cuda_graph.py:6-7,113-132), a padded shape (a tuple) for a step that
         holds prompt portions.  Only for models whose mixers keep nothing but paged keys and values."""
-        if not self.config.compiled_model or self.device.type != "cuda":
-            return 0
+        if not self.config.compiled_model or self.device.type != "cuda" or self.config.timing:
+            return 0          # (timing brackets every operator with events, which a capture cannot hold)
         if any(not grp.paged or grp.state for grp in self.cache.groups):
             return 0
         if batch.max_q_len != 1:
@@ -361,23 +435,28 @@ class Engine:
     def _shape_bucket(self, batch: "_HostBatch"):
         """Steps with prompt portions of up to 1,024 tokens are bound by the host's launches (about
         11 us each, twice the GPU's time at 300 tokens), so they run from captured graphs too: the
-        step's shape is padded to (tokens, requests, single-token items, pairs of prompt tiles, wants
-        logits) with few values each, and a shape that comes a second time is captured.  Padded token
-        rows have request -1 and slot -1, padded tile pairs have no rows: every kernel skips them."""
-        T, R = batch.T, batch.R
-        n_dec, n_pairs, M = len(batch.dec_items), len(batch.pf_tiles) // 8, len(batch.logit_rows)
+        step's shape is padded to (tokens, requests, wants logits, items of each of the operator
+        set's work lists) with few values each, and a shape that comes a second time is captured.
+        Padded token rows have request -1 and slot -1, padded list items are what the operator set
+        says they must be: every kernel skips them."""
+        T, R, M = batch.T, batch.R, len(batch.logit_rows)
         if T > self.GRAPH_MAX_TOKENS:
             return 0
         pow2 = lambda n: 0 if n == 0 else 1 << (n - 1).bit_length()
         step = 64 if T <= 256 else 128
         t_pad = -(-T // step) * step
-        d_pad = pow2(n_dec)
-        if d_pad > n_dec and t_pad == T:
+        lists, needs_free_row = [], False
+        for name, info in sorted(self._work_lists().items()):
+            items = len(batch.work.get(name, ())) // info.width
+            padded = pow2(-(-items // info.group)) * info.group     # whole groups, a power of two of them
+            lists.append((name, padded))
+            needs_free_row |= padded > items and info.pad == PAD_TOKEN_ROW
+        if needs_free_row and t_pad == T:
             t_pad += step                                   # the padded items need a token row that belongs to no request
         r_pad = pow2(R)
         if M > r_pad:
             return 0                                        # (a replay that wants many rows of a prompt)
-        shape = (t_pad, r_pad, d_pad, pow2(n_pairs), 1 if M else 0)
+        shape = (t_pad, r_pad, 1 if M else 0, tuple(lists))
         if shape in self._graphs:
             return shape
         if self._shape_captures >= self.GRAPH_MAX_CAPTURES:
@@ -418,13 +497,21 @@ class Engine:
         shape (a tuple, see ``_shape_bucket``).  While it is captured every token row belongs to no
         request, so the runs that record it touch no page of the cache."""
         width = _pad4(self.cache.max_blocks)
+        infos = self._work_lists()
         if isinstance(bucket, tuple):
-            t_pad, r_pad, d_pad, pairs, wants = bucket
-            layout = _Layout(t_pad, r_pad, r_pad if wants else 0, width, self._paged_groups(), max_tiles=2 * pairs)
-            n_decode, n_tiles, q_lens = d_pad, 2 * pairs, [t_pad] + [1] * (r_pad - 1)
+            t_pad, r_pad, wants, lists = bucket
+            work_items = dict(lists)
+            in_order = {}
+            layout = _Layout(t_pad, r_pad, r_pad if wants else 0, width, self._paged_groups(),
+                             work_sizes={name: n * infos[name].width for name, n in lists})
+            q_lens = [t_pad] + [1] * (r_pad - 1)
         else:
-            layout = _Layout(bucket, bucket, bucket, width, self._paged_groups(), static_rows=True)
-            n_decode, n_tiles, q_lens, wants = bucket, 0, [1] * bucket, 1
+            plan = getattr(self.ops, "plan_step", None)
+            work = plan([1] * bucket, [0] * bucket) if plan is not None else {}
+            work_items, in_order = self._work_items(work), self._work_in_order(work, bucket)
+            layout = _Layout(bucket, bucket, bucket, width, self._paged_groups(), static_rows=True,
+                             work_sizes={name: len(v) for name, v in work.items()})
+            q_lens, wants = [1] * bucket, 1
         host = torch.empty(layout.size, dtype=torch.int32, pin_memory=True)
         h = host.numpy()
         h.fill(0)
@@ -432,13 +519,15 @@ class Engine:
             lo, n = layout.seg[name]
             h[lo:lo + n] = fill
         if layout.static_rows:
-            for name in ("logit_rows", "dec_items"):
-                lo, n = layout.seg[name]
-                h[lo:lo + n] = np.arange(n, dtype=np.int32)
+            lo, n = layout.seg["logit_rows"]
+            h[lo:lo + n] = np.arange(n, dtype=np.int32)
+            for name, values in work.items():
+                lo, n = layout.seg[f"work:{name}"]
+                h[lo:lo + n] = np.asarray(values, dtype=np.int32)
         dev = host.to(self.device)
         splits = self._choose_splits(layout.T, self.config.max_seq_len)
         ctx, cache_view = self._context(dev, layout, q_lens, [self.config.max_seq_len] * layout.R, splits,
-                                        n_decode=n_decode, n_tiles=n_tiles)
+                                        work_items=work_items, in_order=in_order)
 
         def run():
             self.ops.take_tokens(layout.view(dev, "tokens"), layout.view(dev, "token_src"), self.sampled)

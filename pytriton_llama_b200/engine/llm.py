@@ -107,7 +107,8 @@ class LLM:
                 entries.append(StepEntry(req.id, [0], [0], from_row=self._rows[req.id]))
             else:
                 entries.append(StepEntry(req.id, req.tokens(p.start, p.length), [p.length - 1] if p.sample else []))
-        out = self.engine.step(entries, validate=False)   # the plan was checked against the cache; tokens at intake
+        # the plan was checked against the cache and the tokens at intake; the logits are sampled from at once
+        out = self.engine.step(entries, validate=False, own_logits=False)
         reqs = [p.request for p in plan.portions if p.sample]
         launched = _Launched(plan, reqs)
         if reqs:

@@ -16,6 +16,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import build
+from .worklists import PAD_TOKEN_ROW, StepWork, WorkList
 
 _c_int = ctypes.c_int
 _c_ll = ctypes.c_longlong
@@ -155,6 +156,100 @@ class CudaOps:
         self._device_index = device.index if device.index is not None else torch.cuda.current_device()
         self._status = torch.zeros(1, dtype=torch.int32, device=device)
         self.launches = 0      # kernels of this library launched so far (library matrix products not counted)
+
+    # ------------------------------------------------------------------ work lists of a step
+    QUERY_TILE = 128   # query rows per tile of the prompt attention kernels; a block takes a pair of consecutive tiles
+    WORK_LISTS = {
+        # token rows that are the only new token of their request: the split-key decode attention's items
+        "decode_items": WorkList(width=1, group=1, pad=PAD_TOKEN_ROW),
+        # tiles of longer portions: (request row, first token row, rows, first position); in pairs, the
+        # second tile continues the first or has no rows; a padding tile has no rows
+        "prefill_tiles": WorkList(width=4, group=2, pad=0),
+    }
+
+    def plan_step(self, q_lens, starts):
+        """The attention kernels' work lists of a step whose request r brings ``q_lens[r]`` tokens
+        after ``starts[r]`` cached ones (host integers; the engine packs them and hands them back on
+        the device in ``StepContext.work``)."""
+        tile = self.QUERY_TILE
+        dec, tiles, t0 = [], [], 0
+        for r, (n, s) in enumerate(zip(q_lens, starts)):
+            if n == 1:
+                dec.append(t0)
+            else:
+                for a in range(0, n, 2 * tile):       # the kernel fetches every key once for both tiles of a pair
+                    b = a + tile
+                    tiles += [r, t0 + a, min(tile, n - a), s + a,
+                              r, t0 + b, max(0, min(tile, n - b)), s + b]
+            t0 += n
+        return {"decode_items": dec, "prefill_tiles": tiles}
+
+    def hints_for(self, q_lens, ctx_lens):
+        """What the attention operators read of a step context, for callers that launch them
+        without an engine (kernel tests, micro-benchmarks): the work lists of a step whose request r
+        brings ``q_lens[r]`` tokens and holds ``ctx_lens[r]`` afterwards, on the device."""
+        from types import SimpleNamespace
+        lists = self.plan_step(list(q_lens), [c - n for n, c in zip(q_lens, ctx_lens)])
+        T = sum(q_lens)
+        work = {}
+        for name, values in lists.items():
+            info = self.WORK_LISTS[name]
+            t = torch.tensor(values if values else [0], dtype=torch.int32, device=self.device)[:len(values)]
+            work[name] = StepWork(t, len(values) // info.width, info.width == 1 and values == list(range(T)))
+        return SimpleNamespace(work=work, max_ctx_len=max(ctx_lens))
+
+    @staticmethod
+    def _work(hints, name):
+        work = getattr(hints, "work", None)
+        return work.get(name) if work else None
+
+    # ------------------------------------------------------------------ timing by class of kernels (diagnostic)
+    KERNEL_CLASSES = {
+        "embed": "elementwise", "take_tokens": "elementwise", "silu_mul": "elementwise", "add_rmsnorm": "norm",
+        "linear": "product", "linear_add": "product", "gate_up_silu": "product", "gemm_tc": "product",
+        "_qkv_rope_product": "product", "rope_kv_write": "rope", "_rope_table": "rope",
+        "paged_attention": "attention", "_attention_tensor_cores": "attention",
+        "sample": "sampling", "token_logprobs": "sampling",
+    }
+
+    def enable_timing(self) -> None:
+        """From now on every operator call is bracketed by two CUDA events on the launching stream
+        and ``take_timings`` reports the device time by class of kernels.  Operators that only chain
+        others (projection, rotation and attention of a mixer) are not timed themselves, their links
+        are; of nested timed operators the outermost counts.  Not for captured steps: events recorded
+        inside a capture measure nothing."""
+        if getattr(self, "_timed", None) is not None:
+            return
+        self._timed, self._timing_depth = [], 0
+        for name, cls in self.KERNEL_CLASSES.items():
+            setattr(self, name, self._timed_operator(getattr(self, name), cls))
+
+    def _timed_operator(self, fn, cls):
+        def call(*args, **kwargs):
+            if self._timing_depth:
+                return fn(*args, **kwargs)
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self._timing_depth += 1
+            try:
+                start.record()
+                out = fn(*args, **kwargs)
+                end.record()
+            finally:
+                self._timing_depth -= 1
+            self._timed.append((cls, start, end))
+            return out
+        return call
+
+    def take_timings(self) -> dict:
+        """Milliseconds by class of kernels since the last call (waits for the device); {} when timing is off."""
+        if getattr(self, "_timed", None) is None:
+            return {}
+        torch.cuda.synchronize(self.device)
+        out = {}
+        for cls, start, end in self._timed:
+            out[cls] = out.get(cls, 0.0) + start.elapsed_time(end)
+        self._timed = []
+        return out
 
     # ------------------------------------------------------------------ helpers
     def _stream(self) -> int:
@@ -453,8 +548,8 @@ class CudaOps:
         self._want(positions, "positions", torch.int32)
         tokens = q.shape[0]
         out = self.empty((tokens, nq * d), q.dtype)
-        if (q.dtype == torch.bfloat16 and d in (64, 128) and nq // nkv <= 16 and hints is not None
-                and getattr(hints, "decode_items", None) is not None):
+        if (q.dtype == torch.bfloat16 and d in (64, 128) and nq // nkv <= 16 and self._work(hints, "decode_items") is not None
+                and self._work(hints, "prefill_tiles") is not None):
             self._attention_tensor_cores(out, q, cache, block_table, tok_req, positions, nq, nkv, d, page_size, scale,
                                          window, hints)
             return out
@@ -476,9 +571,10 @@ class CudaOps:
         """``rope_kv_write`` followed by ``paged_attention``.  A bfloat16 step of single tokens only
         runs both in the decode attention kernel (rotation over the whole head, head sizes 64 and
         128); everything else takes the two kernels."""
+        dec, tiles = self._work(hints, "decode_items"), self._work(hints, "prefill_tiles")
         fused = (os.environ.get("PTL_FUSED_ROPE", "1") != "0" and qkv.dtype == torch.bfloat16 and d in (64, 128)
-                 and nq // nkv <= 16 and hints is not None and getattr(hints, "decode_items", None) is not None
-                 and getattr(hints, "n_decode", 0) == qkv.shape[0] and not getattr(hints, "n_prefill_tiles", 0)
+                 and nq // nkv <= 16 and dec is not None and tiles is not None
+                 and dec.items == qkv.shape[0] and not tiles.items
                  and (inv_freq is None or rot == d) and qkv.shape[1] >= (nq + 2 * nkv) * d)
         if not fused:
             self.rope_kv_write(qkv, positions, inv_freq, rot, slots if write else None, cache if write else None,
@@ -537,16 +633,23 @@ class CudaOps:
             N = w_qkv.shape[0]
             table = self._rope_table(positions, inv_freq, d // 2)
             qkv = self.empty((M, N), torch.bfloat16)          # only the q columns are written (and read)
-            rc = self.lib.ptl_gemm_tc_bf16_qkv_rope(_p(qkv), _p(x), _p(w_qkv), M, N, K, _p(self._tc_status_word()), _p(table),
-                                                    _p(slots), _p(cache), nq, nkv, d, page_size,
-                                                    cache.shape[0] * page_size, self._stream())
-            if rc != -2:
-                self._check(rc)
+            if self._qkv_rope_product(qkv, x, w_qkv, table, slots, cache, nq, nkv, d, page_size):
                 return self.paged_attention(qkv, cache, block_table, tok_req, positions, nq, nkv, d, page_size, scale,
                                             window=window, splits=splits, hints=hints)
         qkv = self.linear(x, w_qkv)
         return self.rope_attention(qkv, positions, inv_freq, rot, slots, cache, block_table, tok_req, nq, nkv, d, page_size,
                                    scale, window=window, splits=splits, hints=hints, write=write)
+
+    def _qkv_rope_product(self, qkv, x, w_qkv, table, slots, cache, nq, nkv, d, page_size) -> bool:
+        """The q|k|v projection with rotary encoding and the cache write in its epilogue; False where the kernel does not take the sizes."""
+        M, K = x.shape
+        rc = self.lib.ptl_gemm_tc_bf16_qkv_rope(_p(qkv), _p(x), _p(w_qkv), M, w_qkv.shape[0], K, _p(self._tc_status_word()), _p(table),
+                                                _p(slots), _p(cache), nq, nkv, d, page_size,
+                                                cache.shape[0] * page_size, self._stream())
+        if rc == -2:
+            return False
+        self._check(rc)
+        return True
 
     DECODE_BLOCKS = int(os.environ.get("PTL_DECODE_BLOCKS", "592"))    # blocks the decode attention aims for: the four per SM that fit at once
 
@@ -558,9 +661,11 @@ class CudaOps:
         longer portions through the tiled prompt kernel; both write their rows of ``out``."""
         stream = self._stream()
         num_pages = cache.shape[0]
-        if hints.n_decode:
+        dec, tiles = hints.work["decode_items"], hints.work["prefill_tiles"]
+        n_decode, n_tiles = dec.items, tiles.items
+        if n_decode:
             longest = min(hints.max_ctx_len, window) if window else hints.max_ctx_len
-            pairs = hints.n_decode * nkv
+            pairs = n_decode * nkv
             # small batches: 128-key tiles at two blocks per SM (296 in flight); large ones: 64-key tiles, four per SM
             target = 296 if pairs <= 148 else self.DECODE_BLOCKS
             splits = max(1, min(target // pairs, -(-longest // 128)))
@@ -580,32 +685,32 @@ class CudaOps:
                     if getattr(self, "_decode_counters", None) is None:
                         self._decode_counters = torch.zeros(self._DECODE_COUNTERS, dtype=torch.int32, device=self.device)
                     counters = self._decode_counters        # the last block of a token's splits merges them in the kernel
-            items = None if getattr(hints, "decode_in_order", False) else _p(hints.decode_items)
+            items = None if dec.in_order else _p(dec.tensor)
             if rope is not None:
                 rc = self.lib.ptl_decode_attention_rope_bf16(
                     _p(out), _p(part_acc), _p(part_ml), _p(q), _p(cache), _p(block_table), items, _p(tok_req),
-                    _p(positions), hints.n_decode, q.shape[1], nq * d, block_table.shape[1], nq, nkv, d, page_size,
+                    _p(positions), n_decode, q.shape[1], nq * d, block_table.shape[1], nq, nkv, d, page_size,
                     float(scale), int(window), splits, num_pages, _p(counters), _p(rope[0]), _p(rope[1]), stream)
             else:
                 rc = self.lib.ptl_decode_attention_bf16(
                     _p(out), _p(part_acc), _p(part_ml), _p(q), _p(cache), _p(block_table), items, _p(tok_req),
-                    _p(positions), hints.n_decode, q.shape[1], nq * d, block_table.shape[1], nq, nkv, d, page_size,
+                    _p(positions), n_decode, q.shape[1], nq * d, block_table.shape[1], nq, nkv, d, page_size,
                     float(scale), int(window), splits, num_pages, _p(counters), stream)
             group = nq // nkv
-            in_cluster = (hints.n_decode * nkv * splits <= 296 and 2 <= splits <= 8
+            in_cluster = (n_decode * nkv * splits <= 296 and 2 <= splits <= 8
                           and splits * 4 * -(-group // splits) * (d + 2) * 4 <= 16 * 1024)     # as launch_decode decides
             self._check(rc, kernels=2 if splits > 1 and counters is None and not in_cluster else 1)
-        if hints.n_prefill_tiles:
+        if n_tiles:
             if os.environ.get("PTL_PREFILL_TC", "1") != "0":
                 rc = self.lib.ptl_prefill_attention_tc_bf16(
-                    _p(out), _p(q), _p(cache), _p(block_table), _p(hints.prefill_tiles), hints.n_prefill_tiles, q.shape[0],
+                    _p(out), _p(q), _p(cache), _p(block_table), _p(tiles.tensor), n_tiles, q.shape[0],
                     q.shape[1], nq * d, block_table.shape[1], nq, nkv, d, page_size, float(scale), int(window), num_pages,
                     _p(self._tc_status_word()), stream)
                 if rc != -2:          # -2: sizes the tcgen05 kernel leaves to the warp-level one
                     self._check(rc)
                     return
             self._check(self.lib.ptl_prefill_attention_bf16(
-                _p(out), _p(q), _p(cache), _p(block_table), _p(hints.prefill_tiles), hints.n_prefill_tiles, q.shape[1],
+                _p(out), _p(q), _p(cache), _p(block_table), _p(tiles.tensor), n_tiles, q.shape[1],
                 nq * d, block_table.shape[1], nq, nkv, d, page_size, float(scale), int(window), num_pages, stream))
 
     def token_logprobs(self, logits: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:

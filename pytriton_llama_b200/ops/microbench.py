@@ -49,8 +49,7 @@ def run(case: str, reps: int) -> dict:
         rows = torch.arange(batch, dtype=torch.int32, device=dev)
         pos = torch.full((batch,), ctx - 1, dtype=torch.int32, device=dev)
         qkv = torch.randn(batch, (nq + 2 * nkv) * d, device=dev).bfloat16()
-        hints = SimpleNamespace(n_decode=batch, decode_items=rows, n_prefill_tiles=0, prefill_tiles=rows,
-                                max_ctx_len=ctx, decode_in_order=True)
+        hints = ops.hints_for([1] * batch, [ctx] * batch)
         sec = _time(lambda: ops.paged_attention(qkv, cache, table, rows, pos, nq, nkv, d, page, d ** -0.5, hints=hints), reps, ops)
         return {"case": case, "us": sec * 1e6, "bytes": cache.numel() * 2, "GB/s": cache.numel() * 2 / sec / 1e9}
     if case == "decode_step_attention":
@@ -65,8 +64,7 @@ def run(case: str, reps: int) -> dict:
         slots = (rows * per * page + ctx - 1).int()
         inv = (1.0 / (500000.0 ** (torch.arange(0, d, 2, device=dev).float() / d))).contiguous()
         qkv = torch.randn(batch, (nq + 2 * nkv) * d, device=dev).bfloat16()
-        hints = SimpleNamespace(n_decode=batch, decode_items=rows, n_prefill_tiles=0, prefill_tiles=rows,
-                                max_ctx_len=ctx, decode_in_order=True)
+        hints = ops.hints_for([1] * batch, [ctx] * batch)
         sec = _time(lambda: ops.rope_attention(qkv, pos, inv, d, slots, cache, table, rows, nq, nkv, d, page, d ** -0.5,
                                                hints=hints), reps, ops)
         nbytes = cache.numel() * 2
@@ -93,9 +91,7 @@ def run(case: str, reps: int) -> dict:
         rows = torch.zeros(tokens, dtype=torch.int32, device=dev)
         pos = torch.arange(tokens, dtype=torch.int32, device=dev)
         qkv = torch.randn(tokens, (nq + 2 * nkv) * d, device=dev).bfloat16()
-        tiles = torch.tensor([[0, a, 128, a] for a in range(0, tokens, 128)], dtype=torch.int32, device=dev).reshape(-1)   # pairs of consecutive tiles
-        hints = SimpleNamespace(n_decode=0, decode_items=rows[:0], n_prefill_tiles=tokens // 128, prefill_tiles=tiles,
-                                max_ctx_len=tokens, decode_in_order=False)
+        hints = ops.hints_for([tokens], [tokens])
         sec = _time(lambda: ops.paged_attention(qkv, cache, table, rows, pos, nq, nkv, d, page, d ** -0.5, hints=hints), reps, ops)
         flops = 4 * nq * d * tokens * (tokens + 1) // 2
         return {"case": case, "us": sec * 1e6, "flops": flops, "TFLOP/s": flops / sec / 1e12}

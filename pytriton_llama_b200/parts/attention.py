@@ -68,23 +68,34 @@ class GQAttention(Part):
 
     def forward(self, x, ctx, cache, residual=None, next_norm=None):
         ops = self.rt.ops
-        inv_freq, rot = self.position.rotary_table()
-        if inv_freq is None and rot != 0:
-            raise NotImplementedError("a position encoding without a rotary table must rotate q and k itself")
+        table = self.position.rotary_table()
         g = cache.group
         whole = getattr(ops, "projected_rope_attention", None)      # an operator set may run projection, rotation and attention as one
         both = getattr(ops, "rope_attention", None)                 # ... or rotation and attention
+        qkv = None
+        if table is None:
+            # The encoding is no rotation of (j, j + rot/2) pairs by a table of frequencies: it turns
+            # q and k itself (in place, in the projection's output), and the kernels that follow only
+            # store k and v and attend.
+            qkv = ops.linear(x, self.w_qkv)
+            qk_width = (self.heads + self.kv_heads) * self.head_dim
+            self.position.apply(qkv[:, :qk_width], ctx.positions, self.heads + self.kv_heads, self.head_dim)
+            inv_freq, rot, whole = None, 0, None
+        else:
+            inv_freq, rot = table
         if whole is not None:
             o = whole(x, self.w_qkv, ctx.positions, inv_freq, rot, g.slots, cache.kv, g.block_table, ctx.tok_req, self.heads,
                       self.kv_heads, self.head_dim, g.page_size, self.scale, window=self.window,
                       splits=ctx.attn_splits, hints=ctx, write=cache.write)
         elif both is not None:
-            qkv = ops.linear(x, self.w_qkv)
+            if qkv is None:
+                qkv = ops.linear(x, self.w_qkv)
             o = both(qkv, ctx.positions, inv_freq, rot, g.slots, cache.kv, g.block_table, ctx.tok_req, self.heads,
                      self.kv_heads, self.head_dim, g.page_size, self.scale, window=self.window,
                      splits=ctx.attn_splits, hints=ctx, write=cache.write)
         else:
-            qkv = ops.linear(x, self.w_qkv)
+            if qkv is None:
+                qkv = ops.linear(x, self.w_qkv)
             ops.rope_kv_write(qkv, ctx.positions, inv_freq, rot, g.slots if cache.write else None,
                               cache.kv if cache.write else None, self.heads, self.kv_heads, self.head_dim,
                               g.page_size)

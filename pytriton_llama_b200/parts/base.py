@@ -13,9 +13,12 @@ Contracts (``T`` = tokens of the step, all tensors on the runtime's device):
 * norm: ``forward(x, residual, rows=None) -> (y, residual)`` -- adds ``x`` ([T, H], or None when
   the sub-layer before already added its output) into the float32 ``residual`` (None at the first
   layer), returns the normed sum in the compute type;
-* position: ``rotary_table() -> (inv_freq float32 [rot/2], rot)`` or ``None`` when it is not a
-  rotation of the (j, j + rot/2) pairs that the fused cache-write kernel can apply; and
-  ``apply(qk, positions, heads, head_dim)`` for the general case (in place, [T, heads*head_dim]);
+* position: ``rotary_table() -> (inv_freq float32 [rot/2], rot)`` when it is a rotation of the
+  (j, j + rot/2) pairs of every head by position * inv_freq[j], which the kernels apply while they
+  write the cache; ``(None, 0)`` for no encoding at all; ``None`` for anything else, and then the
+  mixer calls ``apply(qk, positions, heads, head_dim)`` on the projected q and k before they are
+  stored (in place; ``qk`` is the [T, heads*head_dim] view of the projection's q and k columns,
+  whose rows are not contiguous);
 * mixer: ``cache_need() -> CacheNeed``; ``forward(x, ctx, cache) -> [T, H]`` where ``ctx`` is the
   step's ``StepContext`` and ``cache`` the ``LayerCacheView`` of the cache entry this run of the
   layer uses (``cache.write`` tells whether this run stores its keys and values);

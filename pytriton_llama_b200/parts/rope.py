@@ -67,7 +67,16 @@ class RotaryPosition(Part):
         return self.inv_freq, self.rot
 
     def apply(self, qk: torch.Tensor, positions: torch.Tensor, heads: int, head_dim: int) -> None:
-        raise NotImplementedError("rotation is applied by the fused cache-write kernel")
+        """Never called by the mixer, which hands ``rotary_table()`` to the kernels that rotate while
+        they write the cache; kept for callers that want the rotation alone (in place)."""
+        half = self.rot // 2
+        ang = positions.to(torch.float32)[:, None] * self.inv_freq[None, :half]
+        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        x = qk.view(qk.shape[0], heads, head_dim) if qk.is_contiguous() else qk.unflatten(1, (heads, head_dim))
+        x1, x2 = x[..., :half].float(), x[..., half:self.rot].float()       # (views of x when it is float32: both results first)
+        y1, y2 = (x1 * cos - x2 * sin).to(qk.dtype), (x2 * cos + x1 * sin).to(qk.dtype)
+        x[..., :half] = y1
+        x[..., half:self.rot] = y2
 
 
 @register_part("position", "none")

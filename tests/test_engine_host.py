@@ -128,25 +128,33 @@ def test_padded_shapes_of_captured_steps(model_folders):
     values per dimension, always room for what the step holds, a spare token row whenever single-token
     items are padded, nothing for steps that are too large or want too many rows, and a shape only
     from its second appearance on."""
+    from types import SimpleNamespace
     from pytriton_llama_b200.engine.engine import _HostBatch
+    from pytriton_llama_b200.ops.cuda import CudaOps
     eng = _engine(model_folders("A"), "A", 16)
+    # the work lists are the CUDA operator set's; its planning is host arithmetic and runs here too
+    plan = lambda q_lens, starts: CudaOps.plan_step(SimpleNamespace(QUERY_TILE=CudaOps.QUERY_TILE), q_lens, starts)
+    eng.ops.WORK_LISTS, eng.ops.plan_step = CudaOps.WORK_LISTS, plan
 
     def batch(q_lens, wants):
         entries = [StepEntry(f"r{i}", [0] * n, []) for i, n in enumerate(q_lens)]
-        return _HostBatch(entries, q_lens, [0] * len(q_lens), [1] * len(q_lens), list(range(len(q_lens))), {}, list(range(wants)))
+        return _HostBatch(entries, q_lens, [0] * len(q_lens), [1] * len(q_lens), list(range(len(q_lens))), {}, list(range(wants)),
+                          work=plan(q_lens, [0] * len(q_lens)))
 
     def shape_of(q_lens, wants=1):
         eng._shape_seen.clear()
         assert eng._shape_bucket(batch(q_lens, wants)) == 0          # the first time a shape is only counted
         return eng._shape_bucket(batch(q_lens, wants))
 
-    assert shape_of([300]) == (384, 1, 0, 2, 1)                       # 300 tokens -> 384, one pair of tiles per 256 rows
-    assert shape_of([30]) == (64, 1, 0, 1, 1)
-    assert shape_of([30], wants=0) == (64, 1, 0, 1, 0)
-    assert shape_of([1000, 1, 1, 1], wants=4) == (1024, 4, 4, 4, 1)   # 1,003 tokens: 21 spare rows for the fourth, padded item
-    t_pad, r_pad, d_pad, pairs, _ = shape_of([61, 1, 1, 1], wants=4)  # 64 tokens fill 64 rows: the padded item needs one more
-    assert (t_pad, r_pad, d_pad, pairs) == (128, 4, 4, 1)
-    assert shape_of([62, 1, 1], wants=3) == (64, 4, 2, 1, 1)          # no item is padded: no spare row needed
+    def shape(t_pad, r_pad, wants, items, tiles):
+        return (t_pad, r_pad, wants, (("decode_items", items), ("prefill_tiles", tiles)))
+
+    assert shape_of([300]) == shape(384, 1, 1, 0, 4)                  # 300 tokens -> 384, one pair of tiles per 256 rows
+    assert shape_of([30]) == shape(64, 1, 1, 0, 2)
+    assert shape_of([30], wants=0) == shape(64, 1, 0, 0, 2)
+    assert shape_of([1000, 1, 1, 1], wants=4) == shape(1024, 4, 1, 4, 8)   # 1,003 tokens: 21 spare rows for the fourth, padded item
+    assert shape_of([61, 1, 1, 1], wants=4) == shape(128, 4, 1, 4, 2)      # 64 tokens fill 64 rows: the padded item needs one more
+    assert shape_of([62, 1, 1], wants=3) == shape(64, 4, 1, 2, 2)          # no item is padded: no spare row needed
     assert shape_of([1025]) == 0 and shape_of([500, 600]) == 0        # more than 1,024 tokens
     assert shape_of([40], wants=2) == 0                               # more wanted rows than padded requests
     eng._shape_captures = eng.GRAPH_MAX_CAPTURES                       # a workload that has captured again and again: no new shapes
@@ -154,9 +162,16 @@ def test_padded_shapes_of_captured_steps(model_folders):
     eng._shape_captures = 0
     for q_lens in ([5, 1, 300, 1, 1], [2, 2], [257], [256, 1]):
         b = batch(q_lens, len(q_lens))
-        t_pad, r_pad, d_pad, pairs, _ = shape_of(q_lens, len(q_lens))
-        assert t_pad >= b.T and r_pad >= b.R and d_pad >= len(b.dec_items) and 2 * pairs >= len(b.pf_tiles) // 4
-        assert d_pad == len(b.dec_items) or t_pad > b.T
+        t_pad, r_pad, _, lists = shape_of(q_lens, len(q_lens))
+        lists = dict(lists)
+        assert t_pad >= b.T and r_pad >= b.R
+        assert lists["decode_items"] >= len(b.work["decode_items"]) and lists["prefill_tiles"] >= len(b.work["prefill_tiles"]) // 4
+        assert lists["decode_items"] == len(b.work["decode_items"]) or t_pad > b.T
+    # an operator set without work lists (the plain one of the tests) pads tokens and requests only
+    del eng.ops.WORK_LISTS, eng.ops.plan_step
+    eng._shape_seen.clear()
+    plain = _HostBatch([StepEntry("r0", [0] * 30, [])], [30], [0], [1], [0], {}, [0])
+    assert eng._shape_bucket(plain) == 0 and eng._shape_bucket(plain) == (64, 1, 1, ())
 
 
 def test_rope_parts_with_equal_parameters_share_their_table():
@@ -173,3 +188,37 @@ def test_rope_parts_with_equal_parameters_share_their_table():
     assert a.inv_freq is b.inv_freq
     assert a.inv_freq is not c.inv_freq and a.inv_freq is not d.inv_freq
     assert not torch.equal(a.inv_freq, d.inv_freq)
+
+
+def test_a_position_part_without_a_table_rotates_q_and_k_itself(tmp_path):
+    """A position encoding that is no rotation of (j, j + rot/2) pairs answers ``rotary_table()``
+    with None; the mixer then calls its ``apply`` on the projected q and k before they are stored.
+    Interleaved-pair rotary, registered by the test, against a plain float64 statement (the GPU test
+    of the same name in test_gpu_parts.py runs it through the kernels)."""
+    import test_gpu_parts as toys
+    from pytriton_llama_b200.config import LlamaConfig, register_architecture
+    from pytriton_llama_b200.models.llama import llama_spec
+    from pytriton_llama_b200.parts import PartSpec
+    from pytriton_llama_b200.weights import read_folder, write_random_model
+    toys._register_toy_interleaved_rotary()
+    cfg = dict(TINY["B"], architectures=["ToyInterleavedHostForCausalLM"])
+
+    def spec(c, norm_init="ones"):
+        sp = llama_spec(LlamaConfig.from_dict(cfg), norm_init="ones_jitter")
+        for layer in sp.layers:
+            layer.parts["mixer"].parts["position"] = PartSpec("toy_interleaved_rotary", {"head_dim": LlamaConfig.from_dict(cfg).head_dim})
+        return sp
+
+    register_architecture("ToyInterleavedHostForCausalLM", LlamaConfig.from_dict, spec)
+    folder = write_random_model(tmp_path / "interleaved", cfg, seed=13, dtype=torch.float32, std=0.08)
+    w = {k: v.double() for k, v in read_folder(folder).items()}
+    seqs = {f"p{i}": random_tokens(n, 384, 170 + i) for i, n in enumerate([37, 9, 50])}
+    ref = {r: toys._plain_interleaved_forward(cfg, w, s) for r, s in seqs.items()}
+    eng = Engine(folder, EngineConfig(dtype="float32", page_size=8, max_gpu_num_blocks=24, max_seq_len=128, max_num_seqs=3),
+                 device="cpu", ops=TorchOps())
+    got = traces.replay(eng, traces.mixed(seqs, live=3))
+    for r in seqs:
+        assert (got[r].double() - ref[r]).abs().max() < FP32_TOL, r
+    # and the plain statement really depends on the pairing: rotate-half gives other logits
+    plain = plain_llama.forward(dict(cfg, rope_theta=100.0, rope_scaling=None), w, seqs["p0"])
+    assert (plain - ref["p0"]).abs().max() > 1e-2

@@ -308,3 +308,164 @@ def test_requests_that_arrive_while_others_decode(model_folders):
         runs.append({tuple(r.prompt): list(r.output) for r in reqs})
     assert runs[0] == runs[1]
     assert len(runs[0]) == len(prompts) and all(1 <= len(o) <= 20 for o in runs[0].values())
+
+
+def _assert_tokens_within_rounding_of_plain(cfg, w, prompts, outputs, min_agree=0.8):
+    """bfloat16 may pick another token where two logits nearly tie: every generated token must be
+    within rounding of the best logit of the plain model fed with the same history."""
+    agree = total = 0
+    for p, out in zip(prompts, outputs):
+        logits = plain_llama.forward(cfg, w, list(p) + list(out))
+        top = float(logits.abs().max())
+        for i, tok in enumerate(out):
+            row = logits[len(p) + i - 1]
+            assert row[tok] >= row.max() - 0.04 * top, (len(p), i, tok)
+            agree += int(tok == int(row.argmax()))
+            total += 1
+    assert agree >= min_agree * total, (agree, total)
+
+
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_scheduler_on_the_bfloat16_tensor_core_path(model_folders, name):
+    """The path the benchmark times, through the scheduler: head sizes 64 and 128 in bfloat16, so
+    the tcgen05 prompt attention, the split-key decode attention with rotary encoding folded in,
+    captured decode graphs and captured mixed shapes, the device-side hand-over of sampled tokens.
+    Roomy and with so few pages that requests are pre-empted and recomputed, overlapped and one
+    step at a time, with requests that arrive while others decode."""
+    from pytriton_llama_b200.sampling import SamplingParams
+    folder = model_folders(name, torch.bfloat16)
+    cfg, w = plain_llama.load_model_folder(folder, dtype=torch.float64)
+    vocab = TINY[name]["vocab_size"]
+    ps = PAGE_SIZE[name]
+    prompts = [random_tokens(n, vocab, 1200 + n) for n in (70, 9, 150, 33, 120, 17, 64, 200)]
+    sp = SamplingParams(temperature=0.0, max_gen_len=24, stop_token_ids=[])
+    roomy = 8 * -(-(200 + 24) // ps)
+    tight = -(-(200 + 24) // ps) + 6                   # the longest request and a little more
+    results = {}
+    for pages in (roomy, tight):
+        for overlap in (True, False):
+            llm = _llm(folder, name, "bfloat16", pages=pages, max_seq_len=256, max_num_seqs=8, max_batched_tokens=64,
+                       overlap_steps=overlap, compiled_model=True)
+            reqs = [llm.add_request(p, sp) for p in prompts[:3]]
+            waiting = list(prompts[3:])
+            steps = 0
+            while True:                                  # the others arrive while these decode
+                for _ in llm.run():
+                    steps += 1
+                    if waiting and steps % 4 == 0:
+                        reqs.append(llm.add_request(waiting.pop(0), sp))
+                if not waiting:
+                    break
+                reqs.append(llm.add_request(waiting.pop(0), sp))
+            llm.engine.check_device_status()
+            llm.engine.cache.check_invariants()
+            assert llm.engine.cache.free_pages() == pages
+            assert all(len(r.output) == 24 and r.finish_reason == "length" for r in reqs)
+            by_prompt = {tuple(r.prompt): list(r.output) for r in reqs}
+            outs = [by_prompt[tuple(p)] for p in prompts]
+            _assert_tokens_within_rounding_of_plain(cfg, w, prompts, outs)
+            kinds = llm.engine._graphs
+            assert any(isinstance(k, int) for k in kinds) and any(isinstance(k, tuple) for k in kinds)
+            if pages == tight:
+                assert sum(r.preemptions for r in reqs) > 0
+            results[(pages, overlap)] = outs
+    # with room for everybody the two modes plan the same steps, which run the same kernels: the same tokens
+    assert results[(roomy, True)] == results[(roomy, False)]
+
+
+@pytest.mark.parametrize("dtype, name", [("bfloat16", "D"), ("float32", "B")])
+def test_more_mixed_shapes_than_captured_graphs_are_kept(model_folders, dtype, name):
+    """Thirty different padded shapes, each stepped three times: the engine keeps at most 24
+    captured graphs (the one used longest ago goes), all in one memory pool, captures evicted
+    shapes again when they come back, and every step's logits equal those of an engine that
+    captures nothing.  The logits handed out survive later steps."""
+    from pytriton_llama_b200.config import EngineConfig
+    from pytriton_llama_b200.engine.engine import Engine, StepEntry
+    folder = model_folders(name, stored_dtype(dtype))
+    vocab = TINY[name]["vocab_size"]
+    lengths = [30, 100, 150, 200, 300, 400, 520, 650, 780, 900]
+    plans = [(L, k) for L in lengths for k in (0, 1, 2)]            # a portion of L tokens beside k single tokens
+    outs = {}
+    for compiled in (False, True):
+        cfg = EngineConfig(dtype=dtype, page_size=PAGE_SIZE[name], max_gpu_num_blocks=-(-1024 // PAGE_SIZE[name]) + 4,
+                           max_seq_len=1024, max_num_seqs=4, max_batched_tokens=1024, compiled_model=compiled, seed=0)
+        eng = Engine(folder, cfg)
+        res, kept = [], []
+        for rnd in range(3):
+            for i, (L, k) in enumerate(plans):
+                entries = [StepEntry("long", random_tokens(L, vocab, 3000 + i), [L - 1])]
+                entries += [StepEntry(f"one{j}", random_tokens(1, vocab, 4000 + 10 * i + j), [0]) for j in range(k)]
+                out = eng.step(entries)
+                kept.append((out.logits, out.logits.clone()))
+                res.append(out.logits.float().cpu())
+                eng.finish_all()
+        eng.check_device_status()
+        for held, copy in kept:                                      # nothing that was handed out has been written again
+            assert torch.equal(held, copy)
+        if compiled:
+            shapes = [g for g in eng._graphs if isinstance(g, tuple)]
+            assert len(shapes) == eng.GRAPH_MAX_SHAPES == 24
+            assert eng._shape_captures > 30                          # the six that had to go were captured again
+        outs[compiled] = res
+    for a, b in zip(outs[False], outs[True]):
+        top = float(a.abs().max())
+        assert float((a - b).abs().max()) <= (1e-5 if dtype == "float32" else 0.03) * top
+
+
+def test_step_statistics_timers_and_a_pool_sized_from_free_memory(model_folders):
+    """``max_gpu_num_blocks=None`` sizes the pool from the memory that is free after the weights
+    (lite_llama/executor/mem_manager.py:98-108), capped at what the requests can ever hold; with
+    ``timing`` every step reports its device time, the pages in use and milliseconds by class of
+    kernels; generation works on such an engine."""
+    from pytriton_llama_b200.config import EngineConfig
+    from pytriton_llama_b200.engine.engine import Engine, StepEntry
+    from pytriton_llama_b200.engine.llm import LLM
+    from pytriton_llama_b200.sampling import SamplingParams
+    name = "B"
+    folder = model_folders(name)
+    ps = PAGE_SIZE[name]
+    cfg = EngineConfig(dtype="float32", page_size=ps, max_gpu_num_blocks=None, max_seq_len=128, max_num_seqs=4, timing=True,
+                       compiled_model=True)
+    llm = LLM(folder, cfg)
+    eng = llm.engine
+    cap = 4 * (128 // ps)
+    rep = eng.memory_report
+    assert rep["pages"] == cap == rep["pages_ever_needed"] and rep["pages_that_fit"] > cap
+    assert eng.cache.free_pages() == cap
+    prompts = [random_tokens(n, 384, 1500 + n) for n in (9, 33, 70)]
+    want = _plain_greedy(folder, prompts, 6, [382, 383])
+    assert llm.generate(prompts, SamplingParams(temperature=0.0, max_gen_len=6)) == want
+    summary = eng.stats.summary()
+    assert summary["steps"] >= 6 and summary["tokens"] >= sum(len(p) for p in prompts)
+    assert summary["step_ms_mean"] > 0 and summary["peak_pages_used"] >= -(-70 // ps)
+    assert {"product", "norm", "attention"} <= set(summary["kernel_ms"]) and all(v > 0 for v in summary["kernel_ms"].values())
+    assert not eng._graphs                                           # timed steps run uncaptured
+    out = eng.step([StepEntry("x", prompts[2], [69]), StepEntry("y", prompts[0][:1], [])])
+    assert out.num_tokens == 71 and out.num_requests == 2
+    assert out.pages_used == -(-70 // ps) + 1 and out.pages_used + out.pages_free == cap
+    assert out.step_ms > 0 and abs(sum(out.kernel_ms.values()) - out.step_ms) < out.step_ms   # the classes add up to about the step
+    eng.finish_all()
+    # a fraction of the free memory that leaves room for ten pages only: the pool is what fits, not the cap
+    free, _ = torch.cuda.mem_get_info()
+    per_page = eng.memory_report["bytes_per_page_all_groups"]
+    small = EngineConfig(dtype="float32", page_size=ps, max_gpu_num_blocks=None, max_seq_len=128, max_num_seqs=4,
+                         gpu_memory_fraction=((2 << 30) + 10.5 * per_page) / free)
+    eng2 = Engine(folder, small)
+    assert 8 <= eng2.memory_report["pages"] <= 10 and eng2.cache.free_pages() == eng2.memory_report["pages"]
+    with pytest.raises(Exception, match="no memory left"):
+        Engine(folder, EngineConfig(dtype="float32", page_size=ps, max_gpu_num_blocks=None, max_seq_len=128, max_num_seqs=4,
+                                    gpu_memory_fraction=1e-6))
+
+
+def test_command_line_prints_statistics(model_folders):
+    folder = model_folders("A")
+    prompt = random_tokens(7, 256, 700)
+    out = subprocess.run([sys.executable, str(ROOT / "cli.py"), "--checkpoints_dir", str(folder), "--dtype", "float32", "--temperature", "0",
+                          "--max_gen_len", "5", "--max_seq_len", "64", "--page_size", "4", "--stats", "--prompt_ids"]
+                         + [str(t) for t in prompt], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [l for l in out.stderr.splitlines() if l.startswith("[stats]")]
+    assert len(lines) == 2 and "cache pool" in lines[0] and '"pages"' in lines[0]
+    import json
+    stats = json.loads(lines[1][len("[stats] "):])
+    assert stats["steps"] >= 5 and stats["step_ms_mean"] > 0 and "product" in stats["kernel_ms"]

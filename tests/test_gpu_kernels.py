@@ -275,20 +275,14 @@ def test_paged_attention_mixed_batch(ops, dtype, nq, nkv, d, page, window, split
 
 
 def _hints(q_lens, ctx):
-    """The work lists the engine hands to the tensor-core attention kernels."""
-    from types import SimpleNamespace
-    dec, tiles, t0 = [], [], 0
-    for r, (n, c) in enumerate(zip(q_lens, ctx)):
-        if n == 1:
-            dec.append(t0)
-        else:
-            for a in range(0, n, 256):                    # pairs: the second tile continues the first or is empty
-                tiles += [r, t0 + a, min(128, n - a), c - n + a]
-                tiles += [r, t0 + a + 128, max(0, min(128, n - a - 128)), c - n + a + 128]
-        t0 += n
-    i32 = lambda x: torch.tensor(x if x else [0], dtype=torch.int32).cuda()
-    return SimpleNamespace(n_decode=len(dec), decode_items=i32(dec)[:len(dec)], n_prefill_tiles=len(tiles) // 4,
-                           prefill_tiles=i32(tiles), max_ctx_len=max(ctx))
+    """The work lists the engine hands to the tensor-core attention kernels, as the operator set plans them."""
+    from pytriton_llama_b200.ops.cuda import CudaOps
+    return CudaOps(torch.device("cuda:0")).hints_for(q_lens, ctx)
+
+
+def _work(tensor, items, in_order=False):
+    from pytriton_llama_b200.ops.worklists import StepWork
+    return StepWork(tensor, items, in_order)
 
 
 @pytest.mark.parametrize("nq, nkv, d, page, window", [
@@ -374,8 +368,7 @@ def test_decode_attention_padding_rows_named_several_times_leave_the_counters_cl
     padded_req = full_req.clone()
     padded_req[real] = -1
     hints = _hints([1] * n_rows, ctx)
-    hints.decode_items = torch.tensor(list(range(real)) + [real] * 12, dtype=torch.int32).cuda()
-    hints.n_decode = real + 12
+    hints.work["decode_items"] = _work(torch.tensor(list(range(real)) + [real] * 12, dtype=torch.int32).cuda(), real + 12)
     hints.decode_splits = 2
     dev = (q.cuda(), cache.cuda(), bt.cuda())
     for _ in range(2):
@@ -473,12 +466,12 @@ def test_attention_finds_one_far_key(ops, dtype, window):
         qd = q.reshape(T, nq * d).to(DT[dtype]).cuda()
         bt6 = bt.repeat(T, 1).cuda()
         req6 = torch.arange(T, dtype=torch.int32).cuda()
-        dec = SimpleNamespace(n_decode=T, decode_items=req6, n_prefill_tiles=0, prefill_tiles=req6, max_ctx_len=ctx)
+        dec = SimpleNamespace(work={"decode_items": _work(req6, T), "prefill_tiles": _work(req6[:0], 0)}, max_ctx_len=ctx)
         outs.append(ops.paged_attention(qd, cache.cuda(), bt6, req6, positions.cuda(), nq, nkv, d, page, 1 / math.sqrt(d),
                                         window=window, hints=dec).float().cpu().view(T, nq, d))
         tiles = torch.tensor([[t, t, 1, int(positions[t]), t, t + 128, 0, int(positions[t]) + 128] for t in range(T)],
                              dtype=torch.int32).reshape(-1).cuda()          # pairs whose second tile is empty
-        pf = SimpleNamespace(n_decode=0, decode_items=req6[:0], n_prefill_tiles=2 * T, prefill_tiles=tiles, max_ctx_len=ctx)
+        pf = SimpleNamespace(work={"decode_items": _work(req6[:0], 0), "prefill_tiles": _work(tiles, 2 * T)}, max_ctx_len=ctx)
         outs.append(ops.paged_attention(qd, cache.cuda(), bt6, req6, positions.cuda(), nq, nkv, d, page, 1 / math.sqrt(d),
                                         window=window, hints=pf).float().cpu().view(T, nq, d))
     for res in outs:
@@ -576,8 +569,8 @@ def test_decode_attention_with_rope_and_cache_write_folded_in(ops, nq, nkv, d, p
     slots = torch.tensor([int(bt[i, (n - 1) // page]) * page + (n - 1) % page for i, n in enumerate(lens)], dtype=torch.int32).cuda()
     tok_req = torch.arange(B, dtype=torch.int32).cuda()
     inv = (1.0 / (10000.0 ** (torch.arange(0, d, 2).float() / d))).cuda() if rotate else None
-    hints = SimpleNamespace(n_decode=B, decode_items=tok_req, decode_in_order=True, n_prefill_tiles=0,
-                            prefill_tiles=tok_req, max_ctx_len=max(lens))
+    hints = SimpleNamespace(work={"decode_items": _work(tok_req, B, in_order=True), "prefill_tiles": _work(tok_req[:0], 0)},
+                            max_ctx_len=max(lens))
     # the two kernels
     qkv_a, cache_a = qkv0.clone().cuda(), cache0.clone().cuda()
     ops.rope_kv_write(qkv_a, pos, inv, d if rotate else 0, slots, cache_a, nq, nkv, d, page)
@@ -634,4 +627,41 @@ def test_product_prepares_the_next_norm_and_the_next_product_finishes_it(ops, M,
     want = g * torch.sigmoid(g) * u
     assert (act.double().cpu() - want).abs().max() <= 2 ** -5 * float(want.abs().max())
     assert (ops.linear(normed, w2.cuda()).double().cpu() - ref).abs().max() <= 2 ** -6 * float(ref.abs().max())
+    assert ops.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("M, N, K", [(100, 128, 256), (8, 128, 128), (40, 96, 192)])
+def test_a_wait_that_runs_out_sets_the_status_and_the_kernel_returns(_ops, M, N, K):
+    """Every wait inside the tcgen05 product is bounded.  The library's self-test entry point launches
+    the product as one block whose first stage is never filled and whose waits give up after 300
+    polls: the kernel must come back by itself, the status word must say which wait gave up (2: for
+    a full stage), the operator set must turn it into an error, and the very next product on the same
+    device must be right -- tensor memory was freed, nothing is left in flight."""
+    import ctypes
+    from pytriton_llama_b200.ops.cuda import KernelError
+    ops = _ops
+    assert ops.gemm_tc_status() == 0
+    lib = ops.lib
+    lib.ptl_gemm_tc_wait_selftest.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_uint, ctypes.c_void_p]
+    lib.ptl_gemm_tc_wait_selftest.restype = ctypes.c_int
+    x, w = rnd((M, K), torch.bfloat16, 61).cuda(), rnd((N, K), torch.bfloat16, 62).cuda()
+    out = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    status = ops._tc_status_word()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    rc = lib.ptl_gemm_tc_wait_selftest(out.data_ptr(), x.data_ptr(), w.data_ptr(), M, N, K, status.data_ptr(), 300,
+                                       torch.cuda.current_stream().cuda_stream)
+    end.record()
+    assert rc == 0, lib.ptl_last_error().decode()
+    torch.cuda.synchronize()                                          # returns: the kernel ended by itself
+    assert start.elapsed_time(end) < 500.0                            # ... within its bounded waits (milliseconds)
+    assert int(status.item()) == 2
+    with pytest.raises(KernelError, match="gave up"):
+        ops.check_status()
+    assert ops.gemm_tc_status() == 0                                  # reading the word cleared it
+    # sizes that would make more than one block are refused: nothing else may be left waiting
+    assert lib.ptl_gemm_tc_wait_selftest(out.data_ptr(), x.data_ptr(), w.data_ptr(), 300, N, K, status.data_ptr(), 300, None) == -1
+    for _ in range(2):
+        got = ops.gemm_tc(x, w, ops.EPI_F32)
+        close(got, x.float() @ w.float().T, "float32", "the product after the self-test", scale=float(K) ** 0.5 * 50)
     assert ops.gemm_tc_status() == 0

@@ -473,3 +473,98 @@ def test_toy_routed_feed_forward_and_toy_position_encoding(tmp_path, dtype):
     got = traces.replay(eng, traces.mixed(seqs, live=3))
     for r in seqs:
         assert_close(got[r], ref[r], dtype, r)
+
+
+# ---------------------------------------------------------------------------------------------
+# A position encoding that is no rotation of (j, j + rot/2) pairs: neighbouring elements
+# (2j, 2j+1) are turned together.  The kernels cannot apply it from a table of frequencies, so the
+# part says so (``rotary_table()`` is None) and the mixer calls its ``apply`` on q and k before the
+# kernels store and attend.
+
+def _register_toy_interleaved_rotary():
+    from pytriton_llama_b200.parts import Part, register_part
+
+    @register_part("position", "toy_interleaved_rotary")
+    class ToyInterleavedRotary(Part):
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            d = spec.params["head_dim"]
+            self.inv_freq = (1.0 / (100.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(runtime.device)
+
+        def rotary_table(self):
+            return None
+
+        def apply(self, qk, positions, heads, head_dim):
+            ang = positions.to(torch.float32)[:, None] * self.inv_freq[None, :]
+            cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+            x = qk.unflatten(1, (heads, head_dim))             # a view of the projection's columns
+            even, odd = x[..., 0::2].float(), x[..., 1::2].float()       # (views of x when it is float32: both results first)
+            new_even, new_odd = (even * cos - odd * sin).to(qk.dtype), (odd * cos + even * sin).to(qk.dtype)
+            x[..., 0::2] = new_even
+            x[..., 1::2] = new_odd
+
+
+def _plain_interleaved_forward(cfg, w, tokens):
+    tokens = torch.as_tensor(tokens)
+    S = len(tokens)
+    nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    d = plain_llama.head_dim_of(cfg)
+    inv_freq = 1.0 / (100.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    ang = (torch.arange(S).float()[:, None] * inv_freq[None, :]).double()
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+    def turn(x):                                               # x [S, heads, d]
+        out = torch.empty_like(x)
+        out[..., 0::2] = x[..., 0::2] * cos - x[..., 1::2] * sin
+        out[..., 1::2] = x[..., 1::2] * cos + x[..., 0::2] * sin
+        return out
+
+    h = w["model.embed_tokens.weight"][tokens]
+    eps = cfg["rms_norm_eps"]
+    for layer in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{layer}."
+        x = plain_llama.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+        q = turn((x @ w[p + "self_attn.q_proj.weight"].T).view(S, nq, d))
+        k = turn((x @ w[p + "self_attn.k_proj.weight"].T).view(S, nkv, d))
+        v = (x @ w[p + "self_attn.v_proj.weight"].T).view(S, nkv, d)
+        h = h + plain_llama.causal_gqa_attention(q, k, v).reshape(S, nq * d) @ w[p + "self_attn.o_proj.weight"].T
+        x = plain_llama.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
+        h = h + plain_llama.swiglu_ffn(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    h = plain_llama.rms_norm(h, w["model.norm.weight"], eps)
+    return h @ w.get("lm_head.weight", w["model.embed_tokens.weight"]).T
+
+
+@pytest.mark.parametrize("dtype, name", [("float32", "B"), ("bfloat16", "D")])
+def test_toy_position_encoding_that_the_kernels_cannot_apply(tmp_path, dtype, name):
+    """Interleaved-pair rotary registered from here: the mixer hands q and k to the part's ``apply``
+    and the kernels only store and attend -- prompts in portions, single tokens (in bfloat16 with
+    head size 64 through the decode kernel that otherwise rotates itself) and captured graphs."""
+    import traces
+    from pytriton_llama_b200.config import EngineConfig, LlamaConfig, register_architecture
+    from pytriton_llama_b200.engine.engine import Engine
+    from pytriton_llama_b200.models.llama import llama_spec
+    from pytriton_llama_b200.parts import PartSpec
+    from pytriton_llama_b200.weights import read_folder, write_random_model
+    _register_toy_interleaved_rotary()
+    cfg = dict(TINY[name], architectures=["ToyInterleavedForCausalLM"])
+
+    def spec(c, norm_init="ones"):
+        sp = llama_spec(LlamaConfig.from_dict(cfg), norm_init="ones_jitter")
+        for layer in sp.layers:
+            layer.parts["mixer"].parts["position"] = PartSpec("toy_interleaved_rotary", {"head_dim": LlamaConfig.from_dict(cfg).head_dim})
+        return sp
+
+    register_architecture("ToyInterleavedForCausalLM", LlamaConfig.from_dict, spec)
+    stored = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = write_random_model(tmp_path / "interleaved", cfg, seed=13, dtype=stored, std=0.08)
+    w = {k: v.double() for k, v in read_folder(folder).items()}
+    vocab = cfg["vocab_size"]
+    seqs = {f"p{i}": random_tokens(n, vocab, 170 + i) for i, n in enumerate([37, 9, 150, 18])}
+    ref = {r: _plain_interleaved_forward(cfg, w, s) for r, s in seqs.items()}
+    for graphs in (False, True):
+        eng = Engine(folder, EngineConfig(dtype=dtype, page_size=16, max_gpu_num_blocks=24, max_seq_len=256, max_num_seqs=3,
+                                          compiled_model=graphs))
+        got = traces.replay(eng, traces.mixed(seqs, live=3, decode_tail=12))
+        for r in seqs:
+            assert_close(got[r], ref[r], dtype, f"{r} graphs={graphs}")
+        eng.check_device_status()
