@@ -49,11 +49,12 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
                         int out_stride, int bt_stride, int nq, int nkv, int page_size, float scale_log2,
                         int window, int splits, int num_pages, int page_shift, int* __restrict__ counters,
                         int cluster_merge, int fused, const float* __restrict__ inv_freq,
-                        const int* __restrict__ slots) {
+                        const int* __restrict__ slots, unsigned long long* timeline) {
   using Cfg = DecodeCfg<D, KP>;
   constexpr int kDecKeys = Cfg::kKeys;
   constexpr int kDecKP = KP;
   extern __shared__ __align__(128) unsigned char smem[];
+  if (threadIdx.x == 0 && timeline) { timeline_stamp(timeline, 0); if (blockIdx.x == 0) timeline[0] = 1; }
   // with a cluster, peers write into this block's shared memory later on: none may do so before
   // every block runs, which the wait that matches this arrival establishes
   if (cluster_merge) cluster_arrive();
@@ -154,6 +155,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   }
   pdl_wait();
   pdl_launch_dependents();
+  if (tid == 0) timeline_stamp(timeline, 1);
   // With `fused`, the block whose key range ends at position p owns the token's new key and
   // value: it rotates the key, sends both to the cache (for later steps; nothing in this step waits
   // for that) and keeps them in shared memory to put them into its last tile, whose copy from the
@@ -226,6 +228,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   for (int tile = 0; tile < ntiles; ++tile) {
     cp_async_wait<Cfg::kStages - 2>();
     __syncthreads();
+    if (tile == 0 && tid == 0) timeline_stamp(timeline, 2);
     {
       const int nxt = tile + Cfg::kStages - 1;
       if (nxt < ntiles) load_tile(nxt, nxt % Cfg::kStages);
@@ -321,6 +324,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   }
   cp_async_wait<0>();
   __syncthreads();
+  if (tid == 0) timeline_stamp(timeline, 3);
 
   if (cluster_merge) {
     // ---- the splits of this (token, kv head) are the blocks of a cluster.  Row r of the group
@@ -343,6 +347,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     }
     cluster_arrive();
     cluster_wait();
+    if (tid == 0) timeline_stamp(timeline, 4);
     const int nsrc = splits * kDecWarps;
     for (int e = tid; e < rows_own * D; e += kDecWarps * 32) {
       const int rloc = e / D, col = e % D;
@@ -359,6 +364,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
       }
       out[(size_t)t * out_stride + (size_t)(kvh * G + row) * D + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     }
+    if (tid == 0) timeline_stamp(timeline, 5);
     return;
   }
 
@@ -542,7 +548,7 @@ int launch_decode(void* out, float* part_acc, float* part_ml, const void* q, con
                                  (__nv_bfloat16*)out, part_acc, part_ml, (const __nv_bfloat16*)q,
                                  (const __nv_bfloat16*)cache, block_table, items, tok_req, positions, q_stride, out_stride, bt_stride,
                                  nq, nkv, page_size, scale * 1.4426950408889634f, window, splits, num_pages, page_shift, counters,
-                                 cluster ? 1 : 0, fused, inv_freq, slots);
+                                 cluster ? 1 : 0, fused, inv_freq, slots, timeline_slot());
   if (rc) return rc;
   if (cluster) return 0;
   if (splits > 1 && counters == nullptr)

@@ -128,6 +128,33 @@ inline int& pdl_flag() {
   return enabled;
 }
 
+// ---------------------------------------------------------------- timeline of a step (measurements only)
+// Between ptl_timeline_begin(buffer, slots) and ptl_timeline_end() the launchers of the decode
+// step's kernels hand every launch a slot of 16 words of `buffer` (device memory), and the first and
+// the last block of the grid write %globaltimer there at fixed points: word 0 the kind of kernel,
+// words 1..7 the first block's stamps, 8..14 the last block's.  Stamps: 0 block entered, 1 the wait on
+// the predecessor returned, 2 first operands arrived, 3 main loop done, 4 accumulators / partial
+// results complete, 5 block done.  Outside such a bracket the slot is null and the kernels skip it.
+struct TimelineState { unsigned long long* buf; int capacity; int next; };
+inline TimelineState& timeline_state() {
+  static TimelineState s = {nullptr, 0, 0};
+  return s;
+}
+inline unsigned long long* timeline_slot() {
+  TimelineState& s = timeline_state();
+  if (!s.buf || s.next >= s.capacity) return nullptr;
+  return s.buf + 16 * (size_t)s.next++;
+}
+__device__ __forceinline__ void timeline_stamp(unsigned long long* slot, int idx) {
+  if (!slot) return;
+  const unsigned block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  const unsigned last = gridDim.x * gridDim.y * gridDim.z - 1;
+  if (block != 0 && block != last) return;
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  slot[1 + (block == 0 ? 0 : 7) + idx] = t;
+}
+
 // One rotary pair: (x1, x2) turned by the angle whose cosine and sine are given.  Products and sums
 // are rounded one by one (no fused multiply-add), so that every kernel that rotates gets the same bits.
 __device__ __forceinline__ void rope_rotate(float x1, float x2, float c, float s, float& o1, float& o2) {

@@ -93,6 +93,8 @@ static int gemm_tc_impl(void* out, const void* X, const void* W, int M, int N, i
   p.out = out; p.status = status;
   p.K = K; p.ld_out = ld_out;
   p.poll_limit = poll_limit; p.withhold_first_load = withhold_first_load;
+  p.timeline = M <= 64 ? timeline_slot() : nullptr;      // (measurements of the decode step)
+  p.timeline_kind = 10 + epi;
   if (xs) {
     if (epi != 2 || N % 32 != 0 || ld_out % 4 != 0) return -2;
     PTL_REQUIRE(norm_w && sumsq && slots_out, "gemm_tc: the next norm's input needs its weight, the sums and a place for their count");

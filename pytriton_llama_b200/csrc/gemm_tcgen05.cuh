@@ -80,6 +80,8 @@ struct GemmParams {
   // run out, and the test sees the status word, the drained roles and the block's clean exit.
   uint32_t poll_limit;
   int withhold_first_load;
+  unsigned long long* timeline;   // measurements: where the first and the last block stamp %globaltimer (null: nowhere)
+  int timeline_kind;
 };
 
 // PAIR: two blocks on the SMs of one TPC work as one (cta_group::2): an MMA of 256 token rows x BN
@@ -192,14 +194,15 @@ __device__ __forceinline__ float half_warp_sum(float v) {
 // The add epilogue for one feature n and token tok with few tokens; `have` is what the residual
 // held if the caller fetched it already.  With p.xs the next norm's input goes out too; every lane of the
 // warp must call this, the lanes of a half warp with the same token and 16 consecutive features.
-__device__ __forceinline__ void add_and_emit(const GemmParams& p, int n, int tok, float v, bool fetched, float have, int lane) {
+__device__ __forceinline__ void add_and_emit(const GemmParams& p, int n, int tok, float v, bool fetched, float have, int lane,
+                                             float norm_w = 0.f) {
   const bool valid = n < p.rows && tok < p.cols;
   float r = 0.f;
   if (valid) {
     float* o = (float*)p.out + (size_t)tok * p.ld_out + n;
     r = (fetched ? have : __ldcg(o)) + v;
     *o = r;
-    if (p.xs) p.xs[(size_t)tok * p.xs_ld + n] = __float2bfloat16_rn(r * __ldg(p.norm_w + n));
+    if (p.xs) p.xs[(size_t)tok * p.xs_ld + n] = __float2bfloat16_rn(r * (fetched ? norm_w : __ldg(p.norm_w + n)));
   }
   if (p.xs) {
     const float sq = half_warp_sum(r * r);
@@ -278,6 +281,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
   float* s_scale = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes + 256);   // few tokens: scale of each token
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0 && p.timeline) { timeline_stamp(p.timeline, 0); if (blockIdx.x == 0 && blockIdx.y == 0) p.timeline[0] = p.timeline_kind; }
   const int num_kb = (p.K + kTileK - 1) / kTileK;
   // swapped mode: one tile per block (blockIdx.x = row tile, blockIdx.y = K split);
   // normal mode: the block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (token tiles fastest)
@@ -367,6 +371,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     }
     pdl_wait();                // (few tokens: the tokens of those stages are requested by the MMA issuers, each for its own stages)
     pdl_launch_dependents();
+    timeline_stamp(p.timeline, 1);
     if (!p.swapped) {
       for (int i = 0; i < pre; ++i) {
         const uint32_t dst = smem_base + i * Cfg::kStageBytes;
@@ -423,6 +428,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       for (int i = issuer; i < my_kb; i += Cfg::kAccWays) {
         const int s = i % Cfg::kStages;
         if (!mbar_wait(full_bar(s), (i / Cfg::kStages) & 1, abort_flag, p.status, 2, p.poll_limit)) break;
+        if (i == 0) timeline_stamp(p.timeline, 2);
         tcgen05_fence_after();
         const uint32_t a = smem_base + s * Cfg::kStageBytes;
         const uint32_t b = a + Cfg::kRowBytes;
@@ -432,6 +438,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
         tcgen05_commit(empty_bar(s));      // the stage is free once these MMAs have read it
       }
       tcgen05_commit(acc_full(0));         // this issuer's accumulator is complete (also when it had nothing to do)
+      if (issuer == 0) timeline_stamp(p.timeline, 3);
     }
   } else if (warp == 1 && lane == 0 && pair_rank == 0) {
     // ------------------------------------------------------------ MMA issuer, many tokens (of a pair: the even block's)
@@ -528,6 +535,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       }
       float ss = 0.f;                          // sum of squares of this thread's share of its row (add epilogue, emitting)
       if (!mbar_wait(acc_full(buf), use & 1, abort_flag, p.status, 3, p.poll_limit)) break;
+      if (warp == 2 && lane == 0 && lt == 0) timeline_stamp(p.timeline, 4);
       tcgen05_fence_after();
       const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
       if (!p.swapped && row_tile * kTileRows >= p.rows) {
@@ -710,12 +718,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       r = EPI == 3 ? 2 * (idx % group) : idx % group;
     };
     cluster_arrive();
-    float res0 = 0.f;                                      // what the add epilogue adds to, fetched under the barrier
+    float res0 = 0.f, nw0 = 0.f;                           // what the add epilogue adds to and multiplies by, fetched under the barrier
     if (EPI == 2 && worker && t < items) {
       int r, col;
       item_pos(t, r, col);
       const int n = row_tile * kTileRows + split * rows_per + r;
-      if (n < p.rows && col < p.cols) res0 = __ldcg((const float*)p.out + (size_t)col * p.ld_out + n);
+      if (n < p.rows && col < p.cols) {
+        res0 = __ldcg((const float*)p.out + (size_t)col * p.ld_out + n);
+        if (p.xs) nw0 = __ldg(p.norm_w + n);
+      }
     }
     cluster_wait();                                        // the partial sums of this block's rows have arrived
     if (worker && !*abort_flag) {
@@ -735,7 +746,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
         const float sc = p.scale_sumsq ? s_scale[col] : 1.f;
         const float v = sum_sources(r, col) * sc;
         if (EPI == 2) {
-          add_and_emit(p, n, col, v, idx == t, res0, lane);     // (every lane: the sums of squares are added over half warps)
+          add_and_emit(p, n, col, v, idx == t, res0, lane, nw0);     // (every lane: the sums of squares are added over half warps)
         } else {
           store_swapped_one<EPI>(p, n, col, v, EPI == 3 ? sum_sources(r + 1, col) * sc : 0.f);
         }
@@ -745,6 +756,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
     tcgen05_fence_before();
     __syncthreads();
   }
+  if (warp == 2 && lane == 0) timeline_stamp(p.timeline, 5);
   if (PAIR) { cluster_arrive(); cluster_wait(); }        // neither block frees TMEM or leaves while the other may still reach into it
   if (warp == 1) {
     if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols) : "memory");

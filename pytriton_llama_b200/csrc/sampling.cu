@@ -245,4 +245,16 @@ PTL_EXPORT const char* ptl_last_error() { return ptl::error_buffer(); }
 // Switches programmatic dependent launch of the library's kernels on (default) or off.
 PTL_EXPORT void ptl_set_dependent_launch(int enabled) { ptl::pdl_flag() = enabled ? 1 : 0; }
 PTL_EXPORT int ptl_get_dependent_launch() { return ptl::pdl_flag(); }
+
+// Measurement only (see common.cuh): from now on the decode step's kernels stamp %globaltimer into
+// `buffer` (device memory, 16 words per launch, `slots` launches); ptl_timeline_end() stops that and
+// says how many slots were handed out.  A captured graph keeps the slots it was captured with.
+PTL_EXPORT void ptl_timeline_begin(unsigned long long* buffer, int slots) {
+  ptl::timeline_state() = ptl::TimelineState{buffer, slots, 0};
+}
+PTL_EXPORT int ptl_timeline_end() {
+  const int used = ptl::timeline_state().next;
+  ptl::timeline_state() = ptl::TimelineState{nullptr, 0, 0};
+  return used;
+}
 PTL_EXPORT int ptl_abi_version() { return 1; }

@@ -95,6 +95,9 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_gemm_tc_bf16_norm.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int,
                                           _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _c_int, _c_int, _c_f, _ptr]
     lib.ptl_gemm_tc_bf16_norm.restype = _c_int
+    lib.ptl_gemm_small_bf16.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr,
+                                        _ptr, _c_int, _c_int, _c_f, _ptr]
+    lib.ptl_gemm_small_bf16.restype = _c_int
     lib.ptl_gemm_tc_bf16_qkv_rope.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int,
                                               _c_int, _c_int, _c_ll, _ptr]
     lib.ptl_gemm_tc_bf16_qkv_rope.restype = _c_int
@@ -359,6 +362,7 @@ class CudaOps:
         return torch.mm(x, w.t())
 
     fuses_next_norm = os.environ.get("PTL_FUSED_NORM", "1") != "0"
+    small_products = os.environ.get("PTL_SMALL_PRODUCTS", "1") != "0"      # steps of up to 8 tokens: gemm_small for weights of a few MB
     # Steps of up to this many tokens fold the norms into the products around them.  With more
     # tokens a step is no longer bound by the number of kernels, and the add epilogue of the
     # products with a short K range has no time to spare for the extra stores.
@@ -442,6 +446,30 @@ class CudaOps:
                                                       _p(self._tc_status_word()), parts, self._stream()))
                 self._check(self.lib.ptl_add_partials(_p(out), _p(partial), parts, M * N, M * N, self._stream()))
                 return out
+        normed = slots = None
+        if emit_norm is not None:
+            weight, eps = emit_norm
+            self._want(weight, "norm weight", torch.float32)
+            width = (N + 7) // 8           # a slot per 8 features at most (the product for a few tokens), per 16 otherwise
+            normed = NormedActivation(self.empty((M, N), torch.bfloat16), self.empty((M, width), torch.float32), 0,
+                                      float(eps), weight)
+            slots = ctypes.c_int(0)
+        if M <= 8 and epi != self.EPI_SILU_MUL and splits == 0 and self.small_products:
+            # a few tokens and a weight of a few megabytes (q|k|v and output projection of a decode step): the
+            # product without tensor memory and clusters, whose latency is a third; -2 where it does not fit
+            rc = self.lib.ptl_gemm_small_bf16(
+                _p(out), _p(x), _p(w), M, N, K, ld, epi,
+                _p(normed.xs) if normed else None, _p(normed.weight) if normed else None,
+                _p(normed.sumsq) if normed else None, normed.sumsq.shape[1] if normed else 0,
+                ctypes.byref(slots) if normed else None,
+                _p(scale.sumsq) if scale else None, scale.slots if scale else 0, scale.sumsq.shape[1] if scale else 0,
+                scale.eps if scale else 0.0, self._stream())
+            if rc != -2:
+                self._check(rc)
+                if normed is not None:
+                    normed.slots = slots.value
+                    return normed
+                return out
         if scale is None and emit_norm is None:
             rc = self.lib.ptl_gemm_tc_bf16(_p(out), _p(x), _p(w), M, N, K, ld, epi, _p(self._tc_status_word()), splits,
                                            self._stream())
@@ -449,14 +477,6 @@ class CudaOps:
                 return None
             self._check(rc)
             return out
-        normed = slots = None
-        if emit_norm is not None:
-            weight, eps = emit_norm
-            self._want(weight, "norm weight", torch.float32)
-            width = (N + 15) // 16
-            normed = NormedActivation(self.empty((M, N), torch.bfloat16), self.empty((M, width), torch.float32), 0,
-                                      float(eps), weight)
-            slots = ctypes.c_int(0)
         rc = self.lib.ptl_gemm_tc_bf16_norm(
             _p(out), _p(x), _p(w), M, N, K, ld, epi, _p(self._tc_status_word()), splits,
             _p(normed.xs) if normed else None, _p(normed.weight) if normed else None,

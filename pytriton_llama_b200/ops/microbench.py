@@ -6,7 +6,12 @@ Cases: ``decode_attention`` (32 requests x 4,096 cached tokens, 268 MB of keys a
 ``decode_step_attention`` (8 requests x 4,096 tokens with rotary encoding and cache write folded in),
 ``gemm_decode`` (8 tokens x a [65536, 2048] weight, 268 MB), ``gemm_prefill`` (2,048 tokens x the
 gate/up weight [16384, 2048] with the SiLU*up epilogue), ``prefill_attention`` (one 2,048-token
-prompt, 32 query heads of size 64; ``prefill_attention_d128``: of size 128).  Inputs are larger than the 126 MB L2 where the kernel is a stream, so
+prompt, 32 query heads of size 64; ``prefill_attention_d128``: of size 128).  ``decode_timeline`` prints, for the kernels of the middle layer of a captured decode step (a
+4-layer model of the same widths, ``--batch`` requests x 4,096 cached tokens), when the first and
+the last block of each grid entered, got past the wait on its predecessor, had its first operands,
+finished its loop, had its results complete and left -- %globaltimer stamps, in microseconds from
+the layer's first stamp: what a sum of kernel times cannot show, the gaps between dependent kernels.
+Inputs are larger than the 126 MB L2 where the kernel is a stream, so
 DRAM figures mean something, yet small enough for a profiler to replay.  Each case prints its
 time from CUDA events after warm-up and the bytes or FLOPs per second that follow from it.
 lite_llama benchmarks its Triton kernels the same way from their ``__main__`` blocks
@@ -37,7 +42,67 @@ def _time(fn, reps: int, ops: CudaOps) -> float:
     return start.elapsed_time(end) / reps * 1e-3
 
 
-def run(case: str, reps: int) -> dict:
+LLAMA_1B_WIDTHS = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": 2048, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192, "vocab_size": 128256, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 131072,
+}
+TIMELINE_KINDS = {1: "decode attention", 10: "product -> bf16", 11: "product -> float32", 12: "product + residual", 13: "product, SiLU*up",
+                  20: "small product -> bf16", 21: "small product -> f32", 22: "small product + res."}
+TIMELINE_STAMPS = ["entered", "wait over", "first operands", "loop done", "results complete", "done"]
+
+
+def decode_timeline(batch: int, layers: int = 4, context: int = 4096) -> dict:
+    """%globaltimer stamps of one captured decode step's kernels (see the module's text)."""
+    import ctypes
+    from ..config.engine import EngineConfig
+    from ..engine.engine import Engine, StepEntry
+    cfg = dict(LLAMA_1B_WIDTHS, num_hidden_layers=layers)
+    pages = batch * (context // 16 + 1) + 8
+    eng = Engine(None, EngineConfig(dtype="bfloat16", page_size=16, max_gpu_num_blocks=pages, max_seq_len=context + 16,
+                                    max_num_seqs=max(batch, 1), max_batched_tokens=2048, compiled_model=True),
+                 model_config=cfg, random_seed=0)
+    gen = torch.Generator().manual_seed(0)
+    reqs = [f"r{i}" for i in range(batch)]
+    for r in reqs:
+        done = 0
+        while done < context - 8:
+            n = min(2048, context - 8 - done)
+            eng.step([StepEntry(r, torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist(), [])])
+            done += n
+    lib = eng.ops.lib
+    lib.ptl_timeline_begin.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    lib.ptl_timeline_end.restype = ctypes.c_int
+    slots = 3 * (5 * layers + 4)                       # capturing a step runs it three times; the third run is the graph's
+    buf = torch.zeros((slots, 16), dtype=torch.int64, device=eng.device)
+    step = lambda: eng.step([StepEntry(r, [1], [0]) for r in reqs], own_logits=False)
+    lib.ptl_timeline_begin(buf.data_ptr(), slots)
+    step()                                              # the first step of this batch size is captured: its kernels keep their slots
+    used = lib.ptl_timeline_end()
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    eng.check_device_status()
+    rows = buf[:used].cpu().tolist()
+    # the graph's own launches are the last third; of those the middle layer: five kernels from a q|k|v product (bf16 store) on
+    per_layer = 5
+    per_run = used // 3
+    first = next(i for i in range(used - per_run + per_run // 2 - per_layer, used) if rows[i][0] in (10, 20))
+    chosen = rows[first:first + per_layer + 1]          # ... and the next layer's first kernel, to see the hand-over
+    t0 = min(v for r in chosen for v in r[1:15] if v)
+    table = []
+    for r in chosen:
+        first_block = [round((v - t0) / 1e3, 2) if v else None for v in r[1:7]]
+        last_block = [round((v - t0) / 1e3, 2) if v else None for v in r[8:14]]
+        table.append({"kernel": TIMELINE_KINDS.get(r[0], str(r[0])), "first block": first_block, "last block": last_block})
+    return {"case": "decode_timeline", "batch": batch, "context": context, "stamps": TIMELINE_STAMPS, "unit": "us", "kernels": table}
+
+
+def run(case: str, reps: int, batch: int = 8) -> dict:
+    if case == "decode_timeline":
+        return decode_timeline(batch)
     dev = torch.device("cuda:0")
     ops = CudaOps(dev)
     nq, nkv, d, page = 32, 8, 64, 16
@@ -101,10 +166,19 @@ def run(case: str, reps: int) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("case", choices=["decode_attention", "decode_step_attention", "gemm_decode", "gemm_prefill", "prefill_attention",
-                                     "prefill_attention_d128"])
+                                     "prefill_attention_d128", "decode_timeline"])
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--batch", type=int, default=8, help="decode_timeline: requests in the step")
     args = ap.parse_args()
-    print(json.dumps(run(args.case, args.reps)))
+    out = run(args.case, args.reps, args.batch)
+    if args.case == "decode_timeline":
+        print(f"decode step, batch {out['batch']}, context {out['context']}: microseconds from the layer's first stamp")
+        print(f"{'kernel':24s} {'block':6s} " + " ".join(f"{s:>16s}" for s in out["stamps"]))
+        for k in out["kernels"]:
+            for which in ("first block", "last block"):
+                print(f"{k['kernel']:24s} {which.split()[0]:6s} " + " ".join(f"{'-' if v is None else v:>16}" for v in k[which]))
+    else:
+        print(json.dumps(out))
 
 
 if __name__ == "__main__":

@@ -665,3 +665,60 @@ def test_a_wait_that_runs_out_sets_the_status_and_the_kernel_returns(_ops, M, N,
         got = ops.gemm_tc(x, w, ops.EPI_F32)
         close(got, x.float() @ w.float().T, "float32", "the product after the self-test", scale=float(K) ** 0.5 * 50)
     assert ops.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("M, N, K", [(1, 2048, 2048), (8, 3072, 2048), (5, 100, 200), (3, 96, 2176), (4, 101, 64), (8, 40, 1000)])
+def test_product_for_a_few_tokens_and_small_weights(_ops, M, N, K):
+    """Up to 8 tokens and a weight of a few megabytes go to a product of their own (a block owns 8
+    output features for the whole K range; mma.sync, no tensor memory, no cluster): every epilogue
+    against float64, and against the tcgen05 product that takes the same call when this one is
+    switched off.  Around a norm: its sums of squares come one per 8 features."""
+    ops = _ops
+    x, w = rnd((M, K), torch.bfloat16, 71), rnd((N, K), torch.bfloat16, 72, 0.5)
+    ref = x.double() @ w.double().T
+    scale = float(ref.abs().max())
+    res0 = rnd((M, N), torch.float32, 73, 3.0)
+    nw = (1.0 + 0.2 * torch.randn(N, generator=torch.Generator().manual_seed(74))).float()
+    eps = 1e-5
+    results = {}
+    for small in (True, False):
+        ops.small_products = small
+        try:
+            out = ops.gemm_tc(x.cuda(), w.cuda(), ops.EPI_BF16)
+            out32 = ops.gemm_tc(x.cuda(), w.cuda(), ops.EPI_F32)
+            acc = res0.clone().cuda()
+            assert ops.gemm_tc(x.cuda(), w.cuda(), ops.EPI_ADD_F32, out=acc) is acc
+            acc2 = res0.clone().cuda()
+            normed = ops.gemm_tc(x.cuda(), w.cuda(), ops.EPI_ADD_F32, out=acc2, emit_norm=(nw.cuda(), eps))
+        finally:
+            ops.small_products = True
+        assert (out.double().cpu() - ref).abs().max() <= 2 ** -8 * scale
+        assert (out32.double().cpu() - ref).abs().max() <= 2e-6 * math.sqrt(K) * scale / 10 + 1e-5
+        want_res = ref + res0.double()
+        assert (acc.double().cpu() - want_res).abs().max() <= 2e-6 * math.sqrt(K) * scale / 10 + 1e-5
+        if normed is not None:                        # (the tcgen05 product prepares a norm only for widths that are multiples of 32)
+            assert torch.equal(acc2, acc)
+            assert normed.slots == (-(-N // 8) if small else -(-N // 16))
+            got_sq = normed.sumsq[:, :normed.slots].double().sum(1).cpu()
+            assert ((got_sq - (want_res ** 2).sum(1)).abs() / (want_res ** 2).sum(1)).max() < 1e-5
+            y = want_res * torch.rsqrt((want_res ** 2).mean(1, keepdim=True) + eps) * nw.double()
+            assert (normed.materialise().double().cpu() - y).abs().max() <= 2 ** -7 * float(y.abs().max())
+            if N % 8 == 0 and N >= 64:
+                # a product that reads the prepared input finishes the norm: both kinds of product
+                w2 = rnd((48, N), torch.bfloat16, 75, 0.3)
+                want2 = y @ w2.double().T
+                for consumer_small in (True, False):
+                    ops.small_products = consumer_small
+                    try:
+                        got2 = ops.gemm_tc(normed, w2.cuda(), ops.EPI_F32)
+                    finally:
+                        ops.small_products = True
+                    assert (got2.double().cpu() - want2).abs().max() <= 2 ** -7 * float(want2.abs().max())
+        elif small:
+            raise AssertionError("the product for few tokens prepares the next norm for every width")
+        results[small] = (out32.cpu(), acc.cpu())
+    # the two products agree to float32 accumulation, and the one for few tokens does not depend on how many there are
+    assert (results[True][0] - results[False][0]).abs().max() <= 2e-6 * math.sqrt(K) * scale / 10 + 1e-5
+    alone = ops.gemm_tc(x[:1].contiguous().cuda(), w.cuda(), ops.EPI_F32)
+    assert torch.equal(alone.cpu()[0], results[True][0][0])
+    assert ops.gemm_tc_status() == 0
