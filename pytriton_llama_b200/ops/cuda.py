@@ -157,6 +157,7 @@ class CudaOps:
             raise KernelError(f"the kernels are compiled for sm_100a only; device reports sm_{major}{minor}")
         self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
         self._device_index = device.index if device.index is not None else torch.cuda.current_device()
+        self._sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         self._status = torch.zeros(1, dtype=torch.int32, device=device)
         self.launches = 0      # kernels of this library launched so far (library matrix products not counted)
 
@@ -353,13 +354,30 @@ class CudaOps:
             out = self.empty((M, N), torch.float32)
             self._check(self.lib.ptl_gemm_simt_f32(_p(out), _p(x), _p(w), M, N, K, K, K, N, 0, self._stream()))
             return out
-        out = self.gemm_tc(x, w, self.EPI_F32 if out_dtype == torch.float32 else self.EPI_BF16)
-        if out is not None:
-            return out
-        # sizes the tensor-core kernel does not take (K no multiple of 8, or below 64): the library product
+        if not (out_dtype == torch.bfloat16 and self.library_product(M, N, K, self.EPI_BF16)):
+            out = self.gemm_tc(x, w, self.EPI_F32 if out_dtype == torch.float32 else self.EPI_BF16)
+            if out is not None:
+                return out
+        # sizes the tensor-core kernel does not take (K no multiple of 8, or below 64) or leaves to the library
         if out_dtype == torch.float32:
             return torch.mm(x, w.t(), out_dtype=torch.float32)
         return torch.mm(x, w.t())
+
+    library_products = os.environ.get("PTL_LIBRARY_PRODUCTS", "1") != "0"
+
+    def library_product(self, M: int, N: int, K: int, epi: int) -> bool:
+        """True where the plain library product (cuBLAS through torch.mm, which is what lite_llama's
+        nn.Linear layers are: lite_llama/models/llama.py:22-24,37-40) is the one to take.  Measured
+        on a B200 with cold caches (``python -m pytriton_llama_b200.ops.microbench product_shapes``):
+        a product of more than 64 tokens whose 128 x 256 tiles do not fill the SMs twice is faster
+        there, by 2 to 10 us, than this library's tcgen05 kernel even after the library's result has
+        been rotated by ``rope_kv_write`` or read once more by the norm that adds it to the residual
+        (q|k|v, output and down projection at 128 to 2,048 tokens: few tiles, each walking a long K
+        range alone).  The products with the SiLU*up epilogue, of few tokens, with float32 results
+        and of many tiles stay with the tcgen05 kernel.  ``PTL_LIBRARY_PRODUCTS=0`` keeps everything there."""
+        if not self.library_products or M <= 64 or epi not in (self.EPI_BF16, self.EPI_ADD_F32):
+            return False
+        return -(-M // 128) * -(-N // 256) <= 2 * self._sm_count
 
     fuses_next_norm = os.environ.get("PTL_FUSED_NORM", "1") != "0"
     small_products = os.environ.get("PTL_SMALL_PRODUCTS", "1") != "0"      # steps of up to 8 tokens: gemm_small for weights of a few MB
@@ -373,7 +391,7 @@ class CudaOps:
         that is not possible the plain product, for the caller to add.  With ``next_norm`` = (weight,
         eps) of the RMS norm that reads the residual next, the epilogue prepares that norm's input
         as well and a ``NormedActivation`` is returned instead of None (where the sizes allow it)."""
-        if x.dtype == torch.bfloat16 and residual is not None:
+        if x.dtype == torch.bfloat16 and residual is not None and not self.library_product(x.shape[0], w.shape[0], x.shape[1], self.EPI_ADD_F32):
             if next_norm is not None and self.fuses_next_norm and x.shape[0] <= self.FUSED_NORM_MAX_TOKENS:
                 normed = self.gemm_tc(x, w, self.EPI_ADD_F32, out=residual, emit_norm=next_norm)
                 if normed is not None:
@@ -641,7 +659,7 @@ class CudaOps:
         fused = (os.environ.get("PTL_FUSED_QKV_ROPE", "1") != "0" and isinstance(x, torch.Tensor) and x.dtype == torch.bfloat16
                  and x.shape[0] > 64 and write and slots is not None and inv_freq is not None and rot == d and d in (64, 128)
                  and w_qkv.shape[0] == (nq + 2 * nkv) * d and cache.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
-                 and x.shape[1] >= 64)
+                 and x.shape[1] >= 64 and not self.library_product(x.shape[0], w_qkv.shape[0], x.shape[1], self.EPI_BF16))
         if fused:
             self._want(x, "x", torch.bfloat16)
             self._want(w_qkv, "w_qkv", torch.bfloat16)

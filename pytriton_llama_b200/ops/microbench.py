@@ -11,6 +11,7 @@ prompt, 32 query heads of size 64; ``prefill_attention_d128``: of size 128).  ``
 the last block of each grid entered, got past the wait on its predecessor, had its first operands,
 finished its loop, had its results complete and left -- %globaltimer stamps, in microseconds from
 the layer's first stamp: what a sum of kernel times cannot show, the gaps between dependent kernels.
+``product_shapes`` times the many-token products of the model beside the library's (torch.mm).
 Inputs are larger than the 126 MB L2 where the kernel is a stream, so
 DRAM figures mean something, yet small enough for a profiler to replay.  Each case prints its
 time from CUDA events after warm-up and the bytes or FLOPs per second that follow from it.
@@ -100,9 +101,60 @@ def decode_timeline(batch: int, layers: int = 4, context: int = 4096) -> dict:
     return {"case": "decode_timeline", "batch": batch, "context": context, "stamps": TIMELINE_STAMPS, "unit": "us", "kernels": table}
 
 
+def product_shapes(reps: int) -> dict:
+    """The many-token products of the Llama-3.2-1B shape, this library's tcgen05 kernel beside the
+    library product (cuBLAS through torch.mm) on the same inputs: q|k|v, output projection, gate/up
+    and down projection at 128 to 2,048 tokens.  ``ours`` includes the fused epilogue where the
+    engine would use one (add into the float32 residual; SiLU*up); ``library`` is the plain
+    bfloat16 product, to which the engine then adds what the epilogue would have done (``extra``:
+    the SiLU*up kernel; reading the product once more in the norm that adds it to the residual)."""
+    dev = torch.device("cuda:0")
+    ops = CudaOps(dev)
+    H, I, QKV = 2048, 8192, 3072
+    rows = []
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device=dev)       # larger than L2: written between timed calls
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        total = 0.0
+        for _ in range(reps):
+            flush.zero_()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize()
+            total += start.elapsed_time(end)
+        return total / reps * 1e3
+
+    for M in (128, 256, 512, 1024, 2048):
+        for name, N, K, epi in (("q|k|v", QKV, H, ops.EPI_BF16), ("output", H, H, ops.EPI_ADD_F32),
+                                ("gate/up", 2 * I, H, ops.EPI_SILU_MUL), ("down", H, I, ops.EPI_ADD_F32)):
+            x = torch.randn(M, K, device=dev).bfloat16()
+            w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+            res = torch.zeros(M, N if epi != ops.EPI_SILU_MUL else N // 2, dtype=torch.float32, device=dev)
+            ours = timed(lambda: ops.gemm_tc(x, w, epi, out=res if epi == ops.EPI_ADD_F32 else None))
+            lib = timed(lambda: torch.mm(x, w.t()))
+            extra = 0.0
+            if epi == ops.EPI_SILU_MUL:
+                gu = torch.mm(x, w.t())
+                extra = timed(lambda: ops.silu_mul(gu))
+            elif epi == ops.EPI_ADD_F32:
+                prod = torch.mm(x, w.t())
+                nw = torch.ones(N, dtype=torch.float32, device=dev)
+                extra = timed(lambda: ops.add_rmsnorm(prod, res, nw, 1e-5)) - timed(lambda: ops.add_rmsnorm(None, res, nw, 1e-5, dtype=torch.bfloat16))
+            rows.append({"product": name, "tokens": M, "N": N, "K": K, "ours_us": round(ours, 1), "library_us": round(lib, 1),
+                         "extra_us": round(extra, 1), "routed_to": "library" if ops.library_product(M, N, K, epi) else "ours"})
+    ops.check_status()
+    return {"case": "product_shapes", "rows": rows}
+
+
 def run(case: str, reps: int, batch: int = 8) -> dict:
     if case == "decode_timeline":
         return decode_timeline(batch)
+    if case == "product_shapes":
+        return product_shapes(reps)
     dev = torch.device("cuda:0")
     ops = CudaOps(dev)
     nq, nkv, d, page = 32, 8, 64, 16
@@ -166,7 +218,7 @@ def run(case: str, reps: int, batch: int = 8) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("case", choices=["decode_attention", "decode_step_attention", "gemm_decode", "gemm_prefill", "prefill_attention",
-                                     "prefill_attention_d128", "decode_timeline"])
+                                     "prefill_attention_d128", "decode_timeline", "product_shapes"])
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--batch", type=int, default=8, help="decode_timeline: requests in the step")
     args = ap.parse_args()
@@ -177,6 +229,10 @@ def main() -> None:
         for k in out["kernels"]:
             for which in ("first block", "last block"):
                 print(f"{k['kernel']:24s} {which.split()[0]:6s} " + " ".join(f"{'-' if v is None else v:>16}" for v in k[which]))
+    elif args.case == "product_shapes":
+        print(f"{'product':8s} {'tokens':>6s} {'N':>6s} {'K':>6s} {'ours us':>9s} {'library us':>11s} {'+extra us':>10s}  routed to")
+        for r in out["rows"]:
+            print(f"{r['product']:8s} {r['tokens']:6d} {r['N']:6d} {r['K']:6d} {r['ours_us']:9.1f} {r['library_us']:11.1f} {r['extra_us']:10.1f}  {r['routed_to']}")
     else:
         print(json.dumps(out))
 

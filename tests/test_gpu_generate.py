@@ -235,14 +235,17 @@ def test_captured_steps_of_mixed_shapes_give_the_same_logits(model_folders, dtyp
         assert float((a - b).abs().max()) <= (1e-5 if dtype == "float32" else 0.03) * top
 
 
+@pytest.mark.parametrize("own_products", [False, True])
 @pytest.mark.parametrize("hidden, heads, kv_heads, head_dim, inter", [(2048, 32, 8, 64, 8192), (3072, 24, 8, 128, 8192)])
-def test_one_layer_of_real_widths_in_bfloat16(tmp_path, hidden, heads, kv_heads, head_dim, inter):
+def test_one_layer_of_real_widths_in_bfloat16(tmp_path, hidden, heads, kv_heads, head_dim, inter, own_products):
     """The tiny configurations never reach the kernels' paths for real widths: products of 2,048-wide
     rows with a few hundred and with more than a thousand tokens (parts of the K range, wide tiles on
     pairs of blocks), 32 query heads over 8 kv heads or 24 over 8 with head size 128, prompts of many
     key tiles.  One layer of the Llama-3.2-1B and -3B widths with a smaller vocabulary: a 1,400-token prompt in portions of 300 and 1,100
     (the first as a captured shape the second time round), then single tokens, against the plain
-    implementation."""
+    implementation.  Once as the engine runs (products of many tokens and few tiles go to the library)
+    and once with every product on this library's own tensor-core kernel (``own_products``: also the
+    q|k|v projection that rotates and writes the cache in its epilogue, and the add epilogues)."""
     from pytriton_llama_b200.config import EngineConfig
     from pytriton_llama_b200.engine.engine import Engine, StepEntry
     from pytriton_llama_b200.weights.random_init import write_random_model
@@ -261,6 +264,7 @@ def test_one_layer_of_real_widths_in_bfloat16(tmp_path, hidden, heads, kv_heads,
     ecfg = EngineConfig(dtype="bfloat16", page_size=16, max_gpu_num_blocks=200, max_seq_len=1536, max_num_seqs=2,
                         max_batched_tokens=2048, compiled_model=True, seed=0)
     eng = Engine(folder, ecfg)
+    eng.ops.library_products = not own_products
     from gpu_common import assert_close
     for attempt in range(2):                     # the second time the 300-token step runs from its captured graph
         out = eng.step([StepEntry("r", prompt[:300], [299])])
