@@ -34,6 +34,27 @@ MODEL = {
 }
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
+
+
+def _llama(layers, hidden, heads, kv_heads, head_dim, inter, factor, tied):
+    return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": layers, "hidden_size": hidden,
+            "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": head_dim, "intermediate_size": inter,
+            "vocab_size": 128256, "rope_theta": 500000.0,
+            "rope_scaling": {"rope_type": "llama3", "factor": factor, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                             "original_max_position_embeddings": 8192},
+            "rms_norm_eps": 1e-5, "tie_word_embeddings": tied, "max_position_embeddings": 131072}
+
+
+# The default run is the Llama-3.2-1B shape (the headline configuration).  ``--shape`` runs the same
+# measurements on the two larger Llama shapes with their own workloads: 3b also times a serving run
+# (32 requests, prompts of 128 to 2,048 tokens, 256 generated tokens each, continuous batching).
+SHAPES = {
+    "1b": {"name": "Llama-3.2-1B", "model": MODEL, "context": 4096, "batch": 8, "points": "1,64", "serving": None},
+    "3b": {"name": "Llama-3.2-3B", "model": _llama(28, 3072, 24, 8, 128, 8192, 32.0, True), "context": 2304, "batch": 32,
+           "points": "1", "serving": {"requests": 32, "prompt_lo": 128, "prompt_hi": 2048, "generated": 256}},
+    "8b": {"name": "Llama-3.1-8B", "model": _llama(32, 4096, 32, 8, 128, 14336, 8.0, False), "context": 8192, "batch": 64,
+           "points": "1", "serving": None},
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -130,9 +151,10 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"], help="fewer layers than the model has (named in config)")
-    ap.add_argument("--points", default="1,64", help="extra decode batch sizes, comma separated ('' for none)")
+    ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="which Llama shape (default: the headline 1B configuration)")
+    ap.add_argument("--batch", type=int, default=None, help="decode batch (default: 8; 32 for 3b; 64 for 8b)")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--points", default=None, help="extra decode batch sizes, comma separated ('' for none)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill measurement (profiling runs)")
@@ -142,8 +164,16 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    shape = SHAPES[args.shape]
+    args.batch = args.batch or shape["batch"]
+    args.points = shape["points"] if args.points is None else args.points
+    args.layers = args.layers or shape["model"]["num_hidden_layers"]
     if args.impl == "reference":
+        if args.shape != "1b":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference arm runs the headline 1B configuration only"}))
+            return 0
         return reference_arm(args)
+    MODEL, CONTEXT = shape["model"], shape["context"]
 
     import torch
     from pytriton_llama_b200.config import EngineConfig
@@ -277,22 +307,41 @@ def main() -> int:
         ms, _, _ = decode_run(pb, steps, W)
         pts[f"decode_b{pb}"] = round(pb / ms * 1e3, 1)
 
+    serving = None
+    if shape["serving"] and not args.no_e2e:
+        # continuous batching through the Python entry point: every request's prompt in portions beside the others' decoding
+        sv = shape["serving"]
+        lens = torch.randint(sv["prompt_lo"], sv["prompt_hi"] + 1, (sv["requests"],), generator=gen).tolist()
+        prompts = [tokens(n) for n in lens]
+        params = SamplingParams(temperature=0.0, max_gen_len=sv["generated"], stop_token_ids=[])
+        llm.generate(prompts[:2], SamplingParams(temperature=0.0, max_gen_len=4, stop_token_ids=[]))     # warm-up
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        outs = llm.generate(prompts, params)
+        torch.cuda.synchronize(dev)
+        dt = time.perf_counter() - t0
+        made = sum(len(o) for o in outs)
+        serving = {"requests": sv["requests"], "prompt_tokens": sum(lens), "generated_tokens": made, "seconds": round(dt, 3),
+                   "generated_tokens_per_s": round(made / dt, 1), "all_tokens_per_s": round((made + sum(lens)) / dt, 1)}
+
     sc = cfg["rope_scaling"]
     out = {
         "metric": "decode_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic", "impl": "ours",
         "config": {
-            "model": "Llama-3.2-1B shape, random weights (seed 0)", "layers": args.layers, "layers_of_model": MODEL["num_hidden_layers"],
+            "model": f"{shape['name']} shape, random weights (seed 0)", "layers": args.layers, "layers_of_model": MODEL["num_hidden_layers"],
             "hidden": cfg["hidden_size"], "heads": nq, "kv_heads": cfg["num_key_value_heads"], "head_dim": d,
             "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "rope_theta": cfg["rope_theta"],
             "rope_scaling": f"llama3 factor {sc['factor']:g} low {sc['low_freq_factor']:g} high {sc['high_freq_factor']:g} original {sc['original_max_position_embeddings']}",
-            "rms_norm_eps": cfg["rms_norm_eps"], "tie_word_embeddings": True, "global_batch": B, "seq_len": CONTEXT,
+            "rms_norm_eps": cfg["rms_norm_eps"], "tie_word_embeddings": cfg["tie_word_embeddings"], "global_batch": B, "seq_len": CONTEXT,
             "page_size": 16, "parallelism": "single-gpu", "cuda_graph": not args.no_graph,
-            "l2": "inputs larger than L2: every step reads all weights (2.5 GB) and the live cache",
+            "l2": f"inputs larger than L2: every step reads all weights ({weight_bytes / 1e9:.1f} GB) and the live cache",
         },
         "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "prefill": prefill, "roofline": roofline, "points": pts,
     }
+    if serving:
+        out["serving"] = serving
     print(json.dumps(out))
     return 0
 
