@@ -718,14 +718,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       r = EPI == 3 ? 2 * (idx % group) : idx % group;
     };
     cluster_arrive();
-    float res0 = 0.f, nw0 = 0.f;                           // what the add epilogue adds to and multiplies by, fetched under the barrier
-    if (EPI == 2 && worker && t < items) {
-      int r, col;
-      item_pos(t, r, col);
-      const int n = row_tile * kTileRows + split * rows_per + r;
-      if (n < p.rows && col < p.cols) {
-        res0 = __ldcg((const float*)p.out + (size_t)col * p.ld_out + n);
-        if (p.xs) nw0 = __ldg(p.norm_w + n);
+    // what the add epilogue adds to and multiplies by, fetched under the barrier: this thread's first
+    // four items (16 to 64 tokens give a thread 1 to 4 of them with eight splits; a fetch inside the
+    // loop below costs a trip to L2 each time, 1 us per round at 64 tokens)
+    constexpr int kAheadItems = 4;
+    float res0[kAheadItems], nw0[kAheadItems];
+#pragma unroll
+    for (int i = 0; i < kAheadItems; ++i) {
+      res0[i] = 0.f;
+      nw0[i] = 0.f;
+      const int idx = t + 256 * i;
+      if (EPI == 2 && worker && idx < items) {
+        int r, col;
+        item_pos(idx, r, col);
+        const int n = row_tile * kTileRows + split * rows_per + r;
+        if (n < p.rows && col < p.cols) {
+          res0[i] = __ldcg((const float*)p.out + (size_t)col * p.ld_out + n);
+          if (p.xs) nw0[i] = __ldg(p.norm_w + n);
+        }
       }
     }
     cluster_wait();                                        // the partial sums of this block's rows have arrived
@@ -739,14 +749,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
         for (int z = 1; z < 8; ++z) v += a[z];
         return v;
       };
-      for (int idx = t; idx < items; idx += 256) {
+#pragma unroll 1
+      for (int idx = t, i = 0; idx < items; idx += 256, ++i) {
         int r, col;
         item_pos(idx, r, col);
         const int n = row_tile * kTileRows + split * rows_per + r;
         const float sc = p.scale_sumsq ? s_scale[col] : 1.f;
         const float v = sum_sources(r, col) * sc;
         if (EPI == 2) {
-          add_and_emit(p, n, col, v, idx == t, res0, lane, nw0);     // (every lane: the sums of squares are added over half warps)
+          float have = 0.f, nwv = 0.f;
+#pragma unroll
+          for (int j = 0; j < kAheadItems; ++j) if (j == i) { have = res0[j]; nwv = nw0[j]; }
+          add_and_emit(p, n, col, v, i < kAheadItems, have, lane, nwv);     // (every lane: the sums of squares are added over half warps)
         } else {
           store_swapped_one<EPI>(p, n, col, v, EPI == 3 ? sum_sources(r + 1, col) * sc : 0.f);
         }
