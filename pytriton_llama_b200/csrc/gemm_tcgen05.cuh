@@ -114,6 +114,16 @@ template <int BN, bool PAIR = false> struct TcCfg {
   static constexpr int kSmem = kPipeSmem + kRecvBytes + kAddStageBytes;
 };
 
+#ifndef PTL_VECTOR_REDUCE_COLUMNS
+#define PTL_VECTOR_REDUCE_COLUMNS 64
+#endif
+constexpr int kVectorReduceColumns = PTL_VECTOR_REDUCE_COLUMNS;   // column tiles from this width on add partial sums four rows per thread
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
 // SiLU for the bfloat16 path: the result is rounded to 8 bits of mantissa, so the fast
 // exponential and reciprocal (about 2 ulp of float32) cost no accuracy that survives.
 __device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
@@ -709,60 +719,170 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       }
     }
     tcgen05_fence_before();
-    const int group = EPI == 3 ? rows_per / 2 : rows_per;  // items per column: rows, or gate/up pairs
-    const int items = group * BN;
-    const int t = threadIdx.x - 64;                        // 0..255 in the epilogue warps
-    const bool worker = warp >= 2;
-    auto item_pos = [&](int idx, int& r, int& col) {
-      col = idx / group;
-      r = EPI == 3 ? 2 * (idx % group) : idx % group;
-    };
-    cluster_arrive();
-    // what the add epilogue adds to and multiplies by, fetched under the barrier: this thread's first
-    // four items (16 to 64 tokens give a thread 1 to 4 of them with eight splits; a fetch inside the
-    // loop below costs a trip to L2 each time, 1 us per round at 64 tokens)
-    constexpr int kAheadItems = 4;
-    float res0[kAheadItems], nw0[kAheadItems];
-#pragma unroll
-    for (int i = 0; i < kAheadItems; ++i) {
-      res0[i] = 0.f;
-      nw0[i] = 0.f;
-      const int idx = t + 256 * i;
-      if (EPI == 2 && worker && idx < items) {
-        int r, col;
-        item_pos(idx, r, col);
-        const int n = row_tile * kTileRows + split * rows_per + r;
+    // Two ways to add the partial sums up.  With many columns (tokens) a thread takes four neighbouring rows of
+    // one column with 16-byte reads and writes; with few columns that leaves most threads idle, and one result
+    // per thread measured faster.
+    if constexpr (BN >= kVectorReduceColumns) {
+      // The owner's threads each take four neighbouring rows (features) of one column (token): chunk q is
+      // rows 4 (q % (rows_per / 4))..+3 of column q / (rows_per / 4).  The partial sums of a chunk are 16
+      // bytes in every source's part of `recv`, its four results 8 or 16 contiguous bytes of the output.
+      const int r4_per = rows_per / 4;
+      const int chunks_total = r4_per * BN;
+      const int t = threadIdx.x - 64;                        // 0..255 in the epilogue warps
+      const bool worker = warp >= 2;
+      cluster_arrive();
+      // what the add epilogue adds to and multiplies by, fetched under the barrier: this thread's first chunk
+      float4 res0 = make_float4(0.f, 0.f, 0.f, 0.f), nw0 = make_float4(0.f, 0.f, 0.f, 0.f);
+      const bool vec_out = p.ld_out % 4 == 0 && p.rows % 4 == 0;      // whole chunks exist and are aligned
+      if (EPI == 2 && worker && t < chunks_total && vec_out) {
+        const int n = row_tile * kTileRows + split * rows_per + 4 * (t % r4_per), col = t / r4_per;
         if (n < p.rows && col < p.cols) {
-          res0[i] = __ldcg((const float*)p.out + (size_t)col * p.ld_out + n);
-          if (p.xs) nw0[i] = __ldg(p.norm_w + n);
+          res0 = __ldcg(reinterpret_cast<const float4*>((const float*)p.out + (size_t)col * p.ld_out + n));
+          if (p.xs) nw0 = __ldg(reinterpret_cast<const float4*>(p.norm_w + n));
         }
       }
-    }
-    cluster_wait();                                        // the partial sums of this block's rows have arrived
-    if (worker && !*abort_flag) {
-      auto sum_sources = [&](int r, int col) {
-        float a[8];
-#pragma unroll
-        for (int z = 0; z < 8; ++z) a[z] = z < S ? recv[(z * BN + col) * rows_per + r] : 0.f;
-        float v = a[0];
-#pragma unroll
-        for (int z = 1; z < 8; ++z) v += a[z];
-        return v;
-      };
+      cluster_wait();                                        // the partial sums of this block's rows have arrived
+      if (worker && !*abort_flag) {
 #pragma unroll 1
-      for (int idx = t, i = 0; idx < items; idx += 256, ++i) {
-        int r, col;
-        item_pos(idx, r, col);
-        const int n = row_tile * kTileRows + split * rows_per + r;
-        const float sc = p.scale_sumsq ? s_scale[col] : 1.f;
-        const float v = sum_sources(r, col) * sc;
-        if (EPI == 2) {
-          float have = 0.f, nwv = 0.f;
+        for (int q = t, i = 0; q < chunks_total; q += 256, ++i) {
+          const int r = 4 * (q % r4_per), col = q / r4_per;
+          const float* src = recv + col * rows_per + r;
+          float4 a[8];
 #pragma unroll
-          for (int j = 0; j < kAheadItems; ++j) if (j == i) { have = res0[j]; nwv = nw0[j]; }
-          add_and_emit(p, n, col, v, i < kAheadItems, have, lane, nwv);     // (every lane: the sums of squares are added over half warps)
-        } else {
-          store_swapped_one<EPI>(p, n, col, v, EPI == 3 ? sum_sources(r + 1, col) * sc : 0.f);
+          for (int z = 0; z < 8; ++z) a[z] = z < S ? *reinterpret_cast<const float4*>(src + z * BN * rows_per) : make_float4(0.f, 0.f, 0.f, 0.f);
+          float v[4] = {a[0].x, a[0].y, a[0].z, a[0].w};
+#pragma unroll
+          for (int z = 1; z < 8; ++z) { v[0] += a[z].x; v[1] += a[z].y; v[2] += a[z].z; v[3] += a[z].w; }     // in rank order: deterministic
+          if (p.scale_sumsq) {
+            const float sc = s_scale[col];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] *= sc;
+          }
+          const int n = row_tile * kTileRows + split * rows_per + r;
+          const bool live = n < p.rows && col < p.cols;
+          if (EPI == 2) {
+            // residual += v; with p.xs the next norm's input and the sum of squares of 16 features (four lanes) go out too
+            float rn[4] = {0.f, 0.f, 0.f, 0.f};
+            if (live && vec_out) {
+              float4* o = reinterpret_cast<float4*>((float*)p.out + (size_t)col * p.ld_out + n);
+              const float4 have = i == 0 ? res0 : __ldcg(o);
+              rn[0] = have.x + v[0]; rn[1] = have.y + v[1]; rn[2] = have.z + v[2]; rn[3] = have.w + v[3];
+              *o = make_float4(rn[0], rn[1], rn[2], rn[3]);
+              if (p.xs) {
+                const float4 w4 = i == 0 ? nw0 : __ldg(reinterpret_cast<const float4*>(p.norm_w + n));
+                uint2 pk;
+                pk.x = pack_bf16x2(rn[0] * w4.x, rn[1] * w4.y);
+                pk.y = pack_bf16x2(rn[2] * w4.z, rn[3] * w4.w);
+                *reinterpret_cast<uint2*>(p.xs + (size_t)col * p.xs_ld + n) = pk;
+              }
+            } else if (col < p.cols) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (n + j < p.rows) {
+                  float* o = (float*)p.out + (size_t)col * p.ld_out + n + j;
+                  rn[j] = __ldcg(o) + v[j];
+                  *o = rn[j];
+                  if (p.xs) p.xs[(size_t)col * p.xs_ld + n + j] = __float2bfloat16_rn(rn[j] * __ldg(p.norm_w + n + j));
+                }
+              }
+            }
+            if (p.xs) {
+              float sq = (rn[0] * rn[0] + rn[1] * rn[1]) + (rn[2] * rn[2] + rn[3] * rn[3]);
+              sq += __shfl_xor_sync(0xffffffffu, sq, 1);       // the four lanes that hold 16 neighbouring features of this token
+              sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+              if ((lane & 3) == 0 && live) p.sumsq[(size_t)col * p.sumsq_ld + n / 16] = sq;
+            }
+          } else if (EPI == 3) {
+            // rows alternate gate_j, up_j: two results
+            if (col < p.cols) {
+              __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)col * p.ld_out + n / 2;
+              if (n + 3 < p.rows && p.ld_out % 2 == 0) {
+                *reinterpret_cast<uint32_t*>(o) = pack_bf16x2(silu_f(v[0]) * v[1], silu_f(v[2]) * v[3]);
+              } else {
+                if (n + 1 < p.rows) o[0] = __float2bfloat16_rn(silu_f(v[0]) * v[1]);
+                if (n + 3 < p.rows) o[1] = __float2bfloat16_rn(silu_f(v[2]) * v[3]);
+              }
+            }
+          } else if (col < p.cols) {
+            if (EPI == 0) {
+              __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)col * p.ld_out + n;
+              if (live && vec_out) {
+                uint2 pk;
+                pk.x = pack_bf16x2(v[0], v[1]);
+                pk.y = pack_bf16x2(v[2], v[3]);
+                *reinterpret_cast<uint2*>(o) = pk;
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) if (n + j < p.rows) o[j] = __float2bfloat16_rn(v[j]);
+              }
+            } else {
+              float* o = (float*)p.out + (size_t)col * p.ld_out + n;
+              if (live && vec_out) {
+                *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) if (n + j < p.rows) o[j] = v[j];
+              }
+            }
+          }
+        }
+      }
+    } else {
+      const int group = EPI == 3 ? rows_per / 2 : rows_per;  // items per column: rows, or gate/up pairs
+      const int items = group * BN;
+      const int t = threadIdx.x - 64;                        // 0..255 in the epilogue warps
+      const bool worker = warp >= 2;
+      auto item_pos = [&](int idx, int& r, int& col) {
+        col = idx / group;
+        r = EPI == 3 ? 2 * (idx % group) : idx % group;
+      };
+      cluster_arrive();
+      // what the add epilogue adds to and multiplies by, fetched under the barrier: this thread's first
+      // four items (16 to 64 tokens give a thread 1 to 4 of them with eight splits; a fetch inside the
+      // loop below costs a trip to L2 each time, 1 us per round at 64 tokens)
+      constexpr int kAheadItems = 4;
+      float res0[kAheadItems], nw0[kAheadItems];
+#pragma unroll
+      for (int i = 0; i < kAheadItems; ++i) {
+        res0[i] = 0.f;
+        nw0[i] = 0.f;
+        const int idx = t + 256 * i;
+        if (EPI == 2 && worker && idx < items) {
+          int r, col;
+          item_pos(idx, r, col);
+          const int n = row_tile * kTileRows + split * rows_per + r;
+          if (n < p.rows && col < p.cols) {
+            res0[i] = __ldcg((const float*)p.out + (size_t)col * p.ld_out + n);
+            if (p.xs) nw0[i] = __ldg(p.norm_w + n);
+          }
+        }
+      }
+      cluster_wait();                                        // the partial sums of this block's rows have arrived
+      if (worker && !*abort_flag) {
+        auto sum_sources = [&](int r, int col) {
+          float a[8];
+#pragma unroll
+          for (int z = 0; z < 8; ++z) a[z] = z < S ? recv[(z * BN + col) * rows_per + r] : 0.f;
+          float v = a[0];
+#pragma unroll
+          for (int z = 1; z < 8; ++z) v += a[z];
+          return v;
+        };
+#pragma unroll 1
+        for (int idx = t, i = 0; idx < items; idx += 256, ++i) {
+          int r, col;
+          item_pos(idx, r, col);
+          const int n = row_tile * kTileRows + split * rows_per + r;
+          const float sc = p.scale_sumsq ? s_scale[col] : 1.f;
+          const float v = sum_sources(r, col) * sc;
+          if (EPI == 2) {
+            float have = 0.f, nwv = 0.f;
+#pragma unroll
+            for (int j = 0; j < kAheadItems; ++j) if (j == i) { have = res0[j]; nwv = nw0[j]; }
+            add_and_emit(p, n, col, v, i < kAheadItems, have, lane, nwv);     // (every lane: the sums of squares are added over half warps)
+          } else {
+            store_swapped_one<EPI>(p, n, col, v, EPI == 3 ? sum_sources(r + 1, col) * sc : 0.f);
+          }
         }
       }
     }

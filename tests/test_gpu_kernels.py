@@ -112,7 +112,8 @@ def test_linear_bfloat16(ops, M, N, K):
     (130, 2048, 8192), (520, 2048, 2048), (1000, 1024, 1024),                                   # ... too few tiles: the add cuts the K range
     (1024, 8192, 128), (600, 4096, 192), (2048, 3072, 256),                                     # ... wide tiles: pairs of blocks (MMAs of 256 rows)
     (1, 304, 80), (8, 3072, 2048), (16, 2048, 2048), (17, 1000, 72), (33, 2048, 8192), (64, 1000, 512),
-    (64, 9600, 512), (40, 16384, 2048), (8, 16384, 2048), (24, 12000, 1024)])   # few: swapped, K split 2, 4 or 8 ways
+    (64, 9600, 512), (40, 16384, 2048), (8, 16384, 2048), (24, 12000, 1024),    # few: swapped, K split 2, 4 or 8 ways
+    (50, 1002, 1024), (64, 2050, 2048), (36, 4098, 512)])                       # ... feature counts that end inside a group of four
 def test_tensor_core_product_and_its_epilogues(ops, M, N, K):
     """The tcgen05/TMEM product against a float64 product: plain bfloat16 and float32 outputs, the
     in-place add into a float32 residual, and SiLU(gate)*up on alternating weight rows."""
