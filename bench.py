@@ -47,9 +47,11 @@ def _llama(layers, hidden, heads, kv_heads, head_dim, inter, factor, tied):
 
 # The default run is the Llama-3.2-1B shape (the headline configuration).  ``--shape`` runs the same
 # measurements on the two larger Llama shapes with their own workloads: 3b also times a serving run
-# (32 requests, prompts of 128 to 2,048 tokens, 256 generated tokens each, continuous batching).
+# (32 requests, prompts of 128 to 2,048 tokens, 256 generated tokens each, continuous batching);
+# 1b-long decodes at the model's longest context (4 and 1 requests of 131,072 tokens).
 SHAPES = {
     "1b": {"name": "Llama-3.2-1B", "model": MODEL, "context": 4096, "batch": 8, "points": "1,64", "serving": None},
+    "1b-long": {"name": "Llama-3.2-1B", "model": MODEL, "context": 131072, "batch": 4, "points": "1", "serving": None},
     "3b": {"name": "Llama-3.2-3B", "model": _llama(28, 3072, 24, 8, 128, 8192, 32.0, True), "context": 2304, "batch": 32,
            "points": "1", "serving": {"requests": 32, "prompt_lo": 128, "prompt_hi": 2048, "generated": 256}},
     "8b": {"name": "Llama-3.1-8B", "model": _llama(32, 4096, 32, 8, 128, 14336, 8.0, False), "context": 8192, "batch": 64,
@@ -274,7 +276,7 @@ def main() -> int:
     if not args.no_e2e:
         # Prompts are cut into 2,048-token portions, so requests reach decoding a few steps apart;
         # they are sized so that none ends (and the batch never shrinks) inside the timed steps.
-        ctx0 = CONTEXT - K - W - 3 * B
+        ctx0 = CONTEXT - K - W - B * (-(-CONTEXT // PREFILL_TOKENS) + 1)
         params = SamplingParams(temperature=0.0, max_gen_len=None, stop_token_ids=[])
         reqs = [llm.add_request(tokens(ctx0), params) for _ in range(B)]
         # ``LLM.run`` is the loop behind ``generate``: it yields every step's tokens as host

@@ -7,7 +7,7 @@ name exists there.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -36,6 +36,8 @@ class EngineConfig:
     max_batched_tokens: int = 2048             # token budget of one step
     compiled_model: bool = False               # capture decode steps in CUDA graphs
     capture_mixed_steps: bool = True           # with compiled_model: also steps that hold prompt portions (padded shapes, up to 1,024 tokens)
+    graph_context_buckets: Tuple[int, ...] = (4096, 16384, 65536)   # with compiled_model: decode steps are captured per class of
+                                               # context length (the key splits of attention are fixed at capture)
     overlap_steps: bool = True                 # plan and launch the next step while the last one's tokens are read
     timing: bool = False                       # diagnostic: CUDA-event time of every step and of every class of kernels; steps run
                                                # uncaptured and the host waits for each (lite_llama/generete_with_probs.py:124-126,176-182 times its loop so)
@@ -48,5 +50,8 @@ class EngineConfig:
                 raise ValueError(f"{name} must be positive")
         if self.max_gpu_num_blocks is not None and self.max_gpu_num_blocks <= 0:
             raise ValueError("max_gpu_num_blocks must be positive")
+        self.graph_context_buckets = tuple(sorted(int(c) for c in self.graph_context_buckets))
+        if any(c <= 0 for c in self.graph_context_buckets):
+            raise ValueError("graph_context_buckets must be positive")
         if not 0 < self.gpu_memory_fraction <= 1:
             raise ValueError("gpu_memory_fraction must be in (0, 1]")

@@ -94,6 +94,7 @@ class _HostBatch:
         self.R = len(entries)
         self.T = sum(q_lens)
         self.max_q_len = max(q_lens)
+        self.max_ctx_len = max(s + n for s, n in zip(starts, q_lens))
         self.work: Dict[str, List[int]] = work or {}      # the operator set's lists for this step (ops.plan_step)
 
 
@@ -119,6 +120,15 @@ class _Layout:
     def view(self, dev: torch.Tensor, name: str) -> torch.Tensor:
         lo, n = self.seg[name]
         return dev[lo:lo + n]
+
+
+@dataclass(frozen=True)
+class _DecodeShape:
+    """Names the captured step of ``batch`` single tokens whose contexts are at most ``context`` tokens
+    long, where that is less than the engine's longest (the captured step for the longest has the
+    plain batch size as its name)."""
+    batch: int
+    context: int
 
 
 @dataclass
@@ -178,7 +188,7 @@ class Engine:
         self.stats = EngineStats()
         if self.config.timing and hasattr(self.ops, "enable_timing"):
             self.ops.enable_timing()
-        self._graphs = {}          # captured steps: padded batch size (single tokens only) or a _StepShape
+        self._graphs = {}          # captured steps: padded batch size or _DecodeShape (single tokens only), or a shape tuple
         self._shape_seen: Dict[tuple, int] = {}
         self._shape_captures = 0
         self._graph_pool = None    # one memory pool for the captured steps of mixed shapes
@@ -426,7 +436,21 @@ class Engine:
         b = 1
         while b < batch.R:
             b *= 2
-        return b if b <= max(64, self.config.max_num_seqs) else 0
+        if b > max(64, self.config.max_num_seqs):
+            return 0
+        context = self._context_bucket(batch.max_ctx_len)
+        return b if context >= self.config.max_seq_len else _DecodeShape(b, context)
+
+    def _context_bucket(self, longest: int) -> int:
+        """The context length a captured step of single tokens is made for: the operator set decides
+        once, at capture, how it cuts the keys of a request into parallel work, and what suits
+        131,072 keys is slow for 2,000.  So steps are captured per class of context length
+        (``graph_context_buckets``; classes that reach within a factor of two of ``max_seq_len`` fall
+        into the last, which is ``max_seq_len`` itself)."""
+        for c in self.config.graph_context_buckets:
+            if longest <= c and 2 * c <= self.config.max_seq_len:
+                return c
+        return self.config.max_seq_len
 
     GRAPH_MAX_TOKENS = 1024      # larger steps keep the GPU busy for longer than the host needs to launch them
     GRAPH_MAX_SHAPES = 24
@@ -498,6 +522,7 @@ class Engine:
         request, so the runs that record it touch no page of the cache."""
         width = _pad4(self.cache.max_blocks)
         infos = self._work_lists()
+        longest = self.config.max_seq_len                    # what the step's kernels are laid out for
         if isinstance(bucket, tuple):
             t_pad, r_pad, wants, lists = bucket
             work_items = dict(lists)
@@ -506,6 +531,8 @@ class Engine:
                              work_sizes={name: n * infos[name].width for name, n in lists})
             q_lens = [t_pad] + [1] * (r_pad - 1)
         else:
+            if isinstance(bucket, _DecodeShape):
+                bucket, longest = bucket.batch, bucket.context
             plan = getattr(self.ops, "plan_step", None)
             work = plan([1] * bucket, [0] * bucket) if plan is not None else {}
             work_items, in_order = self._work_items(work), self._work_in_order(work, bucket)
@@ -525,8 +552,8 @@ class Engine:
                 lo, n = layout.seg[f"work:{name}"]
                 h[lo:lo + n] = np.asarray(values, dtype=np.int32)
         dev = host.to(self.device)
-        splits = self._choose_splits(layout.T, self.config.max_seq_len)
-        ctx, cache_view = self._context(dev, layout, q_lens, [self.config.max_seq_len] * layout.R, splits,
+        splits = self._choose_splits(layout.T, longest)
+        ctx, cache_view = self._context(dev, layout, q_lens, [longest] * layout.R, splits,
                                         work_items=work_items, in_order=in_order)
 
         def run():

@@ -690,6 +690,7 @@ class CudaOps:
         return True
 
     DECODE_BLOCKS = int(os.environ.get("PTL_DECODE_BLOCKS", "592"))    # blocks the decode attention aims for: the four per SM that fit at once
+    DECODE_KEYS_PER_WIDE_BLOCK = int(os.environ.get("PTL_DECODE_KEYS_PER_WIDE_BLOCK", "1024"))   # keys a block of the two-per-SM form walks at most
 
     _DECODE_COUNTERS = 1 << 16
 
@@ -709,6 +710,12 @@ class CudaOps:
             splits = max(1, min(target // pairs, -(-longest // 128)))
             if target == 296 and splits > 8:
                 splits = 8      # what a cluster merges through shared memory; more splits would go through global memory (slower)
+            if target == 296 and longest > self.DECODE_KEYS_PER_WIDE_BLOCK * splits:
+                # Long contexts at small batches: a block of the cluster form has two 128-key tiles in
+                # flight, and with more than eight to walk that no longer covers the memory's latency
+                # (one request of 131,072 tokens: 196 us against 55 us).  Four blocks per SM with three
+                # 64-key tiles each in flight do, merged by the last block of a token's splits.
+                splits = max(splits, min(self.DECODE_BLOCKS // pairs, -(-longest // 128)))
             # The split count of this kernel is decided here, from the number of blocks the machine
             # holds (``attn_splits`` of the step context is the CUDA-core kernel's).  A caller may fix
             # it (``decode_splits``) and leave the counters out (``decode_counters`` False) to pin one

@@ -120,6 +120,36 @@ def test_long_decoding(model_folders, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_from_graphs_captured_per_class_of_context_length(model_folders, dtype):
+    """With ``compiled_model`` a step of single tokens replays the graph captured for its batch size
+    and for the class its longest context falls into (here up to 64, up to 128, and the engine's 512):
+    300 tokens one by one through all three classes, beside a second request that ends on the way."""
+    from pytriton_llama_b200.engine.engine import StepEntry, _DecodeShape
+    name = "A"
+    vocab = TINY[name]["vocab_size"]
+    seqs = {"long": random_tokens(330, vocab, 7), "side": random_tokens(90, vocab, 8)}
+    ref = reference_logits(model_folders(name, stored_dtype(dtype)), seqs)
+    eng = make_engine(model_folders(name, stored_dtype(dtype)), name, dtype, pages=190, max_seq_len=512, compiled_model=True,
+                      graph_context_buckets=(64, 128))
+    out = eng.step([StepEntry("long", seqs["long"][:30], [29]), StepEntry("side", seqs["side"][:5], [])])
+    rows = {"long": [out.logits[0].cpu()], "side": []}
+    for p in range(30, 330):
+        entries = [StepEntry("long", [seqs["long"][p]], [0])]
+        q = 5 + (p - 30)
+        if q < 90:
+            entries.append(StepEntry("side", [seqs["side"][q]], [0]))
+        out = eng.step(entries)
+        rows["long"].append(out.logits[0].cpu())
+        if q < 90:
+            rows["side"].append(out.logits[1].cpu())
+        if q == 89:
+            eng.finish("side")
+    assert set(eng._graphs) >= {_DecodeShape(2, 64), _DecodeShape(2, 128), _DecodeShape(1, 128), 1}
+    assert_close(torch.stack(rows["long"]), ref["long"][29:], dtype, "long")
+    assert_close(torch.stack(rows["side"]), ref["side"][5:], dtype, "side")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(model_folders, references, tmp_path, dtype):
     """bin/trace_run as a user runs it: JSON steps on standard input, <step>.f32 files out."""
     name = "B"
