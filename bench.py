@@ -235,6 +235,8 @@ def main() -> int:
     prefill = {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3),
                "frac": round(prefill_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
 
+    if args.no_prefill:
+        prefill = None
     if args.only_prefill:
         print(json.dumps({"prefill": prefill}))
         return 0

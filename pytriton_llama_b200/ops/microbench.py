@@ -12,6 +12,8 @@ the last block of each grid entered, got past the wait on its predecessor, had i
 finished its loop, had its results complete and left -- %globaltimer stamps, in microseconds from
 the layer's first stamp: what a sum of kernel times cannot show, the gaps between dependent kernels.
 ``product_shapes`` times the many-token products of the model beside the library's (torch.mm).
+``decode_contexts`` times one layer's decode attention at batch 1 to 16 over contexts of 4,096 to
+131,072 tokens, with the split count the operator set chooses and with the cluster form alone.
 Inputs are larger than the 126 MB L2 where the kernel is a stream, so
 DRAM figures mean something, yet small enough for a profiler to replay.  Each case prints its
 time from CUDA events after warm-up and the bytes or FLOPs per second that follow from it.
@@ -150,9 +152,60 @@ def product_shapes(reps: int) -> dict:
     return {"case": "product_shapes", "rows": rows}
 
 
+def decode_contexts(reps: int) -> dict:
+    """Decode attention of one layer (rotary encoding and cache write folded in) from a captured graph,
+    over batch sizes and context lengths: the split count the operator set chooses beside the
+    cluster form alone (at most eight splits of a token's keys, two blocks per SM).  Each timed
+    replay walks enough separate caches that none is still in L2 when its turn comes again."""
+    dev = torch.device("cuda:0")
+    ops = CudaOps(dev)
+    nq, nkv, d, page = 32, 8, 64, 16
+    inv = (1.0 / (500000.0 ** (torch.arange(0, d, 2, device=dev).float() / d))).contiguous()
+
+    def timed(batch, ctx, splits):
+        per = ctx // page
+        layer_bytes = batch * per * 2 * nkv * page * d * 2
+        copies = max(2, min(64, int(400e6 // layer_bytes) + 1))
+        caches = [torch.randn(batch * per, 2, nkv, page, d, device=dev).bfloat16() for _ in range(copies)]
+        table = torch.arange(batch * per, dtype=torch.int32, device=dev).view(batch, per)
+        rows = torch.arange(batch, dtype=torch.int32, device=dev)
+        pos = torch.full((batch,), ctx - 1, dtype=torch.int32, device=dev)
+        slots = (rows * per * page + ctx - 1).int()
+        qkv = torch.randn(batch, (nq + 2 * nkv) * d, device=dev).bfloat16()
+        hints = ops.hints_for([1] * batch, [ctx] * batch)
+        if splits:
+            hints.decode_splits = splits
+
+        def walk():
+            for c in caches:
+                ops.rope_attention(qkv, pos, inv, d, slots, c, table, rows, nq, nkv, d, page, d ** -0.5, hints=hints)
+        walk()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            walk()
+        sec = _time(graph.replay, reps, ops) / copies
+        return round(sec * 1e6, 1), round(layer_bytes / sec / 1e9)
+
+    table = []
+    for batch in (1, 4, 8, 16):
+        for ctx in (4096, 16384, 65536, 131072):
+            if batch * ctx > 8 * 131072:
+                continue
+            pairs = batch * nkv
+            cluster_form = max(1, min(296 // pairs, 8, ctx // 128))
+            us, gbs = timed(batch, ctx, 0)
+            us_c, gbs_c = timed(batch, ctx, cluster_form)
+            table.append({"batch": batch, "context": ctx, "us": us, "GB/s": gbs, "cluster_form_splits": cluster_form,
+                          "cluster_form_us": us_c, "cluster_form_GB/s": gbs_c})
+    return {"case": "decode_contexts", "rows": table}
+
+
 def run(case: str, reps: int, batch: int = 8) -> dict:
     if case == "decode_timeline":
         return decode_timeline(batch)
+    if case == "decode_contexts":
+        return decode_contexts(reps)
     if case == "product_shapes":
         return product_shapes(reps)
     dev = torch.device("cuda:0")
@@ -218,7 +271,7 @@ def run(case: str, reps: int, batch: int = 8) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("case", choices=["decode_attention", "decode_step_attention", "gemm_decode", "gemm_prefill", "prefill_attention",
-                                     "prefill_attention_d128", "decode_timeline", "product_shapes"])
+                                     "prefill_attention_d128", "decode_timeline", "product_shapes", "decode_contexts"])
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--batch", type=int, default=8, help="decode_timeline: requests in the step")
     args = ap.parse_args()
@@ -229,6 +282,11 @@ def main() -> None:
         for k in out["kernels"]:
             for which in ("first block", "last block"):
                 print(f"{k['kernel']:24s} {which.split()[0]:6s} " + " ".join(f"{'-' if v is None else v:>16}" for v in k[which]))
+    elif args.case == "decode_contexts":
+        print(f"{'batch':>5s} {'context':>8s} {'us':>8s} {'GB/s':>6s}   cluster form alone: {'splits':>6s} {'us':>8s} {'GB/s':>6s}")
+        for r in out["rows"]:
+            print(f"{r['batch']:5d} {r['context']:8d} {r['us']:8.1f} {r['GB/s']:6d}   {'':19s} {r['cluster_form_splits']:6d} "
+                  f"{r['cluster_form_us']:8.1f} {r['cluster_form_GB/s']:6d}")
     elif args.case == "product_shapes":
         print(f"{'product':8s} {'tokens':>6s} {'N':>6s} {'K':>6s} {'ours us':>9s} {'library us':>11s} {'+extra us':>10s}  routed to")
         for r in out["rows"]:
