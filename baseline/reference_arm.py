@@ -27,6 +27,7 @@ from __future__ import annotations
 import contextlib
 import io
 import json
+import os
 import shutil
 import statistics
 import sys
@@ -37,7 +38,7 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 REF_DIR = HERE / "_ref"
-REFERENCE_SOURCE = Path("/root/reference")
+REFERENCE_SOURCE = Path(os.environ.get("PTL_REFERENCE_SOURCE", "/root/reference"))     # the lite_llama checkout to copy from
 
 
 class ReferenceUnavailable(RuntimeError):
