@@ -118,13 +118,13 @@ class ClockSampler:
         return {"sm_mhz": int(statistics.median(sm)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def model_bytes_and_flops(cfg, layers):
+def model_bytes_and_flops(cfg, layers, elem=2):
     H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     per_layer = (nq + 2 * nkv) * d * H + H * nq * d + 3 * I * H
     matmul_params = layers * per_layer            # the LM head is counted per wanted row
-    weight_bytes = 2 * (matmul_params + V * H) + 4 * (2 * layers + 1) * H
-    kv_bytes_per_token = layers * 2 * nkv * d * 2
+    weight_bytes = elem * (matmul_params + V * H) + 4 * (2 * layers + 1) * H       # elem: bytes of a weight and of a cached value
+    kv_bytes_per_token = layers * 2 * nkv * d * elem
     return matmul_params, V * H, weight_bytes, kv_bytes_per_token
 
 
@@ -153,6 +153,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                    help="float32: the true 32-bit path (CUDA-core products, compensated sums), for its own numbers")
     ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="which Llama shape (default: the headline 1B configuration)")
     ap.add_argument("--batch", type=int, default=None, help="decode batch (default: 8; 32 for 3b; 64 for 8b)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
@@ -190,7 +192,7 @@ def main() -> int:
     max_batch = max([B] + points)
     max_seq = CONTEXT + 8
     pages = max_batch * (-(-max_seq // 16)) + 64
-    ecfg = EngineConfig(dtype="bfloat16", page_size=16, max_gpu_num_blocks=pages, max_seq_len=max_seq,
+    ecfg = EngineConfig(dtype=args.dtype, page_size=16, max_gpu_num_blocks=pages, max_seq_len=max_seq,
                         max_num_seqs=max_batch, max_batched_tokens=PREFILL_TOKENS, compiled_model=not args.no_graph, seed=0)
     llm = LLM(None, ecfg, model_config=cfg, random_seed=0)
     engine = llm.engine
@@ -228,7 +230,13 @@ def main() -> int:
         if i >= 3:
             times.append(ms)
     prefill_ms = statistics.median(times) if times else float("nan")
-    matmul_params, head_params, weight_bytes, kv_per_token = model_bytes_and_flops(cfg, args.layers)
+    fp32 = args.dtype == "float32"
+    matmul_params, head_params, weight_bytes, kv_per_token = model_bytes_and_flops(cfg, args.layers, 4 if fp32 else 2)
+    if fp32:
+        # the true 32-bit path runs on the CUDA cores: its peak is FMA lanes x 2 x the clock
+        props = torch.cuda.get_device_properties(dev)
+        peaks["bf16_tflops"] = props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12
+        peak_kind += "; float32 flops against 128 FMA lanes per SM at 1,965 MHz"
     nq, d = cfg["num_attention_heads"], cfg["head_dim"]
     attn_flops = args.layers * 4 * nq * d * (PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2)
     prefill_flops = 2 * matmul_params * PREFILL_TOKENS + attn_flops + 2 * head_params
@@ -332,7 +340,7 @@ def main() -> int:
     out = {
         "metric": "decode_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "dtype": "fp32" if fp32 else "bf16", "data": "synthetic", "impl": "ours",
         "config": {
             "model": f"{shape['name']} shape, random weights (seed 0)", "layers": args.layers, "layers_of_model": MODEL["num_hidden_layers"],
             "hidden": cfg["hidden_size"], "heads": nq, "kv_heads": cfg["num_key_value_heads"], "head_dim": d,
