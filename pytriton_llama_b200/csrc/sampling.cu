@@ -1,4 +1,4 @@
-// Next-token choice from float32 logits, one block per row.
+// Next-token choice from float32 logits.
 //
 // temperature[row] <= 0: the index of the largest logit (the lowest index among equals).
 // Otherwise: p_i = exp((x_i - max) / temperature); nucleus filter with lite_llama's rule (a token
@@ -8,9 +8,17 @@
 // not depend on what else is in the batch.
 //
 // The filter needs no sort: with f(x) = sum of p_j over p_j > x, the kept tokens are exactly those
-// with p_i >= x*, where x* is the smallest float with f(x*) <= top_p * total; x* is found by
-// bisection on the bit pattern (positive floats order like their bits).
-// `probs` is scratch memory of [rows, vocab] floats.
+// with p_i >= x*, where x* is the smallest float with f(x*) <= top_p * total.  Positive floats
+// order like their bit patterns, and p <= 1 has 30 significant pattern bits, so x* is found ten
+// bits at a time: a histogram of probability mass over the top ten bits says which bucket x* lies
+// in and how much of the budget is left for it, a second histogram over the next ten bits of that
+// bucket's tokens narrows it again, a third one ends it.  Masses are added as 64-bit fixed-point
+// numbers (p * 2^40): integer sums do not depend on their order, so the histograms can be built
+// with atomics by 32 blocks per row and the choice is still the same in every run.
+// Six launches per call (row maxima by slices; three histogram levels; the kept mass by slices;
+// the draw), 32 blocks per row in the first five, so that a few rows still use many SMs.
+// `probs` is scratch memory of [rows, vocab] floats; `work` of kSampleWorkPerRow 64-bit words per
+// row, zero before the first call and left zero again by every call.
 #include "common.cuh"
 
 namespace ptl {
@@ -43,101 +51,6 @@ __device__ __forceinline__ void block_argmax(float& v, int& idx, float* sv, int*
   __syncthreads();
   v = sv[32];
   idx = si[32];
-}
-
-__global__ void __launch_bounds__(kSampleThreads)
-sample_kernel(int* __restrict__ tokens, const float* __restrict__ logits, float* __restrict__ probs,
-              const float* __restrict__ temperature, const float* __restrict__ top_p,
-              const float* __restrict__ u, int vocab, long long ld) {
-  __shared__ float sv[33];
-  __shared__ int si[33];
-  __shared__ float red[33];
-  __shared__ float chunk_sum[kSampleThreads];
-  pdl_wait();
-  pdl_launch_dependents();
-  const int row = blockIdx.x;
-  const float* x = logits + (size_t)row * ld;
-  const int tid = threadIdx.x;
-
-  float best = -INFINITY;
-  int besti = 0x7fffffff;
-  for (int i = tid; i < vocab; i += blockDim.x) {
-    const float v = x[i];
-    if (v > best || (v == best && i < besti)) { best = v; besti = i; }
-  }
-  block_argmax(best, besti, sv, si);
-  const float temp = temperature ? temperature[row] : 0.f;
-  if (!(temp > 0.f)) {
-    if (tid == 0) tokens[row] = besti;
-    return;
-  }
-  float* pr = probs + (size_t)row * vocab;
-  const float inv_t = 1.0f / temp;
-  float part = 0.f;
-  for (int i = tid; i < vocab; i += blockDim.x) {
-    const float e = expf((x[i] - best) * inv_t);
-    pr[i] = e;
-    part += e;
-  }
-  const float total = block_sum(part, red);
-  const float budget = top_p[row] * total;
-
-  // bisection for the smallest bit pattern b with f(float(b)) <= budget
-  unsigned lo = 0u, hi = __float_as_uint(1.0f);  // f(1) = 0 because the largest p is exactly 1
-  {
-    float s = 0.f;
-    for (int i = tid; i < vocab; i += blockDim.x) { const float e = pr[i]; if (e > 0.f) s += e; }
-    s = block_sum(s, red);
-    if (s <= budget) hi = 0u;  // everything stays
-  }
-  while (hi - lo > 1u && hi != 0u) {
-    const unsigned mid = lo + (hi - lo) / 2u;
-    const float thr = __uint_as_float(mid);
-    float s = 0.f;
-    for (int i = tid; i < vocab; i += blockDim.x) { const float e = pr[i]; if (e > thr) s += e; }
-    s = block_sum(s, red);
-    if (s <= budget) hi = mid; else lo = mid;
-  }
-  const float cut = __uint_as_float(hi);
-
-  // draw: contiguous chunk per thread, exclusive scan over the chunk sums, walk inside one chunk
-  const int per = (vocab + blockDim.x - 1) / blockDim.x;
-  const int c0 = min(tid * per, vocab), c1 = min(c0 + per, vocab);
-  float mine = 0.f;
-  for (int i = c0; i < c1; ++i) { const float e = pr[i]; if (e >= cut) mine += e; }
-  chunk_sum[tid] = mine;
-  __syncthreads();
-  if (tid == 0) {
-    float kept_total = 0.f;
-    for (int k = 0; k < blockDim.x; ++k) kept_total += chunk_sum[k];
-    const float target = u[row] * kept_total;
-    float run = 0.f;       // kept mass of the chunks before `owner`
-    int owner = -1;
-    int last = 0;          // the last non-empty chunk catches a target that rounding pushed past the end
-    float before_last = 0.f;
-    for (int k = 0; k < blockDim.x; ++k) {
-      const float c = chunk_sum[k];
-      if (c > 0.f) {
-        if (run + c > target) { owner = k; break; }
-        last = k;
-        before_last = run;
-        run += c;
-      }
-    }
-    if (owner < 0) { owner = last; run = before_last; }
-    const int o0 = min(owner * per, vocab), o1 = min(o0 + per, vocab);
-    int choice = besti;
-    float acc = run;
-    for (int i = o0; i < o1; ++i) {
-      const float e = pr[i];
-      if (e >= cut) {
-        choice = i;
-        acc += e;
-        if (acc > target) break;
-      }
-    }
-    tokens[row] = choice;
-  }
 }
 
 // log softmax(logits[row])[tokens[row]] of the unscaled logits, one block per row
@@ -207,6 +120,298 @@ __global__ void argmax_final_kernel(int* __restrict__ tokens, const float* __res
   if (lane == 0) tokens[row] = idx;
 }
 
+
+// ---------------------------------------------------------------- temperature and nucleus sampling
+constexpr int kSampleBuckets = 1024;                     // ten pattern bits per level
+constexpr int kSampleLevelThreads = 256;
+constexpr int kSampleBatch = 8;                          // loads a thread has in flight
+constexpr int kSampleWorkPerRow = 3 * kSampleBuckets + 64;   // 64-bit words of `work` per row: three histograms, 32 kept masses, the cut
+constexpr float kSampleFixedPoint = 1099511627776.f;     // 2^40
+
+__device__ __forceinline__ unsigned long long mass_of(float e) { return __float2ull_rz(e * kSampleFixedPoint); }
+
+__device__ __forceinline__ unsigned long long warp_scan_u64(unsigned long long v, int lane) {     // inclusive
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long t = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += t;
+  }
+  return v;
+}
+
+// Inclusive scan over the block's threads in thread order (up to 1,024 threads); every thread also
+// gets the block's total.  `scratch` holds 33 words.
+__device__ __forceinline__ unsigned long long block_scan_u64(unsigned long long v, unsigned long long* scratch,
+                                                             unsigned long long& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_scan_u64(v, lane);
+  __syncthreads();                                       // (scratch may still be read from the scan before)
+  if (lane == 31) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    unsigned long long t = lane < nwarps ? scratch[lane] : 0ull;
+    t = warp_scan_u64(t, lane);
+    scratch[lane] = t;
+    if (lane == 31) scratch[32] = t;
+  }
+  __syncthreads();
+  if (warp > 0) v += scratch[warp - 1];
+  total = scratch[32];
+  return v;
+}
+
+// Where x* lies among the buckets of one histogram: the smallest bucket b such that the mass in
+// the buckets above b is <= budget, and what is left of the budget after that mass.  Every thread
+// of a 256-thread block calls it and gets both.  Bucket 4 (255 - t) + j in thread t's registers.
+__device__ __forceinline__ void find_bucket(const unsigned long long* __restrict__ hist, unsigned long long budget,
+                                            unsigned long long* scratch, int* s_bucket, unsigned long long* s_left,
+                                            int& bucket, unsigned long long& left) {
+  const int t = threadIdx.x;                             // walks the buckets from the top: thread 0 has 1023..1020
+  unsigned long long h[4];
+  const int b0 = kSampleBuckets - 4 * (t + 1);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __ldcg(hist + b0 + j);
+  const unsigned long long mine = h[0] + h[1] + h[2] + h[3];
+  unsigned long long total;
+  const unsigned long long incl = block_scan_u64(mine, scratch, total);
+  unsigned long long above = incl - mine;                // mass in the buckets above this thread's four
+  // the predicate "mass above b <= budget" holds for the top bucket and, going down, up to some bucket: the last one is it
+  int best = -1;
+  unsigned long long best_left = 0ull;
+#pragma unroll
+  for (int j = 3; j >= 0; --j) {                         // from this thread's highest bucket down
+    if (above <= budget) { best = b0 + j; best_left = budget - above; }
+    above += h[j];
+  }
+  // the smallest such bucket over the block: threads further down hold smaller buckets
+  if (best >= 0) atomicMin(s_bucket + 1, best);
+  __syncthreads();
+  if (best >= 0 && best == s_bucket[1]) *s_left = best_left;
+  __syncthreads();
+  bucket = s_bucket[1];
+  left = *s_left;
+}
+
+struct SampleLevelArgs {
+  const float* logits;
+  float* probs;
+  const float* temperature;
+  const float* top_p;
+  const float* part_val;          // [rows][32] maxima of the slices of every row
+  unsigned long long* work;       // [rows][kSampleWorkPerRow]: three histograms, the kept mass of the 32 slices, the cut
+  int vocab;
+  long long ld;
+};
+
+// total mass, budget, and down `levels` histograms of the row: the pattern bits of x* found so far.
+// Every thread of a 256-thread block calls it; s_bucket[1] need not be prepared.
+__device__ __forceinline__ unsigned descend(const unsigned long long* __restrict__ work, float top_p, int levels,
+                                            unsigned long long* scratch, int* s_bucket, unsigned long long* s_left) {
+  unsigned long long total = 0ull;
+  {
+    unsigned long long mine = 0ull;
+    for (int b = threadIdx.x; b < kSampleBuckets; b += blockDim.x) mine += __ldcg(work + b);
+    block_scan_u64(mine, scratch, total);
+  }
+  unsigned long long budget = top_p >= 1.f ? total : (unsigned long long)((double)top_p * (double)total);
+  unsigned prefix = 0u;
+  for (int level = 0; level < levels; ++level) {
+    __syncthreads();
+    if (threadIdx.x == 0) s_bucket[1] = kSampleBuckets;
+    __syncthreads();
+    int bucket;
+    find_bucket(work + level * kSampleBuckets, budget, scratch, s_bucket, s_left, bucket, budget);
+    prefix = (prefix << 10) | (unsigned)bucket;
+  }
+  return prefix;
+}
+
+// A block's histogram of mass lives in shared memory as three 32-bit counters per bucket (14 bits
+// of the 42-bit mass each: 32-bit shared-memory adds are native, 64-bit ones are compare-and-swap
+// loops that crawl when many threads meet in a bucket); a slice has few enough tokens that none overflows.
+__device__ __forceinline__ void hist_add(unsigned* hist, unsigned bucket, unsigned long long q) {
+  atomicAdd(hist + bucket, (unsigned)(q & 0x3fffu));
+  atomicAdd(hist + kSampleBuckets + bucket, (unsigned)((q >> 14) & 0x3fffu));
+  atomicAdd(hist + 2 * kSampleBuckets + bucket, (unsigned)(q >> 28));
+}
+
+// LEVEL 0: p = exp((x - max) / T) into `probs`, histogram of mass over pattern bits 29..20.
+// LEVEL 1: bucket of level 0 from its histogram, histogram over bits 19..10 of that bucket's tokens.
+// LEVEL 2: likewise over bits 9..0.
+// LEVEL 3: the cut is known: the kept mass of this block's slice (and, from slice 0, the cut itself).
+template <int LEVEL>
+__global__ void __launch_bounds__(kSampleLevelThreads)
+sample_level_kernel(const SampleLevelArgs a) {
+  __shared__ unsigned hist[3 * kSampleBuckets];
+  __shared__ unsigned long long scratch[33];
+  __shared__ int s_bucket[2];
+  __shared__ unsigned long long s_left;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int row = blockIdx.x / kArgmaxChunks, chunk = blockIdx.x % kArgmaxChunks;
+  const float temp = a.temperature[row];
+  if (!(temp > 0.f)) return;                             // a greedy row: the last kernel takes the largest logit
+  const int tid = threadIdx.x;
+  if (LEVEL < 3)
+    for (int b = tid; b < 3 * kSampleBuckets; b += blockDim.x) hist[b] = 0u;
+  unsigned long long* work = a.work + (size_t)row * kSampleWorkPerRow;
+  float* pr = a.probs + (size_t)row * a.vocab;
+  const int per = (a.vocab + kArgmaxChunks - 1) / kArgmaxChunks;
+  const int lo = chunk * per, hi = min(lo + per, a.vocab);
+  const unsigned prefix = LEVEL >= 1 ? descend(work, a.top_p[row], LEVEL, scratch, s_bucket, &s_left) : 0u;
+  __syncthreads();
+  if (LEVEL == 0) {
+    float mx = -INFINITY;
+    for (int k = 0; k < kArgmaxChunks; ++k) mx = fmaxf(mx, a.part_val[row * kArgmaxChunks + k]);
+    const float inv_t = 1.0f / temp;
+    const float* x = a.logits + (size_t)row * a.ld;
+    // (loads in batches of eight ahead of the adds: an atomic between two loads would make every load wait for the one before)
+    for (int base = lo + tid; base < hi; base += kSampleBatch * kSampleLevelThreads) {
+      float v[kSampleBatch];
+#pragma unroll
+      for (int j = 0; j < kSampleBatch; ++j) {
+        const int i = base + j * kSampleLevelThreads;
+        v[j] = i < hi ? __ldg(x + i) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < kSampleBatch; ++j) {
+        const int i = base + j * kSampleLevelThreads;
+        if (i < hi) {
+          const float e = expf((v[j] - mx) * inv_t);
+          pr[i] = e;
+          hist_add(hist, min(__float_as_uint(e) >> 20, (unsigned)kSampleBuckets - 1u), mass_of(e));     // (p <= 1 stays below; a NaN must not leave the table)
+        }
+      }
+    }
+  } else if (LEVEL < 3) {
+    const int shift = LEVEL == 1 ? 10 : 0;
+    for (int base = lo + tid; base < hi; base += kSampleBatch * kSampleLevelThreads) {
+      float v[kSampleBatch];
+#pragma unroll
+      for (int j = 0; j < kSampleBatch; ++j) {
+        const int i = base + j * kSampleLevelThreads;
+        v[j] = i < hi ? __ldcg(pr + i) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < kSampleBatch; ++j) {
+        const unsigned pat = __float_as_uint(v[j]);
+        if (base + j * kSampleLevelThreads < hi && (pat >> (shift + 10)) == prefix)
+          hist_add(hist, (pat >> shift) & (kSampleBuckets - 1), mass_of(v[j]));
+      }
+    }
+  } else {
+    unsigned long long mine = 0ull, kept;
+    for (int base = lo + tid; base < hi; base += kSampleBatch * kSampleLevelThreads) {
+      float v[kSampleBatch];
+#pragma unroll
+      for (int j = 0; j < kSampleBatch; ++j) {
+        const int i = base + j * kSampleLevelThreads;
+        v[j] = i < hi ? __ldcg(pr + i) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < kSampleBatch; ++j)
+        if (base + j * kSampleLevelThreads < hi && __float_as_uint(v[j]) >= prefix) mine += mass_of(v[j]);
+    }
+    block_scan_u64(mine, scratch, kept);
+    if (tid == 0) {
+      work[3 * kSampleBuckets + chunk] = kept;
+      if (chunk == 0) work[3 * kSampleBuckets + kArgmaxChunks] = prefix;
+    }
+    return;
+  }
+  __syncthreads();
+  unsigned long long* out = work + LEVEL * kSampleBuckets;
+  for (int b = tid; b < kSampleBuckets; b += blockDim.x) {
+    const unsigned long long q = (unsigned long long)hist[b] + ((unsigned long long)hist[kSampleBuckets + b] << 14) +
+                                 ((unsigned long long)hist[2 * kSampleBuckets + b] << 28);
+    if (q) atomicAdd(out + b, q);
+  }
+}
+
+// One block per row: the slice that holds the draw from the 32 slices' kept masses, the token
+// inside it.  Leaves the row's histograms zero.
+__global__ void __launch_bounds__(kSampleLevelThreads)
+sample_draw_kernel(int* __restrict__ tokens, const SampleLevelArgs a, const int* __restrict__ part_idx,
+                   const float* __restrict__ u) {
+  __shared__ unsigned long long scratch[33];
+  __shared__ int s_owner;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int row = blockIdx.x, tid = threadIdx.x;
+  // the largest of the slices' maxima, the lowest index among equals
+  int top_idx = 0;
+  {
+    float v = tid < kArgmaxChunks ? a.part_val[row * kArgmaxChunks + tid] : -INFINITY;
+    int idx = tid < kArgmaxChunks ? part_idx[row * kArgmaxChunks + tid] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+    }
+    top_idx = idx;                                       // (valid in warp 0)
+  }
+  const float temp = a.temperature ? a.temperature[row] : 0.f;
+  if (!(temp > 0.f)) {
+    if (tid == 0) tokens[row] = top_idx;
+    return;
+  }
+  unsigned long long* work = a.work + (size_t)row * kSampleWorkPerRow;
+  const unsigned long long* kept = work + 3 * kSampleBuckets;
+  const unsigned cut_bits = (unsigned)__ldcg(kept + kArgmaxChunks);
+  // which slice: lane k of every warp holds slice k's kept mass; a scan over the lanes
+  const int lane = tid & 31;
+  const unsigned long long c = __ldcg(kept + lane);
+  const unsigned long long c_incl = warp_scan_u64(c, lane);
+  const unsigned long long kept_total = __shfl_sync(0xffffffffu, c_incl, 31);
+  const unsigned long long target = (unsigned long long)((double)u[row] * (double)kept_total);    // < kept_total because u < 1
+  const unsigned holds = __ballot_sync(0xffffffffu, c > 0ull && c_incl - c <= target && target < c_incl);
+  const int chunk = holds ? __ffs(holds) - 1 : -1;
+  const unsigned long long before_chunk = __shfl_sync(0xffffffffu, c_incl - c, chunk < 0 ? 0 : chunk);
+  for (int b = tid; b < 3 * kSampleBuckets; b += blockDim.x) work[b] = 0ull;      // zero again for the next call
+  if (tid == 0) s_owner = -1;
+  __syncthreads();
+  if (chunk < 0) {                                       // (no mass survived the fixed-point conversion: it cannot, the largest p is 1)
+    if (tid == 0) tokens[row] = top_idx;
+    return;
+  }
+  const float* pr = a.probs + (size_t)row * a.vocab;
+  const int per = (a.vocab + kArgmaxChunks - 1) / kArgmaxChunks;
+  const int lo = chunk * per, hi = min(lo + per, a.vocab);
+  const int mine_n = (hi - lo + blockDim.x - 1) / blockDim.x;
+  const int c0 = min(lo + tid * mine_n, hi), c1 = min(c0 + mine_n, hi);
+  unsigned long long mine = 0ull;
+  for (int i0 = c0; i0 < c1; i0 += kSampleBatch) {
+    float v[kSampleBatch];
+#pragma unroll
+    for (int j = 0; j < kSampleBatch; ++j) v[j] = i0 + j < c1 ? __ldcg(pr + i0 + j) : 0.f;
+#pragma unroll
+    for (int j = 0; j < kSampleBatch; ++j)
+      if (i0 + j < c1 && __float_as_uint(v[j]) >= cut_bits) mine += mass_of(v[j]);
+  }
+  unsigned long long chunk_total;
+  const unsigned long long incl = before_chunk + block_scan_u64(mine, scratch, chunk_total);
+  const unsigned long long before = incl - mine;
+  if (mine > 0ull && before <= target && target < incl) s_owner = tid;        // exactly one thread's tokens hold the target
+  __syncthreads();
+  if (tid == s_owner) {
+    unsigned long long acc = before;
+    int choice = c0;
+    for (int i = c0; i < c1; ++i) {
+      const float e = __ldcg(pr + i);
+      if (__float_as_uint(e) >= cut_bits) {
+        const unsigned long long q = mass_of(e);
+        if (q > 0ull) {
+          choice = i;
+          acc += q;
+          if (acc > target) break;
+        }
+      }
+    }
+    tokens[row] = choice;
+  }
+}
+
 }  // namespace ptl
 
 // scratch: rows * 32 floats and rows * 32 ints
@@ -231,14 +436,38 @@ PTL_EXPORT int ptl_token_logprob(float* out, const float* logits, const int* tok
                             ptl::as_stream(stream), out, logits, tokens, vocab, ld);
 }
 
+// Greedy rows (temperature == nullptr or <= 0) take the largest logit; the others are sampled as the
+// head of this file says.  `part_val`, `part_idx`: scratch of rows * 32 floats and ints; `probs`
+// [rows, vocab] floats; `work` rows * ptl_sample_work_words() 64-bit words, zero before the first
+// call (every call leaves them zero).  Without temperature only the first two are needed.
+PTL_EXPORT int ptl_sample_work_words() { return ptl::kSampleWorkPerRow; }
 PTL_EXPORT int ptl_sample(int* tokens, const float* logits, float* probs, const float* temperature,
-                          const float* top_p, const float* u, int rows, int vocab, long long ld,
-                          void* stream) {
+                          const float* top_p, const float* u, float* part_val, int* part_idx,
+                          unsigned long long* work, int rows, int vocab, long long ld, void* stream) {
+  using namespace ptl;
   PTL_REQUIRE(rows >= 0 && vocab > 0 && ld >= vocab, "sample: bad sizes rows=%d vocab=%d ld=%lld", rows, vocab, ld);
-  PTL_REQUIRE(temperature == nullptr || (probs && top_p && u), "sample: temperature sampling needs probs scratch, top_p and u");
+  PTL_REQUIRE(part_val && part_idx, "sample: needs the scratch of the slices' maxima");
+  PTL_REQUIRE(temperature == nullptr || (probs && top_p && u && work), "sample: temperature sampling needs probs and work scratch, top_p and u");
+  PTL_REQUIRE((long long)rows * kArgmaxChunks <= 0x7fffffffLL, "sample: too many rows");
+  PTL_REQUIRE(temperature == nullptr || vocab < kArgmaxChunks * (1 << 18), "sample: a vocabulary of %d is too large for the 32-bit counters of a slice", vocab);
   if (rows == 0) return 0;
-  return ptl::launch_kernel("sample", ptl::sample_kernel, dim3(rows), dim3(ptl::kSampleThreads), 0, ptl::as_stream(stream),
-                            tokens, logits, probs, temperature, top_p, u, vocab, ld);
+  cudaStream_t s = as_stream(stream);
+  // the slices' maxima (blockIdx.y is the row there: up to 65,535 rows a launch)
+  for (int r0 = 0; r0 < rows; r0 += 65535) {
+    const int n = rows - r0 < 65535 ? rows - r0 : 65535;
+    int rc = launch_kernel("argmax_partial", argmax_partial_kernel, dim3(kArgmaxChunks, n), dim3(kArgmaxThreads), 0, s,
+                           part_val + (size_t)r0 * kArgmaxChunks, part_idx + (size_t)r0 * kArgmaxChunks, logits + (size_t)r0 * ld, vocab, ld);
+    if (rc) return rc;
+  }
+  SampleLevelArgs a{logits, probs, temperature, top_p, part_val, work, vocab, ld};
+  if (temperature) {
+    const dim3 grid((unsigned)rows * kArgmaxChunks), block(kSampleLevelThreads);
+    if (int rc = launch_kernel("sample_level0", sample_level_kernel<0>, grid, block, 0, s, a)) return rc;
+    if (int rc = launch_kernel("sample_level1", sample_level_kernel<1>, grid, block, 0, s, a)) return rc;
+    if (int rc = launch_kernel("sample_level2", sample_level_kernel<2>, grid, block, 0, s, a)) return rc;
+    if (int rc = launch_kernel("sample_kept", sample_level_kernel<3>, grid, block, 0, s, a)) return rc;
+  }
+  return launch_kernel("sample_draw", sample_draw_kernel, dim3(rows), dim3(kSampleLevelThreads), 0, s, tokens, a, (const int*)part_idx, u);
 }
 
 PTL_EXPORT const char* ptl_last_error() { return ptl::error_buffer(); }

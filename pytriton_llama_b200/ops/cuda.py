@@ -116,8 +116,10 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_take_tokens.restype = _c_int
     lib.ptl_token_logprob.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
     lib.ptl_token_logprob.restype = _c_int
-    lib.ptl_sample.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
+    lib.ptl_sample.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
     lib.ptl_sample.restype = _c_int
+    lib.ptl_sample_work_words.argtypes = []
+    lib.ptl_sample_work_words.restype = _c_int
     lib.ptl_last_error.restype = ctypes.c_char_p
     lib.ptl_set_dependent_launch.argtypes = [_c_int]
     lib.ptl_get_dependent_launch.restype = _c_int
@@ -784,11 +786,25 @@ class CudaOps:
             self._check(self.lib.ptl_argmax(_p(out), _p(logits), _p(scratch[0]), _p(scratch[1]), rows, vocab, vocab,
                                             self._stream()), kernels=2)
             return out
-        probs = None
+        probs = work = None
+        kernels = 2
         if temperature is not None:
             for name, t in (("temperature", temperature), ("top_p", top_p), ("u", u)):
                 self._want(t, name, torch.float32)
             probs = self.empty((rows, vocab), torch.float32)
-        self._check(self.lib.ptl_sample(_p(out), _p(logits), _p(probs), _p(temperature), _p(top_p), _p(u), rows,
-                                        vocab, vocab, self._stream()))
+            work = self._sample_work(rows)
+            kernels = 6
+        scratch = self.empty((2, rows, 32), torch.float32)   # per row the maxima of 32 slices, and (as int32) their indices
+        self._check(self.lib.ptl_sample(_p(out), _p(logits), _p(probs), _p(temperature), _p(top_p), _p(u), _p(scratch[0]),
+                                        _p(scratch[1]), _p(work), rows, vocab, vocab, self._stream()), kernels=kernels)
         return out
+
+    def _sample_work(self, rows: int) -> torch.Tensor:
+        """The histograms of the sampling kernels: zero before the first call, and every call leaves
+        them zero, so one buffer serves all calls on this device's stream."""
+        have = getattr(self, "_sample_work_buf", None)
+        words = self.lib.ptl_sample_work_words()
+        if have is None or have.numel() < rows * words:
+            cap = max(64, 1 << (rows - 1).bit_length())
+            self._sample_work_buf = have = torch.zeros(cap * words, dtype=torch.int64, device=self.device)
+        return have

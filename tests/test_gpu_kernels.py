@@ -519,6 +519,32 @@ def test_token_logprobs(ops, vocab):
     assert (got - want).abs().max() < 1e-4
 
 
+def test_sampling_is_the_same_every_time_and_leaves_its_histograms_clean(ops):
+    """The histograms behind the nucleus filter are built with atomics on integer masses: the same
+    call gives the same tokens every time, also after calls with other row counts in between (every
+    call hands the shared work buffer back zeroed), and a peaked row keeps a single token."""
+    vocab = 128256
+    g = torch.Generator().manual_seed(9)
+    logits = (2.5 * torch.randn(16, vocab, generator=g)).cuda()
+    logits[3, 777] = 60.0                                                # nearly all mass on one token
+    temperature = torch.full((16,), 0.7).cuda()
+    top_p = torch.linspace(0.05, 1.0, 16).cuda()
+    u = torch.rand(16, generator=g).cuda()
+    first = ops.sample(logits, temperature, top_p, u).cpu()
+    assert first[3] == 777
+    ops.sample(logits[:5], temperature[:5], top_p[:5], u[:5])
+    ops.sample(logits.repeat(5, 1), temperature.repeat(5), top_p.repeat(5), u.repeat(5))     # more rows than the buffer held
+    for _ in range(3):
+        assert torch.equal(ops.sample(logits, temperature, top_p, u).cpu(), first)
+    words = ops.lib.ptl_sample_work_words()
+    assert int(ops._sample_work_buf.view(-1, words)[:, :3 * 1024].abs().sum()) == 0       # the three histograms of every row
+    for i in range(16):
+        want = plain_llama.sample_token(logits[i].cpu(), 0.7, float(top_p[i]), float(u[i]))
+        if first[i] != want:                                             # (a boundary within rounding: still inside the nucleus)
+            p = torch.softmax(logits[i].double().cpu() / 0.7, -1)
+            assert plain_llama.top_p_keep_mask(p, float(top_p[i]))[first[i]]
+
+
 def test_sampling_follows_the_distribution(ops):
     """Many draws with different uniform numbers reproduce the filtered probabilities."""
     vocab, n = 50, 4000
