@@ -23,7 +23,6 @@
 
 namespace ptl {
 
-constexpr int kSampleThreads = 1024;
 
 __device__ __forceinline__ void block_argmax(float& v, int& idx, float* sv, int* si) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -53,25 +52,51 @@ __device__ __forceinline__ void block_argmax(float& v, int& idx, float* sv, int*
   idx = si[32];
 }
 
-// log softmax(logits[row])[tokens[row]] of the unscaled logits, one block per row
-// (lite_llama/generete_with_probs.py:154-165 takes the same quantity with log_softmax + gather).
-__global__ void __launch_bounds__(kSampleThreads)
-token_logprob_kernel(float* __restrict__ out, const float* __restrict__ logits, const int* __restrict__ tokens,
-                     int vocab, long long ld) {
+// log softmax(logits[row])[tokens[row]] of the unscaled logits
+// (lite_llama/generete_with_probs.py:154-165 takes the same quantity with log_softmax + gather),
+// in two stages so that a few rows still use many SMs: the maximum and the sum of exp(x - maximum)
+// of each of 32 slices of a row, then the 32 pairs of a row brought to one maximum and added in slice order.
+constexpr int kLogprobChunks = 32;
+constexpr int kLogprobThreads = 256;
+
+__global__ void __launch_bounds__(kLogprobThreads)
+token_logprob_partial_kernel(float* __restrict__ part_max, float* __restrict__ part_sum, const float* __restrict__ logits,
+                             int vocab, long long ld) {
   __shared__ float red[33];
   pdl_wait();
   pdl_launch_dependents();
-  const int row = blockIdx.x;
+  const int row = blockIdx.y, chunk = blockIdx.x;
+  const int per = (vocab + kLogprobChunks - 1) / kLogprobChunks;
+  const int lo = chunk * per, hi = min(lo + per, vocab);
   const float* x = logits + (size_t)row * ld;
   float mx = -INFINITY;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, x[i]);
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) mx = fmaxf(mx, x[i]);
   mx = block_max(mx, red);
   float sum = 0.f;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) sum += expf(x[i] - mx);
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) sum += expf(x[i] - mx);
   sum = block_sum(sum, red);
   if (threadIdx.x == 0) {
+    part_max[row * kLogprobChunks + chunk] = mx;
+    part_sum[row * kLogprobChunks + chunk] = sum;
+  }
+}
+
+__global__ void token_logprob_final_kernel(float* __restrict__ out, const float* __restrict__ part_max,
+                                           const float* __restrict__ part_sum, const float* __restrict__ logits,
+                                           const int* __restrict__ tokens, int vocab, long long ld) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int row = blockIdx.x, lane = threadIdx.x;
+  const float m = part_max[row * kLogprobChunks + lane];
+  float mx = m;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  const float mine = m == -INFINITY ? 0.f : part_sum[row * kLogprobChunks + lane] * expf(m - mx);
+  float sum = 0.f;
+  for (int k = 0; k < kLogprobChunks; ++k) sum += __shfl_sync(0xffffffffu, mine, k);      // in slice order
+  if (lane == 0) {
     const int t = tokens[row];
-    out[row] = (t >= 0 && t < vocab) ? x[t] - mx - logf(sum) : -INFINITY;
+    out[row] = (t >= 0 && t < vocab) ? logits[(size_t)row * ld + t] - mx - logf(sum) : -INFINITY;
   }
 }
 
@@ -428,12 +453,23 @@ PTL_EXPORT int ptl_argmax(int* tokens, const float* logits, float* part_val, int
                             (const float*)part_val, (const int*)part_idx);
 }
 
-PTL_EXPORT int ptl_token_logprob(float* out, const float* logits, const int* tokens, int rows, int vocab, long long ld,
-                                 void* stream) {
+// scratch: rows * 32 floats twice
+PTL_EXPORT int ptl_token_logprob(float* out, const float* logits, const int* tokens, float* part_max, float* part_sum,
+                                 int rows, int vocab, long long ld, void* stream) {
+  using namespace ptl;
+  static_assert(kLogprobChunks == 32, "the final stage is one warp");
   PTL_REQUIRE(rows >= 0 && vocab > 0 && ld >= vocab, "token_logprob: bad sizes rows=%d vocab=%d", rows, vocab);
+  PTL_REQUIRE(part_max && part_sum, "token_logprob: needs the scratch of the slices' maxima and sums");
   if (rows == 0) return 0;
-  return ptl::launch_kernel("token_logprob", ptl::token_logprob_kernel, dim3(rows), dim3(ptl::kSampleThreads), 0,
-                            ptl::as_stream(stream), out, logits, tokens, vocab, ld);
+  for (int r0 = 0; r0 < rows; r0 += 65535) {              // (blockIdx.y is the row: up to 65,535 a launch)
+    const int n = rows - r0 < 65535 ? rows - r0 : 65535;
+    int rc = launch_kernel("token_logprob_partial", token_logprob_partial_kernel, dim3(kLogprobChunks, n), dim3(kLogprobThreads), 0,
+                           as_stream(stream), part_max + (size_t)r0 * kLogprobChunks, part_sum + (size_t)r0 * kLogprobChunks,
+                           logits + (size_t)r0 * ld, vocab, ld);
+    if (rc) return rc;
+  }
+  return launch_kernel("token_logprob_final", token_logprob_final_kernel, dim3(rows), dim3(32), 0, as_stream(stream), out,
+                       (const float*)part_max, (const float*)part_sum, logits, tokens, vocab, ld);
 }
 
 // Greedy rows (temperature == nullptr or <= 0) take the largest logit; the others are sampled as the

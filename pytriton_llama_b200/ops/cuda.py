@@ -114,7 +114,7 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_argmax.restype = _c_int
     lib.ptl_take_tokens.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _ptr]
     lib.ptl_take_tokens.restype = _c_int
-    lib.ptl_token_logprob.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
+    lib.ptl_token_logprob.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
     lib.ptl_token_logprob.restype = _c_int
     lib.ptl_sample.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _ptr]
     lib.ptl_sample.restype = _c_int
@@ -766,7 +766,9 @@ class CudaOps:
         self._want(tokens, "tokens", torch.int32)
         rows, vocab = logits.shape
         out = self.empty((rows,), torch.float32)
-        self._check(self.lib.ptl_token_logprob(_p(out), _p(logits), _p(tokens), rows, vocab, vocab, self._stream()))
+        scratch = self.empty((2, rows, 32), torch.float32)   # per row the maxima of 32 slices and their sums of exponentials
+        self._check(self.lib.ptl_token_logprob(_p(out), _p(logits), _p(tokens), _p(scratch[0]), _p(scratch[1]), rows, vocab, vocab,
+                                               self._stream()), kernels=2)
         return out
 
     def sample(self, logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Optional[torch.Tensor],
