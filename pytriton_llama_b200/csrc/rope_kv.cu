@@ -117,6 +117,87 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   }
 }
 
+// The same for whole heads rotated (rot == d) and rows of whole 16-byte packets: four tokens per
+// block, every access a 16-byte packet (a thread takes 4 or 8 neighbouring frequencies of a head:
+// the packet at j and the one at j + d/2; or a packet of v on its way to the cache).  Steps of many
+// tokens are bound by the memory here: 4-byte accesses left a third of its rate unused.
+constexpr int kRopeTokensPerBlock = 4;
+#ifndef PTL_ROPE_PACKET_TOKENS
+#define PTL_ROPE_PACKET_TOKENS 64
+#endif
+constexpr int kRopePacketTokens = PTL_ROPE_PACKET_TOKENS;   // steps of at least this many tokens take the packet kernel
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_kv_write_packets_kernel(T* __restrict__ qkv, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                             const int* __restrict__ slots, T* __restrict__ cache, int tokens, int nq, int nkv, int d,
+                             int page_size, int write_cache, long long num_slots) {
+  extern __shared__ float cs[];            // per token of the block: cos[d/2], sin[d/2]
+  __shared__ int s_slot[kRopeTokensPerBlock];
+  constexpr int N = Vec16<T>::N;
+  const int half = d / 2;
+  const int t0 = blockIdx.x * kRopeTokensPerBlock;
+  // positions, slots and frequencies are inputs of the step, not results of the kernel before this one
+  if (threadIdx.x < kRopeTokensPerBlock) {
+    const int t = t0 + threadIdx.x;
+    int slot = (write_cache && t < tokens) ? __ldcg(slots + t) : -1;
+    if (slot >= num_slots) slot = -1;      // never write outside the pool
+    s_slot[threadIdx.x] = slot;
+  }
+  if (inv_freq) {
+    for (int e = threadIdx.x; e < kRopeTokensPerBlock * half; e += blockDim.x) {
+      const int tt = e / half, j = e % half;
+      if (t0 + tt < tokens) {
+        float sn, c;
+        sincosf((float)__ldcg(positions + t0 + tt) * inv_freq[j], &sn, &c);   // the accurate version: angles reach thousands of radians
+        cs[tt * d + j] = c;
+        cs[tt * d + half + j] = sn;
+      }
+    }
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+  __syncthreads();
+  const int row_len = (nq + 2 * nkv) * d;
+  const int chunks = half / N;                               // packets per half head
+  const int rot_items = (nq + nkv) * chunks, v_items = nkv * (d / N);
+  const int per_token = rot_items + v_items;
+  const size_t plane = (size_t)nkv * page_size * d;          // one of k / v inside a page
+  for (int e = threadIdx.x; e < kRopeTokensPerBlock * per_token; e += blockDim.x) {
+    const int tt = e / per_token, r = e % per_token, t = t0 + tt;
+    if (t >= tokens) break;
+    T* row = qkv + (size_t)t * row_len;
+    const int slot = s_slot[tt];
+    T* kdst = slot >= 0 ? cache + ((size_t)(slot / page_size) * 2) * plane + (size_t)(slot % page_size) * d : nullptr;
+    if (r < rot_items) {
+      const int h = r / chunks, j = (r % chunks) * N;
+      T* head = row + (size_t)h * d;
+      Vec16<T> a = load16(head + j), b = load16(head + j + half);
+      if (inv_freq) {
+        const float* c = cs + tt * d + j;
+        const float* sn = c + half;
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          float o1, o2;
+          rope_rotate(a.get(i), b.get(i), c[i], sn[i], o1, o2);
+          a.set(i, o1);
+          b.set(i, o2);
+        }
+      }
+      store16(head + j, a);
+      store16(head + j + half, b);
+      if (h >= nq && kdst) {
+        T* kd = kdst + (size_t)(h - nq) * page_size * d;
+        store16(kd + j, a);
+        store16(kd + j + half, b);
+      }
+    } else if (kdst) {
+      const int rv = r - rot_items, h = rv / (d / N), i = (rv % (d / N)) * N;
+      store16(kdst + plane + (size_t)h * page_size * d + i, load16(row + (size_t)(nq + nkv + h) * d + i));
+    }
+  }
+}
+
 // (cos, sin) of angle float(position) * inv_freq[j] for every token and frequency, for kernels that
 // rotate without working the angles out themselves: table [tokens, half].
 __global__ void rope_table_kernel(float2* __restrict__ table, const int* __restrict__ positions,
@@ -142,6 +223,11 @@ int rope_kv_write(void* qkv, const int* positions, const float* inv_freq, const 
   // the paired path needs the whole head rotated, whole 16-byte packets per head and aligned rows
   const int vec2_ok = rot == d && d % 16 == 0 && aligned16(qkv) && (cache == nullptr || aligned16(cache)) &&
                       ((size_t)(nq + 2 * nkv) * d * sizeof(T)) % 16 == 0;
+  // many tokens: four per block and 16-byte packets throughout
+  if (vec2_ok && tokens >= kRopePacketTokens && (d / 2) % Vec16<T>::N == 0 && (size_t)kRopeTokensPerBlock * d * sizeof(float) <= 40 * 1024)
+    return launch_kernel("rope_kv_write", rope_kv_write_packets_kernel<T>, dim3((tokens + kRopeTokensPerBlock - 1) / kRopeTokensPerBlock),
+                         dim3(256), (size_t)kRopeTokensPerBlock * d * sizeof(float), as_stream(stream), (T*)qkv, positions, inv_freq,
+                         slots, (T*)cache, tokens, nq, nkv, d, page_size, (int)(cache != nullptr), num_slots);
   const int work = vec2_ok ? (nq + nkv) * (d / 4) : (nq + nkv) * (d - rot / 2);
   const int threads = work >= 2048 ? 256 : 128;
   return launch_kernel("rope_kv_write", rope_kv_write_kernel<T>, dim3(tokens), dim3(threads), (size_t)rot * sizeof(float),

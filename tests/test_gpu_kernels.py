@@ -199,6 +199,37 @@ def test_tensor_core_product_leaves_other_sizes_to_the_library(ops):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T, nq, nkv, d, page", [(70, 6, 2, 64, 16), (131, 8, 2, 128, 32), (64, 5, 5, 48, 8), (257, 32, 8, 64, 16)])
+def test_rope_kv_write_of_many_tokens(ops, dtype, T, nq, nkv, d, page):
+    """From 64 tokens on, whole heads rotated and rows of whole 16-byte packets go through the
+    kernel that takes four tokens per block and moves 16-byte packets only (head size 48 in
+    bfloat16 has no whole packets per half head and keeps the other kernel): token counts that
+    are no multiple of four, a token without a slot, a slot beyond the pool."""
+    pages = -(-T // page) + 3
+    g = torch.Generator().manual_seed(T)
+    qkv = rnd((T, (nq + 2 * nkv) * d), DT[dtype], 18)
+    positions = torch.randint(0, 100000, (T,), generator=g).int()
+    inv_freq = plain_llama.rope_inv_freq({"head_dim": d, "hidden_size": 1, "num_attention_heads": 1, "rope_theta": 500000.0})
+    slots = torch.randperm(pages * page, generator=g)[:T].int()
+    slots[3] = -1
+    cache_ref = torch.zeros((pages, 2, nkv, page, d), dtype=DT[dtype])
+    q_ref = qkv.clone()
+    REF.rope_kv_write(q_ref, positions, inv_freq, d, slots, cache_ref, nq, nkv, d, page)
+    beyond = slots.clone()
+    beyond[5] = pages * page + 2                                         # refused by the kernel: nothing is written for it
+    keep = cache_ref.clone()
+    s5 = int(slots[5])
+    keep[s5 // page, :, :, s5 % page] = 0
+    cache = torch.zeros_like(cache_ref).cuda()
+    q = qkv.clone().cuda()
+    ops.rope_kv_write(q, positions.cuda(), inv_freq.cuda(), d, beyond.cuda(), cache, nq, nkv, d, page)
+    close(q[:, : nq * d], q_ref[:, : nq * d], dtype, "rotated q", scale=4.0)
+    close(cache, keep, dtype, "cache", scale=4.0)
+    assert torch.equal(cache.cpu()[:, 1], keep[:, 1])                      # values are copied, not rotated
+    assert torch.equal(q[:, (nq + nkv) * d:].cpu(), qkv[:, (nq + nkv) * d:])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("rows, inter", [(3, 264), (2, 8192), (5, 101), (1, 24)])
 def test_silu_mul(ops, dtype, rows, inter):
     gu = rnd((rows, 2 * inter), DT[dtype], 7, 3.0)
