@@ -90,6 +90,13 @@ struct PrefillTcParams {
 // again, and it would then wait for ever.
 enum : int { kBarQ = 0, kBarSFull = 1, kBarSFree = 5, kBarPFull = 9, kBarODone = 13, kBarKvFull = 17 };
 
+// the largest of three (one instruction on sm_100: a row maximum over 64 scores takes 32 of them, not 64)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -417,7 +424,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < kMyKeys; ++j) mx8[j & 7] = fmaxf(mx8[j & 7], __uint_as_float(v[j]));
+        for (int j = 0; j < kMyKeys; j += 2) mx8[(j >> 1) & 7] = max3(mx8[(j >> 1) & 7], __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
       }
       float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       mx *= p.scale_log2;                                       // the scale is positive: max and scaling commute
