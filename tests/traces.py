@@ -83,6 +83,47 @@ def mixed(seqs: Dict[str, List[int]], live: int = 4, sizes: Sequence[int] = (5, 
     return steps
 
 
+def random_trace(seqs: Dict[str, List[int]], rng, live: int = 4):
+    """A trace drawn from ``rng`` (a ``random.Random``): requests start in random order while others
+    run, a step gives a request one token, a few, or up to 140, sometimes leaves it out, and wants
+    every place, a random subset of the places, or none."""
+    order = list(seqs)
+    rng.shuffle(order)
+    pos = {r: 0 for r in order}
+    waiting, running, steps = list(order), [], []
+    while waiting or running:
+        while waiting and len(running) < live and (not running or rng.random() < 0.7):
+            running.append(waiting.pop(0))
+        entries, ended = [], []
+        for rid in list(running):
+            if len(running) > 1 and rng.random() < 0.2:
+                continue
+            left = len(seqs[rid]) - pos[rid]
+            kind = rng.random()
+            n = 1 if kind < 0.45 else rng.randint(2, 12) if kind < 0.8 else rng.randint(13, 140)
+            n = min(n, left)
+            want = sorted(rng.sample(range(n), rng.randint(0, n))) if rng.random() < 0.3 else list(range(n))
+            entries.append({"id": rid, "tokens": seqs[rid][pos[rid]:pos[rid] + n], "want": want})
+            pos[rid] += n
+            if pos[rid] == len(seqs[rid]):
+                ended.append(rid)
+                running.remove(rid)
+        if entries:
+            steps.append({"step": len(steps), "entries": entries, "end": ended})
+    return steps
+
+
+def wanted_positions(steps, rid) -> List[int]:
+    """The positions of request ``rid`` whose logits the trace asks for, in order."""
+    out, p = [], 0
+    for s in steps:
+        for e in s["entries"]:
+            if e["id"] == rid:
+                out.extend(p + w for w in e["want"])
+                p += len(e["tokens"])
+    return out
+
+
 def max_live_tokens(steps, round_to: int = 64) -> int:
     """The most tokens live requests hold at any time, each request rounded up to ``round_to``."""
     held: Dict[str, int] = {}
