@@ -187,15 +187,12 @@ __device__ __forceinline__ unsigned long long block_scan_u64(unsigned long long 
 
 // Where x* lies among the buckets of one histogram: the smallest bucket b such that the mass in
 // the buckets above b is <= budget, and what is left of the budget after that mass.  Every thread
-// of a 256-thread block calls it and gets both.  Bucket 4 (255 - t) + j in thread t's registers.
-__device__ __forceinline__ void find_bucket(const unsigned long long* __restrict__ hist, unsigned long long budget,
+// of a 256-thread block calls it with its four buckets h[0..3] = buckets 4 (255 - t) .. + 3 (thread 0
+// has the top four) and gets both, and the histogram's total mass.
+__device__ __forceinline__ void find_bucket(const unsigned long long (&h)[4], unsigned long long budget,
                                             unsigned long long* scratch, int* s_bucket, unsigned long long* s_left,
                                             int& bucket, unsigned long long& left) {
-  const int t = threadIdx.x;                             // walks the buckets from the top: thread 0 has 1023..1020
-  unsigned long long h[4];
-  const int b0 = kSampleBuckets - 4 * (t + 1);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) h[j] = __ldcg(hist + b0 + j);
+  const int b0 = kSampleBuckets - 4 * ((int)threadIdx.x + 1);
   const unsigned long long mine = h[0] + h[1] + h[2] + h[3];
   unsigned long long total;
   const unsigned long long incl = block_scan_u64(mine, scratch, total);
@@ -228,24 +225,29 @@ struct SampleLevelArgs {
   long long ld;
 };
 
-// total mass, budget, and down `levels` histograms of the row: the pattern bits of x* found so far.
-// Every thread of a 256-thread block calls it; s_bucket[1] need not be prepared.
-__device__ __forceinline__ unsigned descend(const unsigned long long* __restrict__ work, float top_p, int levels,
+// total mass, budget, and down LEVELS histograms of the row: the pattern bits of x* found so far.
+// Every thread of a 256-thread block calls it; s_bucket[1] need not be prepared.  The buckets of all
+// levels are fetched at once, before the first scan: the levels then cost no trip to L2 each.
+template <int LEVELS>
+__device__ __forceinline__ unsigned descend(const unsigned long long* __restrict__ work, float top_p,
                                             unsigned long long* scratch, int* s_bucket, unsigned long long* s_left) {
-  unsigned long long total = 0ull;
-  {
-    unsigned long long mine = 0ull;
-    for (int b = threadIdx.x; b < kSampleBuckets; b += blockDim.x) mine += __ldcg(work + b);
-    block_scan_u64(mine, scratch, total);
-  }
+  unsigned long long h[LEVELS][4];
+  const int b0 = kSampleBuckets - 4 * ((int)threadIdx.x + 1);
+#pragma unroll
+  for (int level = 0; level < LEVELS; ++level)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[level][j] = __ldcg(work + level * kSampleBuckets + b0 + j);
+  unsigned long long total;
+  block_scan_u64(h[0][0] + h[0][1] + h[0][2] + h[0][3], scratch, total);
   unsigned long long budget = top_p >= 1.f ? total : (unsigned long long)((double)top_p * (double)total);
   unsigned prefix = 0u;
-  for (int level = 0; level < levels; ++level) {
+#pragma unroll
+  for (int level = 0; level < LEVELS; ++level) {
     __syncthreads();
     if (threadIdx.x == 0) s_bucket[1] = kSampleBuckets;
     __syncthreads();
     int bucket;
-    find_bucket(work + level * kSampleBuckets, budget, scratch, s_bucket, s_left, bucket, budget);
+    find_bucket(h[level], budget, scratch, s_bucket, s_left, bucket, budget);
     prefix = (prefix << 10) | (unsigned)bucket;
   }
   return prefix;
@@ -283,7 +285,8 @@ sample_level_kernel(const SampleLevelArgs a) {
   float* pr = a.probs + (size_t)row * a.vocab;
   const int per = (a.vocab + kArgmaxChunks - 1) / kArgmaxChunks;
   const int lo = chunk * per, hi = min(lo + per, a.vocab);
-  const unsigned prefix = LEVEL >= 1 ? descend(work, a.top_p[row], LEVEL, scratch, s_bucket, &s_left) : 0u;
+  unsigned prefix = 0u;
+  if constexpr (LEVEL >= 1) prefix = descend<LEVEL>(work, a.top_p[row], scratch, s_bucket, &s_left);
   __syncthreads();
   if (LEVEL == 0) {
     float mx = -INFINITY;
@@ -422,14 +425,18 @@ sample_draw_kernel(int* __restrict__ tokens, const SampleLevelArgs a, const int*
   if (tid == s_owner) {
     unsigned long long acc = before;
     int choice = c0;
-    for (int i = c0; i < c1; ++i) {
-      const float e = __ldcg(pr + i);
-      if (__float_as_uint(e) >= cut_bits) {
-        const unsigned long long q = mass_of(e);
-        if (q > 0ull) {
-          choice = i;
+    bool found = false;
+    for (int i0 = c0; i0 < c1 && !found; i0 += kSampleBatch) {
+      float v[kSampleBatch];                             // (fetched together: one trip to L2 per batch, not per token)
+#pragma unroll
+      for (int j = 0; j < kSampleBatch; ++j) v[j] = i0 + j < c1 ? __ldcg(pr + i0 + j) : 0.f;
+#pragma unroll
+      for (int j = 0; j < kSampleBatch; ++j) {
+        const unsigned long long q = mass_of(v[j]);
+        if (!found && i0 + j < c1 && __float_as_uint(v[j]) >= cut_bits && q > 0ull) {
+          choice = i0 + j;
           acc += q;
-          if (acc > target) break;
+          found = acc > target;
         }
       }
     }

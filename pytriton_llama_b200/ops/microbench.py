@@ -12,6 +12,7 @@ the last block of each grid entered, got past the wait on its predecessor, had i
 finished its loop, had its results complete and left -- %globaltimer stamps, in microseconds from
 the layer's first stamp: what a sum of kernel times cannot show, the gaps between dependent kernels.
 ``product_shapes`` times the many-token products of the model beside the library's (torch.mm).
+``sampling`` times the token choice from ``--batch`` rows of 128,256 logits, greedy and with temperature and top_p.
 ``decode_contexts`` times one layer's decode attention at batch 1 to 16 over contexts of 4,096 to
 131,072 tokens, with the split count the operator set chooses and with the cluster form alone.
 Inputs are larger than the 126 MB L2 where the kernel is a stream, so
@@ -201,7 +202,31 @@ def decode_contexts(reps: int) -> dict:
     return {"case": "decode_contexts", "rows": table}
 
 
+def sampling(reps: int, rows: int) -> dict:
+    """Token choice from ``rows`` rows of 128,256 float32 logits: greedy, and temperature 0.6 with
+    top_p 0.9 (lite_llama's defaults, cli.py:11-20), ten calls per replay of a captured graph."""
+    dev = torch.device("cuda:0")
+    ops = CudaOps(dev)
+    vocab = 128256
+    logits = (3.0 * torch.randn(rows, vocab, device=dev)).float()
+    t = torch.full((rows,), 0.6, device=dev)
+    p = torch.full((rows,), 0.9, device=dev)
+    u = torch.rand(rows, device=dev)
+    out = {"case": "sampling", "rows": rows, "vocab": vocab}
+    for name, fn in (("greedy_us", lambda: ops.sample(logits, None, None, None)), ("top_p_us", lambda: ops.sample(logits, t, p, u))):
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(10):
+                fn()
+        out[name] = round(_time(graph.replay, reps, ops) / 10 * 1e6, 1)
+    return out
+
+
 def run(case: str, reps: int, batch: int = 8) -> dict:
+    if case == "sampling":
+        return sampling(reps, batch)
     if case == "decode_timeline":
         return decode_timeline(batch)
     if case == "decode_contexts":
@@ -271,9 +296,9 @@ def run(case: str, reps: int, batch: int = 8) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("case", choices=["decode_attention", "decode_step_attention", "gemm_decode", "gemm_prefill", "prefill_attention",
-                                     "prefill_attention_d128", "decode_timeline", "product_shapes", "decode_contexts"])
+                                     "prefill_attention_d128", "decode_timeline", "product_shapes", "decode_contexts", "sampling"])
     ap.add_argument("--reps", type=int, default=10)
-    ap.add_argument("--batch", type=int, default=8, help="decode_timeline: requests in the step")
+    ap.add_argument("--batch", type=int, default=8, help="decode_timeline: requests in the step; sampling: rows of logits")
     args = ap.parse_args()
     out = run(args.case, args.reps, args.batch)
     if args.case == "decode_timeline":
