@@ -326,7 +326,7 @@ def main() -> int:
         lens = torch.randint(sv["prompt_lo"], sv["prompt_hi"] + 1, (sv["requests"],), generator=gen).tolist()
         prompts = [tokens(n) for n in lens]
         params = SamplingParams(temperature=0.0, max_gen_len=sv["generated"], stop_token_ids=[])
-        llm.generate(prompts[:2], SamplingParams(temperature=0.0, max_gen_len=4, stop_token_ids=[]))     # warm-up
+        llm.generate(prompts, params)     # warm-up: the same workload once (as the batch shrinks, every smaller decode step is captured on first use)
         torch.cuda.synchronize(dev)
         t0 = time.perf_counter()
         outs = llm.generate(prompts, params)
