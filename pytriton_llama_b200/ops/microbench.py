@@ -4,7 +4,8 @@
 
 Cases: ``decode_attention`` (32 requests x 4,096 cached tokens, 268 MB of keys and values),
 ``decode_step_attention`` (8 requests x 4,096 tokens with rotary encoding and cache write folded in),
-``gemm_decode`` (8 tokens x a [65536, 2048] weight, 268 MB), ``gemm_prefill`` (2,048 tokens x the
+``gemm_decode`` (8 tokens x a [65536, 2048] weight, 268 MB), ``gemm_small`` (8 tokens x a [3072, 2048] weight: the
+product for few tokens and small weights), ``gemm_prefill`` (2,048 tokens x the
 gate/up weight [16384, 2048] with the SiLU*up epilogue), ``prefill_attention`` (one 2,048-token
 prompt, 32 query heads of size 64; ``prefill_attention_d128``: of size 128).  ``decode_timeline`` prints, for the kernels of the middle layer of a captured decode step (a
 4-layer model of the same widths, ``--batch`` requests x 4,096 cached tokens), when the first and
@@ -264,6 +265,20 @@ def run(case: str, reps: int, batch: int = 8) -> dict:
                                                hints=hints), reps, ops)
         nbytes = cache.numel() * 2
         return {"case": case, "us": sec * 1e6, "bytes": nbytes, "GB/s": nbytes / sec / 1e9}
+    if case == "gemm_small":
+        # the q|k|v projection of a decode step at batch 8: 8 tokens x a [3072, 2048] weight, a fresh copy
+        # of the weight every call (32 copies, 403 MB) so that it comes from memory, not from L2
+        m, n, k, copies = 8, 3072, 2048, 32
+        x = torch.randn(m, k, device=dev).bfloat16()
+        ws = [torch.randn(n, k, device=dev).bfloat16() for _ in range(copies)]
+        turn = [0]
+
+        def call():
+            turn[0] += 1
+            return ops.gemm_tc(x, ws[turn[0] % copies], ops.EPI_BF16)
+        sec = _time(call, max(reps, copies), ops)
+        return {"case": case, "us": sec * 1e6, "bytes": n * k * 2, "GB/s": n * k * 2 / sec / 1e9,
+                "note": "eager launches: the time includes what the host needs per launch"}
     if case == "gemm_decode":
         m, n, k = 8, 65536, 2048
         x = torch.randn(m, k, device=dev).bfloat16()
@@ -295,7 +310,7 @@ def run(case: str, reps: int, batch: int = 8) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("case", choices=["decode_attention", "decode_step_attention", "gemm_decode", "gemm_prefill", "prefill_attention",
+    ap.add_argument("case", choices=["decode_attention", "decode_step_attention", "gemm_decode", "gemm_small", "gemm_prefill", "prefill_attention",
                                      "prefill_attention_d128", "decode_timeline", "product_shapes", "decode_contexts", "sampling"])
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--batch", type=int, default=8, help="decode_timeline: requests in the step; sampling: rows of logits")
