@@ -181,7 +181,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   // block-table entries of the key range, staged once (the producer thread reads them)
   const int first_block = k_base / p.page_size;
   const int n_blocks = ntiles * pages_per_tile;
-  const int have_blocks = (max(k_end[0], k_end[1]) - 1) / p.page_size - first_block + 1;   // entries that exist for this request
+  // entries that exist for this request: up to the last key of the tiles that are there (an absent tile B has no
+  // keys of its own: counting its would-be range read up to eight entries past the request's, and past the
+  // table's row where the table is only as wide as the step needs), and never past the row
+  const int last_key = max(rows_g[0] > 0 ? k_end[0] : 0, rows_g[1] > 0 ? k_end[1] : 0) - 1;
+  const int have_blocks = min(last_key / p.page_size + 1, p.bt_stride) - first_block;
   const bool staged = n_blocks <= kTcStagedPages;
   if (staged)
     for (int i = threadIdx.x; i < n_blocks; i += Cfg::kThreads) s_pages[i] = i < have_blocks ? bt_global[first_block + i] : -1;

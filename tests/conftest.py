@@ -81,6 +81,33 @@ PAGE_SIZE = {"A": 4, "B": 8, "C": 16, "D": 16, "E": 32}
 NORM_INIT = {"A": "ones_jitter", "B": "ones", "C": "ones_jitter", "D": "ones_jitter", "E": "ones"}
 
 
+def _odd(layers, hidden, nq, nkv, d, inter, vocab, theta=10000.0, scaling=None, eps=1e-5, tied=True, **more):
+    cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": layers, "hidden_size": hidden,
+           "num_attention_heads": nq, "num_key_value_heads": nkv, "head_dim": d, "intermediate_size": inter, "vocab_size": vocab,
+           "rope_theta": theta, "rope_scaling": scaling, "rms_norm_eps": eps, "tie_word_embeddings": tied,
+           "max_position_embeddings": 4096}
+    cfg.update(more)
+    return cfg
+
+
+# More shapes for the random traces (tests/test_gpu_random_traces.py): head sizes 80, 96, 112 and 256,
+# a group of 20 query heads per kv head, as many kv heads as query heads on the tensor-core attention
+# (with a quarter of the head rotated), 16 query heads over 2 kv heads of size 128, vocabularies of 50 to 2,049.
+TINY.update({
+    "F": _odd(2, 288, 3, 1, 96, 200, 1001),
+    "G": _odd(1, 256, 2, 1, 256, 136, 300, tied=False),
+    "H": _odd(2, 320, 20, 1, 64, 264, 777),
+    "I": _odd(2, 72, 3, 3, 80, 104, 131, eps=1e-3),
+    "J": _odd(1, 224, 7, 7, 112, 168, 513, theta=500000.0,
+              scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                       "original_max_position_embeddings": 64}),
+    "K": _odd(3, 128, 16, 2, 128, 96, 2049),
+    "L": _odd(2, 512, 8, 8, 64, 1000, 50, partial_rotary_factor=0.25),
+})
+PAGE_SIZE.update({"F": 16, "G": 8, "H": 16, "I": 4, "J": 32, "K": 64, "L": 16})
+NORM_INIT.update({k: "ones_jitter" for k in "FGHIJKL"})
+
+
 def make_model_folder(folder, name, stored_dtype, seed=11, std=0.08, qk_gain=None):
     """Writes a random-weights folder through the package's random-weights mode, then makes the
     attention scores matter: q and k projections are scaled so that softmax is far from uniform

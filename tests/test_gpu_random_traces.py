@@ -1,7 +1,8 @@
 """Random traces through the engine against the plain implementation: random cuts, live sets and
 skipped steps, wanted places chosen at random, pools with exactly the pages a trace needs or a few
 more, captured steps on and off (with several layouts of their context classes), both compute
-types, all tiny configurations.  Every seed is one trace; a failure names its seed."""
+types, all tiny configurations (the five of the other tests and seven more with head sizes of 80 to
+256, large and trivial groups, odd widths).  Every seed is one trace; a failure names its seed."""
 import random
 
 import pytest
@@ -14,7 +15,7 @@ from gpu_common import assert_close, make_engine, reference_logits, stored_dtype
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("block", range(6))
+@pytest.mark.parametrize("block", range(10))
 def test_random_traces(model_folders, block):
     for seed in range(block * 12, block * 12 + 12):
         rng = random.Random(seed)
