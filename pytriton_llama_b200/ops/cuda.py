@@ -361,9 +361,25 @@ class CudaOps:
             if out is not None:
                 return out
         # sizes the tensor-core kernel does not take (K no multiple of 8, or below 64) or leaves to the library
-        if out_dtype == torch.float32:
-            return torch.mm(x, w.t(), out_dtype=torch.float32)
-        return torch.mm(x, w.t())
+        return self._library_mm(x, w, out_dtype)
+
+    @staticmethod
+    def _library_mm(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """x @ w^T by the library with float32 sums throughout.  torch lets cuBLAS add the parts of a
+        split K range in bfloat16 by default; it does so for widths that are no multiple of 8, and
+        an element that is small beside the partial sums it is made of then comes out wrong by as
+        much as its own size (a [129, 512] x [50, 512]^T product: 0.4 % of the largest element
+        everywhere, 43 % of a small one).  The engine's own shapes are not touched by the setting
+        (same kernels, same time); it is put back after the call."""
+        matmul = torch.backends.cuda.matmul
+        before = matmul.allow_bf16_reduced_precision_reduction
+        matmul.allow_bf16_reduced_precision_reduction = False
+        try:
+            if out_dtype == torch.float32:
+                return torch.mm(x, w.t(), out_dtype=torch.float32)
+            return torch.mm(x, w.t())
+        finally:
+            matmul.allow_bf16_reduced_precision_reduction = before
 
     library_products = os.environ.get("PTL_LIBRARY_PRODUCTS", "1") != "0"
 

@@ -191,6 +191,20 @@ def test_projection_with_rotary_encoding_and_cache_write_in_its_epilogue(ops, M,
     assert bool((out[:, nq * d:] == 7.0).all())          # the k and v columns of the output are left alone
 
 
+@pytest.mark.parametrize("M, N, K", [(129, 50, 512), (520, 50, 4096), (128, 130, 1000), (300, 2048, 2048)])
+def test_library_product_keeps_float32_sums(ops, M, N, K):
+    """Products that go to the library (more than 64 tokens and few tiles) are exact to the rounding
+    of the result, element by element, also for widths that are no multiple of 8, where the
+    library's default would add the parts of a split K range in bfloat16."""
+    x, w = rnd((M, K), torch.bfloat16, 41), rnd((N, K), torch.bfloat16, 42, 0.5)
+    ref = x.double() @ w.double().T
+    assert ops.library_product(M, N, K, ops.EPI_BF16)
+    out = ops.linear(x.cuda(), w.cuda()).double().cpu()
+    err = (out - ref).abs()
+    assert (err <= 2 ** -8 * ref.abs() + 1e-5 * float(ref.abs().max())).all(), float((err / (ref.abs() + 1e-9)).max())
+    assert torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction in (True, False)     # (left as it was found)
+
+
 def test_tensor_core_product_leaves_other_sizes_to_the_library(ops):
     x, w = rnd((4, 100), torch.bfloat16, 1), rnd((32, 100), torch.bfloat16, 2)    # K no multiple of 8
     assert ops.gemm_tc(x.cuda(), w.cuda()) is None
