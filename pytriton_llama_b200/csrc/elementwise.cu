@@ -292,6 +292,37 @@ int silu_mul(void* out, const void* gu, int tokens, int inter, void* stream) {
 
 }  // namespace ptl
 
+namespace ptl {
+
+// y[t, :] = xs[t, :] * rsqrt(sum of the token's `slots` partial sums of squares / width + eps): finishes an RMS norm
+// whose input a product's epilogue prepared (xs = bfloat16(residual * weight)), for a reader that cannot apply
+// the row scale itself.  One block per token.
+__global__ void __launch_bounds__(256)
+finish_norm_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ xs, const float* __restrict__ sumsq,
+                   int slots, int sumsq_ld, int width, float eps) {
+  __shared__ float red[33];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  float sum = 0.f;
+  for (int k = threadIdx.x; k < slots; k += blockDim.x) sum += __ldcg(sumsq + (size_t)t * sumsq_ld + k);
+  sum = block_sum(sum, red);
+  const float scale = rsqrtf(sum / (float)width + eps);
+  const __nv_bfloat16* src = xs + (size_t)t * width;
+  __nv_bfloat16* dst = y + (size_t)t * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = __float2bfloat16_rn(__bfloat162float(src[i]) * scale);
+}
+
+}  // namespace ptl
+
+PTL_EXPORT int ptl_finish_norm_bf16(void* y, const void* xs, const float* sumsq, int tokens, int slots, int sumsq_ld, int width,
+                                    float eps, void* stream) {
+  PTL_REQUIRE(tokens >= 0 && slots > 0 && sumsq_ld >= slots && width > 0 && eps > 0.f, "finish_norm: bad sizes tokens=%d slots=%d width=%d", tokens, slots, width);
+  if (tokens == 0) return 0;
+  return ptl::launch_kernel("finish_norm", ptl::finish_norm_kernel, dim3(tokens), dim3(256), 0, ptl::as_stream(stream),
+                            (__nv_bfloat16*)y, (const __nv_bfloat16*)xs, sumsq, slots, sumsq_ld, width, eps);
+}
+
 PTL_EXPORT int ptl_take_tokens(int* tokens, const int* src, const int* sampled, int n, int n_sampled, void* stream) {
   PTL_REQUIRE(n >= 0 && n_sampled >= 0, "take_tokens: bad sizes n=%d sampled=%d", n, n_sampled);
   if (n == 0) return 0;

@@ -38,10 +38,10 @@ class NormedActivation:
     """The input of an RMS norm whose normalisation is still to be done by the product that reads it:
     ``xs`` = bfloat16(residual * weight) [tokens, width] and, per token, ``slots`` partial sums of
     residual^2 in ``sumsq``.  The row scale rsqrt(sum / width + eps) is applied by the consumer."""
-    __slots__ = ("xs", "sumsq", "slots", "eps", "weight")
+    __slots__ = ("xs", "sumsq", "slots", "eps", "weight", "ops")
 
-    def __init__(self, xs, sumsq, slots, eps, weight):
-        self.xs, self.sumsq, self.slots, self.eps, self.weight = xs, sumsq, slots, eps, weight
+    def __init__(self, xs, sumsq, slots, eps, weight, ops=None):
+        self.xs, self.sumsq, self.slots, self.eps, self.weight, self.ops = xs, sumsq, slots, eps, weight, ops
 
     @property
     def shape(self):
@@ -53,8 +53,7 @@ class NormedActivation:
 
     def materialise(self) -> torch.Tensor:
         """The normed activation as a plain tensor (for consumers that cannot apply the scale)."""
-        scale = torch.rsqrt(self.sumsq[:, :self.slots].sum(dim=1) / self.xs.shape[1] + self.eps)
-        return (self.xs.float() * scale[:, None]).to(self.xs.dtype)
+        return self.ops.finish_norm(self)
 
 
 class KernelError(RuntimeError):
@@ -98,6 +97,8 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_gemm_small_bf16.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr,
                                         _ptr, _c_int, _c_int, _c_f, _ptr]
     lib.ptl_gemm_small_bf16.restype = _c_int
+    lib.ptl_finish_norm_bf16.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_f, _ptr]
+    lib.ptl_finish_norm_bf16.restype = _c_int
     lib.ptl_gemm_tc_bf16_qkv_rope.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int,
                                               _c_int, _c_int, _c_ll, _ptr]
     lib.ptl_gemm_tc_bf16_qkv_rope.restype = _c_int
@@ -488,7 +489,7 @@ class CudaOps:
             self._want(weight, "norm weight", torch.float32)
             width = (N + 7) // 8           # a slot per 8 features at most (the product for a few tokens), per 16 otherwise
             normed = NormedActivation(self.empty((M, N), torch.bfloat16), self.empty((M, width), torch.float32), 0,
-                                      float(eps), weight)
+                                      float(eps), weight, ops=self)
             slots = ctypes.c_int(0)
         if M <= 8 and epi != self.EPI_SILU_MUL and splits == 0 and self.small_products:
             # a few tokens and a weight of a few megabytes (q|k|v and output projection of a decode step): the
@@ -561,6 +562,14 @@ class CudaOps:
         else:
             fn = self.lib.ptl_gemm_simt_bf16
         self._check(fn(_p(out), _p(x), _p(w), M, N, K, K, K, N, 0, self._stream()))
+        return out
+
+    def finish_norm(self, normed: NormedActivation) -> torch.Tensor:
+        """The RMS norm that a product's epilogue prepared, finished as a plain bfloat16 tensor."""
+        tokens, width = normed.xs.shape
+        out = self.empty((tokens, width), torch.bfloat16)
+        self._check(self.lib.ptl_finish_norm_bf16(_p(out), _p(normed.xs), _p(normed.sumsq), tokens, normed.slots, normed.sumsq.shape[1],
+                                                  width, float(normed.eps), self._stream()))
         return out
 
     def silu_mul(self, gu: torch.Tensor) -> torch.Tensor:
