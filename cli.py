@@ -3,7 +3,9 @@ with the same meaning (``temperature`` 0.6, ``top_p`` 0.9, ``max_seq_len`` 2048,
 ``max_gpu_num_blocks``, ``max_gen_len`` 1024, ``compiled_model``), a prompt loop that streams the
 answer and stops at ``exit``.  lite_llama hard-codes the checkpoint folder (cli.py:8); here it is
 ``--checkpoints_dir``, or ``--random_weights`` with ``--config`` and ``--seed`` to make a folder of
-random weights first.  Without a tokenizer in the folder, prompts are lists of token ids.
+random weights first.  Without a tokenizer in the folder, prompts are lists of token ids.  Text
+prompts are wrapped in the Llama 3 chat form with the conversation so far, as lite_llama wraps its
+lines in a template (cli.py:26,49-50), when the tokenizer knows the role headers (``--raw_prompt``: never).
 
     python cli.py --checkpoints_dir DIR --prompt_ids 1 2 3 --max_gen_len 16 --temperature 0
     python cli.py --random_weights /tmp/m --config tiny.json --seed 1     # then the prompt loop
@@ -37,6 +39,10 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--stats", action="store_true",
                     help="time every step on the device (steps then run uncaptured, one at a time) and print, after each "
                          "answer, steps, tokens, tokens/s, pages in use and milliseconds by class of kernels")
+    ap.add_argument("--raw_prompt", action="store_true",
+                    help="text prompts go to the model as they are; default: the Llama 3 chat form (with the conversation so far) "
+                         "when the tokenizer knows its role headers")
+    ap.add_argument("--system", default="", help="system message of the chat form")
     ap.add_argument("--prompt", help="one text prompt (needs a tokenizer in the model folder)")
     ap.add_argument("--prompt_ids", type=int, nargs="+", help="one prompt as token ids")
     return ap
@@ -82,13 +88,17 @@ def main(argv: Optional[List[str]] = None) -> int:
         print()
         show_stats()
 
+    from pytriton_llama_b200.utils import prompt_for_tokenizer
+    chat = prompt_for_tokenizer(generator.tokenizer, raw=args.raw_prompt, system=args.system)
+
     def run_text(text: str) -> None:
         shown = ""
-        for completions in generator.text_completion_stream([text], args.temperature, args.top_p, args.max_gen_len):
+        for completions in generator.text_completion_stream([chat.render(text)], args.temperature, args.top_p, args.max_gen_len):
             new = completions[0]["generation"][len(shown):]
             shown = completions[0]["generation"]
             print(new, end="", flush=True)
         print()
+        chat.record(shown)
         show_stats()
 
     if args.prompt_ids:

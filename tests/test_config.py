@@ -111,3 +111,41 @@ def test_new_architecture_can_be_registered():
     register_architecture("ToyForCausalLM", LlamaConfig.from_dict, llama_spec)
     d = dict(TINY_A, architectures=["ToyForCausalLM"])
     assert resolve_architecture(d).name == "ToyForCausalLM"
+
+
+def test_chat_prompts():
+    """The command line's prompt forms: the Llama 3 chat form renders every turn so far and leaves
+    the assistant's header open; the plain form passes lines through; the choice follows the tokenizer."""
+    from pytriton_llama_b200.utils import Llama3ChatPrompt, PlainPrompt, prompt_for_tokenizer
+    chat = Llama3ChatPrompt(system="Be brief.")
+    first = chat.render("Hi")
+    assert first == ("<|start_header_id|>system<|end_header_id|>\n\nBe brief.<|eot_id|>"
+                     "<|start_header_id|>user<|end_header_id|>\n\nHi<|eot_id|>"
+                     "<|start_header_id|>assistant<|end_header_id|>\n\n")
+    chat.record(" Hello! ")
+    second = chat.render("And now?")
+    assert second.startswith(first + "Hello!<|eot_id|><|start_header_id|>user<|end_header_id|>\n\nAnd now?<|eot_id|>")
+    assert second.endswith("<|start_header_id|>assistant<|end_header_id|>\n\n")
+    chat.reset()
+    assert chat.render("Hi") == first
+    assert Llama3ChatPrompt().render("x") == "<|start_header_id|>user<|end_header_id|>\n\nx<|eot_id|><|start_header_id|>assistant<|end_header_id|>\n\n"
+    plain = PlainPrompt()
+    assert plain.render("as it is") == "as it is"
+    plain.record("answer")
+    assert plain.render("next") == "next"
+    with pytest.raises(RuntimeError):
+        Llama3ChatPrompt().record("nothing was asked")
+
+    class Knows:
+        unk_token_id = 0
+
+        def convert_tokens_to_ids(self, toks):
+            return [128006, 128009]
+
+    class KnowsNot(Knows):
+        def convert_tokens_to_ids(self, toks):
+            return [0, 0]
+    assert isinstance(prompt_for_tokenizer(Knows()), Llama3ChatPrompt)
+    assert isinstance(prompt_for_tokenizer(KnowsNot()), PlainPrompt)
+    assert isinstance(prompt_for_tokenizer(Knows(), raw=True), PlainPrompt)
+    assert isinstance(prompt_for_tokenizer(None), PlainPrompt)
