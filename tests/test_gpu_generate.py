@@ -473,3 +473,49 @@ def test_command_line_prints_statistics(model_folders):
     import json
     stats = json.loads(lines[1][len("[stats] "):])
     assert stats["steps"] >= 5 and stats["step_ms_mean"] > 0 and "product" in stats["kernel_ms"]
+
+
+def test_command_line_with_text_prompts_in_the_chat_form(model_folders, tmp_path):
+    """Text prompts: a folder with a small word-level tokenizer that knows the Llama 3 role headers.
+    The prompt loop wraps every line in the chat form with the conversation so far (the second
+    turn's input holds the first turn and its answer), ``--raw_prompt`` passes lines as they are;
+    the tokens generated are those of the same ids given directly."""
+    import json
+    import shutil
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    folder = tmp_path / "with_tokenizer"
+    shutil.copytree(model_folders("A"), folder)
+    words = ["<pad>", "<|begin_of_text|>", "<|eot_id|>", "<|start_header_id|>", "<|end_header_id|>", "user", "assistant", "system",
+             "hello", "world", "again"] + [f"w{i}" for i in range(200)]
+    tok = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<pad>"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    tok.add_special_tokens(["<|begin_of_text|>", "<|eot_id|>", "<|start_header_id|>", "<|end_header_id|>"])
+    tok.save(str(folder / "tokenizer.json"))
+    (folder / "tokenizer_config.json").write_text(json.dumps(
+        {"tokenizer_class": "PreTrainedTokenizerFast", "eos_token": "<|eot_id|>", "pad_token": "<pad>", "unk_token": "<pad>"}))
+    base = [sys.executable, str(ROOT / "cli.py"), "--checkpoints_dir", str(folder), "--dtype", "float32", "--temperature", "0",
+            "--max_gen_len", "4", "--max_seq_len", "128", "--max_gpu_num_blocks", "40", "--page_size", "4"]
+    from transformers import AutoTokenizer
+    hf = AutoTokenizer.from_pretrained(str(folder), use_fast=True)
+    chat_ids = hf.encode("<|start_header_id|>user<|end_header_id|>\n\nhello world<|eot_id|><|start_header_id|>assistant<|end_header_id|>\n\n")
+    assert chat_ids[:3] == [3, 5, 4] and 2 in chat_ids                       # header tokens and <|eot_id|> are single tokens
+    want_chat = _plain_greedy(model_folders("A"), [chat_ids], 4, [255, 2])[0]
+    want_raw = _plain_greedy(model_folders("A"), [hf.encode("hello world")], 4, [255, 2])[0]
+
+    def cut(ids):
+        return ids[: next((i for i, t in enumerate(ids) if t in (255, 2)), len(ids))]
+    one = subprocess.run(base + ["--prompt", "hello world"], capture_output=True, text=True, timeout=600)
+    assert one.returncode == 0, one.stderr[-2000:]
+    assert one.stdout.split() == hf.decode(cut(want_chat)).split()
+    raw = subprocess.run(base + ["--raw_prompt", "--prompt", "hello world"], capture_output=True, text=True, timeout=600)
+    assert raw.returncode == 0, raw.stderr[-2000:]
+    assert raw.stdout.split() == hf.decode(cut(want_raw)).split()
+    # two turns in the loop: the second answer continues a conversation that holds the first one
+    loop = subprocess.run(base, input="hello world\nagain\nexit\n", capture_output=True, text=True, timeout=600)
+    assert loop.returncode == 0, loop.stderr[-2000:]
+    first_answer = hf.decode(cut(want_chat)).strip()
+    second_ids = hf.encode("<|start_header_id|>user<|end_header_id|>\n\nhello world<|eot_id|><|start_header_id|>assistant<|end_header_id|>\n\n"
+                           + first_answer + "<|eot_id|><|start_header_id|>user<|end_header_id|>\n\nagain<|eot_id|>"
+                           "<|start_header_id|>assistant<|end_header_id|>\n\n")
+    want_second = _plain_greedy(model_folders("A"), [second_ids], 4, [255, 2])[0]
+    assert " ".join(hf.decode(cut(want_second)).split()) in " ".join(loop.stdout.split())
