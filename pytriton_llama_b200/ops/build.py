@@ -26,7 +26,7 @@ LIB_NAME = "libptl_b200.so"
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
-] + os.environ.get("PTL_NVCC_EXTRA", "").split()      # e.g. -DPTL_PF_PROFILE for a measuring build (give it a PTL_BUILD_DIR of its own)
+] + os.environ.get("PTL_NVCC_EXTRA", "").split()      # e.g. -DPTL_VECTOR_REDUCE_COLUMNS=32 for a measuring build (give it a PTL_BUILD_DIR of its own)
 
 
 class BuildError(RuntimeError):
