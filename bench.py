@@ -9,6 +9,11 @@ point (scheduler, step, sampling, token ids back on the host every step).  ``pre
 step of 2,048 prompt tokens; ``roofline`` relates the decode step to the bytes it has to read;
 ``points`` holds decode at batch 1 and 64.  Peaks come from MEASURED_PEAKS.json beside this file
 when it exists, else from the fallback constants below.
+
+lite_llama times whole completions with the wall clock (examples/benchmark.py:42-74: one warm-up
+completion, then ``time.time()`` around ``text_completion``; :175-190 throughput = output tokens /
+seconds); ``--impl reference`` drives its ``GenerateText.generate`` on the same shape instead and
+takes a decode step's time as the difference of two calls (baseline/reference_arm.py).
 """
 from __future__ import annotations
 

@@ -2,7 +2,10 @@
 
 A step carries ``T`` tokens of ``R`` requests, request after request.  Nothing in here says
 whether a request is in its prompt or decoding: a portion is ``q_len`` new tokens that follow
-``ctx_len - q_len`` tokens already in the cache.
+``ctx_len - q_len`` tokens already in the cache.  (lite_llama hands its layers an ``AttentionInfo``
+with the cache buffers, ``cur_select_index`` and ``b_req_tokens_table`` for the same purpose,
+lite_llama/executor/executor_struct.py:13-23, and tells prompt from decode by the sequence length,
+lite_llama/models/llama.py:62-118.)
 """
 from __future__ import annotations
 

@@ -1,4 +1,7 @@
-"""A decoder described as data: which parts each layer has and in which order layers run."""
+"""A decoder described as data: which parts each layer has and in which order layers run.
+(lite_llama writes the same arrangement as code: ``LlamaDecoderLayer`` with its two norms, attention
+and feed-forward, and ``LlamaModel`` with a ``ModuleList`` of them run in order,
+lite_llama/models/llama.py:122-163,165-225.)"""
 from __future__ import annotations
 
 from dataclasses import dataclass, field

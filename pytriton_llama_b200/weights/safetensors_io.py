@@ -2,6 +2,9 @@
 (name -> dtype, shape, data_offsets) and the raw little-endian tensor data.
 
 Tensors are memory-mapped and keep their stored element type; nothing is converted here.
+(lite_llama converts a Hugging Face checkpoint into a ``.pth`` of its own names first,
+lite_llama/executor/weight_convert.py:182-252, and reads that with ``torch.load(mmap=True)``,
+lite_llama/executor/model_executor.py:92-117; here the checkpoint's own file is the input.)
 """
 from __future__ import annotations
 
